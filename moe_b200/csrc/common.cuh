@@ -1,0 +1,86 @@
+// Shared helpers for every kernel file: storage-type conversion, warp and block
+// reductions, the device status word, and launch error reporting.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define MOE_API extern "C" __attribute__((visibility("default")))
+
+// Storage type tags passed across the C boundary.
+enum : int { DT_F32 = 0, DT_BF16 = 1 };
+
+// Bits of the device status word.  Kernels OR them in and carry on with a safe
+// value; the host reads the word after a step and raises.
+enum : int {
+    ST_BAD_TOKEN = 1,     // token id outside the vocabulary
+    ST_BAD_PAGE = 2,      // page table entry outside the pool
+    ST_BAD_EXPERT = 4,    // routing produced an expert id outside [0, E)
+    ST_WAIT_TIMEOUT = 8,  // a bounded wait on a barrier ran out
+    ST_BAD_ROW = 16,      // gather index outside its tensor
+};
+
+__device__ __forceinline__ float ld_f(const float* p) { return *p; }
+__device__ __forceinline__ float ld_f(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void st_f(float* p, float v) { *p = v; }
+__device__ __forceinline__ void st_f(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum; `red` is shared memory of at least 32 floats.  All threads get
+// the result.  Order of additions is fixed, so the result is reproducible.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = (lane < nw) ? red[lane] : 0.f;
+    t = warp_sum(t);
+    return t;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = (lane < nw) ? red[lane] : -INFINITY;
+    t = warp_max(t);
+    return t;
+}
+
+static inline int launch_status() { return (int)cudaGetLastError(); }
+
+// Logical position -> (page, offset) of a paged, optionally ring-shaped, cache.
+//   ring:  positions wrap at `ring` (a multiple of the page size); 0 = no wrap
+//   table: the sequence's page list; page p holds `page_size` consecutive positions
+// One layer's keys (or values) are laid out [page][kv_head][offset][head_dim].
+struct CachePos {
+    int page, off;
+};
+__device__ __forceinline__ CachePos cache_pos(int pos, int ring, const int* table, int page_size, int num_pages,
+                                              int* status) {
+    int r = ring > 0 ? pos % ring : pos;
+    int page = table[r / page_size];
+    if (page < 0 || page >= num_pages) {
+        atomicOr(status, ST_BAD_PAGE);
+        page = 0;
+    }
+    CachePos c;
+    c.page = page;
+    c.off = r % page_size;
+    return c;
+}
+__device__ __forceinline__ size_t cache_index(CachePos c, int kv_head, int num_kv_heads, int page_size, int head_dim) {
+    return (((size_t)c.page * num_kv_heads + kv_head) * page_size + c.off) * head_dim;
+}

@@ -1,0 +1,99 @@
+// Token embedding gather and RMSNorm (with the residual add fused in front of it).
+//
+// RMSNorm: s = 1/sqrt(mean(x^2) + eps); out = x * s * w, the weight multiplying
+// directly and eps inside the square root (reference: src/model.rs:211-216).
+// Statistics, the residual sum and the product are 32-bit; only the optional
+// second output is rounded to bfloat16 for the matrix products that follow.
+#include "common.cuh"
+
+// x[t, :] = table[token[t], :]; a token id outside [0, vocab) sets ST_BAD_TOKEN
+// and reads row 0 (the reference wraps modulo the vocabulary, src/model.rs:664).
+template <typename WT>
+__global__ void embed_kernel(const WT* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ x,
+                             int hidden, int vocab, int* status) {
+    const int t = blockIdx.x;
+    int tok = tokens[t];
+    if (tok < 0 || tok >= vocab) {
+        if (threadIdx.x == 0) atomicOr(status, ST_BAD_TOKEN);
+        tok = 0;
+    }
+    const WT* row = table + (size_t)tok * hidden;
+    float* out = x + (size_t)t * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = ld_f(row + i);
+}
+
+MOE_API int moe_embed(const void* table, int table_dt, const int* tokens, float* x, int num_tokens, int hidden,
+                      int vocab, int* status, cudaStream_t stream) {
+    if (num_tokens <= 0) return 0;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (table_dt == DT_F32)
+        embed_kernel<float><<<num_tokens, threads, 0, stream>>>((const float*)table, tokens, x, hidden, vocab, status);
+    else
+        embed_kernel<__nv_bfloat16>
+            <<<num_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, tokens, x, hidden, vocab, status);
+    return launch_status();
+}
+
+// One block per output row i.  Source row r = rows ? rows[i] : i.
+//   v = x[r] (+ delta[r]);  if write_back: x[r] = v
+//   y = v * rsqrt(mean(v^2) + eps) * w;  out32[i] = y;  out16[i] = bf16(y)
+// The row is held in shared memory so that x is read once.
+__global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, const float* __restrict__ w,
+                               const int* __restrict__ rows, float* __restrict__ out32,
+                               __nv_bfloat16* __restrict__ out16, int hidden, float eps, int write_back,
+                               int num_src_rows, int* status) {
+    extern __shared__ float row[];
+    __shared__ float red[32];
+    const int i = blockIdx.x;
+    int r = rows ? rows[i] : i;
+    if (r < 0 || r >= num_src_rows) {
+        if (threadIdx.x == 0) atomicOr(status, ST_BAD_ROW);
+        r = 0;
+    }
+    float* xr = x + (size_t)r * hidden;
+    const float* dr = delta ? delta + (size_t)r * hidden : nullptr;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+        float v = xr[j];
+        if (dr) {
+            v += dr[j];
+            if (write_back) xr[j] = v;
+        }
+        row[j] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+        const float y = row[j] * scale * w[j];
+        if (out32) out32[(size_t)i * hidden + j] = y;
+        if (out16) out16[(size_t)i * hidden + j] = __float2bfloat16_rn(y);
+    }
+}
+
+MOE_API int moe_rmsnorm(float* x, const float* delta, const float* w, const int* rows, float* out32, void* out16,
+                        int num_out_rows, int num_src_rows, int hidden, float eps, int write_back, int* status,
+                        cudaStream_t stream) {
+    if (num_out_rows <= 0) return 0;
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    const size_t smem = (size_t)hidden * sizeof(float);
+    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    rmsnorm_kernel<<<num_out_rows, threads, smem, stream>>>(x, delta, w, rows, out32, (__nv_bfloat16*)out16, hidden,
+                                                           eps, write_back, num_src_rows, status);
+    return launch_status();
+}
+
+// out[i] = a[i] + b[i] (32-bit residual sum where no norm follows).
+__global__ void add_kernel(float* __restrict__ a, const float* __restrict__ b, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) a[i] += b[i];
+}
+MOE_API int moe_add_inplace(float* a, const float* b, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(a, b, (size_t)n);
+    return launch_status();
+}

@@ -1,0 +1,116 @@
+// Rotary position encoding of queries and keys, and the append of keys and
+// values to the paged cache.
+//
+// Rotation (reference: src/model.rs:324-333): per head, half-split pairs
+// (i, i + rot/2): a' = a cos - b sin, b' = a sin + b cos with the angle
+// float(pos) * inv_freq[i] computed in 32-bit.  Keys are cached after rotation
+// (src/model.rs:729-734).
+#include "common.cuh"
+
+// qkv: [T, (nh + 2 nkv) * hd] 32-bit, biases already added.  One block per token.
+// Writes q [T, nh, hd], k [T, nkv, hd], v [T, nkv, hd] in the activation dtype.
+template <typename OT>
+__global__ void rope_split_kernel(const float* __restrict__ qkv, const int* __restrict__ pos,
+                                  const float* __restrict__ inv_freq, int nh, int nkv, int hd, int rot,
+                                  OT* __restrict__ q, OT* __restrict__ k, OT* __restrict__ v) {
+    const int t = blockIdx.x;
+    const int width = (nh + 2 * nkv) * hd;
+    const float* src = qkv + (size_t)t * width;
+    const float p = (float)pos[t];
+    const int half = rot / 2;
+    const int rot_heads = nh + nkv;   // heads that are rotated: queries then keys
+    // rotated part: one thread per (head, pair)
+    for (int idx = threadIdx.x; idx < rot_heads * half; idx += blockDim.x) {
+        const int h = idx / half, i = idx % half;
+        const float* s = src + (size_t)h * hd;
+        float sn, cs;
+        sincosf(p * inv_freq[i], &sn, &cs);
+        const float a = s[i], b = s[i + half];
+        OT* dst = h < nh ? q + ((size_t)t * nh + h) * hd : k + ((size_t)t * nkv + (h - nh)) * hd;
+        st_f(dst + i, a * cs - b * sn);
+        st_f(dst + i + half, a * sn + b * cs);
+    }
+    // pass-through part of rotated heads (rot < hd)
+    if (rot < hd) {
+        const int rest = hd - rot;
+        for (int idx = threadIdx.x; idx < rot_heads * rest; idx += blockDim.x) {
+            const int h = idx / rest, i = rot + idx % rest;
+            OT* dst = h < nh ? q + ((size_t)t * nh + h) * hd : k + ((size_t)t * nkv + (h - nh)) * hd;
+            st_f(dst + i, src[(size_t)h * hd + i]);
+        }
+    }
+    // values
+    const float* vs = src + (size_t)(nh + nkv) * hd;
+    OT* vd = v + (size_t)t * nkv * hd;
+    for (int i = threadIdx.x; i < nkv * hd; i += blockDim.x) st_f(vd + i, vs[i]);
+}
+
+MOE_API int moe_rope_split(const float* qkv, const int* pos, const float* inv_freq, int num_tokens, int nh, int nkv,
+                           int hd, int rot, void* q, void* k, void* v, int out_dt, cudaStream_t stream) {
+    if (num_tokens <= 0) return 0;
+    if (rot < 0 || rot > hd || (rot & 1)) return (int)cudaErrorInvalidValue;
+    if (rot > 0 && !inv_freq) return (int)cudaErrorInvalidValue;
+    const int threads = 256;
+    if (out_dt == DT_F32)
+        rope_split_kernel<float><<<num_tokens, threads, 0, stream>>>(qkv, pos, inv_freq, nh, nkv, hd, rot, (float*)q,
+                                                                      (float*)k, (float*)v);
+    else
+        rope_split_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(
+            qkv, pos, inv_freq, nh, nkv, hd, rot, (__nv_bfloat16*)q, (__nv_bfloat16*)k, (__nv_bfloat16*)v);
+    return launch_status();
+}
+
+// Append this step's keys and values to one layer of a paged cache.
+//   k_new, v_new: [T, nkv, hd];  cache: [page][nkv][page_size][hd] each
+//   A token is written iff its position is among the last `ring` positions of
+//   its sequence after the step (ring == 0: always), so that in a ring no two
+//   tokens of one step write the same place.
+template <typename T>
+__global__ void kv_commit_kernel(const T* __restrict__ k_new, const T* __restrict__ v_new, T* __restrict__ k_cache,
+                                 T* __restrict__ v_cache, const int* __restrict__ seq_of_token,
+                                 const int* __restrict__ pos, const int* __restrict__ seq_end,
+                                 const int* __restrict__ slots, const int* __restrict__ tables, int table_stride,
+                                 int ring, int page_size, int num_pages, int nkv, int hd, int* status) {
+    const int t = blockIdx.x;
+    const int s = seq_of_token[t];
+    if (s < 0) return;
+    const int p = pos[t];
+    if (ring > 0 && p < seq_end[s] - ring) return;
+    const int* table = tables + (size_t)slots[s] * table_stride;
+    const CachePos cp = cache_pos(p, ring, table, page_size, num_pages, status);
+    for (int i = threadIdx.x; i < nkv * hd; i += blockDim.x) {
+        const int h = i / hd, d = i % hd;
+        const size_t dst = cache_index(cp, h, nkv, page_size, hd) + d;
+        k_cache[dst] = k_new[(size_t)t * nkv * hd + i];
+        v_cache[dst] = v_new[(size_t)t * nkv * hd + i];
+    }
+}
+
+MOE_API int moe_kv_commit(const void* k_new, const void* v_new, void* k_cache, void* v_cache, int dt,
+                          const int* seq_of_token, const int* pos, const int* seq_end, const int* slots,
+                          const int* tables, int table_stride, int ring, int page_size, int num_pages, int num_tokens,
+                          int nkv, int hd, int* status, cudaStream_t stream) {
+    if (num_tokens <= 0) return 0;
+    const int threads = 128;
+    if (dt == DT_F32)
+        kv_commit_kernel<float><<<num_tokens, threads, 0, stream>>>(
+            (const float*)k_new, (const float*)v_new, (float*)k_cache, (float*)v_cache, seq_of_token, pos, seq_end,
+            slots, tables, table_stride, ring, page_size, num_pages, nkv, hd, status);
+    else
+        kv_commit_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(
+            (const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, (__nv_bfloat16*)k_cache,
+            (__nv_bfloat16*)v_cache, seq_of_token, pos, seq_end, slots, tables, table_stride, ring, page_size,
+            num_pages, nkv, hd, status);
+    return launch_status();
+}
+
+// Page-table maintenance: table[slot][index] = page for n (slot, index, page) triples.
+__global__ void table_update_kernel(int* __restrict__ table, int stride, const int* __restrict__ upd, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) table[(size_t)upd[3 * i] * stride + upd[3 * i + 1]] = upd[3 * i + 2];
+}
+MOE_API int moe_table_update(int* table, int stride, const int* upd, int n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    table_update_kernel<<<(n + 127) / 128, 128, 0, stream>>>(table, stride, upd, n);
+    return launch_status();
+}

@@ -1,0 +1,305 @@
+"""Python face of the kernel library ``core``: argument checks, then one C call.
+
+Every function launches on the current CUDA stream and returns at once.  There
+is no fallback: a tensor on the CPU, a dtype the kernels do not take or a
+library that cannot be built raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+from . import build
+
+DT_F32, DT_BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        L = build.load("core")
+        P, I, F, LL = c_void_p, c_int, c_float, c_longlong
+        sig = {
+            "moe_embed": [P, I, P, P, I, I, I, P, P],
+            "moe_rmsnorm": [P, P, P, P, P, P, I, I, I, F, I, P, P],
+            "moe_add_inplace": [P, P, LL, P],
+            "moe_gemm_generic": [P, I, I, P, I, P, I, LL, P, I, I, P, P, I, I, I, I, P, P],
+            "moe_rope_split": [P, P, P, I, I, I, I, I, P, P, P, I, P],
+            "moe_kv_commit": [P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
+            "moe_attention_generic": [P, P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],
+            "moe_router": [P, P, P, I, P, I, I, I, I, I, F, P, P, P, P],
+            "moe_align": [P, I, I, I, P, P, P, P, P],
+            "moe_swiglu": [P, P, I, LL, I, P],
+            "moe_combine": [P, P, P, I, P, P, P, I, I, P],
+            "moe_sample": [P, I, I, P, P, P, I, F, I, F, F, P, P],
+            "moe_seed_rng": [P, P, P, I, P],
+            "moe_table_update": [P, I, P, I, P],
+        }
+        for name, argtypes in sig.items():
+            fn = getattr(L, name)
+            fn.argtypes = argtypes
+            fn.restype = c_int
+        _lib = L
+    return _lib
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return DT_F32
+    if t.dtype == torch.bfloat16:
+        return DT_BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, not {t.dtype}")
+
+
+def _p(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _chk(t: torch.Tensor, name: str, dtype=None, dims: Optional[int] = None):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise KernelError(f"{name}: expected a CUDA tensor; there is no CPU path")
+    if not t.is_contiguous():
+        raise KernelError(f"{name}: must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name}: expected {dtype}, got {t.dtype}")
+    if dims is not None and t.dim() != dims:
+        raise KernelError(f"{name}: expected {dims} dimensions, got {tuple(t.shape)}")
+    return t
+
+
+def _ok(code: int, what: str):
+    if code != 0:
+        try:
+            msg = torch.cuda.cudart().cudaGetErrorString(code)
+        except Exception:
+            msg = "?"
+        raise KernelError(f"{what}: CUDA error {code} ({msg})")
+
+
+# --------------------------------------------------------------------------- status word
+STATUS_BITS = {
+    1: "a token id lies outside the vocabulary",
+    2: "a page table entry lies outside the page pool",
+    4: "routing produced an expert id outside the expert range",
+    8: "a bounded wait inside a kernel ran out",
+    16: "a gather index lies outside its tensor",
+}
+
+
+def new_status(device) -> torch.Tensor:
+    return torch.zeros(4, dtype=torch.int32, device=device)
+
+
+def check_status(status: torch.Tensor):
+    """Read the status word (synchronises) and raise if a kernel flagged a fault."""
+    v = int(status[0].item())
+    if v:
+        status.zero_()
+        raise KernelError("; ".join(m for b, m in STATUS_BITS.items() if v & b) or f"status {v}")
+
+
+# --------------------------------------------------------------------------- kernels
+def embed(table, token_ids, out, status):
+    _chk(table, "table", dims=2), _chk(token_ids, "token_ids", torch.int32, 1), _chk(out, "out", torch.float32, 2)
+    T, H = out.shape
+    if token_ids.numel() < T or table.shape[1] != H:
+        raise KernelError("embed: shape mismatch")
+    _ok(lib().moe_embed(_p(table), _dt(table), _p(token_ids), _p(out), T, H, table.shape[0], _p(status), _stream()),
+        "embed")
+
+
+def rmsnorm(x, weight, eps, *, delta=None, rows=None, out32=None, out16=None, write_back=True, status=None):
+    """y = rmsnorm(x[r] (+ delta[r])) for r in rows (or every row).
+
+    With ``delta`` and ``write_back`` the sum is stored back into ``x`` (the
+    32-bit residual stream).  ``out32`` / ``out16`` receive y in float32 /
+    bfloat16; either may be None."""
+    _chk(x, "x", torch.float32, 2), _chk(weight, "weight", torch.float32, 1)
+    S, H = x.shape
+    n_out = S if rows is None else rows.numel()
+    if weight.numel() != H:
+        raise KernelError("rmsnorm: weight size")
+    if delta is not None:
+        _chk(delta, "delta", torch.float32, 2)
+        if delta.shape != x.shape:
+            raise KernelError("rmsnorm: delta shape")
+    if rows is not None:
+        _chk(rows, "rows", torch.int32, 1)
+    for o, dt in ((out32, torch.float32), (out16, torch.bfloat16)):
+        if o is not None:
+            _chk(o, "out", dt, 2)
+            if o.shape[0] < n_out or o.shape[1] != H:
+                raise KernelError("rmsnorm: output shape")
+    _ok(lib().moe_rmsnorm(_p(x), _p(delta), _p(weight), _p(rows), _p(out32), _p(out16), n_out, S, H, float(eps),
+                          1 if (write_back and rows is None) else 0, _p(status), _stream()), "rmsnorm")
+
+
+def add_inplace(a, b):
+    _chk(a, "a", torch.float32), _chk(b, "b", torch.float32)
+    if a.numel() != b.numel():
+        raise KernelError("add_inplace: sizes differ")
+    _ok(lib().moe_add_inplace(_p(a), _p(b), a.numel(), _stream()), "add_inplace")
+
+
+def gemm_generic(a, w, out, *, bias=None, a_rows=None, group_offsets=None, status=None, m=None):
+    """out[i, :] = a[row(i), :] @ w[g(i)].T (+ bias); the plain kernel, any sizes.
+
+    a: [S, K]; w: [N, K] or [G, N, K]; out: [M, N].  ``a_rows`` int32[M] gathers
+    rows of a; ``group_offsets`` int32[G+1] splits the M rows into groups."""
+    _chk(a, "a", dims=2), _chk(out, "out", dims=2)
+    if not w.is_cuda or not w.is_contiguous():
+        raise KernelError("gemm: weight must be a contiguous CUDA tensor")
+    if w.dim() == 2:
+        G, (N, K) = 1, w.shape
+    elif w.dim() == 3:
+        G, N, K = w.shape
+    else:
+        raise KernelError("gemm: weight must be [N, K] or [G, N, K]")
+    M = out.shape[0] if m is None else m
+    if a.shape[1] != K or out.shape[1] != N or M > out.shape[0]:
+        raise KernelError(f"gemm: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    if a_rows is None and a.shape[0] < M:
+        raise KernelError("gemm: a has fewer rows than out")
+    if a_rows is not None:
+        _chk(a_rows, "a_rows", torch.int32, 1)
+        if a_rows.numel() < M:
+            raise KernelError("gemm: a_rows too short")
+    if group_offsets is not None:
+        _chk(group_offsets, "group_offsets", torch.int32, 1)
+        if group_offsets.numel() != G + 1:
+            raise KernelError("gemm: group_offsets must have G + 1 entries")
+    elif G != 1:
+        raise KernelError("gemm: a stacked weight needs group_offsets")
+    if bias is not None:
+        _chk(bias, "bias", torch.float32, 1)
+        if bias.numel() != N:
+            raise KernelError("gemm: bias size")
+    _ok(lib().moe_gemm_generic(_p(a), _dt(a), a.stride(0), _p(a_rows), a.shape[0], _p(w), _dt(w), N * K, _p(out),
+                               _dt(out), out.stride(0), _p(bias), _p(group_offsets), G, M, N, K, _p(status),
+                               _stream()), "gemm_generic")
+
+
+def rope_split(qkv, pos, inv_freq, nh, nkv, hd, rot, q, k, v):
+    _chk(qkv, "qkv", torch.float32, 2), _chk(pos, "pos", torch.int32, 1)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (nh + 2 * nkv) * hd:
+        raise KernelError("rope_split: qkv width")
+    for t, n in ((q, nh), (k, nkv), (v, nkv)):
+        _chk(t, "q/k/v")
+        if t.numel() < T * n * hd or t.dtype != q.dtype:
+            raise KernelError("rope_split: output size or dtype")
+    if rot:
+        _chk(inv_freq, "inv_freq", torch.float32, 1)
+        if inv_freq.numel() < rot // 2:
+            raise KernelError("rope_split: inv_freq too short")
+    _ok(lib().moe_rope_split(_p(qkv), _p(pos), _p(inv_freq) if rot else None, T, nh, nkv, hd, rot, _p(q), _p(k), _p(v),
+                             _dt(q), _stream()), "rope_split")
+
+
+def kv_commit(k_new, v_new, view, batch, status):
+    """Append the step's keys and values to the cache layer ``view``."""
+    g = view.group
+    T = batch.num_tokens
+    if k_new.dtype != g.dtype:
+        raise KernelError("kv_commit: cache dtype differs from the keys'")
+    _ok(lib().moe_kv_commit(_p(k_new), _p(v_new), _p(view.k), _p(view.v), _dt(k_new), _p(batch.seq_of_token),
+                            _p(batch.pos), _p(batch.seq_end), _p(batch.slots), _p(g.table), g.table.stride(0),
+                            g.ring, g.page_size, g.num_pages, T, g.num_kv_heads, g.head_dim, _p(status), _stream()),
+        "kv_commit")
+
+
+def attention_generic(q, k_new, v_new, view, batch, out, *, nh, window, scale, use_local, status):
+    g = view.group
+    T = batch.num_tokens
+    if q.dtype != g.dtype or out.dtype != q.dtype:
+        raise KernelError("attention: dtypes of queries, cache and output must agree")
+    _ok(lib().moe_attention_generic(_p(q), _p(k_new), _p(v_new), _p(view.k), _p(view.v), _p(out), _dt(q),
+                                    _p(batch.seq_of_token), _p(batch.pos), _p(batch.seq_start), _p(batch.cu_seqlens),
+                                    _p(batch.slots), _p(g.table), g.table.stride(0), g.ring, g.page_size,
+                                    g.num_pages, T, nh, g.num_kv_heads, g.head_dim, int(window or 0), float(scale),
+                                    1 if use_local else 0, _p(status), _stream()), "attention_generic")
+
+
+def router(h32, w_router, top_k, norm_topk, scale, topk_idx, topk_w, *, shared_gate_w=None, shared_gate=None,
+           seq_of_token=None):
+    _chk(h32, "h", torch.float32, 2), _chk(w_router, "router weight", dims=2)
+    T, H = h32.shape
+    E = w_router.shape[0]
+    if w_router.shape[1] != H:
+        raise KernelError("router: weight shape")
+    _chk(topk_idx, "topk_idx", torch.int32), _chk(topk_w, "topk_w", torch.float32)
+    if topk_idx.numel() < T * top_k or topk_w.numel() < T * top_k:
+        raise KernelError("router: output size")
+    if shared_gate_w is not None:
+        _chk(shared_gate_w, "shared gate weight")
+        if shared_gate_w.dtype != w_router.dtype or shared_gate_w.numel() != H:
+            raise KernelError("router: the shared gate weight must have the router's dtype and width")
+        _chk(shared_gate, "shared_gate", torch.float32)
+    _ok(lib().moe_router(_p(h32), _p(w_router), _p(shared_gate_w), _dt(w_router), _p(seq_of_token), T, H, E, top_k,
+                         1 if norm_topk else 0, float(scale), _p(topk_idx), _p(topk_w), _p(shared_gate), _stream()),
+        "router")
+
+
+def moe_align(topk_idx, num_tokens, top_k, num_experts, offsets, sorted_token, pos_of_pair, status):
+    for t in (topk_idx, offsets, sorted_token, pos_of_pair):
+        _chk(t, "align", torch.int32)
+    if offsets.numel() != num_experts + 1 or sorted_token.numel() < num_tokens * top_k:
+        raise KernelError("moe_align: output size")
+    _ok(lib().moe_align(_p(topk_idx), num_tokens, top_k, num_experts, _p(offsets), _p(sorted_token), _p(pos_of_pair),
+                        _p(status), _stream()), "moe_align")
+
+
+def swiglu(gu, act):
+    _chk(gu, "gu", torch.float32, 2), _chk(act, "act", dims=2)
+    rows, two_i = gu.shape
+    if two_i % 2 or act.shape != (rows, two_i // 2):
+        raise KernelError("swiglu: shapes")
+    _ok(lib().moe_swiglu(_p(gu), _p(act), _dt(act), rows, two_i // 2, _stream()), "swiglu")
+
+
+def moe_combine(y, pos_of_pair, topk_w, top_k, out, *, shared=None, shared_gate=None):
+    _chk(y, "y", torch.float32, 2), _chk(out, "out", torch.float32, 2)
+    T, H = out.shape
+    _ok(lib().moe_combine(_p(y), _p(pos_of_pair), _p(topk_w), top_k, _p(shared), _p(shared_gate), _p(out), T, H,
+                          _stream()), "moe_combine")
+
+
+def sample(logits, slots, rng_states, out_tokens, *, temp=0.0, top_k=0, top_p=1.0, repeat_penalty=1.0, history=None):
+    _chk(logits, "logits", torch.float32, 2), _chk(out_tokens, "out_tokens", torch.int32, 1)
+    R, V = logits.shape
+    if temp > 0:
+        _chk(slots, "slots", torch.int32, 1), _chk(rng_states, "rng_states", torch.int64, 1)
+    hl = 0
+    if history is not None:
+        _chk(history, "history", torch.int32, 2)
+        hl = history.shape[1]
+    _ok(lib().moe_sample(_p(logits), R, V, _p(slots), _p(rng_states), _p(history), hl, float(temp), int(top_k),
+                         float(top_p), float(repeat_penalty), _p(out_tokens), _stream()), "sample")
+
+
+def seed_rng(rng_states, slots, seeds):
+    _chk(rng_states, "rng_states", torch.int64, 1), _chk(slots, "slots", torch.int32, 1)
+    _chk(seeds, "seeds", torch.int64, 1)
+    _ok(lib().moe_seed_rng(_p(rng_states), _p(slots), _p(seeds), slots.numel(), _stream()), "seed_rng")
+
+
+def table_update(table, updates, n):
+    """table[slot, index] = page for the first n (slot, index, page) triples of ``updates``."""
+    _chk(table, "table", torch.int32, 2), _chk(updates, "updates", torch.int32)
+    if updates.numel() < 3 * n:
+        raise KernelError("table_update: updates too short")
+    _ok(lib().moe_table_update(_p(table), table.stride(0), _p(updates), n, _stream()), "table_update")

@@ -1,0 +1,103 @@
+"""What every part of a layer looks like to the rest of the library.
+
+A part is built from a ``PartSpec`` (its kind, its constants, a tensor-name
+prefix), says which tensors it needs, is bound to those tensors, and is then
+called once per step.  A part knows its own sizes and nothing about the model
+it sits in.  New kinds are added with ``register_part``; the model builder picks
+them by the ``kind`` string of the spec.
+
+Interfaces by category
+  norm      forward(rt, x, delta=None, rows=None, want32=False, write_back=True) -> Activations
+  position  rotary_table() -> (inv_freq, rotary_dim) or None;  apply(rt, qkv32, layout, positions)
+  mixer     forward(rt, h: Activations, batch, cache_view, state) -> delta [T, hidden] float32
+            kv_request() -> KVRequest | None;  state_request() -> StateRequest | None
+  ffn       forward(rt, h: Activations, batch) -> delta [T, hidden] float32;  wants32: bool
+  block     forward(rt, x, pending, batch, cache_view, state) -> (x, pending)
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Callable, Dict, Optional, Tuple
+
+import torch
+
+from ..config.spec import PartSpec
+
+
+@dataclass(frozen=True)
+class TensorSpec:
+    shape: Tuple[int, ...]
+    init: str = "normal"        # "normal" | "ones" | "zeros" for the random-weights mode
+    vector: bool = False        # small vectors are widened to float32 when bound (exact)
+
+
+class Runtime:
+    """Device, compute dtype and the device status word shared by all parts of a model."""
+
+    def __init__(self, device, compute_dtype: torch.dtype):
+        if compute_dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError("compute dtype must be float32 or bfloat16")
+        self.device = torch.device(device)
+        self.compute_dtype = compute_dtype
+        self.status = None
+        if self.device.type == "cuda":
+            from ..ops import core
+
+            self.status = core.new_status(self.device)
+
+    @property
+    def is_bf16(self) -> bool:
+        return self.compute_dtype == torch.bfloat16
+
+    def empty(self, shape, dtype=None) -> torch.Tensor:
+        return torch.empty(shape, dtype=dtype or self.compute_dtype, device=self.device)
+
+    def check(self) -> None:
+        from ..ops import core
+
+        core.check_status(self.status)
+
+
+@dataclass
+class Activations:
+    """A normed hidden state: in the compute dtype for matrix products (``act``),
+    and in float32 (``f32``) for parts that ask for it (routing)."""
+
+    act: torch.Tensor
+    f32: Optional[torch.Tensor] = None
+
+
+class Part:
+    category = ""
+    kind = ""
+
+    def __init__(self, spec: PartSpec):
+        self.spec = spec
+        self.params = dict(spec.params)
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        """Local tensor name -> shape; the checkpoint name is spec.prefix + local name."""
+        return {}
+
+    def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        """Take ownership of the loaded tensors (re-laying them out is allowed)."""
+        self.rt = rt
+
+
+_REGISTRY: Dict[Tuple[str, str], Callable[[PartSpec], Part]] = {}
+
+
+def register_part(category: str, kind: str, factory: Callable[[PartSpec], Part]) -> None:
+    _REGISTRY[(category, kind)] = factory
+
+
+def make_part(category: str, spec: PartSpec) -> Part:
+    key = (category, spec.kind)
+    if key not in _REGISTRY:
+        known = sorted(k for c, k in _REGISTRY if c == category)
+        raise KeyError(f"no {category} part of kind '{spec.kind}'; registered: {', '.join(known) or '(none)'}")
+    return _REGISTRY[key](spec)
+
+
+def registered_parts(category: str):
+    return sorted(k for c, k in _REGISTRY if c == category)

@@ -1,0 +1,59 @@
+"""Token embedding and the output projection.
+
+x_i = embed[token_i] (src/model.rs:662-665; an id outside the vocabulary is an
+error here, the reference wraps it).  logits = W_lm norm(x) on the requested
+rows only; W_lm is the embedding when the model ties them (src/model.rs:350).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops import core
+from ..ops.linear import linear
+from .base import Part, TensorSpec, register_part
+
+
+class TokenEmbedding(Part):
+    category, kind = "embedding", "token_embedding"
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.vocab = int(self.params["vocab_size"])
+        self.hidden = int(self.params["hidden_size"])
+
+    def tensors(self):
+        return {"weight": TensorSpec((self.vocab, self.hidden))}
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.weight = tensors["weight"].contiguous()
+
+    def forward(self, rt, token_ids, num_tokens):
+        x = rt.empty((num_tokens, self.hidden), torch.float32)
+        core.embed(self.weight, token_ids, x, rt.status)
+        return x
+
+
+class LMHead(Part):
+    category, kind = "head", "lm_head"
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.vocab = int(self.params["vocab_size"])
+        self.hidden = int(self.params["hidden_size"])
+        self.tied = bool(self.params.get("tied", False))
+
+    def tensors(self):
+        return {} if self.tied else {"weight": TensorSpec((self.vocab, self.hidden))}
+
+    def bind(self, tensors, rt, embedding: TokenEmbedding = None):
+        super().bind(tensors, rt)
+        self.weight = embedding.weight if self.tied else tensors["weight"].contiguous()
+
+    def forward(self, rt, h):
+        """h: Activations of the wanted rows -> logits [rows, vocab] float32."""
+        return linear(rt, h.act, self.weight)
+
+
+register_part("embedding", "token_embedding", TokenEmbedding)
+register_part("head", "lm_head", LMHead)

@@ -1,0 +1,141 @@
+"""Feed-forward parts: a dense SwiGLU MLP and routed SwiGLU experts with an
+optional sigmoid-gated shared expert.
+
+SwiGLU (src/model.rs:26-35):   y = Wd (silu(Wg n) * (Wu n))
+Routing (src/model.rs:844-897): softmax over all experts, top k, optional
+  renormalisation, scaling factor.
+Experts (src/model.rs:902-942): out_i = sum_e w_ie * y_e(n_i).
+Shared expert (src/model.rs:956-970): out += sigmoid(Wsg n) * y_s(n).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops import core
+from ..ops.linear import grouped_linear, linear
+from .base import Part, TensorSpec, register_part
+
+
+def _fuse_rows(tensors):
+    dt = tensors[0].dtype if all(t.dtype == tensors[0].dtype for t in tensors) else torch.float32
+    return torch.cat([t.to(dt) for t in tensors], dim=0).contiguous()
+
+
+class DenseSwiGLU(Part):
+    category, kind = "ffn", "dense_swiglu"
+    wants32 = False
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden = int(self.params["hidden_size"])
+        self.size = int(self.params["size"])
+
+    def tensors(self):
+        return {
+            "gate_proj.weight": TensorSpec((self.size, self.hidden)),
+            "up_proj.weight": TensorSpec((self.size, self.hidden)),
+            "down_proj.weight": TensorSpec((self.hidden, self.size)),
+        }
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.w_gu = _fuse_rows([tensors["gate_proj.weight"], tensors["up_proj.weight"]])
+        self.w_down = tensors["down_proj.weight"].contiguous()
+
+    def forward(self, rt, h, batch):
+        T = h.act.shape[0]
+        gu = linear(rt, h.act, self.w_gu)
+        act = rt.empty((T, self.size))
+        core.swiglu(gu, act)
+        return linear(rt, act, self.w_down)
+
+
+class RoutedExperts(Part):
+    category, kind = "ffn", "routed_experts"
+    wants32 = True   # router logits are computed from the 32-bit normed state
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        p = self.params
+        self.hidden = int(p["hidden_size"])
+        self.E = int(p["num_experts"])
+        self.k = int(p["top_k"])
+        self.size = int(p["expert_size"])
+        self.norm_topk = bool(p.get("norm_topk_prob", False))
+        self.scale = float(p.get("routed_scaling_factor", 1.0))
+        self.shared_size = int(p.get("shared_size", 0) or 0)
+        self.shared_gate = bool(p.get("shared_gate", False)) and self.shared_size > 0
+        if not 0 < self.k <= self.E:
+            raise ValueError("top_k must lie in 1..num_experts")
+
+    def tensors(self):
+        t = {"gate.weight": TensorSpec((self.E, self.hidden))}
+        for e in range(self.E):
+            t[f"experts.{e}.gate_proj.weight"] = TensorSpec((self.size, self.hidden))
+            t[f"experts.{e}.up_proj.weight"] = TensorSpec((self.size, self.hidden))
+            t[f"experts.{e}.down_proj.weight"] = TensorSpec((self.hidden, self.size))
+        if self.shared_size:
+            t["shared_expert.gate_proj.weight"] = TensorSpec((self.shared_size, self.hidden))
+            t["shared_expert.up_proj.weight"] = TensorSpec((self.shared_size, self.hidden))
+            t["shared_expert.down_proj.weight"] = TensorSpec((self.hidden, self.shared_size))
+        if self.shared_gate:
+            t["shared_expert_gate.weight"] = TensorSpec((1, self.hidden))
+        return t
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.w_router = tensors["gate.weight"].contiguous()
+        names = [f"experts.{e}.{n}_proj.weight" for e in range(self.E) for n in ("gate", "up", "down")]
+        dts = {tensors[n].dtype for n in names}
+        dt = dts.pop() if len(dts) == 1 else torch.float32
+        dev = self.w_router.device
+        # [E, 2 * size, hidden]: rows [0, size) gate, [size, 2 size) up, as in the fused
+        # checkpoint layout the reference also reads (src/model.rs:401-411)
+        self.w_gu = torch.empty((self.E, 2 * self.size, self.hidden), dtype=dt, device=dev)
+        self.w_down = torch.empty((self.E, self.hidden, self.size), dtype=dt, device=dev)
+        for e in range(self.E):
+            self.w_gu[e, : self.size] = tensors.pop(f"experts.{e}.gate_proj.weight")
+            self.w_gu[e, self.size:] = tensors.pop(f"experts.{e}.up_proj.weight")
+            self.w_down[e] = tensors.pop(f"experts.{e}.down_proj.weight")
+        self.ws_gu = self.ws_down = self.w_sgate = None
+        if self.shared_size:
+            self.ws_gu = _fuse_rows([tensors["shared_expert.gate_proj.weight"], tensors["shared_expert.up_proj.weight"]])
+            self.ws_down = tensors["shared_expert.down_proj.weight"].contiguous()
+        if self.shared_gate:
+            self.w_sgate = tensors["shared_expert_gate.weight"].reshape(-1).to(self.w_router.dtype).contiguous()
+
+    def route(self, rt, h, batch):
+        """-> (topk_idx [T, k] int32, topk_w [T, k] float32, shared_gate [T] float32 or None)"""
+        T = h.f32.shape[0]
+        topk_idx = rt.empty((T, self.k), torch.int32)
+        topk_w = rt.empty((T, self.k), torch.float32)
+        sg = rt.empty((T,), torch.float32) if self.w_sgate is not None else None
+        core.router(h.f32, self.w_router, self.k, self.norm_topk, self.scale, topk_idx, topk_w,
+                    shared_gate_w=self.w_sgate, shared_gate=sg, seq_of_token=getattr(batch, "seq_of_token", None))
+        return topk_idx, topk_w, sg
+
+    def forward(self, rt, h, batch):
+        T = h.act.shape[0]
+        topk_idx, topk_w, sg = self.route(rt, h, batch)
+        P = T * self.k
+        offsets = rt.empty((self.E + 1,), torch.int32)
+        sorted_token = rt.empty((P,), torch.int32)
+        pos_of_pair = rt.empty((P,), torch.int32)
+        core.moe_align(topk_idx, T, self.k, self.E, offsets, sorted_token, pos_of_pair, rt.status)
+        gu = grouped_linear(rt, h.act, self.w_gu, offsets, P, a_rows=sorted_token)
+        act = rt.empty((P, self.size))
+        core.swiglu(gu, act)
+        y = grouped_linear(rt, act, self.w_down, offsets, P)
+        ys = None
+        if self.ws_gu is not None:
+            gus = linear(rt, h.act, self.ws_gu)
+            acts = rt.empty((T, self.shared_size))
+            core.swiglu(gus, acts)
+            ys = linear(rt, acts, self.ws_down)
+        out = rt.empty((T, self.hidden), torch.float32)
+        core.moe_combine(y, pos_of_pair, topk_w, self.k, out, shared=ys, shared_gate=sg)
+        return out
+
+
+register_part("ffn", "dense_swiglu", DenseSwiGLU)
+register_part("ffn", "routed_experts", RoutedExperts)
