@@ -1,0 +1,270 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of moe_b200 on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Default run: the layer sizes of Qwen1.5-MoE-A2.7B with random bfloat16 weights,
+8 sequences with 512-token prompts inside a 4096-token context, K decode steps.
+A "step" is one decode step (inputs copied from pinned memory, every layer, the
+output projection and a greedy pick).  Prints ONE JSON line.
+
+  value    decoded tokens a second, timed on the device with CUDA events
+  e2e      the same through moe_b200.generate(): host token lists in and out
+  prefill  one 2,048-token prompt: tokens a second and fraction of the bf16 peak
+  roofline bytes a decode step must read (every weight it uses once, and the
+           cache of the live requests) / its time, against the measured copy bandwidth
+  points   decode at batch 1 and 64
+
+The reference (JGalego/Moe) is a Rust CPU engine; it installs only with a Rust
+toolchain, which this image lacks, so ``--impl reference`` reports that.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+A27B = dict(
+    architectures=["Qwen2MoeForCausalLM"], model_type="qwen2_moe",
+    num_hidden_layers=24, hidden_size=2048, num_attention_heads=16, num_key_value_heads=16, head_dim=128,
+    num_experts=60, num_experts_per_tok=4, moe_intermediate_size=1408, shared_expert_intermediate_size=5632,
+    intermediate_size=5632, norm_topk_prob=False, decoder_sparse_step=1, mlp_only_layers=[],
+    vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6, use_sliding_window=False, tie_word_embeddings=False,
+    max_position_embeddings=8192,
+)
+FULL_LAYERS = 24
+CONTEXT, PROMPT_LEN, PREFILL_TOKENS = 4096, 512, 2048
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(p):
+        try:
+            with open(p) as f:
+                d = json.load(f)
+            return dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]),
+                        bf16_tflops_sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), source="measured")
+        except Exception:
+            pass
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons during the timed region."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v.lower().startswith("active")})
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+def model_numbers(cfg, layers):
+    """Parameter counts and per-token work of the configuration."""
+    H, V = cfg["hidden_size"], cfg["vocab_size"]
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    E, k, mi, si = cfg["num_experts"], cfg["num_experts_per_tok"], cfg["moe_intermediate_size"], cfg["shared_expert_intermediate_size"]
+    attn = (nh + 2 * nkv) * hd * H + H * nh * hd
+    expert = 3 * mi * H
+    shared = 3 * si * H + H
+    router = E * H
+    return dict(attn=attn, expert=expert, shared=shared, router=router, head=V * H,
+                kv_bytes_per_token_layer=2 * nkv * hd * 2,
+                active_per_token=layers * (attn + k * expert + shared + router))
+
+
+def run_ours(args):
+    import torch
+
+    import moe_b200
+    from moe_b200.engine.generate import GenerationStats
+    from moe_b200.ops import core
+    from moe_b200.sampling.params import SamplingParams
+    from moe_b200.sampling.sampler import DeviceSampler
+
+    pk = peaks()
+    cfg = dict(A27B)
+    layers = args.layers or FULL_LAYERS
+    cfg["num_hidden_layers"] = layers
+    torch.cuda.set_device(0)
+    model = moe_b200.random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+    V = cfg["vocab_size"]
+    nums = model_numbers(cfg, layers)
+    clocks = ClockSampler()
+
+    def decode_run(B, steps, warmup, sample_clocks=False):
+        """-> (ms per step, launches per step, h2d bytes per step, mean cache tokens, unique experts per layer)"""
+        eng = moe_b200.Engine(model, max_tokens=B * (-(-(PROMPT_LEN + steps + warmup + 8) // 64) * 64), max_slots=B)
+        sampler = DeviceSampler(eng.cache.rng_states, eng.rt.device)
+        greedy = SamplingParams()
+        slots = [eng.new_sequence() for _ in range(B)]
+        prompts = [[(i * 7 + 13 + 31 * b) % V for i in range(PROMPT_LEN)] for b in range(B)]
+        for b0 in range(0, B, 8):                       # prompts in groups, to bound the workspace
+            eng.step(slots[b0:b0 + 8], prompts[b0:b0 + 8], [[] for _ in slots[b0:b0 + 8]])
+
+        def one(i):
+            logits = eng.step(slots, [[(i * 13 + 7 * b) % V] for b in range(B)], check=False)
+            return sampler.sample(logits, eng.last_batch.slots, greedy)
+
+        for i in range(warmup):
+            one(i)
+        # which experts a step touches (for the byte count), measured on one extra untimed step
+        routed = [b.ffn for b in model.blocks if b.ffn.kind == "routed_experts"]
+        for r in routed:
+            r.trace = []
+        one(warmup)
+        uniq = sum(len(torch.unique(r.trace[0][0])) for r in routed) / max(len(routed), 1)
+        for r in routed:
+            r.trace = None
+        torch.cuda.synchronize()
+        if sample_clocks:
+            clocks.start()
+        l0 = core.launches
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for i in range(steps):
+            one(warmup + 1 + i)
+        stop.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(stop) / steps
+        clk = clocks.stop() if sample_clocks else None
+        eng.rt.check()
+        launches = (core.launches - l0) / steps
+        mean_len = PROMPT_LEN + warmup + 1 + steps / 2
+        h2d = (3 * B + 4 * B + 2 + B) * 4
+        for s in slots:
+            eng.release(s)
+        del eng
+        torch.cuda.empty_cache()
+        return ms, launches, h2d, mean_len, uniq, clk
+
+    def decode_bytes(B, mean_len, uniq):
+        per_layer = nums["attn"] + nums["shared"] + nums["router"] + uniq * nums["expert"]
+        weights = 2 * (layers * per_layer + nums["head"]) + 2 * B * cfg["hidden_size"]   # bf16, + embedding rows
+        kv = B * mean_len * nums["kv_bytes_per_token_layer"] * layers
+        return weights + kv
+
+    # ---- headline: batch 8 ---------------------------------------------------------------
+    B = 8
+    ms, launches, h2d, mean_len, uniq, clk = decode_run(B, args.steps, args.warmup, sample_clocks=True)
+    value = B / (ms / 1e3)
+    nbytes = decode_bytes(B, mean_len, uniq)
+    achieved = nbytes / (ms / 1e3) / 1e9
+
+    # ---- other batch sizes ----------------------------------------------------------------
+    points = {}
+    for b in (1, 64):
+        m, *_ = decode_run(b, max(8, args.steps // 4), args.warmup)
+        points[f"decode_b{b}"] = round(b / (m / 1e3), 1)
+
+    # ---- prefill of 2,048 tokens ------------------------------------------------------------
+    eng = moe_b200.Engine(model, max_tokens=PREFILL_TOKENS + 64, max_slots=1)
+    ids = [(i * 7 + 13) % V for i in range(PREFILL_TOKENS)]
+    times = []
+    for it in range(args.warmup + 3):
+        s = eng.new_sequence()
+        a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        eng.step([s], [ids], check=False)
+        b_.record()
+        torch.cuda.synchronize()
+        eng.release(s)
+        if it >= args.warmup:
+            times.append(a.elapsed_time(b_))
+    eng.rt.check()
+    pf_ms = sorted(times)[len(times) // 2]
+    T = PREFILL_TOKENS
+    flops = 2 * T * nums["active_per_token"] + 2 * nums["head"] \
+        + layers * 4 * cfg["num_attention_heads"] * cfg["head_dim"] * T * (T + 1) // 2
+    prefill = {"value": round(T / (pf_ms / 1e3), 1), "tokens": T, "ms": round(pf_ms, 3),
+               "frac": round(flops / (pf_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+    del eng
+    torch.cuda.empty_cache()
+
+    # ---- end to end through the Python entry point ----------------------------------------
+    eng = moe_b200.Engine(model, max_tokens=8 * (-(-(PROMPT_LEN + args.steps + 8) // 64) * 64), max_slots=8)
+    prompts = [[(i * 7 + 13 + 31 * b) % V for i in range(PROMPT_LEN)] for b in range(8)]
+    moe_b200.generate(eng, prompts, max_tokens=4, eos=())                       # warm-up
+    st = GenerationStats()
+    moe_b200.generate(eng, prompts, max_tokens=args.steps + 1, eos=(), stats=st)
+    e2e = {"value": round(st.decode_tokens / max(st.decode_seconds, 1e-9), 1), "unit": "tokens/s",
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": (8 + 1) * 4,
+           "prefill_tokens_per_s": round(st.prefill_tokens / max(st.prefill_seconds, 1e-9), 1)}
+
+    out = {
+        "metric": "decode tokens/s (batch 8, Qwen1.5-MoE-A2.7B shape, bf16)", "value": round(value, 1), "unit": "tokens/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic token ids, random weights N(0, 0.02)",
+        "config": {
+            "model": "Qwen1.5-MoE-A2.7B shape", "layers": layers, "layers_of_model": FULL_LAYERS, "hidden": 2048,
+            "heads": 16, "kv_heads": 16, "head_dim": 128, "experts": 60, "top_k": 4, "moe_intermediate": 1408,
+            "shared_intermediate": 5632, "vocab": V, "global_batch": B, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN,
+            "parallelism": "single GPU", "l2": "inputs larger than L2 (weights read per step >> 126 MB)",
+            "peaks": pk["source"],
+        },
+        "clocks": clk,
+        "e2e": e2e,
+        "gpu_launches": int(round(launches * args.steps)),
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(nbytes),
+                     "experts_per_layer": round(uniq, 1), "of": pk["source"]},
+        "points": points,
+    }
+    print(json.dumps(out))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (reported in config)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "JGalego/Moe is a Rust crate (no Python package, "
+                          "no setup.py/pyproject); cargo and rustc are absent from this image and there is no network"}))
+        return 0
+    if args.gpus != 1:
+        print("bench.py: moe_b200 is a single-GPU library; --gpus must be 1")
+        return 2
+    args.warmup = max(args.warmup, 3)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -66,8 +66,16 @@ def __getattr__(name):
         from .engine import Engine
 
         return Engine
-    if name in ("generate", "GenerationResult", "SamplingParams"):
+    if name == "generate":
+        from .api import generate
+
+        return generate
+    if name in ("GenerationResult", "GenerationStats"):
         from .engine import generate as _g
 
         return getattr(_g, name)
+    if name == "SamplingParams":
+        from .sampling.params import SamplingParams
+
+        return SamplingParams
     raise AttributeError(name)

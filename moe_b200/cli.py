@@ -1,0 +1,291 @@
+"""Command line in the reference's manner (src/main.rs:7-125, 127-196).
+
+    moe run   <model> --ids 1,2,3 [-n N] [--temp F] [--top-p F] [--top-k N] [--repeat-penalty F] [--seed N]
+    moe run   <model> --prompts FILE        one list of ids a line = one batch of unequal prompts
+    moe bench <model> [--prompt-len N] [--tokens N] [--batch N]
+    moe info  <model>
+
+Options keep the reference's names, meanings and defaults where it has them
+(``--ids``, ``-n/--tokens`` [128], ``--ctx``, ``--temp`` [0], ``--top-p`` [0.95],
+``--top-k`` [0], ``--repeat-penalty`` [1.0], ``--seed`` [0], ``--prompts``,
+``--no-stream``, ``--stats``, ``--prompt-len`` [32], bench ``--tokens`` [16]).
+Added here: ``--dtype bfloat16|float32`` [bfloat16], ``--batch N``,
+``--max-tokens N`` (cache size).  Prompts are token ids; there is no tokenizer.
+Arguments are parsed as the reference does: ``--k v``, ``--k=v``, short aliases
+``-n -o -h -V``, and a fixed list of boolean flags.
+"""
+from __future__ import annotations
+
+import json
+import sys
+import time
+from typing import Dict, List, Tuple
+
+USAGE = """\
+moe - Qwen2 MoE generation on one B200
+
+USAGE
+  moe run   <model> [options]        generate tokens
+  moe info  <model>                  show the architecture and its footprint
+  moe bench <model> [options]        measure prefill and decode throughput
+
+<model> is a folder with config.json and *.safetensors.
+
+RUN OPTIONS
+      --ids 1,2,3           prompt as token ids
+      --prompts PATH        one prompt a line (ids separated by commas or spaces, or a JSON
+                            list); the prompts form batches; one JSON result a line
+  -n, --tokens N            tokens to generate            [128]
+      --ctx N               context window per sequence   [min(model, 4096), at least prompt + n]
+      --temp F              sampling temperature, 0 = greedy   [0]
+      --top-p F             nucleus cutoff                [0.95]
+      --top-k N             candidate cutoff, 0 = off     [0]
+      --repeat-penalty F    penalty on recent tokens      [1.0]
+      --seed N              sampler seed                  [0]
+      --batch N             requests per batch            [all]
+      --no-stream           print only the finished list
+      --stats               throughput detail
+  -o, --out PATH            with --prompts: write results here instead of stdout
+
+BENCH OPTIONS
+      --prompt-len N        synthetic prompt length       [32]
+      --tokens N            decode steps to time          [16]
+      --batch N             sequences decoded together    [1]
+
+GLOBAL
+      --dtype NAME          bfloat16 | float32            [bfloat16]
+      --max-tokens N        tokens the cache can hold     [what the run needs]
+  -h, --help                this message
+  -V, --version             version
+"""
+
+FLAGS = {"help", "no-stream", "stats", "version"}
+ALIASES = {"n": "tokens", "o": "out", "h": "help", "V": "version"}
+
+
+def parse_args(argv: List[str]) -> Tuple[str, List[str], Dict[str, str]]:
+    pos: List[str] = []
+    opt: Dict[str, str] = {}
+    i = 0
+    while i < len(argv):
+        a = argv[i]
+        name = None
+        if a.startswith("--"):
+            name = a[2:]
+        elif a.startswith("-") and len(a) > 1 and not a[1].isdigit():
+            name = a[1:]
+        if name is not None:
+            key, _, inline = name.partition("=")
+            has_inline = "=" in name
+            key = ALIASES.get(key, key)
+            if has_inline:
+                val = inline
+            elif key in FLAGS:
+                val = "1"
+            else:
+                i += 1
+                val = argv[i] if i < len(argv) else ""
+            opt[key] = val
+        else:
+            pos.append(a)
+        i += 1
+    cmd = pos.pop(0) if pos else ""
+    return cmd, pos, opt
+
+
+def fail(msg) -> "None":
+    print(f"moe: {msg}", file=sys.stderr)
+    raise SystemExit(1)
+
+
+def _num(opt, key, default, typ):
+    if key not in opt:
+        return default
+    try:
+        return typ(opt[key])
+    except ValueError:
+        return default
+
+
+def _ids(text: str) -> List[int]:
+    text = text.strip()
+    if text.startswith("["):
+        return [int(x) for x in json.loads(text)]
+    return [int(x) for x in text.replace(",", " ").split()]
+
+
+def human(n: int) -> str:
+    units = ["B", "KB", "MB", "GB", "TB"]
+    v, i = float(n), 0
+    while v >= 1024 and i < len(units) - 1:
+        v /= 1024
+        i += 1
+    return f"{n} B" if i == 0 else f"{v:.2f} {units[i]}"
+
+
+def _load(path: str, opt):
+    import moe_b200
+
+    try:
+        return moe_b200.load_model(path, dtype=opt.get("dtype", "bfloat16"))
+    except (moe_b200.ConfigError, moe_b200.WeightError, ValueError, OSError) as e:
+        fail(e)
+
+
+def summary(model) -> str:
+    """The reference's ``Spec::summary`` (src/spec.rs:341-376), from the model's parts."""
+    spec = model.spec
+    mixers = [b.mixer for b in model.blocks]
+    m0 = mixers[0]
+    lines = [spec.architecture, f"  layers {len(spec.layers)}  hidden {spec.hidden_size}  vocab {spec.vocab_size}"]
+    lines.append(f"  attention  GQA({m0.nh} q / {m0.nkv} kv heads, head_dim={m0.hd})")
+    pos = m0.position
+    lines.append(f"  rope       theta {getattr(pos, 'theta', 0):.0f}")
+    wins = [m.window for m in mixers]
+    local = [w for w in wins if w]
+    if local:
+        where = "every layer" if len(local) == len(wins) else f"{len(local)} of {len(wins)} layers"
+        lines.append(f"  window     {max(local)} on {where}")
+    ffns = [b.ffn for b in model.blocks]
+    routed = [f for f in ffns if f.kind == "routed_experts"]
+    if routed:
+        f = routed[0]
+        lines.append(f"  ffn        {f.E} experts, top-{f.k}, softmax gate"
+                     + (f", shared expert {f.shared_size}" if f.shared_size else "")
+                     + (f", {len(ffns) - len(routed)} dense layers" if len(routed) != len(ffns) else ""))
+    else:
+        lines.append("  ffn        dense")
+    return "\n".join(lines)
+
+
+def cmd_info(path: str, opt) -> None:
+    model = _load(path, opt)
+    from .models.decoder import expected_tensors
+
+    exp = expected_tensors(model.spec)
+    esize = 2 if model.rt.is_bf16 else 4
+    total = sum(_numel(t.shape) for t in exp.values()) * esize
+    experts = sum(_numel(t.shape) for n, t in exp.items() if ".mlp.experts." in n) * esize
+    print(summary(model))
+    print(f"\nweights    {len(exp)} tensors, {human(total)}")
+    print(f"  dense    {human(total - experts)}")
+    print(f"  experts  {human(experts)} ({100.0 * experts / max(total, 1):.0f}%)")
+    kv = sum(2 * r.num_kv_heads * r.head_dim for r in model.kv_requests().values() if r) * esize * 1024
+    print(f"kv cache   {human(kv)} per 1k tokens")
+    print(f"source     {path} (safetensors)")
+
+
+def _numel(shape) -> int:
+    n = 1
+    for s in shape:
+        n *= s
+    return n
+
+
+def cmd_run(path: str, opt) -> None:
+    import moe_b200
+    from moe_b200.engine.generate import GenerationStats
+
+    if "prompts" in opt:
+        src = sys.stdin.read() if opt["prompts"] == "-" else open(opt["prompts"]).read()
+        prompts = [_ids(l) for l in src.splitlines() if l.strip()]
+        if not prompts:
+            fail(f"{opt['prompts']}: no prompts")
+    elif "ids" in opt:
+        prompts = [_ids(opt["ids"])]
+    else:
+        fail("give one of --ids or --prompts")
+    if any(not p for p in prompts):
+        fail("empty prompt")
+    n_gen = _num(opt, "tokens", 128, int)
+    t_load = time.perf_counter()
+    model = _load(path, opt)
+    batch = _num(opt, "batch", len(prompts), int)
+    longest = max(len(p) for p in prompts)
+    max_ctx = model.spec.max_position_embeddings or 4096
+    ctx = max(_num(opt, "ctx", min(max_ctx, 4096), int), longest + n_gen)
+    need = sum(sorted((-(-(len(p) + n_gen) // 64) * 64 for p in prompts), reverse=True)[:batch])
+    engine = moe_b200.Engine(model, max_tokens=_num(opt, "max-tokens", need, int), max_slots=batch)
+    load_s = time.perf_counter() - t_load
+    stream = "no-stream" not in opt and len(prompts) == 1
+
+    def on_token(i, tok):
+        if stream:
+            print(tok, end=" ", flush=True)
+        return True
+
+    stats = GenerationStats()
+    outs = moe_b200.generate(
+        engine, prompts, max_tokens=n_gen, temp=_num(opt, "temp", 0.0, float), top_p=_num(opt, "top-p", 0.95, float),
+        top_k=_num(opt, "top-k", 0, int), repeat_penalty=_num(opt, "repeat-penalty", 1.0, float),
+        seed=_num(opt, "seed", 0, int), batch_size=batch, ctx=ctx, on_token=on_token, stats=stats)
+    if "prompts" in opt:
+        lines = [json.dumps({"index": i, "prompt": prompts[i], "tokens": o.tokens, "generated": len(o.tokens),
+                             "prompt_tokens": o.prompt_tokens, "finish": o.finish_reason})
+                 for i, o in enumerate(outs)]
+        if "out" in opt:
+            with open(opt["out"], "w") as f:
+                f.write("\n".join(lines) + "\n")
+            print(f"wrote {len(lines)} results to {opt['out']}", file=sys.stderr)
+        else:
+            print("\n".join(lines))
+    elif stream:
+        print()
+    else:
+        print(outs[0].tokens)
+    gen = sum(len(o.tokens) for o in outs)
+    print(f"\nload {load_s:.2f}s | prefill {stats.prefill_tokens} tok in {stats.prefill_seconds:.2f}s "
+          f"({stats.prefill_tokens / max(stats.prefill_seconds, 1e-6):.1f} tok/s) | decode {gen} tok in "
+          f"{stats.decode_seconds:.2f}s ({stats.decode_tokens / max(stats.decode_seconds, 1e-6):.2f} tok/s)",
+          file=sys.stderr)
+    if "stats" in opt:
+        print(f"decode steps {stats.decode_steps} | kv cache {human(engine.cache.bytes())} | "
+              f"finish {[o.stop for o in outs]}", file=sys.stderr)
+
+
+def cmd_bench(path: str, opt) -> None:
+    """``moe bench`` (src/main.rs:1221-1253): ids (i*7+13) % vocab, timed prefill, then timed
+    single-token steps with fixed tokens i % vocab; logits are computed every step."""
+    import torch
+
+    import moe_b200
+
+    model = _load(path, opt)
+    plen, n, B = _num(opt, "prompt-len", 32, int), _num(opt, "tokens", 16, int), _num(opt, "batch", 1, int)
+    V = model.spec.vocab_size
+    ids = [(i * 7 + 13) % V for i in range(plen)]
+    engine = moe_b200.Engine(model, max_tokens=B * (-(-(plen + n + 8) // 64) * 64), max_slots=B)
+    slots = [engine.new_sequence() for _ in range(B)]
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    engine.step(slots, [ids] * B)
+    torch.cuda.synchronize()
+    pf = time.perf_counter() - t0
+    t1 = time.perf_counter()
+    for i in range(n):
+        engine.step(slots, [[i % V]] * B, check=False)
+    torch.cuda.synchronize()
+    dc = time.perf_counter() - t1
+    engine.rt.check()
+    print(summary(model))
+    print(f"\nprefill  {plen * B} tok in {pf:.3f}s   {plen * B / max(pf, 1e-9):.1f} tok/s")
+    print(f"decode   {n * B} tok in {dc:.3f}s   {n * B / max(dc, 1e-9):.2f} tok/s   {1000.0 * dc / max(n, 1):.2f} ms/step")
+    print(f"batch    {B}   dtype {opt.get('dtype', 'bfloat16')}   kv cache {human(engine.cache.bytes())}")
+
+
+def main(argv=None) -> int:
+    import moe_b200
+
+    cmd, pos, opt = parse_args(list(sys.argv[1:] if argv is None else argv))
+    if "version" in opt:
+        print(f"moe {moe_b200.__version__}")
+        return 0
+    if "help" in opt or not cmd:
+        print(USAGE)
+        return 0
+    if cmd not in ("run", "info", "bench"):
+        fail(f"unknown command '{cmd}' (try --help)")
+    if not pos:
+        fail(f"{cmd}: name a model folder")
+    {"run": cmd_run, "info": cmd_info, "bench": cmd_bench}[cmd](pos[0], opt)
+    return 0

@@ -104,6 +104,12 @@ class Engine:
         if want is None:
             want = [[len(t) - 1] for t in tokens]
         counts = [len(t) for t in tokens]
+        if len(want) != B:
+            raise ValueError("slots and want differ in length")
+        for n, w in zip(counts, want):
+            for i in w:
+                if not 0 <= i < n:
+                    raise ValueError(f"wanted place {i} is not among the {n} tokens of this step")
         starts = [self.cache.length(s) if self.cache.ledger.slots.is_held(s) else 0 for s in slots]
         updates = self._reserve(slots, counts)
         T, W = sum(counts), sum(len(w) for w in want)
@@ -128,8 +134,21 @@ class Engine:
             core.table_update(self.cache.groups[gi].table, dev[o:o + 3 * n], n)
         views = {k: dev[a:a + n] for k, (a, n) in info["offsets"].items()}
         batch = StepBatch(**views, **info["facts"])
+        self.last_batch = batch
         logits = self.model.forward(batch, self.cache)
         self.steps_run += 1
         if check:
             self.rt.check()
         return logits
+
+    def step_and_sample(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], sampler, params,
+                        histories=None) -> List[int]:
+        """One step, then one sampled token per sequence from the logits at its last
+        place; tokens come back to the host (one small copy, which also carries the
+        device status word)."""
+        logits = self.step(slots, tokens, None, check=False)
+        picked = sampler.sample(logits, self.last_batch.slots, params, histories)
+        host = torch.cat([picked, self.rt.status[:1]]).cpu()
+        if int(host[-1]):
+            self.rt.check()
+        return host[:-1].tolist()

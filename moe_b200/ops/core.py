@@ -81,7 +81,12 @@ def _chk(t: torch.Tensor, name: str, dtype=None, dims: Optional[int] = None):
     return t
 
 
+launches = 0   # kernels launched through this module since import (benchmarks read the difference)
+
+
 def _ok(code: int, what: str):
+    global launches
+    launches += 1
     if code != 0:
         try:
             msg = torch.cuda.cudart().cudaGetErrorString(code)

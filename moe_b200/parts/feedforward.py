@@ -67,6 +67,9 @@ class RoutedExperts(Part):
         self.shared_gate = bool(p.get("shared_gate", False)) and self.shared_size > 0
         if not 0 < self.k <= self.E:
             raise ValueError("top_k must lie in 1..num_experts")
+        # Set to a list to record every routing decision as (expert ids [T, k], weights [T, k]);
+        # the reference's State::trace does the same per token and layer (src/model.rs:157, 943-950).
+        self.trace = None
 
     def tensors(self):
         t = {"gate.weight": TensorSpec((self.E, self.hidden))}
@@ -117,6 +120,8 @@ class RoutedExperts(Part):
     def forward(self, rt, h, batch):
         T = h.act.shape[0]
         topk_idx, topk_w, sg = self.route(rt, h, batch)
+        if self.trace is not None:
+            self.trace.append((topk_idx.clone(), topk_w.clone()))
         P = T * self.k
         offsets = rt.empty((self.E + 1,), torch.int32)
         sorted_token = rt.empty((P,), torch.int32)

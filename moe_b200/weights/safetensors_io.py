@@ -55,7 +55,7 @@ class SafetensorsFile:
         if size < 8:
             raise SafetensorsError(f"{path}: truncated safetensors file ({size} bytes)")
         self._f = open(path, "rb")
-        self._map = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ)
+        self._map = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_COPY)
         (hlen,) = struct.unpack("<Q", self._map[:8])
         if hlen > size - 8:
             raise SafetensorsError(f"{path}: header claims {hlen} bytes in a {size}-byte file")

@@ -66,13 +66,13 @@ def routing_margin(model_dir: str, tokens: Sequence[int]) -> float:
     gaps = []
     orig = plain.route
 
-    def spy(cfg_, w_, p, n):
+    def spy(cfg_, w_, p, n, forced=None):
         sc = torch.softmax(n @ w_[p + "mlp.gate.weight"].T, dim=-1)
         k = cfg_["num_experts_per_tok"]
         s, _ = torch.sort(sc, dim=-1, descending=True)
         if sc.shape[1] > k:
             gaps.append(float(((s[:, k - 1] - s[:, k]) / s[:, k - 1]).min()))
-        return orig(cfg_, w_, p, n)
+        return orig(cfg_, w_, p, n, forced)
 
     plain.route = spy
     try:
@@ -143,3 +143,88 @@ def replay_batches(engine, requests: Dict[str, List[int]], batch_size: int) -> D
 def max_rel_err(got: torch.Tensor, ref: torch.Tensor) -> float:
     """max |got - ref| / max |ref|."""
     return float((got.double() - ref.double()).abs().max() / ref.double().abs().max().clamp(min=1e-30))
+
+
+# ----------------------------------------------------------------------------- routing-aware comparison
+def routed_parts(model):
+    """The routed feed-forwards in the order the schedule runs them."""
+    return [model.blocks[e.layer].ffn for e in model.spec.schedule
+            if model.blocks[e.layer].ffn.kind == "routed_experts"]
+
+
+def whole_with_picks(engine, tokens: Sequence[int]):
+    """One request alone and whole -> (logits [T, V] on the CPU, [layer][T][k] expert picks)."""
+    parts = routed_parts(engine.model)      # a part appears once per run of its layer
+    for p in parts:
+        p.trace = []
+    try:
+        s = engine.new_sequence()
+        lg = engine.step([s], [list(tokens)], [list(range(len(tokens)))]).cpu()
+        engine.release(s)
+        taken = {}
+        picks = []
+        for p in parts:
+            i = taken.get(id(p), 0)
+            picks.append(p.trace[i][0].cpu().tolist())
+            taken[id(p)] = i + 1
+    finally:
+        for p in parts:
+            p.trace = None
+    return lg, picks
+
+
+def compare_with_plain(model_dir: str, engine, tokens: Sequence[int], flip_margin: float):
+    """Engine (whole request) against the plain implementation.
+
+    Top-k routing is discontinuous: where two experts' probabilities are closer than the
+    arithmetic's own noise, either pick is right.  So the plain implementation is run with the
+    engine's picks, and every pick that differs from its own free choice must sit at a margin
+    below ``flip_margin``.  Returns (max relative error of the logits, fraction of differing picks)."""
+    cfg, w = plain.read_model(model_dir)
+    got, picks = whole_with_picks(engine, tokens)
+    free = []
+    plain.forward(cfg, w, list(tokens), trace=free)
+    ref = plain.forward(cfg, w, list(tokens), forced=picks)
+    differing = total = 0
+    k = cfg["num_experts_per_tok"]
+    li = 0
+    for l in range(cfg["num_hidden_layers"]):
+        if not plain.layer_is_sparse(cfg, l):
+            continue
+        for i in range(len(tokens)):
+            total += 1
+            if sorted(picks[li][i]) != sorted(free[li][0][i]):
+                differing += 1
+        li += 1
+    if differing:
+        # legitimacy of the flips: recompute the margins where they happened
+        margins = flip_margins(cfg, w, tokens, picks)
+        assert max(margins) < flip_margin, f"a routing pick differs at margin {max(margins):.3g}"
+    return max_rel_err(got, ref), differing / max(total, 1)
+
+
+def flip_margins(cfg, w, tokens, picks) -> List[float]:
+    """For every (layer, token) whose forced pick differs from the free one: the relative gap
+    between the probabilities of the experts that were swapped."""
+    out = []
+    state = {"li": 0}
+    orig = plain.route
+
+    def spy(cfg_, w_, p, n, forced=None):
+        sc = torch.softmax(n @ w_[p + "mlp.gate.weight"].T, dim=-1)
+        k = cfg_["num_experts_per_tok"]
+        for i in range(n.shape[0]):
+            free = sorted(range(sc.shape[1]), key=lambda e: (-float(sc[i, e]), e))[:k]
+            if forced is not None and sorted(free) != sorted(int(e) for e in forced[i]):
+                lost = [e for e in free if e not in forced[i]]
+                gained = [int(e) for e in forced[i] if e not in free]
+                hi, lo = max(float(sc[i, e]) for e in lost), min(float(sc[i, e]) for e in gained)
+                out.append((hi - lo) / hi)
+        return orig(cfg_, w_, p, n, forced)
+
+    plain.route = spy
+    try:
+        plain.forward(cfg, w, list(tokens), forced=picks)
+    finally:
+        plain.route = orig
+    return out

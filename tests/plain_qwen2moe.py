@@ -159,15 +159,19 @@ def swiglu_mlp(w, prefix, n) -> torch.Tensor:
     return ((g / (1.0 + torch.exp(-g))) * u) @ w[prefix + "down_proj.weight"].T
 
 
-def route(cfg, w, p, n):
+def route(cfg, w, p, n, forced=None):
     """src/model.rs:844-897: softmax over all experts, top k by descending score (tie: lower index,
-    scripts/oracle.py:323), w = max(sc, 0), optional renormalisation by max(sum, 1e-20), scaling."""
+    scripts/oracle.py:323), w = max(sc, 0), optional renormalisation by max(sum, 1e-20), scaling.
+    ``forced`` ([T][k] expert ids) replaces the pick and keeps the rest, in the manner of the
+    reference's routing overrides (src/model.rs:238-252)."""
     logits = n @ w[p + "mlp.gate.weight"].T
     sc = torch.softmax(logits, dim=-1)
     k = cfg["num_experts_per_tok"]
     picks, weights = [], []
     for i in range(n.shape[0]):
         order = sorted(range(sc.shape[1]), key=lambda e: (-float(sc[i, e]), e))[:k]
+        if forced is not None:
+            order = [int(e) for e in forced[i]]
         ww = torch.stack([sc[i, e].clamp(min=0.0) for e in order])
         if cfg.get("norm_topk_prob", False):
             ww = ww / ww.sum().clamp(min=1e-20)
@@ -177,10 +181,10 @@ def route(cfg, w, p, n):
     return picks, weights
 
 
-def moe_block(cfg, w, p, n, trace=None) -> torch.Tensor:
+def moe_block(cfg, w, p, n, trace=None, forced=None) -> torch.Tensor:
     """src/model.rs:902-970: weighted sum of the picked experts, then the shared expert scaled by
     sigmoid(shared_expert_gate . n)."""
-    picks, weights = route(cfg, w, p, n)
+    picks, weights = route(cfg, w, p, n, forced)
     if trace is not None:
         trace.append((picks, weights))
     out = torch.zeros_like(n)
@@ -196,8 +200,11 @@ def moe_block(cfg, w, p, n, trace=None) -> torch.Tensor:
     return out
 
 
-def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], trace=None) -> torch.Tensor:
-    """Logits [T, vocab] for every position of one whole sequence (src/model.rs:646-687, 578-589)."""
+def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], trace=None, forced=None) -> torch.Tensor:
+    """Logits [T, vocab] for every position of one whole sequence (src/model.rs:646-687, 578-589).
+    ``trace`` (a list) receives (picks, weights) per routed layer; ``forced`` (one [T][k] list per
+    routed layer, in layer order) fixes the picks."""
+    forced = list(forced) if forced is not None else None
     eps = cfg.get("rms_norm_eps", 1e-6)
     wins = layer_windows(cfg)
     positions = torch.arange(len(tokens))
@@ -208,7 +215,7 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], trace=None
         x = x + attention_block(cfg, w, p, n, positions, wins[l])
         n = rmsnorm(x, w[p + "post_attention_layernorm.weight"], eps)
         if layer_is_sparse(cfg, l):
-            x = x + moe_block(cfg, w, p, n, trace)
+            x = x + moe_block(cfg, w, p, n, trace, forced.pop(0) if forced is not None else None)
         else:
             x = x + swiglu_mlp(w, p + "mlp.", n)
     nx = rmsnorm(x, w["model.norm.weight"], eps)
@@ -240,31 +247,20 @@ def sample(logits: np.ndarray, history: List[int], rng: Rng, temp=0.0, top_p=0.9
         for t in list(reversed(history))[:repeat_window]:
             l[t] = l[t] / np.float32(repeat_penalty) if l[t] > 0 else l[t] * np.float32(repeat_penalty)
     if temp <= 0.0:
-        best = 0
-        for i in range(len(l)):
-            if l[i] > l[best]:
-                best = i
-        return best
+        return int(np.argmax(l))                       # the first maximum (strict > in the reference)
     k = len(l) if top_k == 0 else min(top_k, len(l))
-    idx = sorted(range(len(l)), key=lambda i: (-float(l[i]), i))[:k]
+    idx = np.lexsort((np.arange(len(l)), -l))[:k]      # descending; equal logits by index
     mx = l[idx[0]]
     probs = np.exp((l[idx] - mx) / np.float32(temp)).astype(np.float32)
-    probs = probs / probs.sum(dtype=np.float32)
+    probs = probs / np.cumsum(probs, dtype=np.float32)[-1]
     if 0.0 < top_p < 1.0:
-        acc, cut = np.float32(0.0), len(probs)
-        for i, pr in enumerate(probs):
-            acc += pr
-            if acc >= np.float32(top_p):
-                cut = i + 1
-                break
+        acc = np.cumsum(probs, dtype=np.float32)       # sequential float32 sum, as the reference's loop
+        hit = acc >= np.float32(top_p)
+        cut = int(np.argmax(hit)) + 1 if hit.any() else len(probs)
         probs, idx = probs[:cut], idx[:cut]
-        probs = probs / probs.sum(dtype=np.float32)
+        probs = probs / np.cumsum(probs, dtype=np.float32)[-1]
     if len(idx) == 1:
-        return idx[0]
+        return int(idx[0])
     r = np.float32(rng.next_f32())
-    acc = np.float32(0.0)
-    for i, pr in enumerate(probs):
-        acc += pr
-        if r < acc:
-            return idx[i]
-    return idx[-1]
+    hit = r < np.cumsum(probs, dtype=np.float32)
+    return int(idx[int(np.argmax(hit))]) if hit.any() else int(idx[-1])

@@ -1,0 +1,150 @@
+"""The engine against the plain implementation, in 32-bit and in bfloat16, under every cut.
+
+Mirrors the reference's tests/oracle.rs: token by token (:46-56), whole (:60-69), split
+(:71-75), every row (:100-118); plus batches of unequal lengths, which the reference has not."""
+import pytest
+import torch
+
+import gpu_util as G
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+CASES = [(n, dt, std) for n in ("A", "B") for dt in ("float32", "bfloat16") for std in G.STD[dt]]
+LENGTHS = [5, 9, 12, 40, 77, 1, 33]
+
+
+def requests_for(name):
+    V = helpers.CONFIGS[name]["vocab_size"]
+    return {f"r{i}": helpers.random_tokens(V, n, 100 + i) for i, n in enumerate(LENGTHS)}
+
+
+@pytest.mark.parametrize("name,dtype,std", CASES)
+def test_each_request_alone_and_whole_matches_plain(model_dirs, name, dtype, std):
+    d, eng = G.engine_for(model_dirs, name, dtype, std)
+    flips = []
+    for rid, toks in requests_for(name).items():
+        err, frac = helpers.compare_with_plain(d, eng, toks, G.flip(dtype))
+        flips.append(frac)
+        assert err < G.tol(dtype), f"{rid}: relative error {err:.3g}"
+    assert sum(flips) / len(flips) < (0.001 if dtype == "float32" else 0.05), f"routing differs too often: {flips}"
+    assert eng.cache.ledger.slots.num_held == 0
+
+
+@pytest.mark.parametrize("name,dtype,std", CASES)
+def test_last_32_tokens_one_by_one_equal_whole(model_dirs, name, dtype, std):
+    d, eng = G.engine_for(model_dirs, name, dtype, std)
+    reqs = requests_for(name)
+    whole = helpers.replay_whole(eng, reqs)
+    tail = helpers.replay_tail(eng, reqs, 32)
+    for rid in reqs:
+        assert tail[rid].shape == whole[rid].shape
+        err = helpers.max_rel_err(tail[rid], whole[rid])
+        assert err < G.tol_cut(dtype), f"{rid}: first wrong place {first_bad(tail[rid], whole[rid], G.tol_cut(dtype))}"
+
+
+@pytest.mark.parametrize("name,dtype,std", CASES)
+def test_unequal_batches_one_after_another_equal_whole(model_dirs, name, dtype, std):
+    # 3 slots for 7 requests: every slot is given back and used again
+    d, eng = G.engine_for(model_dirs, name, dtype, std, max_tokens=64 * 6, max_slots=3)
+    reqs = requests_for(name)
+    whole = helpers.replay_whole(eng, reqs)
+    batched = helpers.replay_batches(eng, reqs, 3)
+    for rid in reqs:
+        err = helpers.max_rel_err(batched[rid], whole[rid])
+        assert err < G.tol_cut(dtype), f"{rid}: first wrong place {first_bad(batched[rid], whole[rid], G.tol_cut(dtype))}"
+    led = eng.cache.ledger
+    assert led.slots.num_held == 0 and all(g.pool.num_free == g.pool.num_pages - 1 for g in led.groups)
+
+
+def first_bad(got, ref, tol):
+    scale = float(ref.abs().max())
+    bad = ((got.double() - ref.double()).abs().amax(dim=1) > tol * scale).nonzero()
+    return int(bad[0]) if len(bad) else None
+
+
+@pytest.mark.parametrize("name,dtype", [(n, dt) for n in ("A", "B") for dt in ("float32", "bfloat16")])
+def test_the_first_tokens_of_a_sequence(model_dirs, name, dtype):
+    """Positions 0, 1, 2 decoded one by one from an empty slot (a prompt of one token)."""
+    d, eng = G.engine_for(model_dirs, name, dtype)
+    toks = helpers.random_tokens(helpers.CONFIGS[name]["vocab_size"], 4, 9)
+    got = helpers.replay_tail(eng, {"x": toks}, tail=10)["x"]
+    err, _ = helpers.compare_with_plain(d, eng, toks, G.flip(dtype))
+    whole = helpers.replay_whole(eng, {"x": toks})["x"]
+    assert err < G.tol(dtype) and helpers.max_rel_err(got, whole) < G.tol_cut(dtype)
+
+
+@pytest.mark.parametrize("name,dtype", [(n, dt) for n in ("A", "B") for dt in ("float32", "bfloat16")])
+def test_long_decoding(model_dirs, name, dtype):
+    """3 prompt tokens, then 330 tokens one by one: several pages, the window's ring wrapping many
+    times (B), and hundreds of keys behind every query."""
+    d, eng = G.engine_for(model_dirs, name, dtype)
+    toks = helpers.random_tokens(helpers.CONFIGS[name]["vocab_size"], 333, 5)
+    one_by_one = helpers.replay_tail(eng, {"x": toks}, tail=330)["x"]
+    err, frac = helpers.compare_with_plain(d, eng, toks, G.flip(dtype))
+    whole = helpers.replay_whole(eng, {"x": toks})["x"]
+    assert err < G.tol(dtype), f"whole against plain: {err:.3g}"
+    cut = helpers.max_rel_err(one_by_one, whole)
+    assert cut < G.tol_cut(dtype), f"first wrong place {first_bad(one_by_one, whole, G.tol_cut(dtype))}"
+
+
+def test_a_reused_slot_never_shows_what_it_held_before(model_dirs):
+    """The same request on a fresh engine and on one whose slot and pages held other sequences."""
+    import moe_b200
+    from moe_b200.engine import Engine
+
+    for name in ("A", "B"):
+        d = model_dirs.get(name, "float32", seed=1, std=0.2)
+        V = helpers.CONFIGS[name]["vocab_size"]
+        toks = helpers.random_tokens(V, 70, 1)
+        fresh = Engine(moe_b200.load_model(d, dtype="float32"), max_tokens=256, max_slots=1)
+        want = helpers.replay_tail(fresh, {"x": toks}, 20)["x"]
+        used = Engine(moe_b200.load_model(d, dtype="float32"), max_tokens=256, max_slots=1)
+        for seed in (7, 8):                       # fill every page with other sequences' keys, then give them back
+            helpers.replay_whole(used, {"y": helpers.random_tokens(V, 250, seed)})
+        got = helpers.replay_tail(used, {"x": toks}, 20)["x"]
+        assert torch.equal(got, want)
+
+
+def test_cache_full_is_an_error_and_changes_nothing(model_dirs):
+    from moe_b200.cache import CacheError
+
+    d, eng = G.engine_for(model_dirs, "A", "float32", max_tokens=192, max_slots=2)
+    a, b = eng.new_sequence(), eng.new_sequence()
+    eng.step([a], [[1] * 64])
+    with pytest.raises(CacheError):
+        eng.step([a, b], [[2], [3] * 65])          # a needs 1 more page, b needs 2: only 2 are free
+    assert eng.length(a) == 64 and eng.length(b) == 0
+    eng.step([a, b], [[2], [3] * 10])              # still usable
+    eng.release(a), eng.release(b)
+
+
+def test_a_token_outside_the_vocabulary_is_reported(model_dirs):
+    from moe_b200.ops.core import KernelError
+
+    d, eng = G.engine_for(model_dirs, "A", "float32")
+    s = eng.new_sequence()
+    with pytest.raises(KernelError) as e:
+        eng.step([s], [[1, 256, 3]])
+    assert "vocabulary" in str(e.value)
+    eng.release(s)
+    # the engine is still usable
+    toks = helpers.random_tokens(256, 5, 0)
+    assert helpers.compare_with_plain(d, eng, toks, G.FLIP_F32)[0] < G.TOL_F32
+
+
+def test_wanted_places_select_rows(model_dirs):
+    d, eng = G.engine_for(model_dirs, "B", "float32")
+    toks = helpers.random_tokens(384, 20, 4)
+    whole = helpers.replay_whole(eng, {"x": toks})["x"]
+    s = eng.new_sequence()
+    assert eng.step([s], [toks[:10]], [[]]) is None
+    got = eng.step([s], [toks[10:]], [[9, 0, 4]]).cpu()
+    eng.release(s)
+    assert helpers.max_rel_err(got, whole[[19, 10, 14]]) < G.TOL_CUT_F32
+    with pytest.raises(ValueError):
+        s = eng.new_sequence()
+        try:
+            eng.step([s], [[1, 2]], [[2]])
+        finally:
+            eng.release(s)

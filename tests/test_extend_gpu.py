@@ -1,0 +1,179 @@
+"""Adding to the library from outside: a toy mixer with state of its own and a toy architecture,
+both defined here, are registered, given random weights, loaded, and stepped through the
+engine -- without a change to the library's files.  The toy model also names a layer twice in
+its schedule and lets one layer read another layer's cache."""
+import json
+
+import pytest
+import torch
+
+import gpu_util as G
+import helpers
+import plain_qwen2moe as plain
+
+pytestmark = pytest.mark.gpu
+
+
+def register_toy():
+    import moe_b200
+    from moe_b200.cache import StateRequest
+    from moe_b200.config import Architecture, LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    from moe_b200.parts import Part, TensorSpec
+
+    class DecayMixer(Part):
+        """s_t = decay * s_{t-1} + W_in n_t;  out_t = W_out s_t.  The carry s lives in the cache's
+        per-sequence state of fixed size; tokens of a sequence are scanned in order."""
+        category, kind = "mixer", "toy_decay"
+
+        def __init__(self, spec):
+            super().__init__(spec)
+            self.hidden, self.decay = int(self.params["hidden_size"]), float(self.params["decay"])
+
+        def tensors(self):
+            return {"in_proj.weight": TensorSpec((self.hidden, self.hidden)),
+                    "out_proj.weight": TensorSpec((self.hidden, self.hidden))}
+
+        def kv_request(self):
+            return None
+
+        def state_request(self):
+            return StateRequest((self.hidden,), torch.float32)
+
+        def bind(self, tensors, rt):
+            super().bind(tensors, rt)
+            self.w_in, self.w_out = tensors["in_proj.weight"].float(), tensors["out_proj.weight"].float()
+
+        def forward(self, rt, h, batch, cache_view, state):
+            assert cache_view is None and state is not None
+            u = h.act.float() @ self.w_in.T
+            out = torch.empty_like(u)
+            cu, slots = batch.cu_seqlens.tolist(), batch.slots.tolist()
+            for s in range(batch.num_seqs):
+                carry = state[slots[s]]
+                for t in range(cu[s], cu[s + 1]):
+                    carry = self.decay * carry + u[t]
+                    out[t] = carry
+                state[slots[s]] = carry
+            return (out @ self.w_out.T).contiguous()
+
+    moe_b200.register_part("mixer", "toy_decay", DecayMixer)
+
+    def parse(cfg):
+        return dict(cfg)
+
+    def spec_of(c):
+        H, V = c["hidden_size"], c["vocab_size"]
+        norm = lambda p: PartSpec("rmsnorm", {"size": H, "eps": c["eps"]}, p)
+        attn = lambda p, own: PartSpec("gqa_attention", {
+            "hidden_size": H, "num_heads": c["heads"], "num_kv_heads": c["kv_heads"], "head_dim": c["head_dim"],
+            "qkv_bias": False, "window": None, "own_kv": own,
+            "position": {"kind": "rotary", "theta": c["theta"], "rotary_dim": c["head_dim"]}}, p)
+        dense = lambda p: PartSpec("dense_swiglu", {"hidden_size": H, "size": c["ffn"]}, p)
+        routed = lambda p: PartSpec("routed_experts", {"hidden_size": H, "num_experts": 4, "top_k": 2,
+                                                       "expert_size": c["ffn"] // 2, "norm_topk_prob": True}, p)
+        layers = (
+            LayerSpec("prenorm", norm("l0.n1."), attn("l0.attn.", True), norm("l0.n2."), dense("l0.ffn.")),
+            LayerSpec("prenorm", norm("l1.n1."), PartSpec("toy_decay", {"hidden_size": H, "decay": c["decay"]}, "l1.mix."),
+                      norm("l1.n2."), routed("l1.ffn.")),
+            LayerSpec("prenorm", norm("l2.n1."), attn("l2.attn.", False), norm("l2.n2."), dense("l2.ffn.")),
+        )
+        schedule = (ScheduleEntry(0, 0, True), ScheduleEntry(1, 1, True), ScheduleEntry(2, 0, False),
+                    ScheduleEntry(1, 2, True))                     # layer 1 runs twice, with a state for each run
+        return ModelSpec("ToyDecayForCausalLM", H, V, PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H}, "emb."),
+                         layers, schedule, norm("final."),
+                         PartSpec("lm_head", {"vocab_size": V, "hidden_size": H, "tied": True}, "head."))
+
+    moe_b200.register_architecture(Architecture("ToyDecayForCausalLM", parse, spec_of, dict))
+
+
+TOY = dict(architectures=["ToyDecayForCausalLM"], hidden_size=48, vocab_size=101, heads=3, kv_heads=1, head_dim=16,
+           ffn=64, eps=1e-6, theta=1e4, decay=0.7)
+
+
+def toy_plain(w, tokens, trace=None, forced=None):
+    """The toy model, whole sequence, float64."""
+    c = TOY
+    cfg = dict(num_attention_heads=c["heads"], num_key_value_heads=c["kv_heads"], head_dim=c["head_dim"],
+               rope_theta=c["theta"], num_experts_per_tok=2, norm_topk_prob=True)
+    T = len(tokens)
+    pos = torch.arange(T)
+    inv = plain.rope_inv_freq(c["theta"], c["head_dim"])
+    x = w["emb.weight"][torch.tensor(tokens)].clone()
+    forced = list(forced) if forced is not None else None
+
+    def ffn_routed(n):
+        ww = {k.replace("l1.ffn.", "p.mlp."): v for k, v in w.items() if k.startswith("l1.ffn.")}
+        return plain.moe_block(cfg, ww, "p.", n, trace, forced.pop(0) if forced is not None else None)
+
+    def toy(n):
+        u = n @ w["l1.mix.in_proj.weight"].T
+        out, carry = torch.zeros_like(u), torch.zeros(c["hidden_size"], dtype=torch.float64)
+        for t in range(T):
+            carry = c["decay"] * carry + u[t]
+            out[t] = carry
+        return out @ w["l1.mix.out_proj.weight"].T
+
+    # layer 0: attention that owns cache 0
+    n = plain.rmsnorm(x, w["l0.n1.weight"], c["eps"])
+    k0 = plain.rope((n @ w["l0.attn.k_proj.weight"].T).reshape(T, c["kv_heads"], c["head_dim"]), pos, inv)
+    v0 = (n @ w["l0.attn.v_proj.weight"].T).reshape(T, c["kv_heads"], c["head_dim"])
+    q0 = plain.rope((n @ w["l0.attn.q_proj.weight"].T).reshape(T, c["heads"], c["head_dim"]), pos, inv)
+    x = x + plain.attention(q0, k0, v0, None) @ w["l0.attn.o_proj.weight"].T
+    x = x + plain.swiglu_mlp({k.replace("l0.ffn.", "m."): v for k, v in w.items()}, "m.",
+                             plain.rmsnorm(x, w["l0.n2.weight"], c["eps"]))
+    # layer 1 (first run)
+    x = x + toy(plain.rmsnorm(x, w["l1.n1.weight"], c["eps"]))
+    x = x + ffn_routed(plain.rmsnorm(x, w["l1.n2.weight"], c["eps"]))
+    # layer 2: queries of its own over layer 0's keys and values
+    n = plain.rmsnorm(x, w["l2.n1.weight"], c["eps"])
+    q2 = plain.rope((n @ w["l2.attn.q_proj.weight"].T).reshape(T, c["heads"], c["head_dim"]), pos, inv)
+    x = x + plain.attention(q2, k0, v0, None) @ w["l2.attn.o_proj.weight"].T
+    x = x + plain.swiglu_mlp({k.replace("l2.ffn.", "m."): v for k, v in w.items()}, "m.",
+                             plain.rmsnorm(x, w["l2.n2.weight"], c["eps"]))
+    # layer 1 again
+    x = x + toy(plain.rmsnorm(x, w["l1.n1.weight"], c["eps"]))
+    x = x + ffn_routed(plain.rmsnorm(x, w["l1.n2.weight"], c["eps"]))
+    return plain.rmsnorm(x, w["final.weight"], c["eps"]) @ w["emb.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_with_a_stateful_mixer(tmp_path, dtype):
+    import moe_b200
+    from moe_b200.engine import Engine
+
+    register_toy()
+    d = str(tmp_path / "toy")
+    moe_b200.write_random_model(d, TOY, seed=3, std=G.STD[dtype][1], dtype=dtype)
+    assert json.load(open(d + "/config.json"))["architectures"] == ["ToyDecayForCausalLM"]
+    model = moe_b200.load_model(d, dtype=dtype)
+    eng = Engine(model, max_tokens=512, max_slots=3)
+    assert len(eng.cache.groups) == 1 and len(eng.cache.groups[0].cache_ids) == 1     # only cache 0 holds keys
+    assert eng.cache.state(1) is not None and eng.cache.state(2) is not None and eng.cache.state(0) is None
+
+    _, w = plain.read_model(d)
+    reqs = {f"r{i}": helpers.random_tokens(101, n, 50 + i) for i, n in enumerate([7, 30, 1, 12, 19])}
+    whole = {}
+    for rid, toks in reqs.items():
+        got, picks = helpers.whole_with_picks(eng, toks)
+        ref = toy_plain(w, toks, forced=picks)
+        assert helpers.max_rel_err(got, ref) < G.tol(dtype), rid
+        whole[rid] = got
+    # cut differently, in batches on 3 slots: the state follows each sequence, and a slot that is
+    # used again starts from a zero state
+    tail = helpers.replay_tail(eng, reqs, 5)
+    batched = helpers.replay_batches(eng, reqs, 3)
+    for rid in reqs:
+        assert helpers.max_rel_err(tail[rid], whole[rid]) < G.tol_cut(dtype)
+        assert helpers.max_rel_err(batched[rid], whole[rid]) < G.tol_cut(dtype)
+    assert eng.cache.ledger.slots.num_held == 0
+    out = moe_b200.generate(eng, [reqs["r0"], reqs["r3"]], max_tokens=4)
+    assert [len(o.tokens) for o in out] == [4, 4]
+
+
+def test_unknown_part_kind_is_a_clear_error():
+    from moe_b200.config.spec import PartSpec
+    from moe_b200.parts import make_part
+
+    with pytest.raises(KeyError) as e:
+        make_part("mixer", PartSpec("no_such_mixer", {}))
+    assert "gqa_attention" in str(e.value)

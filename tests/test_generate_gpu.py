@@ -1,0 +1,111 @@
+"""Generation through the Python entry point and the command line, on the GPU."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import gpu_util as G
+import helpers
+import plain_qwen2moe as plain
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def engine_logits(eng, tokens):
+    return helpers.replay_whole(eng, {"x": list(tokens)})["x"]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_batch_of_three(model_dirs, dtype):
+    """Configuration A's workload: prompts of 5, 9 and 12 tokens, then 8 greedy steps."""
+    import moe_b200
+
+    d, eng = G.engine_for(model_dirs, "A", dtype)
+    prompts = [helpers.random_tokens(256, n, 20 + n) for n in (5, 9, 12)]
+    stats = moe_b200.GenerationStats()
+    outs = moe_b200.generate(eng, prompts, max_tokens=9, eos=(), stats=stats)
+    assert [len(o.tokens) for o in outs] == [9, 9, 9] and all(o.stop == "length" for o in outs)
+    assert stats.decode_steps == 8 and stats.prefill_tokens == 26
+    assert eng.cache.ledger.slots.num_held == 0
+    cfg, w = plain.read_model(d)
+    for p, o in zip(prompts, outs):
+        seq = p + o.tokens
+        ref = plain.forward(cfg, w, seq)[len(p) - 1:-1]           # the logits each token was picked from
+        if dtype == "float32":
+            # greedy on the plain logits gives the same tokens unless two logits are within rounding
+            gap = torch.topk(ref, 2, dim=-1).values
+            sure = (gap[:, 0] - gap[:, 1]) > 1e-3 * ref.abs().max()
+            assert torch.equal(ref.argmax(-1)[sure], torch.tensor(o.tokens)[sure]) and sure.float().mean() > 0.8
+        # every generated token is the argmax of the engine's own logits for the same history
+        own = engine_logits(eng, seq)[len(p) - 1:-1]
+        picked = own[torch.arange(len(o.tokens)), torch.tensor(o.tokens)]
+        assert torch.all(picked >= own.max(-1).values - G.tol_cut(dtype) * own.abs().max())
+
+
+def test_sequences_that_end_earlier_and_batches_in_a_row(model_dirs):
+    import moe_b200
+
+    d, eng = G.engine_for(model_dirs, "B", "float32", std=0.2, max_tokens=64 * 4, max_slots=2)
+    prompts = [helpers.random_tokens(384, n, 40 + n) for n in (1, 7, 16, 23, 3)]
+    free_run = moe_b200.generate(eng, prompts, max_tokens=10, eos=(), batch_size=2)
+    # make the 4th token of request 1 an end-of-sequence token: it stops there, the others do not change
+    eos = free_run[1].tokens[3]
+    outs = moe_b200.generate(eng, prompts, max_tokens=10, eos=[eos], batch_size=2)
+    for i, (a, b) in enumerate(zip(free_run, outs)):
+        want = a.tokens[:a.tokens.index(eos)] if eos in a.tokens else a.tokens
+        assert b.tokens == want and b.stop == ("eos" if eos in a.tokens else "length"), i
+    assert outs[1].stop == "eos" and len(outs[1].tokens) <= 3 and eng.cache.ledger.slots.num_held == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_seeded_temperature_sampling_workload_b(model_dirs, dtype):
+    """Configuration B's workload: prompts of 1, 7, 16 and 23 tokens, 12 tokens at temperature 0.8.
+    Request i samples with seed + i; the plain sampler on the engine's own logits gives the same."""
+    import moe_b200
+
+    d, eng = G.engine_for(model_dirs, "B", dtype)
+    prompts = [helpers.random_tokens(384, n, 60 + n) for n in (1, 7, 16, 23)]
+    kw = dict(temp=0.8, top_p=0.95, seed=5)
+    outs = moe_b200.generate(eng, prompts, max_tokens=12, eos=(), **kw)
+    again = moe_b200.generate(eng, prompts, max_tokens=12, eos=(), **kw)
+    assert [o.tokens for o in outs] == [o.tokens for o in again]                    # reproducible
+    other = moe_b200.generate(eng, prompts, max_tokens=12, eos=(), temp=0.8, seed=6)
+    assert [o.tokens for o in outs] != [o.tokens for o in other]
+    for i, (p, o) in enumerate(zip(prompts, outs)):
+        assert len(o.tokens) == 12
+        own = engine_logits(eng, p + o.tokens)[len(p) - 1:-1].numpy()
+        rng = plain.Rng(5 + i)
+        agree = sum(plain.sample(own[j], [], rng, temp=0.8, top_p=0.95) == o.tokens[j] for j in range(12))
+        assert agree >= (12 if dtype == "float32" else 11), f"request {i}: {agree} of 12"
+
+
+def test_command_line_run_info_bench(model_dirs, tmp_path):
+    d = model_dirs.get("A", "bfloat16", seed=1, std=0.08)
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    run = lambda *a: subprocess.run([sys.executable, os.path.join(ROOT, "bin", "moe"), *a], capture_output=True,
+                                    text=True, env=env, timeout=600)
+    r = run("run", d, "--ids", "5,17,3,9", "-n", "6", "--no-stream")
+    assert r.returncode == 0, r.stderr
+    toks = json.loads(r.stdout.strip().splitlines()[-1])
+    assert len(toks) == 6 and "decode" in r.stderr and "prefill 4 tok" in r.stderr
+    import moe_b200
+
+    _, eng = G.engine_for(model_dirs, "A", "bfloat16")
+    assert moe_b200.generate(eng, [[5, 17, 3, 9]], max_tokens=6)[0].tokens == toks
+    pf = tmp_path / "prompts.txt"
+    pf.write_text("1,2,3\n[9, 8, 7, 6, 5]\n4 4\n")
+    r = run("run", d, "--prompts", str(pf), "--tokens=3", "--temp", "0.7", "--seed", "2", "--batch", "2")
+    assert r.returncode == 0, r.stderr
+    lines = [json.loads(l) for l in r.stdout.strip().splitlines()]
+    assert [l["index"] for l in lines] == [0, 1, 2] and all(l["generated"] == len(l["tokens"]) <= 3 for l in lines)
+    r = run("info", d)
+    assert r.returncode == 0 and "Qwen2MoeForCausalLM" in r.stdout and "4 experts, top-2" in r.stdout
+    r = run("bench", d, "--prompt-len", "16", "--tokens", "4", "--batch", "2")
+    assert r.returncode == 0 and "decode" in r.stdout and "tok/s" in r.stdout, r.stderr
+    r = run("run", str(tmp_path / "nothing"), "--ids", "1")
+    assert r.returncode == 1 and r.stderr.startswith("moe:")
