@@ -1,0 +1,481 @@
+// Tensor-core matrix product of the bfloat16 path: Y[t, n] = sum_k X[t, k] * W[n, k].
+//
+// Written for sm_100a: operands are brought into shared memory by TMA
+// (cp.async.bulk.tensor, 128-byte swizzle), multiplied by tcgen05.mma with the
+// accumulator in tensor memory, and read back with tcgen05.ld for the epilogue.
+//
+// The WEIGHT is the M operand of the instruction (tiles of 128 output features)
+// and the TOKENS are its N operand (tiles of 16 ... 256), so a decode step of a few
+// tokens wastes no tensor-core rows and a prefill uses the widest shape.  One CTA
+// computes one (feature tile, token tile[, K split]):
+//
+//   warp 0      TMA producer: W tile(s) [128 x 64] and X tile [BN x 64] per stage
+//   warp 1      allocates tensor memory, issues the MMAs, commits to the barriers
+//   warps 2-5   epilogue: tensor memory -> registers -> global memory
+//
+// Modes
+//   PLAIN    out[t, n] = acc (+ bias[n]); out is float32 or bfloat16
+//   SWIGLU   W holds gate rows [0, I) and up rows [I, 2I) per group; two accumulators;
+//            out[t, j] = silu(gate) * up  (reference: src/model.rs:26-35)
+// Groups (routed experts): rows of X are partitioned by group_offsets[G + 1]; group g
+// uses the weight slab g.  Split K: each split writes float32 partial sums to scratch;
+// the CTA that arrives last at the tile's ticket adds them in split order (so the sum
+// does not depend on arrival order) and runs the epilogue.
+//
+// Every wait on a barrier is bounded.  A wait that runs out sets ST_WAIT_TIMEOUT in the
+// status word and the CTA drains, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int TILE_W = 128;   // output features per CTA (UMMA M)
+constexpr int BK = 64;        // K elements per stage = one 128-byte swizzle row of bf16
+constexpr int UMMA_K = 16;
+constexpr uint32_t WAIT_LIMIT = 1u << 24;
+
+enum { MODE_PLAIN = 0, MODE_SWIGLU = 1 };
+
+struct Params {
+    void* out;
+    int out_bf16;
+    int ldo;
+    const float* bias;
+    const int* group_offsets;   // null: one group of M rows
+    int num_groups;
+    int M;                      // rows of X in total
+    int N;                      // output features per group (SWIGLU: the intermediate size I)
+    int K;
+    int w_rows_per_group;       // N, or 2 N for SWIGLU
+    int splits;                 // K splits (>= 1), every split non-empty
+    int kb_per_split;
+    float* partials;            // [splits][M][cols] float32, cols = N or 2 N
+    int* tickets;               // one per (grid.y, grid.x), zero before and after the launch
+    int* status;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false if the barrier did not complete in time or another role gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (abort_flag && (i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes,
+// groups of 8 rows 1024 bytes apart (SBO), descriptor version 1 (sm_100), layout type 2.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;                 // leading byte offset (ignored with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset
+    d |= (uint64_t)1 << 46;                 // version
+    d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
+    return d;
+}
+
+template <int BN>
+__host__ __device__ constexpr uint32_t instr_desc() {
+    // c = f32 (1 << 4), a = bf16 (1 << 7), b = bf16 (1 << 10), both K-major, N >> 3 at 17, M >> 4 at 24
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TILE_W >> 4) << 24);
+}
+
+template <int BN, int MODE>
+struct Cfg {
+    static constexpr int NW = MODE == MODE_SWIGLU ? 2 : 1;
+    static constexpr int W_BYTES = TILE_W * BK * 2;
+    static constexpr int X_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = NW * W_BYTES + X_BYTES;
+    static constexpr int BUDGET = (MODE == MODE_PLAIN && BN <= 64) ? 100 * 1024 : 196 * 1024;
+    static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_RAW > 8 ? 8 : (STAGES_RAW < 2 ? 2 : STAGES_RAW);
+    static constexpr int TMEM_COLS_RAW = NW * BN;
+    static constexpr int TMEM_COLS = TMEM_COLS_RAW < 32 ? 32 : TMEM_COLS_RAW;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
+
+template <int BN, int MODE>
+__global__ void __launch_bounds__(192)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const Params p) {
+    using C = Cfg<BN, MODE>;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ int s_work[4];          // group, first row, end row, is_last
+    __shared__ volatile int s_abort;
+    __shared__ uint32_t s_tmem;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * TILE_W;
+    const int split = blockIdx.z;
+
+    // ---- which rows of X this CTA owns -------------------------------------------------
+    if (threadIdx.x == 0) {
+        int g = 0, r0 = 0, r1 = p.M, tile = blockIdx.y;
+        if (p.group_offsets) {
+            g = -1;
+            for (int i = 0; i < p.num_groups; i++) {
+                const int b = p.group_offsets[i], e = p.group_offsets[i + 1];
+                const int tiles = (e - b + BN - 1) / BN;
+                if (tile < tiles) {
+                    g = i, r0 = b + tile * BN, r1 = e;
+                    break;
+                }
+                tile -= tiles;
+            }
+        } else {
+            r0 = tile * BN;
+            if (r0 >= p.M) g = -1;
+        }
+        s_work[0] = g, s_work[1] = r0, s_work[2] = r1, s_work[3] = 0;
+        s_abort = 0;
+    }
+    __syncthreads();
+    const int g = s_work[0];
+    if (g < 0) return;                 // uniform: nothing to do for this tile index
+    const int row0 = s_work[1], row_end = s_work[2];
+
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar_base = base + C::STAGES * C::STAGE_BYTES;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (C::STAGES + s); };
+    const uint32_t acc_bar = bar_base + 8u * (2 * C::STAGES);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; s++) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(acc_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(&s_tmem), C::TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem;
+
+    const int kb_total = (p.K + BK - 1) / BK;
+    const int kb0 = split * p.kb_per_split;
+    const int kb1 = min(kb_total, kb0 + p.kb_per_split);
+    const int w_row = g * p.w_rows_per_group + n0;
+
+    if (warp == 0) {
+        // ---- producer ---------------------------------------------------------------------
+        if (lane == 0) {
+            int issued = 0;
+            bool ok = true;
+            for (int kb = kb0; kb < kb1 && ok; kb++, issued++) {
+                const int s = issued % C::STAGES;
+                const uint32_t ph = (issued / C::STAGES) & 1;
+                ok = mbar_wait(empty_bar(s), ph ^ 1, &s_abort);
+                if (!ok) break;
+                const uint32_t st = base + s * C::STAGE_BYTES;
+                mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+                tma_load_2d(st, &tmW, kb * BK, w_row, full_bar(s));
+                if (MODE == MODE_SWIGLU) tma_load_2d(st + C::W_BYTES, &tmW, kb * BK, w_row + p.N, full_bar(s));
+                tma_load_2d(st + C::NW * C::W_BYTES, &tmX, kb * BK, row0, full_bar(s));
+            }
+            if (!ok) {
+                atomicOr(p.status, ST_WAIT_TIMEOUT);
+                s_abort = 1;
+                // copies already issued must land before the CTA may leave
+                for (int i = max(0, issued - C::STAGES); i < issued; i++)
+                    mbar_wait(full_bar(i % C::STAGES), (i / C::STAGES) & 1, nullptr);
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer -------------------------------------------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc<BN>();
+            bool ok = true;
+            int it = 0;
+            for (int kb = kb0; kb < kb1; kb++, it++) {
+                const int s = it % C::STAGES;
+                ok = mbar_wait(full_bar(s), (it / C::STAGES) & 1, &s_abort);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t st = base + s * C::STAGE_BYTES;
+#pragma unroll
+                for (int k4 = 0; k4 < BK / UMMA_K; k4++) {
+                    const uint32_t koff = k4 * UMMA_K * 2;
+                    const uint64_t bdesc = smem_desc(st + C::NW * C::W_BYTES + koff);
+                    const uint32_t acc = (it > 0 || k4 > 0) ? 1u : 0u;
+                    umma_bf16(tmem, smem_desc(st + koff), bdesc, idesc, acc);
+                    if (MODE == MODE_SWIGLU) umma_bf16(tmem + BN, smem_desc(st + C::W_BYTES + koff), bdesc, idesc, acc);
+                }
+                umma_commit(empty_bar(s));      // frees the stage when these MMAs have read it
+            }
+            if (ok) {
+                umma_commit(acc_bar);           // accumulator complete
+            } else {
+                atomicOr(p.status, ST_WAIT_TIMEOUT);
+                s_abort = 1;
+            }
+        }
+    } else {
+        // ---- epilogue -----------------------------------------------------------------------
+        const int q = warp & 3;                        // tensor-memory lane group of this warp
+        const int n = n0 + q * 32 + lane;              // output feature of this thread
+        const bool n_ok = n < p.N;
+        const bool ok = mbar_wait(acc_bar, 0, &s_abort);
+        if (!ok) {
+            if (lane == 0) {
+                atomicOr(p.status, ST_WAIT_TIMEOUT);
+                s_abort = 1;
+            }
+        } else {
+            tc_fence_after();
+            const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16);
+            const int cols = MODE == MODE_SWIGLU ? 2 * p.N : p.N;
+            const float bias = (MODE == MODE_PLAIN && p.bias && n_ok) ? p.bias[n] : 0.f;
+            const int rows_here = min(BN, row_end - row0);
+            if (p.splits == 1) {
+                for (int c0 = 0; c0 < rows_here; c0 += 16) {      // trip count uniform per warp
+                    float a[16], b[16];
+                    __syncwarp();
+                    tmem_ld16(taddr + c0, a);
+                    if (MODE == MODE_SWIGLU) tmem_ld16(taddr + BN + c0, b);
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        const int t = row0 + c0 + j;
+                        if (n_ok && t < row_end) {
+                            const float v = MODE == MODE_SWIGLU ? silu_mul(a[j], b[j]) : a[j] + bias;
+                            if (p.out_bf16)
+                                ((__nv_bfloat16*)p.out)[(size_t)t * p.ldo + n] = __float2bfloat16_rn(v);
+                            else
+                                ((float*)p.out)[(size_t)t * p.ldo + n] = v;
+                        }
+                    }
+                }
+            } else {
+                // partial sums of this split
+                float* mine = p.partials + (size_t)split * p.M * cols;
+                for (int c0 = 0; c0 < rows_here; c0 += 16) {
+                    float a[16], b[16];
+                    __syncwarp();
+                    tmem_ld16(taddr + c0, a);
+                    if (MODE == MODE_SWIGLU) tmem_ld16(taddr + BN + c0, b);
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        const int t = row0 + c0 + j;
+                        if (n_ok && t < row_end) {
+                            mine[(size_t)t * cols + n] = a[j];
+                            if (MODE == MODE_SWIGLU) mine[(size_t)t * cols + p.N + n] = b[j];
+                        }
+                    }
+                }
+                __threadfence();
+                // the four epilogue warps meet, one thread takes the ticket
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (warp == 2 && lane == 0) {
+                    int* ticket = p.tickets + (size_t)blockIdx.y * gridDim.x + blockIdx.x;
+                    const int old = atomicAdd(ticket, 1);
+                    const int last = old == p.splits - 1;
+                    if (last) *ticket = 0;                 // ready for the next launch
+                    s_work[3] = last;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (s_work[3]) {
+                    __threadfence();
+                    if (n_ok) {
+                        for (int t = row0; t < row0 + rows_here; t++) {
+                            float sa = 0.f, sb = 0.f;
+                            for (int s = 0; s < p.splits; s++) {
+                                const float* src = p.partials + ((size_t)s * p.M + t) * cols;
+                                sa += __ldcg(src + n);
+                                if (MODE == MODE_SWIGLU) sb += __ldcg(src + p.N + n);
+                            }
+                            const float v = MODE == MODE_SWIGLU ? silu_mul(sa, sb) : sa + bias;
+                            if (p.out_bf16)
+                                ((__nv_bfloat16*)p.out)[(size_t)t * p.ldo + n] = __float2bfloat16_rn(v);
+                            else
+                                ((float*)p.out)[(size_t)t * p.ldo + n] = v;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, C::TMEM_COLS);
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)sym;
+    });
+    return fn;
+}
+
+// 2-D bf16 row-major [rows, cols] with row pitch ld (elements); box [box_rows, 64], 128-byte swizzle
+bool make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int MODE>
+int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& p, dim3 grid, cudaStream_t stream) {
+    using C = Cfg<BN, MODE>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    gemm_tc_kernel<BN, MODE><<<grid, 192, C::SMEM, stream>>>(tmW, tmX, p);
+    return launch_status();
+}
+
+}  // namespace
+
+// X: [M, K] bf16 with row pitch ldx; W: [G * w_rows, K] bf16 contiguous; out: [M, ldo].
+//   mode 0: w_rows = N; mode 1 (SwiGLU): w_rows = 2 N, gate rows first.
+//   bn: token tile (16, 32, 64, 128 or 256).  splits >= 1; with splits > 1, partials holds
+//   splits * M * (mode ? 2 N : N) floats and tickets grid.y * grid.x zeroed ints.
+// Returns 0, a CUDA error code, or -1 if the shape cannot be handled (the caller falls back).
+MOE_API int moe_gemm_tc(const void* X, int ldx, const void* W, int num_groups, int N, int K, int mode, void* out,
+                        int out_bf16, int ldo, const float* bias, const int* group_offsets, int M, int bn, int splits,
+                        float* partials, int* tickets, int* status, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K % 8 != 0 || ldx % 8 != 0 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return -1;
+    const int w_rows = mode == MODE_SWIGLU ? 2 * N : N;
+    CUtensorMap tmW, tmX;
+    if (!make_map(&tmW, W, (uint64_t)num_groups * w_rows, K, K, TILE_W)) return -1;
+    if (!make_map(&tmX, X, M, K, ldx, bn)) return -1;
+    const int kb_total = (K + BK - 1) / BK;
+    if (splits < 1) splits = 1;
+    if (splits > kb_total) splits = kb_total;
+    const int per = (kb_total + splits - 1) / splits;
+    splits = (kb_total + per - 1) / per;
+    if (splits > 1 && (!partials || !tickets)) return -1;
+    Params p;
+    p.out = out, p.out_bf16 = out_bf16, p.ldo = ldo, p.bias = bias, p.group_offsets = group_offsets;
+    p.num_groups = num_groups, p.M = M, p.N = N, p.K = K, p.w_rows_per_group = w_rows, p.splits = splits;
+    p.kb_per_split = per, p.partials = partials, p.tickets = tickets, p.status = status;
+    const int m_tiles = (M + bn - 1) / bn + (group_offsets ? num_groups : 0);
+    dim3 grid((N + TILE_W - 1) / TILE_W, m_tiles, splits);
+    if (grid.y > 65535 || grid.z > 65535) return -1;
+#define GO(BN_)                                                                              \
+    if (bn == BN_)                                                                           \
+        return mode == MODE_SWIGLU ? launch<BN_, MODE_SWIGLU>(tmW, tmX, p, grid, stream)     \
+                                   : launch<BN_, MODE_PLAIN>(tmW, tmX, p, grid, stream);
+    GO(16) GO(32) GO(64) GO(128) GO(256)
+#undef GO
+    return -1;
+}
+
+// How many K splits the kernel will really use for (K, splits asked), and its grid.y for tickets.
+MOE_API int moe_gemm_tc_plan(int K, int splits, int M, int bn, int num_groups, int grouped, int* grid_y) {
+    const int kb_total = (K + BK - 1) / BK;
+    if (splits < 1) splits = 1;
+    if (splits > kb_total) splits = kb_total;
+    const int per = (kb_total + splits - 1) / splits;
+    *grid_y = (M + bn - 1) / bn + (grouped ? num_groups : 0);
+    return (kb_total + per - 1) / per;
+}
+
+// dst[i, :] = src[rows[i], :] for bf16 rows of `width` elements (expert dispatch before the grouped product)
+__global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ rows,
+                                   __nv_bfloat16* __restrict__ dst, int width, int src_rows, int* status) {
+    const int i = blockIdx.x;
+    int r = rows[i];
+    if (r < 0 || r >= src_rows) {
+        if (threadIdx.x == 0) atomicOr(status, ST_BAD_ROW);
+        r = 0;
+    }
+    const uint4* s = reinterpret_cast<const uint4*>(src + (size_t)r * width);
+    uint4* d = reinterpret_cast<uint4*>(dst + (size_t)i * width);
+    for (int j = threadIdx.x; j < width / 8; j += blockDim.x) d[j] = s[j];
+}
+MOE_API int moe_gather_rows_bf16(const void* src, const int* rows, void* dst, int n, int width, int src_rows,
+                                 int* status, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (width % 8) return (int)cudaErrorInvalidValue;
+    gather_rows_kernel<<<n, 128, 0, stream>>>((const __nv_bfloat16*)src, rows, (__nv_bfloat16*)dst, width, src_rows, status);
+    return launch_status();
+}

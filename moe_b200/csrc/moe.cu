@@ -133,6 +133,8 @@ moe_align_kernel(const int* __restrict__ topk_idx, int pairs, int top_k, int num
             pos_of_pair[i] = -1;
         }
     }
+    // positions past the last routed pair (padding rows dropped out): a valid row index, never used
+    for (int i = offsets[num_experts] + threadIdx.x; i < pairs; i += blockDim.x) sorted_token[i] = 0;
 }
 
 // act[m, j] = silu(gu[m, j]) * gu[m, inter + j], silu(a) = a / (1 + exp(-a))

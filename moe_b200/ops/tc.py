@@ -1,0 +1,135 @@
+"""Python face of the kernel library ``tc``: the tcgen05 / TMA matrix product of the
+bfloat16 path (``csrc/gemm_tc.cu``).
+
+``gemm_tc`` returns False when the kernel refuses a shape (K or a row pitch that is
+no multiple of 8 elements, an unaligned pointer); the caller then uses the plain kernel.
+"""
+from __future__ import annotations
+
+from ctypes import c_int, c_void_p
+from typing import Optional
+
+import torch
+
+from . import build, core
+
+_lib = None
+_NUM_SMS = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        L = build.load("tc")
+        P, I = c_void_p, c_int
+        L.moe_gemm_tc.argtypes = [P, I, P, I, I, I, I, P, I, I, P, P, I, I, I, P, P, P, P]
+        L.moe_gemm_tc.restype = c_int
+        L.moe_gemm_tc_plan.argtypes = [I, I, I, I, I, I, P]
+        L.moe_gemm_tc_plan.restype = c_int
+        L.moe_gather_rows_bf16.argtypes = [P, P, P, I, I, I, P, P]
+        L.moe_gather_rows_bf16.restype = c_int
+        _lib = L
+    return _lib
+
+
+def num_sms(device) -> int:
+    global _NUM_SMS
+    if _NUM_SMS is None:
+        _NUM_SMS = torch.cuda.get_device_properties(device).multi_processor_count
+    return _NUM_SMS
+
+
+class Workspace:
+    """Scratch of the split-K reduction: float32 partial sums (grown on demand) and the
+    tile tickets, which every launch leaves at zero."""
+
+    TICKETS = 1 << 16
+
+    def __init__(self, device):
+        self.device = device
+        self.partials = torch.empty(1 << 24, dtype=torch.float32, device=device)   # 64 MB
+        self.tickets = torch.zeros(self.TICKETS, dtype=torch.int32, device=device)
+
+    def partials_for(self, n: int) -> torch.Tensor:
+        if self.partials.numel() < n:
+            if torch.cuda.is_current_stream_capturing():
+                raise core.KernelError("the split-K workspace must be sized before a CUDA graph is captured")
+            self.partials = torch.empty(max(n, 2 * self.partials.numel()), dtype=torch.float32, device=self.device)
+        return self.partials
+
+
+_workspaces = {}
+
+
+def workspace(device) -> Workspace:
+    key = torch.device(device).index or 0
+    if key not in _workspaces:
+        _workspaces[key] = Workspace(device)
+    return _workspaces[key]
+
+
+def token_tile(rows_per_group: float) -> int:
+    """Smallest token tile (the MMA's N) that holds the expected rows of a group."""
+    for bn in (16, 32, 64, 128, 256):
+        if rows_per_group <= bn:
+            return bn
+    return 256
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swiglu: bool = False,
+            bias: Optional[torch.Tensor] = None, group_offsets: Optional[torch.Tensor] = None,
+            bn: Optional[int] = None, splits: Optional[int] = None, status=None) -> bool:
+    """out = x @ w[g].T (PLAIN) or silu(x @ gate.T) * (x @ up.T) (SwiGLU, w rows = gate then up).
+
+    x: [M, K] bf16 (row pitch a multiple of 8); w: [N', K] or [G, N', K] bf16 contiguous;
+    out: [M, N] float32 or bfloat16 with N = N' (PLAIN) or N' / 2 (SwiGLU)."""
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not x.is_cuda:
+        return False
+    G = w.shape[0] if w.dim() == 3 else 1
+    w_rows, K = w.shape[-2], w.shape[-1]
+    N = w_rows // 2 if swiglu else w_rows
+    M = x.shape[0]
+    if x.shape[1] != K or out.shape[1] != N or out.shape[0] < M or x.stride(1) != 1 or not w.is_contiguous():
+        raise core.KernelError(f"gemm_tc: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    if (G > 1 or group_offsets is not None) and (group_offsets is None or group_offsets.numel() != G + 1):
+        raise core.KernelError("gemm_tc: group_offsets must have G + 1 entries")
+    grouped = group_offsets is not None
+    if bn is None:
+        bn = token_tile(M / max(G, 1) if grouped else min(M, 256))
+    L = lib()
+    n_tiles = -(-N // 128)
+    gy = c_int(0)
+    if splits is None:
+        # enough CTAs to keep every SM streaming: aim at two waves' worth at most
+        tiles = n_tiles * (max(1, -(-M // bn)) if not grouped else max(1, min(G, M)))
+        splits = max(1, min(16, (2 * num_sms(x.device)) // max(tiles, 1), -(-K // 64) // 4))
+    splits = L.moe_gemm_tc_plan(K, int(splits), M, bn, G, 1 if grouped else 0, core.ctypes.byref(gy))
+    partials = tickets = None
+    if splits > 1:
+        ws = workspace(x.device)
+        if gy.value * n_tiles > ws.TICKETS:
+            splits = 1
+        else:
+            partials = ws.partials_for(splits * M * (2 * N if swiglu else N))
+            tickets = ws.tickets
+    code = L.moe_gemm_tc(x.data_ptr(), x.stride(0), w.data_ptr(), G, N, K, 1 if swiglu else 0, out.data_ptr(),
+                         1 if out.dtype == torch.bfloat16 else 0, out.stride(0),
+                         None if bias is None else bias.data_ptr(),
+                         None if group_offsets is None else group_offsets.data_ptr(), M, bn, splits,
+                         None if partials is None else partials.data_ptr(),
+                         None if tickets is None else tickets.data_ptr(),
+                         None if status is None else status.data_ptr(), core._stream())
+    if code == -1:
+        return False
+    core._ok(code, "gemm_tc")
+    return True
+
+
+def gather_rows(src: torch.Tensor, rows: torch.Tensor, n: int, status) -> torch.Tensor:
+    """dst[i] = src[rows[i]] for bf16 rows (expert dispatch)."""
+    if src.dtype != torch.bfloat16 or src.shape[1] % 8:
+        raise core.KernelError("gather_rows: bfloat16 rows of a multiple of 8 elements")
+    dst = torch.empty((n, src.shape[1]), dtype=torch.bfloat16, device=src.device)
+    core._ok(lib().moe_gather_rows_bf16(src.data_ptr(), rows.data_ptr(), dst.data_ptr(), n, src.shape[1],
+                                        src.shape[0], status.data_ptr(), core._stream()), "gather_rows")
+    return dst

@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 
 from ..ops import core
-from ..ops.linear import grouped_linear, linear
+from ..ops.linear import grouped_linear, grouped_swiglu_linear, linear, swiglu_linear
 from .base import Part, TensorSpec, register_part
 
 
@@ -43,11 +43,7 @@ class DenseSwiGLU(Part):
         self.w_down = tensors["down_proj.weight"].contiguous()
 
     def forward(self, rt, h, batch):
-        T = h.act.shape[0]
-        gu = linear(rt, h.act, self.w_gu)
-        act = rt.empty((T, self.size))
-        core.swiglu(gu, act)
-        return linear(rt, act, self.w_down)
+        return linear(rt, swiglu_linear(rt, h.act, self.w_gu), self.w_down)
 
 
 class RoutedExperts(Part):
@@ -127,16 +123,11 @@ class RoutedExperts(Part):
         sorted_token = rt.empty((P,), torch.int32)
         pos_of_pair = rt.empty((P,), torch.int32)
         core.moe_align(topk_idx, T, self.k, self.E, offsets, sorted_token, pos_of_pair, rt.status)
-        gu = grouped_linear(rt, h.act, self.w_gu, offsets, P, a_rows=sorted_token)
-        act = rt.empty((P, self.size))
-        core.swiglu(gu, act)
+        act = grouped_swiglu_linear(rt, h.act, self.w_gu, offsets, sorted_token, P)
         y = grouped_linear(rt, act, self.w_down, offsets, P)
         ys = None
         if self.ws_gu is not None:
-            gus = linear(rt, h.act, self.ws_gu)
-            acts = rt.empty((T, self.shared_size))
-            core.swiglu(gus, acts)
-            ys = linear(rt, acts, self.ws_down)
+            ys = linear(rt, swiglu_linear(rt, h.act, self.ws_gu), self.ws_down)
         out = rt.empty((T, self.hidden), torch.float32)
         core.moe_combine(y, pos_of_pair, topk_w, self.k, out, shared=ys, shared_gate=sg)
         return out

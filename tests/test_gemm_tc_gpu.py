@@ -1,0 +1,101 @@
+"""The tcgen05 / TMA matrix product against a float64 product of the same bfloat16 values:
+plain and SwiGLU epilogues, every token tile, K splits, groups with gaps, ragged edges."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def tc():
+    from moe_b200.ops import tc as t
+
+    t.lib()
+    return t
+
+
+def status():
+    return torch.zeros(4, dtype=torch.int32, device=DEV)
+
+
+def rel(got, ref):
+    return float((got.double() - ref).abs().max() / ref.abs().max().clamp(min=1e-30))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 200, 72), (13, 2056, 2048), (64, 384, 200), (100, 130, 1408),
+                                    (300, 256, 512), (2, 6144, 2048)])
+@pytest.mark.parametrize("bn", [16, 64, 256])
+@pytest.mark.parametrize("splits", [1, 3])
+def test_plain(tc, M, N, K, bn, splits):
+    torch.manual_seed(M * 1000 + N + K)
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.1).to(torch.bfloat16)
+    b = torch.randn(N, device=DEV)
+    ref = x.double() @ w.double().T + b.double()
+    for odt, tol in ((torch.float32, 1e-5), (torch.bfloat16, 1e-2)):
+        out = torch.full((M, N), float("nan"), device=DEV, dtype=odt)
+        st = status()
+        assert tc.gemm_tc(x, w, out, bias=b, bn=bn, splits=splits, status=st)
+        assert int(st[0]) == 0 and rel(out, ref) < tol
+    assert int(tc.workspace(DEV).tickets.sum()) == 0          # tickets are left at zero
+
+
+@pytest.mark.parametrize("M,I,K", [(5, 128, 64), (8, 1408, 2048), (70, 48, 96), (33, 200, 520)])
+@pytest.mark.parametrize("bn", [16, 128])
+@pytest.mark.parametrize("splits", [1, 4])
+def test_swiglu(tc, M, I, K, bn, splits):
+    torch.manual_seed(M + I)
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(2 * I, K, device=DEV) * 0.1).to(torch.bfloat16)
+    g, u = x.double() @ w[:I].double().T, x.double() @ w[I:].double().T
+    ref = g / (1 + torch.exp(-g)) * u
+    out = torch.full((M, I), float("nan"), device=DEV, dtype=torch.bfloat16)
+    st = status()
+    assert tc.gemm_tc(x, w, out, swiglu=True, bn=bn, splits=splits, status=st)
+    assert int(st[0]) == 0
+    err = (out.double() - ref).abs()
+    assert bool((err <= 2.0 ** -8 * ref.abs() + 1e-3 * float(ref.abs().max())).all())
+
+
+@pytest.mark.parametrize("swiglu", [False, True])
+@pytest.mark.parametrize("bn", [16, 32, 128])
+@pytest.mark.parametrize("splits", [1, 2])
+def test_grouped(tc, swiglu, bn, splits):
+    G, N, K = 7, 160, 264
+    counts = [0, 40, 1, 0, 17, 130, 3]                      # empty groups; one longer than a tile
+    M = sum(counts)
+    torch.manual_seed(bn)
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(G, (2 * N if swiglu else N), K, device=DEV) * 0.1).to(torch.bfloat16)
+    offs = torch.tensor(np.concatenate([[0], np.cumsum(counts)]), dtype=torch.int32, device=DEV)
+    out = torch.full((M, N), float("nan"), device=DEV)
+    st = status()
+    assert tc.gemm_tc(x, w, out, swiglu=swiglu, group_offsets=offs, bn=bn, splits=splits, status=st)
+    ref = torch.empty(M, N, dtype=torch.float64, device=DEV)
+    o = 0
+    for g, c in enumerate(counts):
+        xs = x[o:o + c].double()
+        if swiglu:
+            a, b = xs @ w[g, :N].double().T, xs @ w[g, N:].double().T
+            ref[o:o + c] = a / (1 + torch.exp(-a)) * b
+        else:
+            ref[o:o + c] = xs @ w[g].double().T
+        o += c
+    assert int(st[0]) == 0 and rel(out, ref) < 2e-5
+
+
+def test_refused_shapes_return_false(tc):
+    x = torch.randn(4, 68, device=DEV).to(torch.bfloat16)       # K no multiple of 8 elements... 68 is not
+    w = torch.randn(128, 68, device=DEV).to(torch.bfloat16)
+    out = torch.empty(4, 128, device=DEV)
+    assert tc.gemm_tc(x[:, :66].contiguous(), w[:, :66].contiguous(), out, status=status()) is False
+    assert tc.gemm_tc(x.float(), w, out, status=status()) is False
+
+
+def test_gather_rows(tc):
+    src = torch.randn(50, 72, device=DEV).to(torch.bfloat16)
+    rows = torch.randint(0, 50, (33,), device=DEV, dtype=torch.int32)
+    st = status()
+    assert torch.equal(tc.gather_rows(src, rows, 33, st), src[rows.long()]) and int(st[0]) == 0

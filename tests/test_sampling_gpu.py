@@ -61,10 +61,11 @@ def test_seeded_sampling_follows_the_plain_sampler(sampler, vocab, kw):
                 ra, rb = int(np.where(order == got[i])[0][0]), int(np.where(order == want)[0][0])
                 # the reference adds 32-bit probabilities one after the other, the kernel block-wise:
                 # deep in the tail of a large vocabulary the two sums part by rounding, and the picks
-                # then sit at the same place of the exact cumulative distribution
+                # then sit at the same place of the exact cumulative distribution (a sequential 32-bit
+                # sum of 150k terms is itself only good to a few 1e-4)
                 p64 = np.exp((host[i][order].astype(np.float64) - float(host[i].max())) / kw["temp"])
                 cdf = np.cumsum(p64) / p64.sum()
-                assert abs(cdf[ra] - cdf[rb]) < 1e-4, f"row {i}: got {got[i]} (rank {ra}), plain {want} (rank {rb})"
+                assert abs(cdf[ra] - cdf[rb]) < (1e-5 if vocab < 100000 else 1e-3), f"row {i}: got {got[i]} (rank {ra}), plain {want} (rank {rb})"
     assert exact >= total - (2 if vocab < 100000 else total // 2)
     # the generator states agree at the end: as many numbers were drawn on both sides
     states = sampler.rng_states.cpu().numpy().view(np.uint64)
