@@ -37,6 +37,8 @@ constexpr int TILE_W = 128;   // output features per CTA (UMMA M)
 constexpr int BK = 64;        // K elements per stage = one 128-byte swizzle row of bf16
 constexpr int UMMA_K = 16;
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
+constexpr int MAX_SMEM_GROUPS = 256;
+constexpr int MAX_SPLITS = 16;
 
 enum { MODE_PLAIN = 0, MODE_SWIGLU = 1 };
 
@@ -172,12 +174,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     const int split = blockIdx.z;
 
     // ---- which rows of X this CTA owns -------------------------------------------------
+    // (the offsets are fetched by all threads at once: a scan straight from global memory would
+    // pay one memory latency per group)
+    __shared__ int s_offs[MAX_SMEM_GROUPS + 1];
+    const bool offs_in_smem = p.group_offsets && p.num_groups <= MAX_SMEM_GROUPS;
+    if (offs_in_smem) {
+        for (int i = threadIdx.x; i <= p.num_groups; i += blockDim.x) s_offs[i] = p.group_offsets[i];
+        __syncthreads();
+    }
     if (threadIdx.x == 0) {
         int g = 0, r0 = 0, r1 = p.M, tile = blockIdx.y;
         if (p.group_offsets) {
             g = -1;
+            const int* offs = offs_in_smem ? s_offs : p.group_offsets;
             for (int i = 0; i < p.num_groups; i++) {
-                const int b = p.group_offsets[i], e = p.group_offsets[i + 1];
+                const int b = offs[i], e = offs[i + 1];
                 const int tiles = (e - b + BN - 1) / BN;
                 if (tile < tiles) {
                     g = i, r0 = b + tile * BN, r1 = e;
@@ -341,12 +352,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 if (s_work[3]) {
                     __threadfence();
                     if (n_ok) {
+                        const size_t split_stride = (size_t)p.M * cols;
                         for (int t = row0; t < row0 + rows_here; t++) {
+                            // all splits' values are requested before any is used: one memory latency
+                            // per row instead of one per split; the sum keeps the split order
+                            const float* src = p.partials + (size_t)t * cols + n;
+                            float va[MAX_SPLITS], vb[MAX_SPLITS];
+#pragma unroll
+                            for (int s = 0; s < MAX_SPLITS; s++) {
+                                va[s] = s < p.splits ? __ldcg(src + s * split_stride) : 0.f;
+                                if (MODE == MODE_SWIGLU) vb[s] = s < p.splits ? __ldcg(src + s * split_stride + p.N) : 0.f;
+                            }
                             float sa = 0.f, sb = 0.f;
-                            for (int s = 0; s < p.splits; s++) {
-                                const float* src = p.partials + ((size_t)s * p.M + t) * cols;
-                                sa += __ldcg(src + n);
-                                if (MODE == MODE_SWIGLU) sb += __ldcg(src + p.N + n);
+#pragma unroll
+                            for (int s = 0; s < MAX_SPLITS; s++) {
+                                sa += va[s];
+                                if (MODE == MODE_SWIGLU) sb += vb[s];
                             }
                             const float v = MODE == MODE_SWIGLU ? silu_mul(sa, sb) : sa + bias;
                             if (p.out_bf16)
@@ -429,6 +450,7 @@ MOE_API int moe_gemm_tc(const void* X, int ldx, const void* W, int num_groups, i
     if (!make_map(&tmX, X, M, K, ldx, bn)) return -1;
     const int kb_total = (K + BK - 1) / BK;
     if (splits < 1) splits = 1;
+    if (splits > MAX_SPLITS) splits = MAX_SPLITS;
     if (splits > kb_total) splits = kb_total;
     const int per = (kb_total + splits - 1) / splits;
     splits = (kb_total + per - 1) / per;
@@ -437,7 +459,9 @@ MOE_API int moe_gemm_tc(const void* X, int ldx, const void* W, int num_groups, i
     p.out = out, p.out_bf16 = out_bf16, p.ldo = ldo, p.bias = bias, p.group_offsets = group_offsets;
     p.num_groups = num_groups, p.M = M, p.N = N, p.K = K, p.w_rows_per_group = w_rows, p.splits = splits;
     p.kb_per_split = per, p.partials = partials, p.tickets = tickets, p.status = status;
-    const int m_tiles = (M + bn - 1) / bn + (group_offsets ? num_groups : 0);
+    // token tiles: sum over groups of ceil(rows / bn) <= (non-empty groups) + floor(M / bn); CTAs past
+    // the real count leave at once, but each still reserves its shared memory, so the bound is kept tight
+    const int m_tiles = group_offsets ? (M < num_groups ? M : num_groups) + M / bn : (M + bn - 1) / bn;
     dim3 grid((N + TILE_W - 1) / TILE_W, m_tiles, splits);
     if (grid.y > 65535 || grid.z > 65535) return -1;
 #define GO(BN_)                                                                              \
@@ -455,7 +479,7 @@ MOE_API int moe_gemm_tc_plan(int K, int splits, int M, int bn, int num_groups, i
     if (splits < 1) splits = 1;
     if (splits > kb_total) splits = kb_total;
     const int per = (kb_total + splits - 1) / splits;
-    *grid_y = (M + bn - 1) / bn + (grouped ? num_groups : 0);
+    *grid_y = grouped ? (M < num_groups ? M : num_groups) + M / bn : (M + bn - 1) / bn;
     return (kb_total + per - 1) / per;
 }
 

@@ -13,55 +13,123 @@
 
 namespace {
 
+constexpr int TOK_TILE = 8;         // tokens per block: a weight row is read once for all of them
+
 template <typename WT>
-__device__ __forceinline__ float row_dot(const float* __restrict__ x, const WT* __restrict__ w, int n, int lane) {
-    float s = 0.f;
-    for (int i = lane; i < n; i += 32) s = fmaf(x[i], ld_f(w + i), s);
-    return warp_sum(s);
+__device__ __forceinline__ void w_load8(const WT* p, float* out);
+template <>
+__device__ __forceinline__ void w_load8<float>(const float* p, float* out) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    out[0] = a.x, out[1] = a.y, out[2] = a.z, out[3] = a.w, out[4] = b.x, out[5] = b.y, out[6] = b.z, out[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void w_load8<__nv_bfloat16>(const __nv_bfloat16* p, float* out) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        out[2 * i] = __uint_as_float(w[i] << 16);
+        out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
 }
 
-// One block (4 warps) per token.
-template <typename WT>
+// logits[t, r] = h[t, :] . W[r, :] for r < rows; row `num_experts` (if wsg) is the shared gate.
+// 32-bit products and sums in a fixed order.  A block has ROWS x KSPLIT warps: warp (r, ks) takes
+// router row r and the ks-th slice of the hidden dimension for 8 tokens; the slices are added in
+// order.  Few tokens: many small blocks (ROWS 2, KSPLIT 4); many tokens: ROWS 8, KSPLIT 1, so that
+// the activations are re-read 8 times less.  Grid: (ceil(rows / ROWS), ceil(T / 8)).
+template <typename WT, int ROWS, int KSPLIT>
+__global__ void __launch_bounds__(ROWS * KSPLIT * 32)
+router_logits_kernel(const float* __restrict__ h, const WT* __restrict__ wr, const WT* __restrict__ wsg,
+                     int num_tokens, int hidden, int num_experts, int rows, int vec_ok,
+                     float* __restrict__ logits) {
+    __shared__ float part[ROWS][KSPLIT][TOK_TILE];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rr = warp / KSPLIT, ks = warp % KSPLIT;
+    const int r = blockIdx.x * ROWS + rr;
+    const int t0 = blockIdx.y * TOK_TILE;
+    const int nt = min(TOK_TILE, num_tokens - t0);
+    float acc[TOK_TILE];
+#pragma unroll
+    for (int i = 0; i < TOK_TILE; i++) acc[i] = 0.f;
+    if (r < rows) {
+        const WT* w = r < num_experts ? wr + (size_t)r * hidden : wsg;
+        // slice of the hidden dimension of this warp, in whole groups of 8 elements
+        const int groups = vec_ok ? hidden / 8 : 0;
+        const int gper = (groups + KSPLIT - 1) / KSPLIT;
+        const int g0 = ks * gper, g1 = min(groups, g0 + gper);
+#pragma unroll 2
+        for (int gi = g0 + lane; gi < g1; gi += 32) {
+            const int c = gi * 8;
+            float wv[8];
+            w_load8<WT>(w + c, wv);
+#pragma unroll
+            for (int i = 0; i < TOK_TILE; i++) {
+                if (i < nt) {
+                    const float* x = h + (size_t)(t0 + i) * hidden + c;
+                    const float4 a = *reinterpret_cast<const float4*>(x), b = *reinterpret_cast<const float4*>(x + 4);
+                    float s = acc[i];
+                    s = fmaf(a.x, wv[0], s), s = fmaf(a.y, wv[1], s), s = fmaf(a.z, wv[2], s), s = fmaf(a.w, wv[3], s);
+                    s = fmaf(b.x, wv[4], s), s = fmaf(b.y, wv[5], s), s = fmaf(b.z, wv[6], s), s = fmaf(b.w, wv[7], s);
+                    acc[i] = s;
+                }
+            }
+        }
+        if (ks == KSPLIT - 1) {   // the elements past the last whole group
+            for (int c = groups * 8 + lane; c < hidden; c += 32) {
+                const float wv = ld_f(w + c);
+#pragma unroll
+                for (int i = 0; i < TOK_TILE; i++)
+                    if (i < nt) acc[i] = fmaf(h[(size_t)(t0 + i) * hidden + c], wv, acc[i]);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < TOK_TILE; i++) {
+        const float s = warp_sum(acc[i]);
+        if (lane == 0) part[rr][ks][i] = s;
+    }
+    __syncthreads();
+    if (ks == 0 && lane < nt && r < rows) {
+        float s = 0.f;
+#pragma unroll
+        for (int k = 0; k < KSPLIT; k++) s += part[rr][k][lane];
+        logits[(size_t)(t0 + lane) * rows + r] = s;
+    }
+}
+
+// One warp per token: softmax over all experts, top-k, weights.
 __global__ void __launch_bounds__(128)
-router_kernel(const float* __restrict__ h, const WT* __restrict__ wr, const WT* __restrict__ wsg,
-              const int* __restrict__ seq_of_token, int hidden, int num_experts, int top_k, int norm_topk,
-              float scale, int* __restrict__ topk_idx, float* __restrict__ topk_w, float* __restrict__ shared_gate) {
-    extern __shared__ float sc[];   // num_experts scores
-    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+router_topk_kernel(const float* __restrict__ logits, const int* __restrict__ seq_of_token, int num_tokens,
+                   int num_experts, int rows, int top_k, int norm_topk, float scale, int* __restrict__ topk_idx,
+                   float* __restrict__ topk_w, float* __restrict__ shared_gate) {
+    extern __shared__ float sc_all[];   // 4 warps x num_experts
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= num_tokens) return;
+    float* sc = sc_all + (size_t)warp * num_experts;
     if (seq_of_token && seq_of_token[t] < 0) {   // padding row: no expert
-        for (int j = threadIdx.x; j < top_k; j += blockDim.x) {
+        for (int j = lane; j < top_k; j += 32) {
             topk_idx[(size_t)t * top_k + j] = -1;
             topk_w[(size_t)t * top_k + j] = 0.f;
         }
-        if (shared_gate && threadIdx.x == 0) shared_gate[t] = 0.f;
+        if (shared_gate && lane == 0) shared_gate[t] = 0.f;
         return;
     }
-    const float* x = h + (size_t)t * hidden;
-    for (int e = warp; e < num_experts + (wsg ? 1 : 0); e += 4) {
-        if (e < num_experts) {
-            const float d = row_dot(x, wr + (size_t)e * hidden, hidden, lane);
-            if (lane == 0) sc[e] = d;
-        } else {
-            const float d = row_dot(x, wsg, hidden, lane);
-            if (lane == 0) shared_gate[t] = 1.0f / (1.0f + expf(-d));
-        }
-    }
-    __syncthreads();
-    if (warp != 0) return;
-    // softmax over all experts
+    const float* lg = logits + (size_t)t * rows;
+    if (shared_gate && rows > num_experts && lane == 0) shared_gate[t] = 1.0f / (1.0f + expf(-lg[num_experts]));
     float m = -INFINITY;
-    for (int e = lane; e < num_experts; e += 32) m = fmaxf(m, sc[e]);
+    for (int e = lane; e < num_experts; e += 32) m = fmaxf(m, lg[e]);
     m = warp_max(m);
     float z = 0.f;
     for (int e = lane; e < num_experts; e += 32) {
-        const float v = expf(sc[e] - m);
+        const float v = expf(lg[e] - m);
         sc[e] = v;
         z += v;
     }
     z = warp_sum(z);
     for (int e = lane; e < num_experts; e += 32) sc[e] = sc[e] / z;
     __syncwarp();
-    // top-k by repeated argmax; a tie goes to the lower index
     float wsum = 0.f;
     for (int j = 0; j < top_k; j++) {
         float best = -1.f;
@@ -121,8 +189,10 @@ moe_align_kernel(const int* __restrict__ topk_idx, int pairs, int top_k, int num
             run += counts[e];
         }
         offsets[num_experts] = run;
+        counts[0] = run;
     }
     __syncthreads();
+    const int total = counts[0];
     for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
         const int e = topk_idx[i];
         if (e >= 0 && e < num_experts) {
@@ -134,7 +204,7 @@ moe_align_kernel(const int* __restrict__ topk_idx, int pairs, int top_k, int num
         }
     }
     // positions past the last routed pair (padding rows dropped out): a valid row index, never used
-    for (int i = offsets[num_experts] + threadIdx.x; i < pairs; i += blockDim.x) sorted_token[i] = 0;
+    for (int i = total + threadIdx.x; i < pairs; i += blockDim.x) sorted_token[i] = 0;
 }
 
 // act[m, j] = silu(gu[m, j]) * gu[m, inter + j], silu(a) = a / (1 + exp(-a))
@@ -170,21 +240,32 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
 
 }  // namespace
 
+// logits: scratch of num_tokens * (num_experts + (wsg ? 1 : 0)) floats.
 MOE_API int moe_router(const float* h, const void* wr, const void* wsg, int w_dt, const int* seq_of_token,
                        int num_tokens, int hidden, int num_experts, int top_k, int norm_topk, float scale,
-                       int* topk_idx, float* topk_w, float* shared_gate, cudaStream_t stream) {
+                       float* logits, int* topk_idx, float* topk_w, float* shared_gate, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
-    if (top_k <= 0 || top_k > num_experts || num_experts > 8192) return (int)cudaErrorInvalidValue;
+    if (top_k <= 0 || top_k > num_experts || num_experts > 2048 || !logits) return (int)cudaErrorInvalidValue;
     if (wsg && !shared_gate) return (int)cudaErrorInvalidValue;
-    const size_t smem = (size_t)num_experts * sizeof(float);
-    if (w_dt == DT_F32)
-        router_kernel<float><<<num_tokens, 128, smem, stream>>>(h, (const float*)wr, (const float*)wsg, seq_of_token,
-                                                               hidden, num_experts, top_k, norm_topk, scale, topk_idx,
-                                                               topk_w, shared_gate);
-    else
-        router_kernel<__nv_bfloat16><<<num_tokens, 128, smem, stream>>>(
-            h, (const __nv_bfloat16*)wr, (const __nv_bfloat16*)wsg, seq_of_token, hidden, num_experts, top_k,
-            norm_topk, scale, topk_idx, topk_w, shared_gate);
+    const int rows = num_experts + (wsg ? 1 : 0);
+    const size_t elt = w_dt == DT_F32 ? 4 : 2;
+    const int vec_ok = (hidden % 8 == 0) && ((uintptr_t)h % 16 == 0) && ((uintptr_t)wr % 16 == 0) &&
+                       (!wsg || (uintptr_t)wsg % 16 == 0) && ((hidden * elt) % 16 == 0);
+    const int ty = (num_tokens + TOK_TILE - 1) / TOK_TILE;
+    if (ty > 65535) return (int)cudaErrorInvalidValue;
+#define LOGITS(WT, ROWS, KSPLIT)                                                                          \
+    router_logits_kernel<WT, ROWS, KSPLIT><<<dim3((rows + ROWS - 1) / ROWS, ty), ROWS * KSPLIT * 32, 0, stream>>>( \
+        h, (const WT*)wr, (const WT*)wsg, num_tokens, hidden, num_experts, rows, vec_ok, logits)
+    if (num_tokens <= 64) {
+        if (w_dt == DT_F32) LOGITS(float, 2, 4); else LOGITS(__nv_bfloat16, 2, 4);
+    } else {
+        if (w_dt == DT_F32) LOGITS(float, 8, 1); else LOGITS(__nv_bfloat16, 8, 1);
+    }
+#undef LOGITS
+    const size_t smem = (size_t)4 * num_experts * sizeof(float);
+    router_topk_kernel<<<(num_tokens + 3) / 4, 128, smem, stream>>>(logits, seq_of_token, num_tokens, num_experts, rows,
+                                                                   top_k, norm_topk, scale, topk_idx, topk_w,
+                                                                   shared_gate);
     return launch_status();
 }
 

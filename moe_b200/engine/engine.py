@@ -6,6 +6,12 @@ returns the float32 logits of the wanted places, in the order given.  Sequences
 may bring different numbers of tokens; a result does not depend on what else is
 in the batch (reference: one sequence per call, src/model.rs:565-589; prefill
 and decode are the same code there too).
+
+A step in which every sequence brings one token is launch-bound, so it is
+replayed from a CUDA graph: one graph per batch-size bucket, captured the first
+time the bucket is met.  The batch is padded to the bucket with rows that belong
+to no sequence (``seq_of_token = -1``): they read and write only the scratch page,
+get no expert and change no result.
 """
 from __future__ import annotations
 
@@ -18,11 +24,98 @@ from ..cache.allocator import CacheError, pages_for
 from ..cache.kv import KVCache
 from ..models.decoder import DecoderModel
 from ..ops import core
-from .batch import StepBatch, fill_host
+from .batch import StepBatch, fill_host, layout
+
+GRAPH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+
+
+class _DecodeGraph:
+    """Static buffers and the captured graph of one batch-size bucket."""
+
+    def __init__(self, engine: "Engine", size: int):
+        self.size = size
+        ngroups = len(engine.cache.groups)
+        offs, o = {}, 0
+        for name, n in layout(size, size, size):
+            offs[name] = (o, n)
+            o += n
+        self.upd_off = []
+        for _ in range(ngroups):
+            self.upd_off.append(o)
+            o += 3 * size
+        self.used = o
+        self.offsets = offs
+        self.host = torch.zeros(o, dtype=torch.int32).pin_memory()
+        self.dev = torch.zeros(o, dtype=torch.int32, device=engine.rt.device)
+        views = {k: self.dev[a:a + n] for k, (a, n) in offs.items()}
+        self.batch = StepBatch(**views, num_tokens=size, num_seqs=size, num_want=size, max_new=1, max_end=0,
+                               all_decode=True, all_fresh=False)
+        self.event = torch.cuda.Event()
+        self.busy = False
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+
+    def fill(self, engine: "Engine", slots, starts, tokens, updates) -> None:
+        if self.busy:
+            self.event.synchronize()
+            self.busy = False
+        B, S = len(slots), self.size
+        h = self.host.numpy()
+        v = {k: h[a:a + n] for k, (a, n) in self.offsets.items()}
+        pad = engine.cache.padding_slot
+        v["token_ids"][:B] = tokens
+        v["token_ids"][B:] = 0
+        v["seq_of_token"][:B] = np.arange(B, dtype=np.int32)
+        v["seq_of_token"][B:] = -1
+        v["pos"][:B] = starts
+        v["pos"][B:] = 0
+        v["cu_seqlens"][:B + 1] = np.arange(B + 1, dtype=np.int32)
+        v["cu_seqlens"][B + 1:] = B
+        v["slots"][:B] = slots
+        v["slots"][B:] = pad
+        v["seq_start"][:B] = starts
+        v["seq_start"][B:] = 0
+        v["seq_end"][:B] = np.asarray(starts, dtype=np.int32) + 1
+        v["seq_end"][B:] = 1
+        v["want_rows"][:] = np.arange(S, dtype=np.int32)
+        for gi, o in enumerate(self.upd_off):
+            u = h[o:o + 3 * S].reshape(S, 3)
+            u[:, 0], u[:, 1], u[:, 2] = pad, 0, 0          # no-op: the padding row's first entry stays 0
+            mine = [(s, i, p) for g, s, i, p in updates if g == gi]
+            if mine:
+                u[:len(mine)] = np.asarray(mine, dtype=np.int32)
+        self.dev.copy_(self.host, non_blocking=True)
+        self.event.record()
+        self.busy = True
+
+    def run(self, engine: "Engine") -> torch.Tensor:
+        S = self.size
+
+        def body():
+            for gi, o in enumerate(self.upd_off):
+                core.table_update(engine.cache.groups[gi].table, self.dev[o:o + 3 * S], S)
+            return engine.model.forward(self.batch, engine.cache)
+
+        if self.graph is None:
+            # one eager run first: lazy builds, kernel attributes and workspaces happen outside the
+            # capture (running the step twice is harmless: it writes the same keys to the same places)
+            body()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            l0 = core.launches
+            with torch.cuda.graph(g):
+                self.logits = body()
+            self.launches = core.launches - l0
+            self.graph = g
+        else:
+            core.launches += self.launches
+        self.graph.replay()
+        return self.logits
 
 
 class Engine:
-    def __init__(self, model: DecoderModel, max_tokens: int, max_slots: Optional[int] = None):
+    def __init__(self, model: DecoderModel, max_tokens: int, max_slots: Optional[int] = None,
+                 use_graphs: Optional[bool] = None):
         self.model = model
         self.rt = model.rt
         if self.rt.device.type != "cuda":
@@ -38,6 +131,11 @@ class Engine:
         self._stage_event = torch.cuda.Event()
         self._stage_busy = False
         self.steps_run = 0
+        parts = [p for b in model.blocks for p in b.parts()] + [model.embedding, model.final_norm, model.head]
+        graph_safe = all(getattr(p, "graph_safe", False) for p in parts)
+        self.use_graphs = graph_safe if use_graphs is None else (use_graphs and graph_safe)
+        self._routed = [p for p in parts if hasattr(p, "trace")]
+        self._graphs: Dict[int, _DecodeGraph] = {}
 
     # ---- sequences -----------------------------------------------------------------
     def new_sequence(self) -> int:
@@ -89,13 +187,20 @@ class Engine:
             updates.extend(led.extend(s, led.length[s] + n))
         return updates
 
+    def _bucket(self, B: int) -> Optional[int]:
+        for b in GRAPH_BUCKETS:
+            if b >= B:
+                return b
+        return None
+
     def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
              want: Optional[Sequence[Sequence[int]]] = None, check: bool = True) -> Optional[torch.Tensor]:
         """Run ``tokens[i]`` for the sequence in ``slots[i]``; return logits at ``want[i]``.
 
         ``want[i]`` lists places among ``tokens[i]`` (0 = its first token of this
         step); by default the last place of each sequence.  The result is a float32
-        CUDA tensor [sum(len(w)), vocab], or None if nothing is wanted."""
+        CUDA tensor [sum(len(w)), vocab], or None if nothing is wanted.  It may alias
+        a buffer that the next step overwrites."""
         B = len(slots)
         if B == 0:
             return None
@@ -112,6 +217,25 @@ class Engine:
                     raise ValueError(f"wanted place {i} is not among the {n} tokens of this step")
         starts = [self.cache.length(s) if self.cache.ledger.slots.is_held(s) else 0 for s in slots]
         updates = self._reserve(slots, counts)
+        self.steps_run += 1
+
+        # ---- one token each: replay the bucket's graph -----------------------------------
+        if (self.use_graphs and all(n == 1 for n in counts) and all(len(w) == 1 for w in want)
+                and not any(p.trace is not None for p in self._routed)):
+            size = self._bucket(B)
+            if size is not None:
+                g = self._graphs.get(size)
+                if g is None:
+                    g = self._graphs[size] = _DecodeGraph(self, size)
+                g.fill(self, slots, starts, [t[0] for t in tokens], updates)
+                logits = g.run(self)
+                self.last_batch = g.batch
+                self.last_rows = B
+                if check:
+                    self.rt.check()
+                return logits[:B]
+
+        # ---- the general step -----------------------------------------------------------------
         T, W = sum(counts), sum(len(w) for w in want)
         n_upd = len(updates)
         host, dev = self._staging(3 * T + 4 * B + 2 + max(W, 1) + 3 * n_upd)
@@ -135,8 +259,8 @@ class Engine:
         views = {k: dev[a:a + n] for k, (a, n) in info["offsets"].items()}
         batch = StepBatch(**views, **info["facts"])
         self.last_batch = batch
+        self.last_rows = B
         logits = self.model.forward(batch, self.cache)
-        self.steps_run += 1
         if check:
             self.rt.check()
         return logits
@@ -147,7 +271,8 @@ class Engine:
         place; tokens come back to the host (one small copy, which also carries the
         device status word)."""
         logits = self.step(slots, tokens, None, check=False)
-        picked = sampler.sample(logits, self.last_batch.slots, params, histories)
+        B = len(slots)
+        picked = sampler.sample(logits, self.last_batch.slots[:B], params, histories)
         host = torch.cat([picked, self.rt.status[:1]]).cpu()
         if int(host[-1]):
             self.rt.check()

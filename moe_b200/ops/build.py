@@ -29,7 +29,8 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompil
 
 # library name -> sources; what a model needs is decided by the caller
 LIBRARIES: Dict[str, List[str]] = {
-    "core": ["embed_norm.cu", "gemm_generic.cu", "rope_cache.cu", "attention_generic.cu", "moe.cu", "sampling.cu"],
+    "core": ["embed_norm.cu", "gemm_generic.cu", "rope_cache.cu", "attention_generic.cu", "attention_decode.cu",
+             "moe.cu", "sampling.cu"],
     # tcgen05 / TMA kernels of the bfloat16 path; a float32 model never builds or loads them
     "tc": ["gemm_tc.cu"],
 }

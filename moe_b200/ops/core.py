@@ -37,7 +37,8 @@ def lib():
             "moe_rope_split": [P, P, P, I, I, I, I, I, P, P, P, I, P],
             "moe_kv_commit": [P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
             "moe_attention_generic": [P, P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],
-            "moe_router": [P, P, P, I, P, I, I, I, I, I, F, P, P, P, P],
+            "moe_router": [P, P, P, I, P, I, I, I, I, I, F, P, P, P, P, P],
+            "moe_attention_decode": [P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],
             "moe_align": [P, I, I, I, P, P, P, P, P],
             "moe_swiglu": [P, P, I, LL, I, P],
             "moe_combine": [P, P, P, I, P, P, P, I, I, P],
@@ -254,9 +255,38 @@ def router(h32, w_router, top_k, norm_topk, scale, topk_idx, topk_w, *, shared_g
         if shared_gate_w.dtype != w_router.dtype or shared_gate_w.numel() != H:
             raise KernelError("router: the shared gate weight must have the router's dtype and width")
         _chk(shared_gate, "shared_gate", torch.float32)
+    logits = torch.empty((T, E + (1 if shared_gate_w is not None else 0)), dtype=torch.float32, device=h32.device)
     _ok(lib().moe_router(_p(h32), _p(w_router), _p(shared_gate_w), _dt(w_router), _p(seq_of_token), T, H, E, top_k,
-                         1 if norm_topk else 0, float(scale), _p(topk_idx), _p(topk_w), _p(shared_gate), _stream()),
-        "router")
+                         1 if norm_topk else 0, float(scale), _p(logits), _p(topk_idx), _p(topk_w), _p(shared_gate),
+                         _stream()), "router")
+
+
+_SMS = {}
+
+
+def decode_splits(device, num_tokens: int, nkv: int) -> int:
+    """Key splits of the decode attention: about eight small CTAs per SM (each is a chain of
+    dependent loads, so many must be in flight)."""
+    idx = torch.device(device).index or 0
+    if idx not in _SMS:
+        _SMS[idx] = torch.cuda.get_device_properties(device).multi_processor_count
+    return max(1, min(32, (8 * _SMS[idx]) // max(1, num_tokens * nkv)))
+
+
+def attention_decode(q, view, batch, out, *, nh, window, scale, status):
+    """Attention of one new token per sequence over the cache alone (its own key already
+    appended); split along the keys and merged."""
+    g = view.group
+    T = batch.num_tokens
+    if q.dtype != g.dtype or out.dtype != q.dtype:
+        raise KernelError("attention: dtypes of queries, cache and output must agree")
+    nsplit = decode_splits(q.device, T, g.num_kv_heads)
+    partial = torch.empty(T * nh * nsplit * (g.head_dim + 2), dtype=torch.float32, device=q.device)
+    _ok(lib().moe_attention_decode(_p(q), _p(view.k), _p(view.v), _p(out), _p(partial), _dt(q),
+                                   _p(batch.seq_of_token), _p(batch.pos), _p(batch.slots), _p(g.table),
+                                   g.table.stride(0), g.ring, g.page_size, g.num_pages, T, nh, g.num_kv_heads,
+                                   g.head_dim, int(window or 0), float(scale), nsplit, _p(status), _stream()),
+        "attention_decode")
 
 
 def moe_align(topk_idx, num_tokens, top_k, num_experts, offsets, sorted_token, pos_of_pair, status):

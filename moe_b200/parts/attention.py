@@ -24,6 +24,7 @@ from .base import Part, TensorSpec, make_part, register_part
 
 class GQAttention(Part):
     category, kind = "mixer", "gqa_attention"
+    graph_safe = True
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -91,10 +92,18 @@ class GQAttention(Part):
             self.position.apply(rt, qkv, self.nh, nkv, self.hd, batch.pos)
         core.rope_split(qkv, batch.pos, table, self.nh, nkv, self.hd, rot, q, k_new, v_new)
         ctx = rt.empty((T, self.nh * self.hd))
-        core.attention_generic(q, k_new, v_new, cache_view, batch, ctx, nh=self.nh, window=self.window,
-                               scale=self.scale, use_local=self.own_kv, status=rt.status)
-        if self.own_kv:
-            core.kv_commit(k_new, v_new, cache_view, batch, rt.status)
+        if batch.all_decode:
+            # one token per sequence: append first, then attend over the cache alone, split along the keys
+            if self.own_kv:
+                core.kv_commit(k_new, v_new, cache_view, batch, rt.status)
+            core.attention_decode(q, cache_view, batch, ctx, nh=self.nh, window=self.window, scale=self.scale,
+                                  status=rt.status)
+        else:
+            # keys of earlier steps from the cache, keys of this step from its own buffers, then append
+            core.attention_generic(q, k_new, v_new, cache_view, batch, ctx, nh=self.nh, window=self.window,
+                                   scale=self.scale, use_local=self.own_kv, status=rt.status)
+            if self.own_kv:
+                core.kv_commit(k_new, v_new, cache_view, batch, rt.status)
         return linear(rt, ctx, self.wo)
 
 

@@ -70,6 +70,9 @@ class Activations:
 class Part:
     category = ""
     kind = ""
+    # True if forward() only launches kernels on the current stream (no host synchronisation, no
+    # data-dependent host control flow), so that a decode step may be captured in a CUDA graph.
+    graph_safe = False
 
     def __init__(self, spec: PartSpec):
         self.spec = spec

@@ -15,6 +15,7 @@ from .base import Part, TensorSpec, register_part
 
 class TokenEmbedding(Part):
     category, kind = "embedding", "token_embedding"
+    graph_safe = True
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -36,6 +37,7 @@ class TokenEmbedding(Part):
 
 class LMHead(Part):
     category, kind = "head", "lm_head"
+    graph_safe = True
 
     def __init__(self, spec):
         super().__init__(spec)

@@ -23,6 +23,7 @@ def _fuse_rows(tensors):
 
 class DenseSwiGLU(Part):
     category, kind = "ffn", "dense_swiglu"
+    graph_safe = True
     wants32 = False
 
     def __init__(self, spec):
@@ -48,6 +49,7 @@ class DenseSwiGLU(Part):
 
 class RoutedExperts(Part):
     category, kind = "ffn", "routed_experts"
+    graph_safe = True
     wants32 = True   # router logits are computed from the 32-bit normed state
 
     def __init__(self, spec):

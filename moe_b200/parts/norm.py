@@ -9,6 +9,7 @@ from .base import Activations, Part, TensorSpec, register_part
 
 class RMSNorm(Part):
     category, kind = "norm", "rmsnorm"
+    graph_safe = True
 
     def __init__(self, spec):
         super().__init__(spec)

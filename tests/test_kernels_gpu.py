@@ -167,7 +167,13 @@ def _attention_case(core, dt, nh, nkv, hd, window, lens_before, lens_new, seed=0
     # after the commit, the same queries must see the same thing from the cache alone
     core.kv_commit(kn, vn, view, b1, st)
     out2 = torch.empty_like(out)
-    if all(n == 1 for n in lens_new) or window is None:
+    if all(n == 1 for n in lens_new):
+        # the decode kernel (split along the keys) and the plain kernel, both over the cache alone
+        core.attention_decode(q, view, b1, out2, nh=nh, window=window, scale=scale, status=st)
+        out3 = torch.empty_like(out)
+        core.attention_generic(q, kn, vn, view, b1, out3, nh=nh, window=window, scale=scale, use_local=False, status=st)
+        assert float((out3.double() - out2.double()).abs().max()) < 2e-2 * float(out3.double().abs().max())
+    elif window is None:
         core.attention_generic(q, kn, vn, view, b1, out2, nh=nh, window=window, scale=scale, use_local=False, status=st)
     else:
         out2 = None
