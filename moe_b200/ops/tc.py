@@ -28,6 +28,10 @@ def lib():
         L.moe_gemm_tc_plan.restype = c_int
         L.moe_gather_rows_bf16.argtypes = [P, P, P, I, I, I, P, P]
         L.moe_gather_rows_bf16.restype = c_int
+        from ctypes import c_float
+
+        L.moe_attention_prefill_bf16.argtypes = [P, P, P, P, P, I, I, I, I, I, I, c_float, P]
+        L.moe_attention_prefill_bf16.restype = c_int
         _lib = L
     return _lib
 
@@ -122,6 +126,21 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swiglu: bool
     if code == -1:
         return False
     core._ok(code, "gemm_tc")
+    return True
+
+
+def attention_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, batch, out: torch.Tensor, *, nh: int, nkv: int,
+                      hd: int, window, scale: float) -> bool:
+    """Causal (optionally windowed) attention of whole prompts on the tensor cores; every
+    sequence of ``batch`` must start at position 0.  False if the head size is not taken."""
+    if q.dtype != torch.bfloat16 or hd not in (16, 32, 64, 128):
+        return False
+    code = lib().moe_attention_prefill_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                            batch.cu_seqlens.data_ptr(), batch.num_seqs, batch.num_tokens, nh, nkv,
+                                            hd, int(window or 0), float(scale), core._stream())
+    if code == -1:
+        return False
+    core._ok(code, "attention_prefill")
     return True
 
 

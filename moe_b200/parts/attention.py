@@ -99,9 +99,17 @@ class GQAttention(Part):
             core.attention_decode(q, cache_view, batch, ctx, nh=self.nh, window=self.window, scale=self.scale,
                                   status=rt.status)
         else:
-            # keys of earlier steps from the cache, keys of this step from its own buffers, then append
-            core.attention_generic(q, k_new, v_new, cache_view, batch, ctx, nh=self.nh, window=self.window,
-                                   scale=self.scale, use_local=self.own_kv, status=rt.status)
+            done = False
+            if batch.all_fresh and self.own_kv and rt.is_bf16:
+                # whole prompts: nothing is read from the cache; tensor-core kernel
+                from ..ops import tc
+
+                done = tc.attention_prefill(q, k_new, v_new, batch, ctx, nh=self.nh, nkv=self.nkv, hd=self.hd,
+                                            window=self.window, scale=self.scale)
+            if not done:
+                # keys of earlier steps from the cache, keys of this step from its own buffers
+                core.attention_generic(q, k_new, v_new, cache_view, batch, ctx, nh=self.nh, window=self.window,
+                                       scale=self.scale, use_local=self.own_kv, status=rt.status)
             if self.own_kv:
                 core.kv_commit(k_new, v_new, cache_view, batch, rt.status)
         return linear(rt, ctx, self.wo)

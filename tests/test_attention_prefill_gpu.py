@@ -1,0 +1,73 @@
+"""The tensor-core prefill attention against the plain attention function: unequal sequences in
+one batch, grouped heads, windows whose edge falls inside and across key tiles, a far key that
+must dominate."""
+import math
+
+import pytest
+import torch
+
+import gpu_util as G
+import plain_qwen2moe as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def tc():
+    from moe_b200.ops import tc as t
+
+    t.lib()
+    return t
+
+
+def run(tc, q, k, v, lens, nh, nkv, hd, window):
+    batch = G.make_batch(DEV, list(range(len(lens))), [0] * len(lens), lens)
+    out = torch.full((sum(lens), nh * hd), float("nan"), device=DEV, dtype=torch.bfloat16)
+    assert tc.attention_prefill(q, k, v, batch, out, nh=nh, nkv=nkv, hd=hd, window=window, scale=1.0 / math.sqrt(hd))
+    return out
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (3, 1, 32), (6, 3, 64), (2, 2, 128), (5, 1, 128)])
+@pytest.mark.parametrize("window", [None, 1, 8, 64, 100])
+def test_against_plain(tc, nh, nkv, hd, window):
+    torch.manual_seed(hd + (window or 0))
+    lens = [1, 63, 64, 65, 200, 7]
+    T = sum(lens)
+    q = torch.randn(T, nh, hd, device=DEV).to(torch.bfloat16)
+    k = torch.randn(T, nkv, hd, device=DEV).to(torch.bfloat16)
+    v = torch.randn(T, nkv, hd, device=DEV).to(torch.bfloat16)
+    out = run(tc, q, k, v, lens, nh, nkv, hd, window).double().cpu()
+    o = 0
+    for n in lens:
+        ref = plain.attention(q[o:o + n].double().cpu(), k[o:o + n].double().cpu(), v[o:o + n].double().cpu(), window)
+        err = float((out[o:o + n] - ref).abs().max())
+        assert err < 2e-2 * float(ref.abs().max()), (n, err)
+        o += n
+    assert torch.isfinite(out).all()
+
+
+def test_a_far_key_among_hundreds_and_the_windows_edge(tc):
+    """One key is made to stand out (query and key scaled): without a window the last query must
+    return that key's value; with a window the key counts exactly while it is inside."""
+    nh = nkv = 1
+    hd, n, far = 64, 700, 5
+    torch.manual_seed(1)
+    q = (torch.randn(n, 1, hd) * 0.1)
+    k = (torch.randn(n, 1, hd) * 0.1)
+    v = torch.randn(n, 1, hd)
+    u = torch.zeros(hd)
+    u[3] = 1.0
+    k[far, 0] = 40.0 * u
+    q[n - 1, 0] = 40.0 * u                      # score 1600 / 8 = 200 against key `far`
+    q[far + 99, 0] = 40.0 * u
+    q[far + 100, 0] = 40.0 * u
+    qd, kd, vd = (t.to(DEV).to(torch.bfloat16) for t in (q, k, v))
+    full = run(tc, qd, kd, vd, [n], nh, nkv, hd, None).float().cpu()
+    assert torch.allclose(full[n - 1], vd[far, 0].float().cpu(), atol=2e-2)
+    win = run(tc, qd, kd, vd, [n], nh, nkv, hd, 100).float().cpu()
+    # position far + 99 still sees `far` (window 100 includes itself); far + 100 no longer does
+    assert torch.allclose(win[far + 99], vd[far, 0].float().cpu(), atol=2e-2)
+    assert not torch.allclose(win[far + 100], vd[far, 0].float().cpu(), atol=0.2)
+    ref = plain.attention(qd.double().cpu(), kd.double().cpu(), vd.double().cpu(), 100)
+    assert float((win.double() - ref).abs().max()) < 2e-2 * float(ref.abs().max())
