@@ -439,3 +439,75 @@ MOE_API int moe_attention_decode(const void* q, const void* k_cache, const void*
                                  ring, page_size, num_pages, num_tokens, nh, nkv, hd, window, scale, nsplit, status,
                                  stream);
 }
+
+// ---- the entry point that allocates nothing (see attention_decode_noalloc.h) -----------------
+#include "attention_decode_noalloc.h"
+
+#include <mutex>
+
+namespace {
+
+// Scratch for the per-split partial results.  In host code this name is only a handle for
+// cudaGetSymbolAddress; the kernels are given the device address obtained below.
+static __device__ __align__(256) float g_noalloc_scratch[MOE_NOALLOC_SCRATCH_FLOATS];
+
+constexpr int MAX_DEVICES = 64;
+float* g_scratch_ptr[MAX_DEVICES] = {};
+std::mutex g_scratch_mutex;
+
+// Device address of the scratch array on the current device; looked up once per device.
+float* noalloc_scratch() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return nullptr;
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (!g_scratch_ptr[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || !p) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        g_scratch_ptr[dev] = static_cast<float*>(p);
+    }
+    return g_scratch_ptr[dev];
+}
+
+}  // namespace
+
+MOE_API long long moe_attention_decode_noalloc_need(int num_tokens, int num_heads, int head_dim, int nsplit) {
+    return (long long)num_tokens * num_heads * nsplit * (head_dim + 2);
+}
+
+MOE_API const char* moe_noalloc_strerror(int code) {
+    switch (code) {
+        case MOE_NOALLOC_OK: return "ok";
+        case MOE_NOALLOC_TOO_LARGE:
+            return "the call needs more than the 2M floats (8 MiB) of scratch built into the library; "
+                   "use fewer key splits or fewer tokens per call, or the entry point that takes scratch";
+        case MOE_NOALLOC_BAD_ARGUMENT: return "a size or head layout the decode attention kernels do not take";
+        case MOE_NOALLOC_NO_DEVICE: return "the device address of the built-in scratch array could not be obtained";
+        default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown code";
+    }
+}
+
+MOE_API int moe_attention_decode_noalloc(const void* q, const void* k_cache, const void* v_cache, void* out, int dt,
+                                         const int* seq_of_token, const int* pos, const int* slots,
+                                         const int* tables, int table_stride, int ring, int page_size, int num_pages,
+                                         int num_tokens, int num_heads, int num_kv_heads, int head_dim, int window,
+                                         float scale, int nsplit, int* status, cudaStream_t stream) {
+    if (num_tokens <= 0) return MOE_NOALLOC_OK;
+    if (head_dim % 16 != 0 || head_dim > MAX_HD || head_dim <= 0 || num_kv_heads <= 0 ||
+        num_heads % num_kv_heads != 0 || nsplit < 1 || nsplit > 65535 || num_kv_heads > 65535 || num_tokens > 65535 ||
+        (dt != DT_F32 && dt != DT_BF16))
+        return MOE_NOALLOC_BAD_ARGUMENT;
+    if (moe_attention_decode_noalloc_need(num_tokens, num_heads, head_dim, nsplit) > MOE_NOALLOC_SCRATCH_FLOATS)
+        return MOE_NOALLOC_TOO_LARGE;
+    float* scratch = noalloc_scratch();
+    if (!scratch) return MOE_NOALLOC_NO_DEVICE;
+    if (dt == DT_F32)
+        return launch<float>(q, k_cache, v_cache, out, scratch, seq_of_token, pos, slots, tables, table_stride, ring,
+                             page_size, num_pages, num_tokens, num_heads, num_kv_heads, head_dim, window, scale,
+                             nsplit, status, stream);
+    return launch<__nv_bfloat16>(q, k_cache, v_cache, out, scratch, seq_of_token, pos, slots, tables, table_stride,
+                                 ring, page_size, num_pages, num_tokens, num_heads, num_kv_heads, head_dim, window,
+                                 scale, nsplit, status, stream);
+}
