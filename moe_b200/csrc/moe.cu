@@ -98,26 +98,69 @@ router_logits_kernel(const float* __restrict__ h, const WT* __restrict__ wr, con
     }
 }
 
-// One warp per token: softmax over all experts, top-k, weights.
-__global__ void __launch_bounds__(128)
-router_topk_kernel(const float* __restrict__ logits, const int* __restrict__ seq_of_token, int num_tokens,
-                   int num_experts, int rows, int top_k, int norm_topk, float scale, int* __restrict__ topk_idx,
-                   float* __restrict__ topk_w, float* __restrict__ shared_gate) {
-    extern __shared__ float sc_all[];   // 4 warps x num_experts
+// The same product for many tokens (a prompt): a block takes 8 router rows (one per warp) and 16
+// tokens, and walks the hidden dimension in chunks of 512 that are staged in shared memory, so
+// that an activation is read from global memory once per 8 rows and a weight once per 16 tokens.
+// hidden must be a multiple of 8.  Grid: (ceil(rows / 8), ceil(T / 16)).
+constexpr int PT = 16, PKC = 512;
+template <typename WT>
+__global__ void __launch_bounds__(256)
+router_logits_tiled_kernel(const float* __restrict__ h, const WT* __restrict__ wr, const WT* __restrict__ wsg,
+                           int num_tokens, int hidden, int num_experts, int rows, float* __restrict__ logits) {
+    __shared__ __align__(16) float xs[PT][PKC];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * 4 + warp;
-    if (t >= num_tokens) return;
-    float* sc = sc_all + (size_t)warp * num_experts;
-    if (seq_of_token && seq_of_token[t] < 0) {   // padding row: no expert
-        for (int j = lane; j < top_k; j += 32) {
-            topk_idx[(size_t)t * top_k + j] = -1;
-            topk_w[(size_t)t * top_k + j] = 0.f;
+    const int r = blockIdx.x * 8 + warp;
+    const int t0 = blockIdx.y * PT;
+    const int nt = min(PT, num_tokens - t0);
+    const WT* w = r < num_experts ? wr + (size_t)r * hidden : wsg;
+    float acc[PT];
+#pragma unroll
+    for (int i = 0; i < PT; i++) acc[i] = 0.f;
+    for (int c0 = 0; c0 < hidden; c0 += PKC) {
+        const int kc = min(PKC, hidden - c0);            // a multiple of 8
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < PT * (PKC / 4); idx += blockDim.x) {
+            const int i = idx / (PKC / 4), c = (idx % (PKC / 4)) * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (i < nt && c < kc) v = *reinterpret_cast<const float4*>(h + (size_t)(t0 + i) * hidden + c0 + c);
+            *reinterpret_cast<float4*>(&xs[i][c]) = v;
         }
-        if (shared_gate && lane == 0) shared_gate[t] = 0.f;
+        __syncthreads();
+        if (r < rows) {
+            for (int c = lane * 8; c < kc; c += 256) {
+                float wv[8];
+                w_load8<WT>(w + c0 + c, wv);
+#pragma unroll
+                for (int i = 0; i < PT; i++) {
+                    const float4 a = *reinterpret_cast<const float4*>(&xs[i][c]);
+                    const float4 b = *reinterpret_cast<const float4*>(&xs[i][c + 4]);
+                    float s = acc[i];
+                    s = fmaf(a.x, wv[0], s), s = fmaf(a.y, wv[1], s), s = fmaf(a.z, wv[2], s), s = fmaf(a.w, wv[3], s);
+                    s = fmaf(b.x, wv[4], s), s = fmaf(b.y, wv[5], s), s = fmaf(b.z, wv[6], s), s = fmaf(b.w, wv[7], s);
+                    acc[i] = s;
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < PT; i++) {
+        const float s = warp_sum(acc[i]);
+        if (lane == 0 && i < nt && r < rows) logits[(size_t)(t0 + i) * rows + r] = s;
+    }
+}
+
+// Softmax over all experts, top-k and weights of ONE token, by one warp.  `sc` is shared memory
+// of num_experts floats owned by the warp.
+__device__ __forceinline__ void route_token(const float* __restrict__ lg, float* sc, int lane, bool padding,
+                                            int num_experts, int rows, int top_k, int norm_topk, float scale,
+                                            int* __restrict__ idx_out, float* __restrict__ w_out,
+                                            float* __restrict__ gate_out) {
+    if (padding) {   // a row that belongs to no sequence: no expert
+        for (int j = lane; j < top_k; j += 32) idx_out[j] = -1, w_out[j] = 0.f;
+        if (gate_out && lane == 0) *gate_out = 0.f;
         return;
     }
-    const float* lg = logits + (size_t)t * rows;
-    if (shared_gate && rows > num_experts && lane == 0) shared_gate[t] = 1.0f / (1.0f + expf(-lg[num_experts]));
+    if (gate_out && rows > num_experts && lane == 0) *gate_out = 1.0f / (1.0f + expf(-lg[num_experts]));
     float m = -INFINITY;
     for (int e = lane; e < num_experts; e += 32) m = fmaxf(m, lg[e]);
     m = warp_max(m);
@@ -149,28 +192,41 @@ router_topk_kernel(const float* __restrict__ logits, const int* __restrict__ seq
         wsum += w;
         if (lane == 0) {
             sc[bi] = -2.f;   // taken
-            topk_idx[(size_t)t * top_k + j] = bi;
-            topk_w[(size_t)t * top_k + j] = w;
+            idx_out[j] = bi;
+            w_out[j] = w;
         }
         __syncwarp();
     }
     if (lane == 0) {
         const float zz = norm_topk ? fmaxf(wsum, 1e-20f) : 1.0f;
         for (int j = 0; j < top_k; j++) {
-            float w = topk_w[(size_t)t * top_k + j];
+            float w = w_out[j];
             if (norm_topk) w = w / zz;
-            topk_w[(size_t)t * top_k + j] = w * scale;
+            w_out[j] = w * scale;
         }
     }
 }
 
-// Single block.  pairs = tokens * top_k entries of topk_idx (expert id, or -1).
-__global__ void __launch_bounds__(1024)
-moe_align_kernel(const int* __restrict__ topk_idx, int pairs, int top_k, int num_experts, int* __restrict__ offsets,
-                 int* __restrict__ sorted_token, int* __restrict__ pos_of_pair, int* status) {
-    extern __shared__ int sm[];   // counts[E], cursor[E]
-    int* counts = sm;
-    int* cursor = sm + num_experts;
+// One warp per token.
+__global__ void __launch_bounds__(128)
+router_topk_kernel(const float* __restrict__ logits, const int* __restrict__ seq_of_token, int num_tokens,
+                   int num_experts, int rows, int top_k, int norm_topk, float scale, int* __restrict__ topk_idx,
+                   float* __restrict__ topk_w, float* __restrict__ shared_gate) {
+    extern __shared__ float sc_all[];   // 4 warps x num_experts
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= num_tokens) return;
+    route_token(logits + (size_t)t * rows, sc_all + (size_t)warp * num_experts, lane,
+                seq_of_token && seq_of_token[t] < 0, num_experts, rows, top_k, norm_topk, scale,
+                topk_idx + (size_t)t * top_k, topk_w + (size_t)t * top_k, shared_gate ? shared_gate + t : nullptr);
+}
+
+// Inverting the (token, expert) table, by one block.  pairs = tokens * top_k entries of topk_idx
+// (expert id, or -1).  counts and cursor are shared memory of num_experts ints each.
+__device__ __forceinline__ void align_block(const int* __restrict__ topk_idx, int pairs, int top_k, int num_experts,
+                                            int* counts, int* cursor, int* __restrict__ offsets,
+                                            int* __restrict__ sorted_token, int* __restrict__ pos_of_pair,
+                                            int* status) {
     for (int e = threadIdx.x; e < num_experts; e += blockDim.x) counts[e] = 0;
     __syncthreads();
     for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
@@ -207,6 +263,42 @@ moe_align_kernel(const int* __restrict__ topk_idx, int pairs, int top_k, int num
     for (int i = total + threadIdx.x; i < pairs; i += blockDim.x) sorted_token[i] = 0;
 }
 
+__global__ void __launch_bounds__(1024)
+moe_align_kernel(const int* __restrict__ topk_idx, int pairs, int top_k, int num_experts, int* __restrict__ offsets,
+                 int* __restrict__ sorted_token, int* __restrict__ pos_of_pair, int* status) {
+    extern __shared__ int sm[];   // counts[E], cursor[E]
+    align_block(topk_idx, pairs, top_k, num_experts, sm, sm + num_experts, offsets, sorted_token, pos_of_pair, status);
+}
+
+// Few tokens (a decode step): pick, inversion and the gather of the picked tokens' activations in
+// ONE block, to spare two launches.  xs[p, :] = x[sorted_token[p], :] for 16-byte units.
+__global__ void __launch_bounds__(1024)
+route_dispatch_kernel(const float* __restrict__ logits, const int* __restrict__ seq_of_token, int num_tokens,
+                      int num_experts, int rows, int top_k, int norm_topk, float scale, int* __restrict__ topk_idx,
+                      float* __restrict__ topk_w, float* __restrict__ shared_gate, int* __restrict__ offsets,
+                      int* __restrict__ sorted_token, int* __restrict__ pos_of_pair, const uint4* __restrict__ x,
+                      uint4* __restrict__ xs, int row_units, int* status) {
+    extern __shared__ float dyn[];   // 32 warps x num_experts floats, then counts[E], cursor[E]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int t = warp; t < num_tokens; t += 32)
+        route_token(logits + (size_t)t * rows, dyn + (size_t)warp * num_experts, lane,
+                    seq_of_token && seq_of_token[t] < 0, num_experts, rows, top_k, norm_topk, scale,
+                    topk_idx + (size_t)t * top_k, topk_w + (size_t)t * top_k, shared_gate ? shared_gate + t : nullptr);
+    __syncthreads();   // the picks were written by this block: visible to it after the barrier
+    int* counts = reinterpret_cast<int*>(dyn + (size_t)32 * num_experts);
+    const int pairs = num_tokens * top_k;
+    align_block(topk_idx, pairs, top_k, num_experts, counts, counts + num_experts, offsets, sorted_token, pos_of_pair,
+                status);
+    __syncthreads();
+    if (x) {
+        const int total = offsets[num_experts];
+        for (int i = threadIdx.x; i < total * row_units; i += blockDim.x) {
+            const int p = i / row_units, c = i % row_units;
+            xs[(size_t)p * row_units + c] = x[(size_t)sorted_token[p] * row_units + c];
+        }
+    }
+}
+
 // act[m, j] = silu(gu[m, j]) * gu[m, inter + j], silu(a) = a / (1 + exp(-a))
 // (reference: src/model.rs:31-33).
 template <typename OT>
@@ -240,13 +332,12 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
 
 }  // namespace
 
-// logits: scratch of num_tokens * (num_experts + (wsg ? 1 : 0)) floats.
-MOE_API int moe_router(const float* h, const void* wr, const void* wsg, int w_dt, const int* seq_of_token,
-                       int num_tokens, int hidden, int num_experts, int top_k, int norm_topk, float scale,
-                       float* logits, int* topk_idx, float* topk_w, float* shared_gate, cudaStream_t stream) {
+// logits[t, r] = h[t] . W[r] for the router rows (and the shared-gate row, if wsg): num_tokens *
+// (num_experts + (wsg ? 1 : 0)) floats.
+MOE_API int moe_router_logits(const float* h, const void* wr, const void* wsg, int w_dt, int num_tokens, int hidden,
+                              int num_experts, float* logits, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
-    if (top_k <= 0 || top_k > num_experts || num_experts > 2048 || !logits) return (int)cudaErrorInvalidValue;
-    if (wsg && !shared_gate) return (int)cudaErrorInvalidValue;
+    if (num_experts <= 0 || !logits) return (int)cudaErrorInvalidValue;
     const int rows = num_experts + (wsg ? 1 : 0);
     const size_t elt = w_dt == DT_F32 ? 4 : 2;
     const int vec_ok = (hidden % 8 == 0) && ((uintptr_t)h % 16 == 0) && ((uintptr_t)wr % 16 == 0) &&
@@ -258,10 +349,31 @@ MOE_API int moe_router(const float* h, const void* wr, const void* wsg, int w_dt
         h, (const WT*)wr, (const WT*)wsg, num_tokens, hidden, num_experts, rows, vec_ok, logits)
     if (num_tokens <= 64) {
         if (w_dt == DT_F32) LOGITS(float, 2, 4); else LOGITS(__nv_bfloat16, 2, 4);
+    } else if (vec_ok && (num_tokens + PT - 1) / PT <= 65535) {
+        const dim3 tg((rows + 7) / 8, (num_tokens + PT - 1) / PT);
+        if (w_dt == DT_F32)
+            router_logits_tiled_kernel<float><<<tg, 256, 0, stream>>>(h, (const float*)wr, (const float*)wsg,
+                                                                      num_tokens, hidden, num_experts, rows, logits);
+        else
+            router_logits_tiled_kernel<__nv_bfloat16><<<tg, 256, 0, stream>>>(
+                h, (const __nv_bfloat16*)wr, (const __nv_bfloat16*)wsg, num_tokens, hidden, num_experts, rows, logits);
     } else {
         if (w_dt == DT_F32) LOGITS(float, 8, 1); else LOGITS(__nv_bfloat16, 8, 1);
     }
 #undef LOGITS
+    return launch_status();
+}
+
+// logits: scratch of num_tokens * (num_experts + (wsg ? 1 : 0)) floats.
+MOE_API int moe_router(const float* h, const void* wr, const void* wsg, int w_dt, const int* seq_of_token,
+                       int num_tokens, int hidden, int num_experts, int top_k, int norm_topk, float scale,
+                       float* logits, int* topk_idx, float* topk_w, float* shared_gate, cudaStream_t stream) {
+    if (num_tokens <= 0) return 0;
+    if (top_k <= 0 || top_k > num_experts || num_experts > 2048 || !logits) return (int)cudaErrorInvalidValue;
+    if (wsg && !shared_gate) return (int)cudaErrorInvalidValue;
+    const int rc = moe_router_logits(h, wr, wsg, w_dt, num_tokens, hidden, num_experts, logits, stream);
+    if (rc) return rc;
+    const int rows = num_experts + (wsg ? 1 : 0);
     const size_t smem = (size_t)4 * num_experts * sizeof(float);
     router_topk_kernel<<<(num_tokens + 3) / 4, 128, smem, stream>>>(logits, seq_of_token, num_tokens, num_experts, rows,
                                                                    top_k, norm_topk, scale, topk_idx, topk_w,
@@ -275,6 +387,23 @@ MOE_API int moe_align(const int* topk_idx, int num_tokens, int top_k, int num_ex
     const size_t smem = (size_t)num_experts * 2 * sizeof(int);
     moe_align_kernel<<<1, 1024, smem, stream>>>(topk_idx, num_tokens * top_k, top_k, num_experts, offsets,
                                                sorted_token, pos_of_pair, status);
+    return launch_status();
+}
+
+// logits -> picks, weights, shared gate, inverted table and (optionally) gathered activations, one
+// launch.  For at most 64 tokens and 256 experts.  x / xs: rows of row_bytes bytes (a multiple of 16).
+MOE_API int moe_route_dispatch(const float* logits, const int* seq_of_token, int num_tokens, int num_experts,
+                               int has_gate_row, int top_k, int norm_topk, float scale, int* topk_idx, float* topk_w,
+                               float* shared_gate, int* offsets, int* sorted_token, int* pos_of_pair, const void* x,
+                               void* xs, int row_bytes, int* status, cudaStream_t stream) {
+    if (num_tokens <= 0) return 0;
+    if (num_tokens > 64 || num_experts > 256 || top_k <= 0 || top_k > num_experts || row_bytes % 16)
+        return (int)cudaErrorInvalidValue;
+    const size_t smem = (size_t)32 * num_experts * sizeof(float) + (size_t)2 * num_experts * sizeof(int);
+    route_dispatch_kernel<<<1, 1024, smem, stream>>>(logits, seq_of_token, num_tokens, num_experts,
+                                                    num_experts + (has_gate_row ? 1 : 0), top_k, norm_topk, scale,
+                                                    topk_idx, topk_w, shared_gate, offsets, sorted_token, pos_of_pair,
+                                                    (const uint4*)x, (uint4*)xs, row_bytes / 16, status);
     return launch_status();
 }
 

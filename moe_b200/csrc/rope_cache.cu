@@ -109,6 +109,82 @@ __global__ void table_update_kernel(int* __restrict__ table, int stride, const i
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) table[(size_t)upd[3 * i] * stride + upd[3 * i + 1]] = upd[3 * i + 2];
 }
+// A decode step (one token per sequence): rotate, write the query, and append key and value
+// straight into the cache, in one launch.  Same arithmetic as rope_split_kernel followed by
+// kv_commit_kernel.  One block per token.
+template <typename OT>
+__global__ void rope_commit_kernel(const float* __restrict__ qkv, const int* __restrict__ pos,
+                                   const float* __restrict__ inv_freq, int nh, int nkv, int hd, int rot,
+                                   OT* __restrict__ q, OT* __restrict__ k_cache, OT* __restrict__ v_cache,
+                                   const int* __restrict__ seq_of_token, const int* __restrict__ slots,
+                                   const int* __restrict__ tables, int table_stride, int ring, int page_size,
+                                   int num_pages, int* status) {
+    const int t = blockIdx.x;
+    const int width = (nh + 2 * nkv) * hd;
+    const float* src = qkv + (size_t)t * width;
+    const int s = seq_of_token[t];
+    const int p_int = pos[t];
+    const float p = (float)p_int;
+    const int half = rot / 2;
+    CachePos cp;
+    cp.page = 0, cp.off = 0;
+    if (s >= 0) cp = cache_pos(p_int, ring, tables + (size_t)slots[s] * table_stride, page_size, num_pages, status);
+    const int rot_heads = nh + nkv;
+    for (int idx = threadIdx.x; idx < rot_heads * half; idx += blockDim.x) {
+        const int h = idx / half, i = idx % half;
+        const float* sp = src + (size_t)h * hd;
+        float sn, cs;
+        sincosf(p * inv_freq[i], &sn, &cs);
+        const float a = sp[i], b = sp[i + half];
+        OT* dst;
+        if (h < nh) {
+            dst = q + ((size_t)t * nh + h) * hd;
+        } else {
+            if (s < 0) continue;                          // a padding row has no cache
+            dst = k_cache + cache_index(cp, h - nh, nkv, page_size, hd);
+        }
+        st_f(dst + i, a * cs - b * sn);
+        st_f(dst + i + half, a * sn + b * cs);
+    }
+    if (rot < hd) {
+        const int rest = hd - rot;
+        for (int idx = threadIdx.x; idx < rot_heads * rest; idx += blockDim.x) {
+            const int h = idx / rest, i = rot + idx % rest;
+            OT* dst;
+            if (h < nh) {
+                dst = q + ((size_t)t * nh + h) * hd;
+            } else {
+                if (s < 0) continue;
+                dst = k_cache + cache_index(cp, h - nh, nkv, page_size, hd);
+            }
+            st_f(dst + i, src[(size_t)h * hd + i]);
+        }
+    }
+    if (s >= 0) {
+        const float* vs = src + (size_t)(nh + nkv) * hd;
+        for (int i = threadIdx.x; i < nkv * hd; i += blockDim.x)
+            st_f(v_cache + cache_index(cp, i / hd, nkv, page_size, hd) + i % hd, vs[i]);
+    }
+}
+
+MOE_API int moe_rope_commit(const float* qkv, const int* pos, const float* inv_freq, int num_tokens, int nh, int nkv,
+                            int hd, int rot, void* q, void* k_cache, void* v_cache, int dt, const int* seq_of_token,
+                            const int* slots, const int* tables, int table_stride, int ring, int page_size,
+                            int num_pages, int* status, cudaStream_t stream) {
+    if (num_tokens <= 0) return 0;
+    if (rot < 0 || rot > hd || (rot & 1)) return (int)cudaErrorInvalidValue;
+    if (rot > 0 && !inv_freq) return (int)cudaErrorInvalidValue;
+    if (dt == DT_F32)
+        rope_commit_kernel<float><<<num_tokens, 256, 0, stream>>>(
+            qkv, pos, inv_freq, nh, nkv, hd, rot, (float*)q, (float*)k_cache, (float*)v_cache, seq_of_token, slots,
+            tables, table_stride, ring, page_size, num_pages, status);
+    else
+        rope_commit_kernel<__nv_bfloat16><<<num_tokens, 256, 0, stream>>>(
+            qkv, pos, inv_freq, nh, nkv, hd, rot, (__nv_bfloat16*)q, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
+            seq_of_token, slots, tables, table_stride, ring, page_size, num_pages, status);
+    return launch_status();
+}
+
 MOE_API int moe_table_update(int* table, int stride, const int* upd, int n, cudaStream_t stream) {
     if (n <= 0) return 0;
     table_update_kernel<<<(n + 127) / 128, 128, 0, stream>>>(table, stride, upd, n);

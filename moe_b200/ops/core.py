@@ -38,6 +38,9 @@ def lib():
             "moe_kv_commit": [P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
             "moe_attention_generic": [P, P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],
             "moe_router": [P, P, P, I, P, I, I, I, I, I, F, P, P, P, P, P],
+            "moe_router_logits": [P, P, P, I, I, I, I, P, P],
+            "moe_route_dispatch": [P, P, I, I, I, I, I, F, P, P, P, P, P, P, P, P, I, P, P],
+            "moe_rope_commit": [P, P, P, I, I, I, I, I, P, P, P, I, P, P, P, I, I, I, I, P, P],
             "moe_attention_decode": [P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],
             "moe_align": [P, I, I, I, P, P, P, P, P],
             "moe_swiglu": [P, P, I, LL, I, P],
@@ -338,3 +341,54 @@ def table_update(table, updates, n):
     if updates.numel() < 3 * n:
         raise KernelError("table_update: updates too short")
     _ok(lib().moe_table_update(_p(table), table.stride(0), _p(updates), n, _stream()), "table_update")
+
+
+def rope_commit(qkv, pos, inv_freq, nh, nkv, hd, rot, q, view, batch, status):
+    """Decode step: rotate, write the queries, and append keys and values straight into the
+    cache layer ``view`` (one launch instead of rope_split + kv_commit)."""
+    _chk(qkv, "qkv", torch.float32, 2), _chk(pos, "pos", torch.int32, 1)
+    g = view.group
+    T = qkv.shape[0]
+    if qkv.shape[1] != (nh + 2 * nkv) * hd or nkv != g.num_kv_heads or hd != g.head_dim or q.dtype != g.dtype:
+        raise KernelError("rope_commit: shapes or dtypes do not fit the cache")
+    if rot:
+        _chk(inv_freq, "inv_freq", torch.float32, 1)
+    _ok(lib().moe_rope_commit(_p(qkv), _p(pos), _p(inv_freq) if rot else None, T, nh, nkv, hd, rot, _p(q), _p(view.k),
+                              _p(view.v), _dt(q), _p(batch.seq_of_token), _p(batch.slots), _p(g.table),
+                              g.table.stride(0), g.ring, g.page_size, g.num_pages, _p(status), _stream()),
+        "rope_commit")
+
+
+def route_dispatch(h32, w_router, top_k, norm_topk, scale, *, shared_gate_w=None, seq_of_token=None, gather=None,
+                   status=None):
+    """Few tokens (<= 64) and <= 256 experts: router logits, then pick + table inversion + gather in
+    ONE more launch.  Returns (topk_idx, topk_w, shared_gate, offsets, sorted_token, pos_of_pair,
+    gathered) where ``gathered[p] = gather[sorted_token[p]]`` (or None)."""
+    _chk(h32, "h", torch.float32, 2), _chk(w_router, "router weight", dims=2)
+    T, H = h32.shape
+    E = w_router.shape[0]
+    dev = h32.device
+    rows = E + (1 if shared_gate_w is not None else 0)
+    logits = torch.empty((T, rows), dtype=torch.float32, device=dev)
+    _ok(lib().moe_router_logits(_p(h32), _p(w_router), _p(shared_gate_w), _dt(w_router), T, H, E, _p(logits),
+                                _stream()), "router_logits")
+    P_ = T * top_k
+    topk_idx = torch.empty((T, top_k), dtype=torch.int32, device=dev)
+    topk_w = torch.empty((T, top_k), dtype=torch.float32, device=dev)
+    sg = torch.empty((T,), dtype=torch.float32, device=dev) if shared_gate_w is not None else None
+    offsets = torch.empty((E + 1,), dtype=torch.int32, device=dev)
+    sorted_token = torch.empty((P_,), dtype=torch.int32, device=dev)
+    pos_of_pair = torch.empty((P_,), dtype=torch.int32, device=dev)
+    xs, row_bytes = None, 0
+    if gather is not None:
+        _chk(gather, "gather", dims=2)
+        row_bytes = gather.shape[1] * gather.element_size()
+        if row_bytes % 16:
+            gather = None
+        else:
+            xs = torch.empty((P_, gather.shape[1]), dtype=gather.dtype, device=dev)
+    _ok(lib().moe_route_dispatch(_p(logits), _p(seq_of_token), T, E, 1 if shared_gate_w is not None else 0, top_k,
+                                 1 if norm_topk else 0, float(scale), _p(topk_idx), _p(topk_w), _p(sg), _p(offsets),
+                                 _p(sorted_token), _p(pos_of_pair), _p(gather), _p(xs), row_bytes, _p(status),
+                                 _stream()), "route_dispatch")
+    return topk_idx, topk_w, sg, offsets, sorted_token, pos_of_pair, xs

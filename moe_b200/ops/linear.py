@@ -48,15 +48,16 @@ def swiglu_linear(rt, a: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
 
 
 def grouped_swiglu_linear(rt, a: torch.Tensor, w_gate_up: torch.Tensor, group_offsets: torch.Tensor,
-                          rows: torch.Tensor, num_rows: int) -> torch.Tensor:
+                          rows: torch.Tensor, num_rows: int, gathered: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Row i of the result is the SwiGLU of a[rows[i]] under the weights of i's group
-    (w_gate_up: [G, 2 I, K]); returns [num_rows, I] in the compute dtype."""
+    (w_gate_up: [G, 2 I, K]); returns [num_rows, I] in the compute dtype.  ``gathered`` may bring
+    a[rows] already gathered."""
     inter = w_gate_up.shape[1] // 2
     act = torch.empty((num_rows, inter), dtype=rt.compute_dtype, device=a.device)
     if _use_tc(rt, a, w_gate_up) and a.shape[1] % 8 == 0:
         from . import tc
 
-        xs = tc.gather_rows(a, rows, num_rows, rt.status)
+        xs = gathered if gathered is not None else tc.gather_rows(a, rows, num_rows, rt.status)
         if tc.gemm_tc(xs, w_gate_up, act, swiglu=True, group_offsets=group_offsets, status=rt.status):
             return act
     gu = torch.empty((num_rows, 2 * inter), dtype=torch.float32, device=a.device)

@@ -66,10 +66,20 @@ _workspaces = {}
 
 
 def workspace(device) -> Workspace:
-    key = torch.device(device).index or 0
+    """The scratch of the calling stream: products on the side stream (``Runtime.side_stream``)
+    have a workspace of their own, since they may run beside products on the main stream."""
+    side = torch.cuda.current_stream(device) in _side_streams
+    key = (torch.device(device).index or 0, side)
     if key not in _workspaces:
         _workspaces[key] = Workspace(device)
     return _workspaces[key]
+
+
+_side_streams = set()
+
+
+def register_side_stream(stream) -> None:
+    _side_streams.add(stream)
 
 
 def token_tile(rows_per_group: float) -> int:
@@ -104,9 +114,14 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swiglu: bool
     n_tiles = -(-N // 128)
     gy = c_int(0)
     if splits is None:
-        # enough CTAs to keep every SM streaming: aim at two waves' worth at most
-        tiles = n_tiles * (max(1, -(-M // bn)) if not grouped else max(1, min(G, M)))
-        splits = max(1, min(16, (2 * num_sms(x.device)) // max(tiles, 1), -(-K // 64) // 4))
+        if bn > 64:
+            # many tokens: the product is bound by the tensor cores and by L2, and the split-K
+            # merge (one CTA re-reading every partial tile) costs more than it gains
+            splits = 1
+        else:
+            # few tokens: the weight stream bounds the time; enough CTAs to keep every SM loading
+            tiles = n_tiles * (max(1, -(-M // bn)) if not grouped else max(1, min(G, M)))
+            splits = max(1, min(16, (2 * num_sms(x.device)) // max(tiles, 1), -(-K // 64) // 4))
     splits = L.moe_gemm_tc_plan(K, int(splits), M, bn, G, 1 if grouped else 0, core.ctypes.byref(gy))
     partials = tickets = None
     if splits > 1:

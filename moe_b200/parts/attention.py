@@ -85,17 +85,22 @@ class GQAttention(Part):
         nkv = self.nkv if self.own_kv else 0
         qkv = linear(rt, h.act, self.wqkv, bias=self.bqkv)
         q = rt.empty((T, self.nh, self.hd))
-        k_new = rt.empty((T, max(nkv, 1), self.hd))
-        v_new = rt.empty((T, max(nkv, 1), self.hd))
         table, rot = self.position.rotary_table()
         if table is None and hasattr(self.position, "apply"):
             self.position.apply(rt, qkv, self.nh, nkv, self.hd, batch.pos)
-        core.rope_split(qkv, batch.pos, table, self.nh, nkv, self.hd, rot, q, k_new, v_new)
         ctx = rt.empty((T, self.nh * self.hd))
+        if batch.all_decode and self.own_kv:
+            # one token per sequence: rotate and append in one launch, then attend over the cache
+            # alone, split along the keys
+            core.rope_commit(qkv, batch.pos, table, self.nh, nkv, self.hd, rot, q, cache_view, batch, rt.status)
+            core.attention_decode(q, cache_view, batch, ctx, nh=self.nh, window=self.window, scale=self.scale,
+                                  status=rt.status)
+            return linear(rt, ctx, self.wo)
+        k_new = rt.empty((T, max(nkv, 1), self.hd))
+        v_new = rt.empty((T, max(nkv, 1), self.hd))
+        core.rope_split(qkv, batch.pos, table, self.nh, nkv, self.hd, rot, q, k_new, v_new)
         if batch.all_decode:
-            # one token per sequence: append first, then attend over the cache alone, split along the keys
-            if self.own_kv:
-                core.kv_commit(k_new, v_new, cache_view, batch, rt.status)
+            # a layer that reads another layer's cache: queries only
             core.attention_decode(q, cache_view, batch, ctx, nh=self.nh, window=self.window, scale=self.scale,
                                   status=rt.status)
         else:

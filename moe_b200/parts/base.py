@@ -49,6 +49,15 @@ class Runtime:
     def is_bf16(self) -> bool:
         return self.compute_dtype == torch.bfloat16
 
+    def side_stream(self) -> "torch.cuda.Stream":
+        """A second stream of this runtime, for a branch that may run beside the main one."""
+        if getattr(self, "_side", None) is None:
+            from ..ops import tc
+
+            self._side = torch.cuda.Stream(device=self.device)
+            tc.register_side_stream(self._side)     # its products get a split-K workspace of their own
+        return self._side
+
     def empty(self, shape, dtype=None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.compute_dtype, device=self.device)
 

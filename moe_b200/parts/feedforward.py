@@ -115,21 +115,44 @@ class RoutedExperts(Part):
                     shared_gate_w=self.w_sgate, shared_gate=sg, seq_of_token=getattr(batch, "seq_of_token", None))
         return topk_idx, topk_w, sg
 
+    def _shared(self, rt, h):
+        return linear(rt, swiglu_linear(rt, h.act, self.ws_gu), self.ws_down)
+
     def forward(self, rt, h, batch):
         T = h.act.shape[0]
-        topk_idx, topk_w, sg = self.route(rt, h, batch)
+        P = T * self.k
+        few = T <= 64 and self.E <= 256
+        ys = side = None
+        if self.ws_gu is not None and few:
+            # few tokens: neither branch fills the GPU, so the shared expert runs beside the routed
+            # ones on a second stream (inside a captured graph this becomes a fork and a join)
+            main = torch.cuda.current_stream()
+            side = rt.side_stream()
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                ys = self._shared(rt, h)
+        if few:
+            # pick, table inversion and gather in one launch after the logits
+            topk_idx, topk_w, sg, offsets, sorted_token, pos_of_pair, xs = core.route_dispatch(
+                h.f32, self.w_router, self.k, self.norm_topk, self.scale, shared_gate_w=self.w_sgate,
+                seq_of_token=getattr(batch, "seq_of_token", None),
+                gather=h.act if h.act.dtype == torch.bfloat16 else None, status=rt.status)
+        else:
+            topk_idx, topk_w, sg = self.route(rt, h, batch)
+            offsets = rt.empty((self.E + 1,), torch.int32)
+            sorted_token = rt.empty((P,), torch.int32)
+            pos_of_pair = rt.empty((P,), torch.int32)
+            core.moe_align(topk_idx, T, self.k, self.E, offsets, sorted_token, pos_of_pair, rt.status)
+            xs = None
         if self.trace is not None:
             self.trace.append((topk_idx.clone(), topk_w.clone()))
-        P = T * self.k
-        offsets = rt.empty((self.E + 1,), torch.int32)
-        sorted_token = rt.empty((P,), torch.int32)
-        pos_of_pair = rt.empty((P,), torch.int32)
-        core.moe_align(topk_idx, T, self.k, self.E, offsets, sorted_token, pos_of_pair, rt.status)
-        act = grouped_swiglu_linear(rt, h.act, self.w_gu, offsets, sorted_token, P)
+        act = grouped_swiglu_linear(rt, h.act, self.w_gu, offsets, sorted_token, P, gathered=xs)
         y = grouped_linear(rt, act, self.w_down, offsets, P)
-        ys = None
-        if self.ws_gu is not None:
-            ys = linear(rt, swiglu_linear(rt, h.act, self.ws_gu), self.ws_down)
+        if self.ws_gu is not None and side is None:
+            ys = self._shared(rt, h)
+        if side is not None:
+            torch.cuda.current_stream().wait_stream(side)
+            ys.record_stream(torch.cuda.current_stream())
         out = rt.empty((T, self.hidden), torch.float32)
         core.moe_combine(y, pos_of_pair, topk_w, self.k, out, shared=ys, shared_gate=sg)
         return out

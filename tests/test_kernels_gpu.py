@@ -207,8 +207,8 @@ def test_attention_over_cache_and_new_keys(core, dt, nh, nkv, hd, window):
 @pytest.mark.parametrize("E,k,H,norm,scale", [(10, 3, 72, True, 1.0), (60, 4, 200, False, 1.0), (7, 7, 33, True, 2.5),
                                                (130, 8, 64, False, 0.5)])
 @pytest.mark.parametrize("wdt", [torch.float32, torch.bfloat16])
-def test_router_and_shared_gate(core, E, k, H, norm, scale, wdt):
-    T = 29
+@pytest.mark.parametrize("T", [29, 150])              # few tokens and many: two kernels
+def test_router_and_shared_gate(core, E, k, H, norm, scale, wdt, T):
     h = torch.randn(T, H, device=DEV)
     wr = torch.randn(E, H, device=DEV).to(wdt)
     wsg = torch.randn(H, device=DEV).to(wdt)
