@@ -247,6 +247,43 @@ def run_ours(args):
     return 0
 
 
+def profile_step(args):
+    """A small case for a profiler: the model's layer sizes, few layers, graphs off (every kernel is
+    a launch of its own); only the steps between cudaProfilerStart and cudaProfilerStop matter."""
+    import torch
+
+    import moe_b200
+
+    cfg = dict(A27B)
+    cfg["num_hidden_layers"] = args.layers or 2
+    model = moe_b200.random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+    V = cfg["vocab_size"]
+    if args.profile_step == "decode":
+        B = args.batch
+        eng = moe_b200.Engine(model, max_tokens=B * 1024, max_slots=B, use_graphs=False)
+        slots = [eng.new_sequence() for _ in range(B)]
+        eng.step(slots, [[(i * 7 + 31 * b) % V for i in range(PROMPT_LEN)] for b in range(B)], [[] for _ in slots])
+        run = lambda i: eng.step(slots, [[(i * 13 + 7 * b) % V] for b in range(B)])
+    else:
+        eng = moe_b200.Engine(model, max_tokens=PREFILL_TOKENS + 64, max_slots=1, use_graphs=False)
+        ids = [(i * 7 + 13) % V for i in range(PREFILL_TOKENS)]
+
+        def run(i):
+            s = eng.new_sequence()
+            eng.step([s], [ids])
+            eng.release(s)
+    for i in range(3):
+        run(i)
+    torch.cuda.synchronize()
+    torch.cuda.cudart().cudaProfilerStart()
+    for i in range(max(1, min(args.steps, 2))):
+        run(3 + i)
+    torch.cuda.synchronize()
+    torch.cuda.cudart().cudaProfilerStop()
+    print(f"profiled {args.profile_step} step(s)")
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -254,6 +291,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (reported in config)")
+    ap.add_argument("--profile-step", choices=["decode", "prefill"], default=None,
+                    help="run a few steps of one kind between cudaProfilerStart/Stop (for ncu "
+                         "--profile-from-start off) and print no benchmark line")
+    ap.add_argument("--batch", type=int, default=8, help="with --profile-step decode: sequences in the batch")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "JGalego/Moe is a Rust crate (no Python package, "
@@ -263,6 +304,8 @@ def main():
         print("bench.py: moe_b200 is a single-GPU library; --gpus must be 1")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.profile_step:
+        return profile_step(args)
     return run_ours(args)
 
 
