@@ -71,6 +71,7 @@ attn_decode_fast_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
     constexpr int NI = LPR;                // load instructions per tile of 32 rows
     constexpr int REC = HD + 2;
     __shared__ float red[WARPS][GH][REC];
+    pdl_sync();
 
     const int split = blockIdx.x, nsplit = gridDim.x, kvh = blockIdx.y, t = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -225,6 +226,7 @@ attn_decode_rows_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
                         const int* __restrict__ tables, int table_stride, int ring, int page_size, int num_pages,
                         int nh, int nkv, int hd, int window, float scale, int* status) {
     extern __shared__ float sm[];
+    pdl_sync();
     const int split = blockIdx.x, nsplit = gridDim.x, kvh = blockIdx.y, t = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int group = nh / nkv;
@@ -355,6 +357,7 @@ attn_decode_rows_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
 template <typename T>
 __global__ void attn_decode_merge_kernel(const float* __restrict__ partial, T* __restrict__ out,
                                          const int* __restrict__ seq_of_token, int nh, int hd, int nsplit) {
+    pdl_sync();
     const int t = blockIdx.x, h = blockIdx.y;
     const int rec = hd + 2;
     T* o = out + ((size_t)t * nh + h) * hd;
@@ -391,9 +394,9 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, f
     const bool fast = page_size % 32 == 0 && (ring % 32 == 0) &&
                       (row_bytes == 64 || row_bytes == 128 || row_bytes == 256 || row_bytes == 512);
 #define FAST(LPR, GH)                                                                                          \
-    attn_decode_fast_kernel<T, LPR, GH><<<grid, WARPS * 32, 0, stream>>>(                                      \
-        (const T*)q, (const T*)k_cache, (const T*)v_cache, partial, seq_of_token, pos, slots, tables, table_stride, \
-        ring, page_size, num_pages, nh, nkv, window, scale, status)
+    launch_pdl(attn_decode_fast_kernel<T, LPR, GH>, grid, WARPS * 32, 0, stream, (const T*)q, (const T*)k_cache, \
+               (const T*)v_cache, partial, seq_of_token, pos, slots, tables, table_stride, ring, page_size,      \
+               num_pages, nh, nkv, window, scale, status)
 #define FAST_G(LPR)                  \
     do {                             \
         if (group == 1)              \
@@ -410,14 +413,14 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, f
         }
     } else {
         const size_t smem = ((size_t)GHS * hd + (size_t)WARPS * GHS * (hd + 2)) * sizeof(float);
-        attn_decode_rows_kernel<T><<<grid, WARPS * 32, smem, stream>>>(
-            (const T*)q, (const T*)k_cache, (const T*)v_cache, partial, seq_of_token, pos, slots, tables, table_stride,
-            ring, page_size, num_pages, nh, nkv, hd, window, scale, status);
+        launch_pdl(attn_decode_rows_kernel<T>, grid, WARPS * 32, smem, stream, (const T*)q, (const T*)k_cache,
+                   (const T*)v_cache, partial, seq_of_token, pos, slots, tables, table_stride, ring, page_size,
+                   num_pages, nh, nkv, hd, window, scale, status);
     }
 #undef FAST
 #undef FAST_G
-    attn_decode_merge_kernel<T><<<dim3(num_tokens, nh), 128, 0, stream>>>(partial, (T*)out, seq_of_token, nh, hd, nsplit);
-    return launch_status();
+    return launch_pdl(attn_decode_merge_kernel<T>, dim3(num_tokens, nh), 128, 0, stream, (const float*)partial, (T*)out,
+                      seq_of_token, nh, hd, nsplit);
 }
 
 }  // namespace

@@ -61,6 +61,44 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 
 static inline int launch_status() { return (int)cudaGetLastError(); }
 
+// ---- programmatic dependent launch ------------------------------------------------------
+// A decode step is a chain of short kernels.  Launched with the programmatic-serialization
+// attribute, a kernel may be scheduled while its predecessor in the stream is still running;
+// it must then call pdl_wait() before it reads anything the predecessor wrote or writes
+// anything the predecessor may still read (the wait returns once the predecessor grid has
+// completed and its memory operations are visible).  pdl_launch_dependents() lets the NEXT
+// kernel be scheduled early in the same way.  Both are no-ops for a kernel launched normally.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// The usual opening of a kernel in the chain: wait for the predecessor, then let the successor
+// be scheduled.  In this order only ONE successor is ever resident ahead of the running kernel;
+// releasing the successor before the wait lets the whole chain pile up on the SMs as waiting
+// CTAs, which takes room from a running kernel that needs several waves.
+__device__ __forceinline__ void pdl_sync() {
+    pdl_wait();
+    pdl_launch_dependents();
+}
+
+// One switch per shared library (set through moe_set_pdl / moe_tc_set_pdl).
+inline int g_pdl_enabled = 1;
+
+// Launch `kernel` with the attribute (if enabled).  ONLY for kernels that call pdl_wait().
+template <typename... KArgs, typename... Args>
+static inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_pdl_enabled ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Logical position -> (page, offset) of a paged, optionally ring-shaped, cache.
 //   ring:  positions wrap at `ring` (a multiple of the page size); 0 = no wrap
 //   table: the sequence's page list; page p holds `page_size` consecutive positions

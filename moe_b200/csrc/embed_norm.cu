@@ -11,6 +11,7 @@
 template <typename WT>
 __global__ void embed_kernel(const WT* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ x,
                              int hidden, int vocab, int* status) {
+    pdl_sync();
     const int t = blockIdx.x;
     int tok = tokens[t];
     if (tok < 0 || tok >= vocab) {
@@ -27,11 +28,10 @@ MOE_API int moe_embed(const void* table, int table_dt, const int* tokens, float*
     if (num_tokens <= 0) return 0;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (table_dt == DT_F32)
-        embed_kernel<float><<<num_tokens, threads, 0, stream>>>((const float*)table, tokens, x, hidden, vocab, status);
-    else
-        embed_kernel<__nv_bfloat16>
-            <<<num_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, tokens, x, hidden, vocab, status);
-    return launch_status();
+        return launch_pdl(embed_kernel<float>, num_tokens, threads, 0, stream, (const float*)table, tokens, x, hidden,
+                          vocab, status);
+    return launch_pdl(embed_kernel<__nv_bfloat16>, num_tokens, threads, 0, stream, (const __nv_bfloat16*)table, tokens,
+                      x, hidden, vocab, status);
 }
 
 // One block per output row i.  Source row r = rows ? rows[i] : i.
@@ -44,6 +44,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
                                int num_src_rows, int* status) {
     extern __shared__ float row[];
     __shared__ float red[32];
+    pdl_sync();
     const int i = blockIdx.x;
     int r = rows ? rows[i] : i;
     if (r < 0 || r >= num_src_rows) {
@@ -82,10 +83,12 @@ MOE_API int moe_rmsnorm(float* x, const float* delta, const float* w, const int*
         cudaError_t e = cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    rmsnorm_kernel<<<num_out_rows, threads, smem, stream>>>(x, delta, w, rows, out32, (__nv_bfloat16*)out16, hidden,
-                                                           eps, write_back, num_src_rows, status);
-    return launch_status();
+    return launch_pdl(rmsnorm_kernel, num_out_rows, threads, smem, stream, x, delta, w, rows, out32,
+                      (__nv_bfloat16*)out16, hidden, eps, write_back, num_src_rows, status);
 }
+
+// Programmatic dependent launch on or off for every kernel of this library (on by default).
+MOE_API void moe_set_pdl(int enabled) { g_pdl_enabled = enabled ? 1 : 0; }
 
 // out[i] = a[i] + b[i] (32-bit residual sum where no norm follows).
 __global__ void add_kernel(float* __restrict__ a, const float* __restrict__ b, size_t n) {

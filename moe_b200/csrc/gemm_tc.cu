@@ -173,6 +173,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     const int n0 = blockIdx.x * TILE_W;
     const int split = blockIdx.z;
 
+    // Programmatic dependent launch: this kernel may have been scheduled while its predecessor
+    // still runs.  Weights never depend on the predecessor, so an ungrouped product sets itself up
+    // and starts streaming its weight tiles before it waits (in the producer, below); a grouped one
+    // needs the group offsets the predecessor wrote, and waits here.
+    const bool grouped = p.group_offsets != nullptr;
+    if (grouped) pdl_sync();
+
     // ---- which rows of X this CTA owns -------------------------------------------------
     // (the offsets are fetched by all threads at once: a scan straight from global memory would
     // pay one memory latency per group)
@@ -238,7 +245,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         if (lane == 0) {
             int issued = 0;
             bool ok = true;
-            for (int kb = kb0; kb < kb1 && ok; kb++, issued++) {
+            int kb_next = kb0;
+            if (!grouped) {
+                // weight tiles of the first stages, then wait for the predecessor, then their activations
+                const int pre = min(C::STAGES, kb1 - kb0);
+                for (int i = 0; i < pre; i++) {
+                    const uint32_t st = base + i * C::STAGE_BYTES;
+                    mbar_expect_tx(full_bar(i), C::STAGE_BYTES);
+                    tma_load_2d(st, &tmW, (kb0 + i) * BK, w_row, full_bar(i));
+                    if (MODE == MODE_SWIGLU) tma_load_2d(st + C::W_BYTES, &tmW, (kb0 + i) * BK, w_row + p.N, full_bar(i));
+                }
+                pdl_sync();
+                for (int i = 0; i < pre; i++)
+                    tma_load_2d(base + i * C::STAGE_BYTES + C::NW * C::W_BYTES, &tmX, (kb0 + i) * BK, row0, full_bar(i));
+                issued = pre;
+                kb_next = kb0 + pre;
+            }
+            for (int kb = kb_next; kb < kb1 && ok; kb++, issued++) {
                 const int s = issued % C::STAGES;
                 const uint32_t ph = (issued / C::STAGES) & 1;
                 ok = mbar_wait(empty_bar(s), ph ^ 1, &s_abort);
@@ -428,8 +451,7 @@ int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& p, dim3
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    gemm_tc_kernel<BN, MODE><<<grid, 192, C::SMEM, stream>>>(tmW, tmX, p);
-    return launch_status();
+    return launch_pdl(gemm_tc_kernel<BN, MODE>, grid, dim3(192), (size_t)C::SMEM, stream, tmW, tmX, p);
 }
 
 }  // namespace
@@ -472,6 +494,9 @@ MOE_API int moe_gemm_tc(const void* X, int ldx, const void* W, int num_groups, i
 #undef GO
     return -1;
 }
+
+// Programmatic dependent launch on or off for the kernels of this library (on by default).
+MOE_API void moe_tc_set_pdl(int enabled) { g_pdl_enabled = enabled ? 1 : 0; }
 
 // How many K splits the kernel will really use for (K, splits asked), and its grid.y for tickets.
 MOE_API int moe_gemm_tc_plan(int K, int splits, int M, int bn, int num_groups, int grouped, int* grid_y) {

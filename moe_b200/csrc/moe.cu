@@ -44,6 +44,7 @@ router_logits_kernel(const float* __restrict__ h, const WT* __restrict__ wr, con
                      int num_tokens, int hidden, int num_experts, int rows, int vec_ok,
                      float* __restrict__ logits) {
     __shared__ float part[ROWS][KSPLIT][TOK_TILE];
+    pdl_sync();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rr = warp / KSPLIT, ks = warp % KSPLIT;
     const int r = blockIdx.x * ROWS + rr;
@@ -279,6 +280,7 @@ route_dispatch_kernel(const float* __restrict__ logits, const int* __restrict__ 
                       int* __restrict__ sorted_token, int* __restrict__ pos_of_pair, const uint4* __restrict__ x,
                       uint4* __restrict__ xs, int row_units, int* status) {
     extern __shared__ float dyn[];   // 32 warps x num_experts floats, then counts[E], cursor[E]
+    pdl_sync();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int t = warp; t < num_tokens; t += 32)
         route_token(logits + (size_t)t * rows, dyn + (size_t)warp * num_experts, lane,
@@ -315,6 +317,7 @@ __global__ void swiglu_kernel(const float* __restrict__ gu, OT* __restrict__ act
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos_of_pair,
                                    const float* __restrict__ topk_w, int top_k, const float* __restrict__ shared,
                                    const float* __restrict__ shared_gate, float* __restrict__ out, int hidden) {
+    pdl_sync();
     const int t = blockIdx.x;
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
         float acc = 0.f;
@@ -345,8 +348,8 @@ MOE_API int moe_router_logits(const float* h, const void* wr, const void* wsg, i
     const int ty = (num_tokens + TOK_TILE - 1) / TOK_TILE;
     if (ty > 65535) return (int)cudaErrorInvalidValue;
 #define LOGITS(WT, ROWS, KSPLIT)                                                                          \
-    router_logits_kernel<WT, ROWS, KSPLIT><<<dim3((rows + ROWS - 1) / ROWS, ty), ROWS * KSPLIT * 32, 0, stream>>>( \
-        h, (const WT*)wr, (const WT*)wsg, num_tokens, hidden, num_experts, rows, vec_ok, logits)
+    launch_pdl(router_logits_kernel<WT, ROWS, KSPLIT>, dim3((rows + ROWS - 1) / ROWS, ty), ROWS * KSPLIT * 32, 0,   \
+               stream, h, (const WT*)wr, (const WT*)wsg, num_tokens, hidden, num_experts, rows, vec_ok, logits)
     if (num_tokens <= 64) {
         if (w_dt == DT_F32) LOGITS(float, 2, 4); else LOGITS(__nv_bfloat16, 2, 4);
     } else if (vec_ok && (num_tokens + PT - 1) / PT <= 65535) {
@@ -400,11 +403,9 @@ MOE_API int moe_route_dispatch(const float* logits, const int* seq_of_token, int
     if (num_tokens > 64 || num_experts > 256 || top_k <= 0 || top_k > num_experts || row_bytes % 16)
         return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)32 * num_experts * sizeof(float) + (size_t)2 * num_experts * sizeof(int);
-    route_dispatch_kernel<<<1, 1024, smem, stream>>>(logits, seq_of_token, num_tokens, num_experts,
-                                                    num_experts + (has_gate_row ? 1 : 0), top_k, norm_topk, scale,
-                                                    topk_idx, topk_w, shared_gate, offsets, sorted_token, pos_of_pair,
-                                                    (const uint4*)x, (uint4*)xs, row_bytes / 16, status);
-    return launch_status();
+    return launch_pdl(route_dispatch_kernel, 1, 1024, smem, stream, logits, seq_of_token, num_tokens, num_experts,
+                      num_experts + (has_gate_row ? 1 : 0), top_k, norm_topk, scale, topk_idx, topk_w, shared_gate,
+                      offsets, sorted_token, pos_of_pair, (const uint4*)x, (uint4*)xs, row_bytes / 16, status);
 }
 
 MOE_API int moe_swiglu(const float* gu, void* act, int out_dt, long long rows, int inter, cudaStream_t stream) {
@@ -421,7 +422,6 @@ MOE_API int moe_swiglu(const float* gu, void* act, int out_dt, long long rows, i
 MOE_API int moe_combine(const float* y, const int* pos_of_pair, const float* topk_w, int top_k, const float* shared,
                         const float* shared_gate, float* out, int num_tokens, int hidden, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
-    moe_combine_kernel<<<num_tokens, 256, 0, stream>>>(y, pos_of_pair, topk_w, top_k, shared, shared_gate, out,
-                                                      hidden);
-    return launch_status();
+    return launch_pdl(moe_combine_kernel, num_tokens, 256, 0, stream, y, pos_of_pair, topk_w, top_k, shared,
+                      shared_gate, out, hidden);
 }

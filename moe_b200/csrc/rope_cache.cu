@@ -106,6 +106,7 @@ MOE_API int moe_kv_commit(const void* k_new, const void* v_new, void* k_cache, v
 
 // Page-table maintenance: table[slot][index] = page for n (slot, index, page) triples.
 __global__ void table_update_kernel(int* __restrict__ table, int stride, const int* __restrict__ upd, int n) {
+    pdl_sync();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) table[(size_t)upd[3 * i] * stride + upd[3 * i + 1]] = upd[3 * i + 2];
 }
@@ -119,6 +120,7 @@ __global__ void rope_commit_kernel(const float* __restrict__ qkv, const int* __r
                                    const int* __restrict__ seq_of_token, const int* __restrict__ slots,
                                    const int* __restrict__ tables, int table_stride, int ring, int page_size,
                                    int num_pages, int* status) {
+    pdl_sync();
     const int t = blockIdx.x;
     const int width = (nh + 2 * nkv) * hd;
     const float* src = qkv + (size_t)t * width;
@@ -175,18 +177,15 @@ MOE_API int moe_rope_commit(const float* qkv, const int* pos, const float* inv_f
     if (rot < 0 || rot > hd || (rot & 1)) return (int)cudaErrorInvalidValue;
     if (rot > 0 && !inv_freq) return (int)cudaErrorInvalidValue;
     if (dt == DT_F32)
-        rope_commit_kernel<float><<<num_tokens, 256, 0, stream>>>(
-            qkv, pos, inv_freq, nh, nkv, hd, rot, (float*)q, (float*)k_cache, (float*)v_cache, seq_of_token, slots,
-            tables, table_stride, ring, page_size, num_pages, status);
-    else
-        rope_commit_kernel<__nv_bfloat16><<<num_tokens, 256, 0, stream>>>(
-            qkv, pos, inv_freq, nh, nkv, hd, rot, (__nv_bfloat16*)q, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
-            seq_of_token, slots, tables, table_stride, ring, page_size, num_pages, status);
-    return launch_status();
+        return launch_pdl(rope_commit_kernel<float>, num_tokens, 256, 0, stream, qkv, pos, inv_freq, nh, nkv, hd, rot,
+                          (float*)q, (float*)k_cache, (float*)v_cache, seq_of_token, slots, tables, table_stride, ring,
+                          page_size, num_pages, status);
+    return launch_pdl(rope_commit_kernel<__nv_bfloat16>, num_tokens, 256, 0, stream, qkv, pos, inv_freq, nh, nkv, hd,
+                      rot, (__nv_bfloat16*)q, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, seq_of_token, slots,
+                      tables, table_stride, ring, page_size, num_pages, status);
 }
 
 MOE_API int moe_table_update(int* table, int stride, const int* upd, int n, cudaStream_t stream) {
     if (n <= 0) return 0;
-    table_update_kernel<<<(n + 127) / 128, 128, 0, stream>>>(table, stride, upd, n);
-    return launch_status();
+    return launch_pdl(table_update_kernel, (n + 127) / 128, 128, 0, stream, table, stride, upd, n);
 }

@@ -7,6 +7,7 @@ library that cannot be built raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional
 
@@ -53,6 +54,10 @@ def lib():
             fn = getattr(L, name)
             fn.argtypes = argtypes
             fn.restype = c_int
+        L.moe_set_pdl.argtypes = [c_int]
+        L.moe_set_pdl.restype = None
+        if os.environ.get("MOE_B200_PDL", "1") == "0":      # programmatic dependent launch off
+            L.moe_set_pdl(0)
         _lib = L
     return _lib
 

@@ -32,6 +32,12 @@ def lib():
 
         L.moe_attention_prefill_bf16.argtypes = [P, P, P, P, P, I, I, I, I, I, I, c_float, P]
         L.moe_attention_prefill_bf16.restype = c_int
+        L.moe_tc_set_pdl.argtypes = [c_int]
+        L.moe_tc_set_pdl.restype = None
+        import os
+
+        if os.environ.get("MOE_B200_PDL", "1") == "0":      # programmatic dependent launch off
+            L.moe_tc_set_pdl(0)
         _lib = L
     return _lib
 
