@@ -316,18 +316,53 @@ __global__ void swiglu_kernel(const float* __restrict__ gu, OT* __restrict__ act
 // One block per token: out[t] = sum_j w[t, j] * y[pos_of_pair[t k + j]] + g[t] * shared[t]
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos_of_pair,
                                    const float* __restrict__ topk_w, int top_k, const float* __restrict__ shared,
-                                   const float* __restrict__ shared_gate, float* __restrict__ out, int hidden) {
+                                   const float* __restrict__ shared_gate, float* __restrict__ out, int hidden,
+                                   int vec) {
+    extern __shared__ int pick[];   // pos[top_k], then weight[top_k]
     pdl_sync();
     const int t = blockIdx.x;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    int* sp = pick;
+    float* sw = reinterpret_cast<float*>(pick + top_k);
+    for (int j = threadIdx.x; j < top_k; j += blockDim.x) {
+        sp[j] = pos_of_pair[(size_t)t * top_k + j];
+        sw[j] = topk_w[(size_t)t * top_k + j];
+    }
+    const float g = shared_gate ? shared_gate[t] : 1.0f;
+    __syncthreads();
+    const int first = blockIdx.y * blockDim.x + threadIdx.x, step = gridDim.y * blockDim.x;
+    if (vec) {   // four columns per thread, 16-byte accesses
+        for (int c4 = first; c4 < hidden / 4; c4 += step) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+            for (int j = 0; j < top_k; j++) {
+                const int p = sp[j];
+                if (p >= 0) {
+                    const float4 v = *reinterpret_cast<const float4*>(y + (size_t)p * hidden + 4 * c4);
+                    const float w = sw[j];
+                    acc.x = fmaf(w, v.x, acc.x), acc.y = fmaf(w, v.y, acc.y);
+                    acc.z = fmaf(w, v.z, acc.z), acc.w = fmaf(w, v.w, acc.w);
+                }
+            }
+            if (shared) {
+                const float4 s = *reinterpret_cast<const float4*>(shared + (size_t)t * hidden + 4 * c4);
+                if (shared_gate)
+                    acc.x += g * s.x, acc.y += g * s.y, acc.z += g * s.z, acc.w += g * s.w;
+                else
+                    acc.x += s.x, acc.y += s.y, acc.z += s.z, acc.w += s.w;
+            }
+            *reinterpret_cast<float4*>(out + (size_t)t * hidden + 4 * c4) = acc;
+        }
+        return;
+    }
+    for (int c = first; c < hidden; c += step) {
         float acc = 0.f;
         for (int j = 0; j < top_k; j++) {
-            const int p = pos_of_pair[(size_t)t * top_k + j];
-            if (p >= 0) acc = fmaf(topk_w[(size_t)t * top_k + j], y[(size_t)p * hidden + c], acc);
+            const int p = sp[j];
+            if (p >= 0) acc = fmaf(sw[j], y[(size_t)p * hidden + c], acc);
         }
         if (shared) {
             const float s = shared[(size_t)t * hidden + c];
-            acc += shared_gate ? shared_gate[t] * s : s;
+            acc += shared_gate ? g * s : s;
         }
         out[(size_t)t * hidden + c] = acc;
     }
@@ -422,6 +457,11 @@ MOE_API int moe_swiglu(const float* gu, void* act, int out_dt, long long rows, i
 MOE_API int moe_combine(const float* y, const int* pos_of_pair, const float* topk_w, int top_k, const float* shared,
                         const float* shared_gate, float* out, int num_tokens, int hidden, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
-    return launch_pdl(moe_combine_kernel, num_tokens, 256, 0, stream, y, pos_of_pair, topk_w, top_k, shared,
-                      shared_gate, out, hidden);
+    if (top_k < 0 || top_k > 4096) return (int)cudaErrorInvalidValue;
+    const int vec = hidden % 4 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)out % 16 == 0 &&
+                    (!shared || (uintptr_t)shared % 16 == 0);
+    const int units = vec ? hidden / 4 : hidden;
+    const int by = max(1, min(64, (units + 127) / 128));
+    return launch_pdl(moe_combine_kernel, dim3(num_tokens, by), 128, (size_t)top_k * 8, stream, y, pos_of_pair, topk_w,
+                      top_k, shared, shared_gate, out, hidden, vec);
 }

@@ -132,11 +132,14 @@ __global__ void rope_commit_kernel(const float* __restrict__ qkv, const int* __r
     cp.page = 0, cp.off = 0;
     if (s >= 0) cp = cache_pos(p_int, ring, tables + (size_t)slots[s] * table_stride, page_size, num_pages, status);
     const int rot_heads = nh + nkv;
+    // the token's angles once (all heads share them): cos[half], sin[half]
+    extern __shared__ float angle_tab[];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(p * inv_freq[i], &angle_tab[half + i], &angle_tab[i]);
+    __syncthreads();
     for (int idx = threadIdx.x; idx < rot_heads * half; idx += blockDim.x) {
         const int h = idx / half, i = idx % half;
         const float* sp = src + (size_t)h * hd;
-        float sn, cs;
-        sincosf(p * inv_freq[i], &sn, &cs);
+        const float cs = angle_tab[i], sn = angle_tab[half + i];
         const float a = sp[i], b = sp[i + half];
         OT* dst;
         if (h < nh) {
@@ -176,11 +179,13 @@ MOE_API int moe_rope_commit(const float* qkv, const int* pos, const float* inv_f
     if (num_tokens <= 0) return 0;
     if (rot < 0 || rot > hd || (rot & 1)) return (int)cudaErrorInvalidValue;
     if (rot > 0 && !inv_freq) return (int)cudaErrorInvalidValue;
+    if (rot > 8192) return (int)cudaErrorInvalidValue;
+    const size_t smem = (size_t)rot * sizeof(float);
     if (dt == DT_F32)
-        return launch_pdl(rope_commit_kernel<float>, num_tokens, 256, 0, stream, qkv, pos, inv_freq, nh, nkv, hd, rot,
-                          (float*)q, (float*)k_cache, (float*)v_cache, seq_of_token, slots, tables, table_stride, ring,
-                          page_size, num_pages, status);
-    return launch_pdl(rope_commit_kernel<__nv_bfloat16>, num_tokens, 256, 0, stream, qkv, pos, inv_freq, nh, nkv, hd,
+        return launch_pdl(rope_commit_kernel<float>, num_tokens, 512, smem, stream, qkv, pos, inv_freq, nh, nkv, hd,
+                          rot, (float*)q, (float*)k_cache, (float*)v_cache, seq_of_token, slots, tables, table_stride,
+                          ring, page_size, num_pages, status);
+    return launch_pdl(rope_commit_kernel<__nv_bfloat16>, num_tokens, 512, smem, stream, qkv, pos, inv_freq, nh, nkv, hd,
                       rot, (__nv_bfloat16*)q, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, seq_of_token, slots,
                       tables, table_stride, ring, page_size, num_pages, status);
 }
