@@ -174,6 +174,15 @@ def run_ours(args):
         kv = B * mean_len * nums["kv_bytes_per_token_layer"] * layers
         return weights + kv
 
+    if args.sweep:
+        # decode only, one line per batch size (not the benchmark record)
+        for b in [int(v) for v in args.sweep.split(",")]:
+            m, _, _, mean_len, uniq, _ = decode_run(b, max(8, args.steps // 2), args.warmup)
+            gbs = decode_bytes(b, mean_len, uniq) / (m / 1e3) / 1e9
+            print(json.dumps({"batch": b, "ms_per_step": round(m, 4), "tokens_per_s": round(b / (m / 1e3), 1),
+                              "hbm_frac": round(gbs / pk["hbm_gbs"], 4)}))
+        return 0
+
     # ---- headline: batch 8 ---------------------------------------------------------------
     B = 8
     ms, launches, h2d, mean_len, uniq, clk = decode_run(B, args.steps, args.warmup, sample_clocks=True)
@@ -295,6 +304,8 @@ def main():
                     help="run a few steps of one kind between cudaProfilerStart/Stop (for ncu "
                          "--profile-from-start off) and print no benchmark line")
     ap.add_argument("--batch", type=int, default=8, help="with --profile-step decode: sequences in the batch")
+    ap.add_argument("--sweep", default=None, help="comma-separated batch sizes: print decode throughput for each "
+                                                  "and no benchmark line")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "JGalego/Moe is a Rust crate (no Python package, "

@@ -57,42 +57,123 @@ struct Chunk<__nv_bfloat16> {
 
 // partial layout: [token][head][split] records of (hd + 2) floats: acc[hd], m, l
 
+__device__ __forceinline__ float through(float v, const float*) { return v; }
+__device__ __forceinline__ float through(float v, const __nv_bfloat16*) {
+    return __bfloat162float(__float2bfloat16_rn(v));
+}
+__device__ __forceinline__ void store_chunk(float* p, const float* v) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store_chunk(__nv_bfloat16* p, const float* v) {
+    uint4 u;
+    unsigned* w = &u.x;
+#pragma unroll
+    for (int i = 0; i < 4; i++)   // v already holds bfloat16 values: the low halves are zero
+        w[i] = (__float_as_uint(v[2 * i]) >> 16) | (__float_as_uint(v[2 * i + 1]) & 0xffff0000u);
+    *reinterpret_cast<uint4*>(p) = u;
+}
+
+// What the fused form of the kernel needs beside the attention itself: it takes the step's
+// 32-bit q/k/v rows (biases added), rotates them, appends key and value to the cache, and the CTA
+// that finishes last for a (token, kv head) merges the splits and writes the output.
+struct FusedArgs {
+    const float* qkv;        // [T, (nh + 2 nkv) * hd]
+    const float* inv_freq;   // [rot / 2] (null if rot == 0)
+    int rot;
+    void* k_append;          // the cache arrays again, as the place of the append
+    void* v_append;
+    void* out;               // [T, nh * hd]
+    int* tickets;            // [T * nkv], zero before and after the launch
+};
+
+// EPC consecutive elements d0 .. of one head's 32-bit row, rotated (same arithmetic as
+// rope_commit_kernel) and rounded through the storage type.  ang: cos[half], sin[half].
+template <typename T, int EPC>
+__device__ __forceinline__ void rotated_chunk(const float* __restrict__ src, int d0, int half, int rot,
+                                              const float* ang, float* out) {
+#pragma unroll
+    for (int e = 0; e < EPC; e++) {
+        const int d = d0 + e;
+        float v;
+        if (d < rot) {
+            const int i = d < half ? d : d - half;
+            const float a = src[i], b = src[i + half], cs = ang[i], sn = ang[half + i];
+            v = d < half ? a * cs - b * sn : a * sn + b * cs;
+        } else {
+            v = src[d];
+        }
+        out[e] = through(v, (const T*)nullptr);
+    }
+}
+
 // LPR: lanes per key row (row bytes / 16); GH: query heads handled together.
-template <typename T, int LPR, int GH>
-__global__ void __launch_bounds__(WARPS * 32)
+template <typename T, int LPR, int GH, bool FUSED>
+__global__ void __launch_bounds__(WARPS * 32, (GH == 1 && LPR <= 16) ? 4 : 1)
 attn_decode_fast_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                         float* __restrict__ partial, const int* __restrict__ seq_of_token,
                         const int* __restrict__ pos, const int* __restrict__ slots, const int* __restrict__ tables,
                         int table_stride, int ring, int page_size, int num_pages, int nh, int nkv, int window,
-                        float scale, int* status) {
+                        float scale, int* status, const FusedArgs fa) {
     constexpr int EPC = Chunk<T>::N;       // elements per 16-byte chunk
     constexpr int HD = LPR * EPC;
     constexpr int RPI = 32 / LPR;          // rows per load instruction
     constexpr int NI = LPR;                // load instructions per tile of 32 rows
     constexpr int REC = HD + 2;
     __shared__ float red[WARPS][GH][REC];
-    pdl_sync();
+    __shared__ float ang[FUSED ? HD : 1];
+    __shared__ int s_last;
 
+    // Before the wait for the predecessor: everything that depends only on the step's layout
+    // (positions, slots and page tables were written at the start of the step, more than one
+    // kernel ago) and on the cache of earlier steps.  The CTA asks for its keys and values in L2
+    // and forms the rotation angles, so that their latency passes while the predecessor ends.
     const int split = blockIdx.x, nsplit = gridDim.x, kvh = blockIdx.y, t = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane % LPR, rgrp = lane / LPR;
     const int group = nh / nkv;
     const int s = seq_of_token[t];
-    if (s < 0) return;                                   // padding row: the merge kernel writes zeros
-    const int p = pos[t];
+    const int p = s < 0 ? 0 : pos[t];
     const int lo = window > 0 ? max(0, p + 1 - window) : 0;
+    // fused: position p is this step's own key, which comes from the q/k/v row, not from the cache
+    const int hi = FUSED ? p - 1 : p;
+    const int half = FUSED ? fa.rot / 2 : 0;
+    const int width = (nh + 2 * nkv) * HD;
+    const bool owner = FUSED && split == nsplit - 1 && warp == 0;   // takes the new key and appends it
     // tiles of 32 positions, aligned to 32: the keys of a tile are contiguous in one page
     const int tile_lo = lo / 32, tile_hi = p / 32 + 1;
     const int tps = (tile_hi - tile_lo + nsplit - 1) / nsplit;
     const int tb = tile_lo + split * tps, te = min(tile_hi, tb + tps);
-    const int* table = tables + (size_t)slots[s] * table_stride;
+    const int* table = tables + (size_t)(s < 0 ? 0 : slots[s]) * table_stride;
+    if (s >= 0) {
+        constexpr int LINES = 32 * HD * (int)sizeof(T) / 128;     // 128-byte lines of a tile of keys
+        for (int i = threadIdx.x; i < (te - tb) * 2 * LINES; i += blockDim.x) {
+            const int tile = tb + i / (2 * LINES), r = i % (2 * LINES);
+            const CachePos cp = cache_pos(tile * 32, ring, table, page_size, num_pages, nullptr);
+            const size_t at = cache_index(cp, kvh, nkv, page_size, HD) + (size_t)(r % LINES) * (128 / sizeof(T));
+            prefetch_l2((r < LINES ? k_cache : v_cache) + at);
+        }
+        if (FUSED)
+            for (int i = threadIdx.x; i < half; i += blockDim.x)
+                sincosf((float)p * fa.inv_freq[i], &ang[half + i], &ang[i]);
+    }
+    pdl_sync();
+    if (s < 0) {                                         // padding row: zeros (unfused: by the merge kernel)
+        if (FUSED && split == 0)
+            for (int i = threadIdx.x; i < group * HD; i += blockDim.x)
+                st_f((T*)fa.out + ((size_t)t * nh + (size_t)kvh * group) * HD + i, 0.f);
+        return;
+    }
+    if (FUSED) __syncthreads();
 
     for (int h0 = 0; h0 < group; h0 += GH) {
         const int gh = min(GH, group - h0);
         float qc[GH][EPC];
 #pragma unroll
         for (int g = 0; g < GH; g++) {
-            if (g < gh)
+            if (g < gh && FUSED)
+                rotated_chunk<T, EPC>(fa.qkv + (size_t)t * width + (size_t)(kvh * group + h0 + g) * HD, sub * EPC,
+                                      half, fa.rot, ang, qc[g]);
+            else if (g < gh)
                 Chunk<T>::load(q + ((size_t)t * nh + kvh * group + h0 + g) * HD + sub * EPC, qc[g]);
             else
 #pragma unroll
@@ -117,7 +198,7 @@ attn_decode_fast_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
             for (int i = 0; i < NI; i++) raw[i] = *reinterpret_cast<const uint4*>(kt + (size_t)i * RPI * HD);
             const int my_row = sub * RPI + rgrp;          // the row whose score this lane ends up with
             const int my_j = j0 + my_row;
-            const bool valid = my_j >= lo && my_j <= p;
+            const bool valid = my_j >= lo && my_j <= hi;
             float sc[GH];
 #pragma unroll
             for (int g = 0; g < GH; g++) {
@@ -167,12 +248,46 @@ attn_decode_fast_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
                     // rows outside [lo, p] may hold anything: they are skipped, not multiplied by zero
                     const int j = j0 + i * RPI + rgrp;
                     const float pi = __shfl_sync(0xffffffffu, pr, lane - sub + i);   // holder of row (i, rgrp)
-                    if (j >= lo && j <= p) {
+                    if (j >= lo && j <= hi) {
                         float vc[EPC];
                         Chunk<T>::unpack(raw[i], vc);
 #pragma unroll
                         for (int e = 0; e < EPC; e++) acc[g][e] = fmaf(pi, vc[e], acc[g][e]);
                     }
+                }
+            }
+        }
+        if (owner) {
+            // this step's own key and value: appended to the cache, and one more position of the
+            // running softmax
+            float kn[EPC], vn[EPC];
+            const float* row = fa.qkv + (size_t)t * width;
+            rotated_chunk<T, EPC>(row + (size_t)(nh + kvh) * HD, sub * EPC, half, fa.rot, ang, kn);
+            rotated_chunk<T, EPC>(row + (size_t)(nh + nkv + kvh) * HD, sub * EPC, 0, 0, ang, vn);
+            if (rgrp == 0 && h0 == 0) {
+                const CachePos cp = cache_pos(p, ring, table, page_size, num_pages, status);
+                const size_t at = cache_index(cp, kvh, nkv, page_size, HD) + sub * EPC;
+                store_chunk((T*)fa.k_append + at, kn);
+                store_chunk((T*)fa.v_append + at, vn);
+            }
+#pragma unroll
+            for (int g = 0; g < GH; g++) {
+                if (g >= gh) continue;                    // uniform
+                float d = 0.f;
+#pragma unroll
+                for (int e = 0; e < EPC; e++) d = fmaf(kn[e], qc[g][e], d);
+#pragma unroll
+                for (int off = LPR / 2; off >= 1; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+                const float x = d * scale;
+                const float m_new = fmaxf(m[g], x);
+                const float alpha = (m[g] == -INFINITY) ? 0.f : expf(m[g] - m_new);
+                const float pr = expf(x - m_new);
+                l[g] = l[g] * alpha + pr;
+                m[g] = m_new;
+#pragma unroll
+                for (int e = 0; e < EPC; e++) {
+                    acc[g][e] *= alpha;
+                    if (rgrp == 0) acc[g][e] = fmaf(pr, vn[e], acc[g][e]);
                 }
             }
         }
@@ -213,6 +328,36 @@ attn_decode_fast_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
             out[d] = a;
             if (d == 0) out[HD] = mm, out[HD + 1] = ll;
         }
+    }
+    if (!FUSED) return;
+    // the CTA that arrives last at the ticket of (token, kv head) merges the splits, in split
+    // order (same arithmetic as attn_decode_merge_kernel), so the result does not depend on
+    // which CTA that is
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int* ticket = fa.tickets + (size_t)t * nkv + kvh;
+        const int last = atomicAdd(ticket, 1) == nsplit - 1;
+        if (last) *ticket = 0;                 // ready for the next launch
+        s_last = last;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int idx = threadIdx.x; idx < group * HD; idx += blockDim.x) {
+        const int h = kvh * group + idx / HD, d = idx % HD;
+        const float* base = partial + ((size_t)t * nh + h) * nsplit * REC;
+        float mm = -INFINITY;
+        for (int sp = 0; sp < nsplit; sp++) mm = fmaxf(mm, __ldcg(base + (size_t)sp * REC + HD));
+        float ll = 0.f, a = 0.f;
+        for (int sp = 0; sp < nsplit; sp++) {
+            const float ms = __ldcg(base + (size_t)sp * REC + HD);
+            if (ms == -INFINITY) continue;
+            const float f = expf(ms - mm);
+            ll += f * __ldcg(base + (size_t)sp * REC + HD + 1);
+            a += f * __ldcg(base + (size_t)sp * REC + d);
+        }
+        st_f((T*)fa.out + ((size_t)t * nh + h) * HD + d, a / ll);
     }
 }
 
@@ -387,16 +532,25 @@ template <typename T>
 int launch(const void* q, const void* k_cache, const void* v_cache, void* out, float* partial,
            const int* seq_of_token, const int* pos, const int* slots, const int* tables, int table_stride, int ring,
            int page_size, int num_pages, int num_tokens, int nh, int nkv, int hd, int window, float scale, int nsplit,
-           int* status, cudaStream_t stream) {
+           int* status, cudaStream_t stream, const FusedArgs* fused = nullptr) {
     dim3 grid(nsplit, nkv, num_tokens);
     const int group = nh / nkv;
     const int row_bytes = hd * (int)sizeof(T);
     const bool fast = page_size % 32 == 0 && (ring % 32 == 0) &&
                       (row_bytes == 64 || row_bytes == 128 || row_bytes == 256 || row_bytes == 512);
-#define FAST(LPR, GH)                                                                                          \
-    launch_pdl(attn_decode_fast_kernel<T, LPR, GH>, grid, WARPS * 32, 0, stream, (const T*)q, (const T*)k_cache, \
-               (const T*)v_cache, partial, seq_of_token, pos, slots, tables, table_stride, ring, page_size,      \
-               num_pages, nh, nkv, window, scale, status)
+    if (fused && !fast) return -1;
+    const FusedArgs fa = fused ? *fused : FusedArgs{};
+#define FAST(LPR, GH)                                                                                             \
+    do {                                                                                                          \
+        if (fused)                                                                                                \
+            rc = launch_pdl(attn_decode_fast_kernel<T, LPR, GH, true>, grid, WARPS * 32, 0, stream, (const T*)q,  \
+                            (const T*)k_cache, (const T*)v_cache, partial, seq_of_token, pos, slots, tables,      \
+                            table_stride, ring, page_size, num_pages, nh, nkv, window, scale, status, fa);        \
+        else                                                                                                      \
+            rc = launch_pdl(attn_decode_fast_kernel<T, LPR, GH, false>, grid, WARPS * 32, 0, stream, (const T*)q, \
+                            (const T*)k_cache, (const T*)v_cache, partial, seq_of_token, pos, slots, tables,      \
+                            table_stride, ring, page_size, num_pages, nh, nkv, window, scale, status, fa);        \
+    } while (0)
 #define FAST_G(LPR)                  \
     do {                             \
         if (group == 1)              \
@@ -404,6 +558,7 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, f
         else                         \
             FAST(LPR, 2);            \
     } while (0)
+    int rc = 0;
     if (fast) {
         switch (row_bytes / 16) {
             case 4: FAST_G(4); break;
@@ -419,11 +574,41 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, f
     }
 #undef FAST
 #undef FAST_G
+    if (fused || rc) return rc;
     return launch_pdl(attn_decode_merge_kernel<T>, dim3(num_tokens, nh), 128, 0, stream, (const float*)partial, (T*)out,
                       seq_of_token, nh, hd, nsplit);
 }
 
 }  // namespace
+
+// A step of ONE token per sequence in one launch: rotation of the step's q/k/v rows, the append
+// of key and value to the cache, the attention split along the keys, and the merge of the splits.
+//   qkv: [T, (nh + 2 nkv) * hd] 32-bit with biases added; inv_freq: [rot / 2];
+//   tickets: T * nkv ints, zero before the call (the kernel leaves them zero);
+//   partial: T * nh * nsplit * (hd + 2) floats of scratch; out: [T, nh * hd].
+// Returns -1 (nothing launched) for a head size the fast kernel does not take: the caller then
+// uses moe_rope_commit and moe_attention_decode.
+MOE_API int moe_attention_decode_fused(const float* qkv, const float* inv_freq, int rot, void* k_cache, void* v_cache,
+                                       void* out, float* partial, int* tickets, int dt, const int* seq_of_token,
+                                       const int* pos, const int* slots, const int* tables, int table_stride,
+                                       int ring, int page_size, int num_pages, int num_tokens, int nh, int nkv, int hd,
+                                       int window, float scale, int nsplit, int* status, cudaStream_t stream) {
+    if (num_tokens <= 0) return 0;
+    if (hd % 16 != 0 || hd > MAX_HD || hd <= 0 || nkv <= 0 || nh % nkv != 0 || nsplit < 1 || nsplit > 65535 ||
+        nkv > 65535 || num_tokens > 65535 || rot < 0 || rot > hd || (rot & 1) || (rot > 0 && !inv_freq) || !tickets)
+        return (int)cudaErrorInvalidValue;
+    if (((uintptr_t)qkv | (uintptr_t)k_cache | (uintptr_t)v_cache) % 16) return -1;
+    FusedArgs fa;
+    fa.qkv = qkv, fa.inv_freq = inv_freq, fa.rot = rot, fa.k_append = k_cache, fa.v_append = v_cache, fa.out = out;
+    fa.tickets = tickets;
+    if (dt == DT_F32)
+        return launch<float>(nullptr, k_cache, v_cache, out, partial, seq_of_token, pos, slots, tables, table_stride,
+                             ring, page_size, num_pages, num_tokens, nh, nkv, hd, window, scale, nsplit, status,
+                             stream, &fa);
+    return launch<__nv_bfloat16>(nullptr, k_cache, v_cache, out, partial, seq_of_token, pos, slots, tables,
+                                 table_stride, ring, page_size, num_pages, num_tokens, nh, nkv, hd, window, scale,
+                                 nsplit, status, stream, &fa);
+}
 
 // q: [T, nh, hd]; out: [T, nh * hd]; partial: T * nh * nsplit * (hd + 2) floats of scratch.
 MOE_API int moe_attention_decode(const void* q, const void* k_cache, const void* v_cache, void* out, float* partial,

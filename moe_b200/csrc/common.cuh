@@ -79,6 +79,11 @@ __device__ __forceinline__ void pdl_sync() {
     pdl_launch_dependents();
 }
 
+// Ask for the 128-byte line of `p` in L2.  Weights (and cache contents of earlier steps) do not
+// depend on the predecessor, so a kernel may ask for them BEFORE pdl_wait(): the memory latency
+// then passes while the predecessor finishes.
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 // One switch per shared library (set through moe_set_pdl / moe_tc_set_pdl).
 inline int g_pdl_enabled = 1;
 
@@ -111,7 +116,7 @@ __device__ __forceinline__ CachePos cache_pos(int pos, int ring, const int* tabl
     int r = ring > 0 ? pos % ring : pos;
     int page = table[r / page_size];
     if (page < 0 || page >= num_pages) {
-        atomicOr(status, ST_BAD_PAGE);
+        if (status) atomicOr(status, ST_BAD_PAGE);
         page = 0;
     }
     CachePos c;

@@ -155,7 +155,10 @@ router_logits_tiled_kernel(const float* __restrict__ h, const WT* __restrict__ w
 __device__ __forceinline__ void route_token(const float* __restrict__ lg, float* sc, int lane, bool padding,
                                             int num_experts, int rows, int top_k, int norm_topk, float scale,
                                             int* __restrict__ idx_out, float* __restrict__ w_out,
-                                            float* __restrict__ gate_out) {
+                                            float* __restrict__ gate_out, float* wk = nullptr) {
+    // wk: top_k floats of shared memory for the picked weights before scaling (else they are
+    // staged in w_out itself, which costs round trips to global memory)
+    if (!wk) wk = w_out;
     if (padding) {   // a row that belongs to no sequence: no expert
         for (int j = lane; j < top_k; j += 32) idx_out[j] = -1, w_out[j] = 0.f;
         if (gate_out && lane == 0) *gate_out = 0.f;
@@ -194,12 +197,18 @@ __device__ __forceinline__ void route_token(const float* __restrict__ lg, float*
         if (lane == 0) {
             sc[bi] = -2.f;   // taken
             idx_out[j] = bi;
-            w_out[j] = w;
+            wk[j] = w;
         }
         __syncwarp();
     }
-    if (lane == 0) {
-        const float zz = norm_topk ? fmaxf(wsum, 1e-20f) : 1.0f;
+    const float zz = norm_topk ? fmaxf(wsum, 1e-20f) : 1.0f;   // wsum is the same in every lane
+    if (wk != w_out) {
+        for (int j = lane; j < top_k; j += 32) {
+            float w = wk[j];
+            if (norm_topk) w = w / zz;
+            w_out[j] = w * scale;
+        }
+    } else if (lane == 0) {
         for (int j = 0; j < top_k; j++) {
             float w = w_out[j];
             if (norm_topk) w = w / zz;
@@ -368,7 +377,240 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
     }
 }
 
+// Few tokens (a decode step): the norm before the feed-forward, the router and the dispatch in
+// ONE launch.  A block per token adds the pending delta to the stream, normalises the row
+// (as rmsnorm_kernel), forms the token's router logits from the 32-bit normalised row in shared
+// memory (one warp per router row) and picks its experts; the block that finishes last inverts
+// the table and gathers the picked tokens' activations (as route_dispatch_kernel).
+struct NormRouteParams {
+    float* x;                 // [T, hidden] stream, updated in place if delta
+    const float* delta;       // pending sum or null
+    const float* norm_w;
+    float eps;
+    int hidden, num_tokens;
+    float* out32;             // normalised rows, 32-bit (or null)
+    __nv_bfloat16* out16;     // normalised rows, bfloat16 (or null)
+    const void* wr;           // [E, hidden]
+    const void* wsg;          // [hidden] or null
+    int num_experts, rows, top_k, norm_topk;
+    float scale;
+    const int* seq_of_token;
+    int* topk_idx;
+    float* topk_w;
+    float* shared_gate;
+    int* offsets;
+    int* sorted_token;
+    int* pos_of_pair;
+    uint4* xs;                // gathered bfloat16 rows or null
+    int row_units;            // 16-byte units per bfloat16 row
+    int* ticket;              // one int, zero before and after
+    int* status;
+    int vec_ok;
+};
+
+template <typename WT>
+__global__ void __launch_bounds__(1024) norm_route_kernel(const NormRouteParams p) {
+    extern __shared__ __align__(16) float nr_smem[];
+    __shared__ float red[32];
+    __shared__ int s_last;
+    const int t = blockIdx.x, H = p.hidden, E = p.num_experts;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    {
+        // the weights do not depend on the predecessor: they are asked into L2 before the wait
+        // (the blocks share the router's lines among them)
+        const size_t line = 128, w_bytes = (size_t)E * H * sizeof(WT);
+        for (size_t off = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * line; off < w_bytes;
+             off += (size_t)gridDim.x * blockDim.x * line)
+            prefetch_l2((const char*)p.wr + off);
+        for (size_t off = threadIdx.x * line; off < (size_t)H * sizeof(float); off += blockDim.x * line)
+            prefetch_l2((const char*)p.norm_w + off);
+        if (p.wsg)
+            for (size_t off = threadIdx.x * line; off < (size_t)H * sizeof(WT); off += blockDim.x * line)
+                prefetch_l2((const char*)p.wsg + off);
+    }
+    pdl_sync();
+    float* row = nr_smem;                              // [H] (H rounded up to 4)
+    float* logit = row + ((H + 3) & ~3);               // [rows]
+    float* sc = logit + p.rows;                        // [E]
+    float* wk = sc + E;                                // [top_k]
+    int* picks = reinterpret_cast<int*>(wk + p.top_k); // [pairs]
+    const int pairs = p.num_tokens * p.top_k;
+    int* sorted = picks + pairs;                       // [pairs]
+    int* counts = sorted + pairs;                      // [E], then cursor [E]
+
+    // ---- the norm --------------------------------------------------------------------------
+    float* xr = p.x + (size_t)t * H;
+    const float* dr = p.delta ? p.delta + (size_t)t * H : nullptr;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        float v = xr[j];
+        if (dr) {
+            v += dr[j];
+            xr[j] = v;
+        }
+        row[j] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float rs = 1.0f / sqrtf(ss / (float)H + p.eps);
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        const float y = row[j] * rs * p.norm_w[j];
+        row[j] = y;
+        if (p.out32) p.out32[(size_t)t * H + j] = y;
+        if (p.out16) p.out16[(size_t)t * H + j] = __float2bfloat16_rn(y);
+    }
+    __syncthreads();
+
+    // ---- router logits: one warp per router row, 32-bit products and sums in a fixed order ----
+    // (a warp takes two rows at a time, so that the loads of both are in flight together)
+    const int groups = p.vec_ok ? H / 8 : 0;
+    for (int r = warp; r < p.rows; r += 2 * nwarps) {
+        const int r2 = r + nwarps;
+        const bool two = r2 < p.rows;
+        const WT* w = r < E ? (const WT*)p.wr + (size_t)r * H : (const WT*)p.wsg;
+        const WT* w2 = !two ? w : (r2 < E ? (const WT*)p.wr + (size_t)r2 * H : (const WT*)p.wsg);
+        float acc = 0.f, acc2 = 0.f;
+#pragma unroll 4
+        for (int gi = lane; gi < groups; gi += 32) {
+            float wv[8], wv2[8];
+            w_load8<WT>(w + gi * 8, wv);
+            w_load8<WT>(w2 + gi * 8, wv2);
+            const float4 a = *reinterpret_cast<const float4*>(row + gi * 8);
+            const float4 b = *reinterpret_cast<const float4*>(row + gi * 8 + 4);
+            acc = fmaf(a.x, wv[0], acc), acc = fmaf(a.y, wv[1], acc), acc = fmaf(a.z, wv[2], acc);
+            acc = fmaf(a.w, wv[3], acc), acc = fmaf(b.x, wv[4], acc), acc = fmaf(b.y, wv[5], acc);
+            acc = fmaf(b.z, wv[6], acc), acc = fmaf(b.w, wv[7], acc);
+            acc2 = fmaf(a.x, wv2[0], acc2), acc2 = fmaf(a.y, wv2[1], acc2), acc2 = fmaf(a.z, wv2[2], acc2);
+            acc2 = fmaf(a.w, wv2[3], acc2), acc2 = fmaf(b.x, wv2[4], acc2), acc2 = fmaf(b.y, wv2[5], acc2);
+            acc2 = fmaf(b.z, wv2[6], acc2), acc2 = fmaf(b.w, wv2[7], acc2);
+        }
+        for (int c = groups * 8 + lane; c < H; c += 32) {
+            acc = fmaf(row[c], ld_f(w + c), acc);
+            acc2 = fmaf(row[c], ld_f(w2 + c), acc2);
+        }
+        acc = warp_sum(acc);
+        acc2 = warp_sum(acc2);
+        if (lane == 0) {
+            logit[r] = acc;
+            if (two) logit[r2] = acc2;
+        }
+    }
+    __syncthreads();
+
+    // ---- this token's experts ------------------------------------------------------------------
+    if (warp == 0)
+        route_token(logit, sc, lane, p.seq_of_token && p.seq_of_token[t] < 0, E, p.rows, p.top_k, p.norm_topk, p.scale,
+                    p.topk_idx + (size_t)t * p.top_k, p.topk_w + (size_t)t * p.top_k,
+                    p.shared_gate ? p.shared_gate + t : nullptr, wk);
+
+    // ---- the block that finishes last inverts the table and gathers ----------------------------
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int last = atomicAdd(p.ticket, 1) == p.num_tokens - 1;
+        if (last) *p.ticket = 0;
+        s_last = last;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    int* cursor = counts + E;
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) picks[i] = __ldcg(p.topk_idx + i);
+    for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const int e = picks[i];
+        if (e >= 0 && e < E)
+            atomicAdd(&counts[e], 1);
+        else if (e != -1)
+            atomicOr(p.status, ST_BAD_EXPERT);
+    }
+    __syncthreads();
+    if (warp == 0) {   // exclusive scan of the counts, 32 experts at a time
+        int run = 0;
+        for (int e0 = 0; e0 < E; e0 += 32) {
+            const int e = e0 + lane;
+            const int c = e < E ? counts[e] : 0;
+            int inc = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int n = __shfl_up_sync(0xffffffffu, inc, o);
+                if (lane >= o) inc += n;
+            }
+            if (e < E) {
+                p.offsets[e] = run + inc - c;
+                cursor[e] = run + inc - c;
+            }
+            run += __shfl_sync(0xffffffffu, inc, 31);
+        }
+        if (lane == 0) {
+            p.offsets[E] = run;
+            s_last = run;          // total, for the whole block
+        }
+    }
+    __syncthreads();
+    const int total = s_last;
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const int e = picks[i];
+        if (e >= 0 && e < E) {
+            const int q = atomicAdd(&cursor[e], 1);
+            sorted[q] = i / p.top_k;
+            p.sorted_token[q] = i / p.top_k;
+            p.pos_of_pair[i] = q;
+        } else {
+            p.pos_of_pair[i] = -1;
+        }
+    }
+    for (int i = total + threadIdx.x; i < pairs; i += blockDim.x) p.sorted_token[i] = 0;
+    __syncthreads();
+    if (p.xs) {
+        const uint4* src = reinterpret_cast<const uint4*>(p.out16);
+        const int n = total * p.row_units;
+#pragma unroll 8
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const int q = i / p.row_units, c = i % p.row_units;
+            p.xs[i] = __ldcg(src + (size_t)sorted[q] * p.row_units + c);
+        }
+    }
+}
+
 }  // namespace
+
+// The norm before a routed feed-forward, the router and the dispatch of a step of few tokens, one
+// launch (see norm_route_kernel).  Returns -1, with nothing launched, for sizes it does not take
+// (more than 64 tokens, 256 experts or 4096 (token, expert) pairs, or a row too long for shared
+// memory): the caller then runs the separate kernels.
+MOE_API int moe_norm_route(float* x, const float* delta, const float* norm_w, float eps, int hidden, int num_tokens,
+                           float* out32, void* out16, const void* wr, const void* wsg, int w_dt, int num_experts,
+                           int top_k, int norm_topk, float scale, const int* seq_of_token, int* topk_idx,
+                           float* topk_w, float* shared_gate, int* offsets, int* sorted_token, int* pos_of_pair,
+                           void* xs, int* ticket, int* status, cudaStream_t stream) {
+    if (num_tokens <= 0) return 0;
+    if (top_k <= 0 || top_k > num_experts || hidden <= 0 || !ticket || (wsg && !shared_gate) || (xs && !out16))
+        return (int)cudaErrorInvalidValue;
+    const int pairs = num_tokens * top_k;
+    if (num_tokens > 64 || num_experts > 256 || pairs > 4096) return -1;
+    NormRouteParams p;
+    p.x = x, p.delta = delta, p.norm_w = norm_w, p.eps = eps, p.hidden = hidden, p.num_tokens = num_tokens;
+    p.out32 = out32, p.out16 = (__nv_bfloat16*)out16, p.wr = wr, p.wsg = wsg, p.num_experts = num_experts;
+    p.rows = num_experts + (wsg ? 1 : 0), p.top_k = top_k, p.norm_topk = norm_topk, p.scale = scale;
+    p.seq_of_token = seq_of_token, p.topk_idx = topk_idx, p.topk_w = topk_w, p.shared_gate = shared_gate;
+    p.offsets = offsets, p.sorted_token = sorted_token, p.pos_of_pair = pos_of_pair;
+    p.xs = (uint4*)xs, p.row_units = hidden * 2 / 16, p.ticket = ticket, p.status = status;
+    if (xs && ((hidden * 2) % 16 || (uintptr_t)xs % 16 || (uintptr_t)out16 % 16)) return -1;
+    const size_t elt = w_dt == DT_F32 ? 4 : 2;
+    p.vec_ok = (hidden % 8 == 0) && ((uintptr_t)wr % 16 == 0) && (!wsg || (uintptr_t)wsg % 16 == 0) &&
+               ((hidden * elt) % 16 == 0);
+    const size_t smem = ((size_t)((hidden + 3) & ~3) + p.rows + num_experts + top_k) * sizeof(float) +
+                        ((size_t)2 * pairs + 2 * num_experts) * sizeof(int);
+    if (smem > 200 * 1024) return -1;
+    auto kernel = w_dt == DT_F32 ? norm_route_kernel<float> : norm_route_kernel<__nv_bfloat16>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return launch_pdl(kernel, num_tokens, 1024, smem, stream, p);
+}
 
 // logits[t, r] = h[t] . W[r] for the router rows (and the shared-gate row, if wsg): num_tokens *
 // (num_experts + (wsg ? 1 : 0)) floats.

@@ -43,6 +43,9 @@ def lib():
             "moe_route_dispatch": [P, P, I, I, I, I, I, F, P, P, P, P, P, P, P, P, I, P, P],
             "moe_rope_commit": [P, P, P, I, I, I, I, I, P, P, P, I, P, P, P, I, I, I, I, P, P],
             "moe_attention_decode": [P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],
+            "moe_attention_decode_fused": [P, P, I, P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],
+            "moe_norm_route": [P, P, P, F, I, I, P, P, P, P, I, I, I, I, F, P, P, P, P, P, P, P, P, P, P, P],
+            "moe_l2_prefetch": [P, LL, I, P],
             "moe_align": [P, I, I, I, P, P, P, P, P],
             "moe_swiglu": [P, P, I, LL, I, P],
             "moe_combine": [P, P, P, I, P, P, P, I, I, P],
@@ -278,7 +281,8 @@ def decode_splits(device, num_tokens: int, nkv: int) -> int:
     idx = torch.device(device).index or 0
     if idx not in _SMS:
         _SMS[idx] = torch.cuda.get_device_properties(device).multi_processor_count
-    return max(1, min(32, (8 * _SMS[idx]) // max(1, num_tokens * nkv)))
+    per_sm = int(os.environ.get("MOE_B200_DECODE_CTAS", "4"))
+    return max(1, min(32, (per_sm * _SMS[idx]) // max(1, num_tokens * nkv)))
 
 
 def attention_decode(q, view, batch, out, *, nh, window, scale, status):
@@ -295,6 +299,53 @@ def attention_decode(q, view, batch, out, *, nh, window, scale, status):
                                    g.table.stride(0), g.ring, g.page_size, g.num_pages, T, nh, g.num_kv_heads,
                                    g.head_dim, int(window or 0), float(scale), nsplit, _p(status), _stream()),
         "attention_decode")
+
+
+def l2_prefetch(t: torch.Tensor) -> None:
+    """Ask for a tensor (weights a later kernel will stream) in L2; changes no result."""
+    idx = t.device.index or 0
+    if idx not in _SMS:
+        _SMS[idx] = torch.cuda.get_device_properties(t.device).multi_processor_count
+    _ok(lib().moe_l2_prefetch(_p(t), t.numel() * t.element_size(), 2 * _SMS[idx], _stream()), "l2_prefetch")
+
+
+_TICKETS = {}
+
+
+def _tickets(device, n: int) -> torch.Tensor:
+    """Zeroed counters that kernels with a 'last CTA finishes the job' step use and leave zero."""
+    idx = torch.device(device).index or 0
+    t = _TICKETS.get(idx)
+    if t is None or t.numel() < n:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("the ticket array must be sized before a CUDA graph is captured")
+        t = _TICKETS[idx] = torch.zeros(max(n, 1 << 14), dtype=torch.int32, device=device)
+    return t
+
+
+def attention_decode_fused(qkv, inv_freq, rot, view, batch, out, *, nh, window, scale, status) -> bool:
+    """One token per sequence, ONE launch: rotate the step's q/k/v rows, append key and value to
+    the cache layer ``view``, attend over the cache split along the keys, merge.  False (nothing
+    launched) if the head size is not one the fast kernel takes."""
+    _chk(qkv, "qkv", torch.float32, 2)
+    g = view.group
+    T = batch.num_tokens
+    if qkv.shape[1] != (nh + 2 * g.num_kv_heads) * g.head_dim or out.dtype != g.dtype:
+        raise KernelError("attention_decode_fused: shapes or dtypes do not fit the cache")
+    if rot:
+        _chk(inv_freq, "inv_freq", torch.float32, 1)
+    nsplit = decode_splits(qkv.device, T, g.num_kv_heads)
+    partial = torch.empty(T * nh * nsplit * (g.head_dim + 2), dtype=torch.float32, device=qkv.device)
+    tickets = _tickets(qkv.device, T * g.num_kv_heads)
+    code = lib().moe_attention_decode_fused(_p(qkv), _p(inv_freq) if rot else None, rot, _p(view.k), _p(view.v),
+                                            _p(out), _p(partial), _p(tickets), _dt(out), _p(batch.seq_of_token),
+                                            _p(batch.pos), _p(batch.slots), _p(g.table), g.table.stride(0), g.ring,
+                                            g.page_size, g.num_pages, T, nh, g.num_kv_heads, g.head_dim,
+                                            int(window or 0), float(scale), nsplit, _p(status), _stream())
+    if code == -1:
+        return False
+    _ok(code, "attention_decode_fused")
+    return True
 
 
 def moe_align(topk_idx, num_tokens, top_k, num_experts, offsets, sorted_token, pos_of_pair, status):
@@ -364,6 +415,39 @@ def rope_commit(qkv, pos, inv_freq, nh, nkv, hd, rot, q, view, batch, status):
         "rope_commit")
 
 
+def norm_route(x, delta, norm_w, eps, w_router, top_k, norm_topk, scale, *, bf16, shared_gate_w=None,
+               seq_of_token=None, status=None):
+    """Few tokens: ``x += delta``, RMS norm, router logits, pick, table inversion and gather of the
+    normalised bfloat16 rows in ONE launch.  Returns None (nothing launched) for sizes the kernel
+    does not take, else (out32 or None, out16 or None, topk_idx, topk_w, shared_gate, offsets,
+    sorted_token, pos_of_pair, gathered or None)."""
+    _chk(x, "x", torch.float32, 2), _chk(norm_w, "norm weight", torch.float32, 1), _chk(w_router, "router weight", dims=2)
+    T, H = x.shape
+    E = w_router.shape[0]
+    if T > 64 or E > 256 or T * top_k > 4096 or norm_w.numel() != H or w_router.shape[1] != H:
+        return None
+    dev = x.device
+    out16 = torch.empty((T, H), dtype=torch.bfloat16, device=dev) if bf16 else None
+    out32 = None if bf16 else torch.empty((T, H), dtype=torch.float32, device=dev)
+    P_ = T * top_k
+    topk_idx = torch.empty((T, top_k), dtype=torch.int32, device=dev)
+    topk_w = torch.empty((T, top_k), dtype=torch.float32, device=dev)
+    sg = torch.empty((T,), dtype=torch.float32, device=dev) if shared_gate_w is not None else None
+    offsets = torch.empty((E + 1,), dtype=torch.int32, device=dev)
+    sorted_token = torch.empty((P_,), dtype=torch.int32, device=dev)
+    pos_of_pair = torch.empty((P_,), dtype=torch.int32, device=dev)
+    xs = torch.empty((P_, H), dtype=torch.bfloat16, device=dev) if bf16 and (H * 2) % 16 == 0 else None
+    ticket = _tickets(dev, 1)
+    code = lib().moe_norm_route(_p(x), _p(delta), _p(norm_w), float(eps), H, T, _p(out32), _p(out16), _p(w_router),
+                                _p(shared_gate_w), _dt(w_router), E, top_k, 1 if norm_topk else 0, float(scale),
+                                _p(seq_of_token), _p(topk_idx), _p(topk_w), _p(sg), _p(offsets), _p(sorted_token),
+                                _p(pos_of_pair), _p(xs), _p(ticket), _p(status), _stream())
+    if code == -1:
+        return None
+    _ok(code, "norm_route")
+    return out32, out16, topk_idx, topk_w, sg, offsets, sorted_token, pos_of_pair, xs
+
+
 def route_dispatch(h32, w_router, top_k, norm_topk, scale, *, shared_gate_w=None, seq_of_token=None, gather=None,
                    status=None):
     """Few tokens (<= 64) and <= 256 experts: router logits, then pick + table inversion + gather in
@@ -389,7 +473,7 @@ def route_dispatch(h32, w_router, top_k, norm_topk, scale, *, shared_gate_w=None
         _chk(gather, "gather", dims=2)
         row_bytes = gather.shape[1] * gather.element_size()
         if row_bytes % 16:
-            gather = None
+            gather, row_bytes = None, 0
         else:
             xs = torch.empty((P_, gather.shape[1]), dtype=gather.dtype, device=dev)
     _ok(lib().moe_route_dispatch(_p(logits), _p(seq_of_token), T, E, 1 if shared_gate_w is not None else 0, top_k,

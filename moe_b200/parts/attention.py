@@ -84,18 +84,23 @@ class GQAttention(Part):
         T = batch.num_tokens
         nkv = self.nkv if self.own_kv else 0
         qkv = linear(rt, h.act, self.wqkv, bias=self.bqkv)
-        q = rt.empty((T, self.nh, self.hd))
         table, rot = self.position.rotary_table()
         if table is None and hasattr(self.position, "apply"):
             self.position.apply(rt, qkv, self.nh, nkv, self.hd, batch.pos)
         ctx = rt.empty((T, self.nh * self.hd))
         if batch.all_decode and self.own_kv:
-            # one token per sequence: rotate and append in one launch, then attend over the cache
-            # alone, split along the keys
+            # one token per sequence: rotation, append, attention split along the keys and the
+            # merge in ONE launch where the head size allows it
+            if core.attention_decode_fused(qkv, table, rot, cache_view, batch, ctx, nh=self.nh, window=self.window,
+                                           scale=self.scale, status=rt.status):
+                return linear(rt, ctx, self.wo)
+            # else: rotate and append in one launch, then attend over the cache alone
+            q = rt.empty((T, self.nh, self.hd))
             core.rope_commit(qkv, batch.pos, table, self.nh, nkv, self.hd, rot, q, cache_view, batch, rt.status)
             core.attention_decode(q, cache_view, batch, ctx, nh=self.nh, window=self.window, scale=self.scale,
                                   status=rt.status)
             return linear(rt, ctx, self.wo)
+        q = rt.empty((T, self.nh, self.hd))
         k_new = rt.empty((T, max(nkv, 1), self.hd))
         v_new = rt.empty((T, max(nkv, 1), self.hd))
         core.rope_split(qkv, batch.pos, table, self.nh, nkv, self.hd, rot, q, k_new, v_new)

@@ -30,6 +30,13 @@ class PreNormBlock:
         Returns (x, pending)."""
         h = self.norm1.forward(rt, x, delta=pending, want32=getattr(self.mixer, "wants32", False))
         delta = self.mixer.forward(rt, h, batch, cache_view, state)
+        # a feed-forward may offer to run the norm before it itself (fused with its first
+        # kernels); it returns None where it cannot, and nothing has happened then
+        prenorm = getattr(self.ffn, "forward_prenorm", None)
+        if prenorm is not None:
+            out = prenorm(rt, x, delta, self.norm2, batch)
+            if out is not None:
+                return x, out
         h = self.norm2.forward(rt, x, delta=delta, want32=getattr(self.ffn, "wants32", False))
         return x, self.ffn.forward(rt, h, batch)
 

@@ -9,11 +9,13 @@ Shared expert (src/model.rs:956-970): out += sigmoid(Wsg n) * y_s(n).
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..ops import core
 from ..ops.linear import grouped_linear, grouped_swiglu_linear, linear, swiglu_linear
-from .base import Part, TensorSpec, register_part
+from .base import Activations, Part, TensorSpec, register_part
 
 
 def _fuse_rows(tensors):
@@ -68,6 +70,12 @@ class RoutedExperts(Part):
         # Set to a list to record every routing decision as (expert ids [T, k], weights [T, k]);
         # the reference's State::trace does the same per token and layer (src/model.rs:157, 943-950).
         self.trace = None
+        # measured on a B200: asking for the shared expert's weights in L2 during the norm delays
+        # the shared expert behind the routed ones and loses more than it gains (off); the fused
+        # norm + router + dispatch launch wins up to 8 tokens and loses from 16 on, where its
+        # single gathering block is the bottleneck
+        self.prefetch_shared = os.environ.get("MOE_B200_PREFETCH", "0") != "0"
+        self.fused_norm_tokens = int(os.environ.get("MOE_B200_NORM_ROUTE_MAX", "8"))
 
     def tensors(self):
         t = {"gate.weight": TensorSpec((self.E, self.hidden))}
@@ -119,6 +127,34 @@ class RoutedExperts(Part):
         return linear(rt, swiglu_linear(rt, h.act, self.ws_gu), self.ws_down)
 
     def forward(self, rt, h, batch):
+        return self._run(rt, h, batch, None)
+
+    def forward_prenorm(self, rt, x, delta, norm, batch):
+        """The block's offer to take the norm before this feed-forward along: for a step of few
+        tokens, norm, router and dispatch are one launch.  None if the sizes or the kind of norm do
+        not allow it (the block then runs the norm itself and calls ``forward``)."""
+        if getattr(norm, "kind", None) != "rmsnorm" or x.shape[0] > self.fused_norm_tokens or self.E > 256:
+            return None
+        if self.ws_gu is not None and self.prefetch_shared:
+            # the step is bound by latency until the routed experts begin: meanwhile the shared
+            # expert's weights are asked into L2 on the second stream, so that its products do not
+            # share the memory bandwidth with the routed ones
+            main = torch.cuda.current_stream()
+            side = rt.side_stream()
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                core.l2_prefetch(self.ws_gu)
+                core.l2_prefetch(self.ws_down)
+        routed = core.norm_route(x, delta, norm.weight, norm.eps, self.w_router, self.k, self.norm_topk, self.scale,
+                                 bf16=rt.is_bf16, shared_gate_w=self.w_sgate,
+                                 seq_of_token=getattr(batch, "seq_of_token", None), status=rt.status)
+        if routed is None:
+            return None
+        out32, out16 = routed[:2]
+        h = Activations(act=out16 if rt.is_bf16 else out32, f32=out32)
+        return self._run(rt, h, batch, routed[2:])
+
+    def _run(self, rt, h, batch, routed):
         T = h.act.shape[0]
         P = T * self.k
         few = T <= 64 and self.E <= 256
@@ -131,7 +167,9 @@ class RoutedExperts(Part):
             side.wait_stream(main)
             with torch.cuda.stream(side):
                 ys = self._shared(rt, h)
-        if few:
+        if routed is not None:
+            topk_idx, topk_w, sg, offsets, sorted_token, pos_of_pair, xs = routed
+        elif few:
             # pick, table inversion and gather in one launch after the logits
             topk_idx, topk_w, sg, offsets, sorted_token, pos_of_pair, xs = core.route_dispatch(
                 h.f32, self.w_router, self.k, self.norm_topk, self.scale, shared_gate_w=self.w_sgate,

@@ -88,3 +88,119 @@ def test_route_dispatch_equals_router_align_gather(core, E, k, H, norm, T, wdt):
         seen.add(p)
     assert len(seen) == total
     assert torch.equal(xs[:total], act[sorted_token[:total].long()])
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,rot,window", [(4, 2, 32, 32, None), (3, 1, 64, 32, 72), (2, 2, 128, 128, None),
+                                                  (5, 1, 128, 64, 100), (6, 2, 16, 16, None), (2, 1, 48, 48, None)])
+def test_attention_decode_fused_equals_rope_commit_then_attention(core, dt, nh, nkv, hd, rot, window):
+    """Rotation + append + attention + merge in one launch against the three launches it replaces:
+    the same cache afterwards and the same output.  Sequences at a page's first and last place, in
+    the middle of a ring that has wrapped, and a padding row."""
+    from moe_b200.cache import KVCache, KVRequest
+
+    lens = [0, 63, 64, 200, 321]
+    B = len(lens)
+    torch.manual_seed(hd + nh)
+    qkv = torch.randn(B + 1, (nh + 2 * nkv) * hd, device=DEV)
+    inv = plain.rope_inv_freq(1e4, rot).to(DEV)
+    st = torch.zeros(4, dtype=torch.int32, device=DEV)
+    outs = []
+    fast_ok = (hd * (4 if dt == torch.float32 else 2)) in (64, 128, 256, 512)
+    for fused in (False, True):
+        cache = KVCache({0: KVRequest(nkv, hd, window)}, {0: None}, 4096, B, dt, DEV)
+        view = cache.view(0)
+        g = torch.Generator(device=DEV).manual_seed(7)
+        view.group.storage.copy_(torch.randn(view.group.storage.shape, device=DEV, generator=g).to(dt))
+        slots = [cache.acquire() for _ in range(B)]
+        for s, n in zip(slots, lens):
+            G.give_pages(cache, s, n + 1)
+        batch = G.make_batch(DEV, slots + [cache.padding_slot], lens + [0], [1] * (B + 1))
+        batch.seq_of_token[B] = -1
+        out = torch.full((B + 1, nh * hd), 7.0, device=DEV, dtype=dt)
+        scale = 1.0 / hd ** 0.5
+        if fused:
+            done = core.attention_decode_fused(qkv, inv, rot, view, batch, out, nh=nh, window=window, scale=scale,
+                                               status=st)
+            assert done == fast_ok
+            if not done:
+                return
+        else:
+            q = torch.zeros(B + 1, nh, hd, device=DEV, dtype=dt)
+            core.rope_commit(qkv, batch.pos, inv, nh, nkv, hd, rot, q, view, batch, st)
+            core.attention_decode(q, view, batch, out, nh=nh, window=window, scale=scale, status=st)
+        outs.append((out.float().clone(), view.group.storage.float().clone()))
+    assert int(st[0]) == 0
+    tol = 1e-5 if dt == torch.float32 else 2.0 ** -7
+    assert torch.allclose(outs[0][1], outs[1][1], rtol=tol, atol=tol * 1e-2)          # the cache
+    assert float(outs[1][0][B].abs().sum()) == 0.0                                       # padding row: zeros
+    err = (outs[0][0] - outs[1][0]).abs().max() / outs[0][0].abs().max()
+    assert float(err) < tol, float(err)
+    # the tickets are left at zero
+    assert int(core._tickets(DEV, 1).abs().sum()) == 0
+
+
+@pytest.mark.parametrize("E,k,H,norm,T", [(60, 4, 2048, False, 8), (8, 3, 96, True, 1), (4, 2, 64, False, 64),
+                                           (200, 8, 72, True, 13), (5, 5, 100, True, 3)])
+@pytest.mark.parametrize("wdt", [torch.float32, torch.bfloat16])
+def test_norm_route_equals_rmsnorm_then_route_dispatch(core, E, k, H, norm, T, wdt):
+    """Norm + router + dispatch in one launch against the separate kernels: the same stream, the
+    same normalised rows, the same picks (unless two experts are closer than rounding), a valid
+    inversion and the gathered rows."""
+    torch.manual_seed(E + T)
+    bf16 = wdt == torch.bfloat16
+    x0 = torch.randn(T, H, device=DEV)
+    delta = torch.randn(T, H, device=DEV)
+    nw = 1.0 + 0.1 * torch.randn(H, device=DEV)
+    wr = torch.randn(E, H, device=DEV).to(wdt)
+    wsg = torch.randn(H, device=DEV).to(wdt)
+    seq = torch.zeros(T, dtype=torch.int32, device=DEV)
+    if T > 4:
+        seq[T - 2] = -1                                           # a padding row
+    st = torch.zeros(4, dtype=torch.int32, device=DEV)
+    eps = 1e-5
+    # the separate kernels
+    x1 = x0.clone()
+    o32 = torch.empty(T, H, device=DEV)
+    o16 = torch.empty(T, H, device=DEV, dtype=torch.bfloat16) if bf16 else None
+    core.rmsnorm(x1, nw, eps, delta=delta, out32=o32, out16=o16, write_back=True, status=st)
+    idx1, w1, sg1, offs1, _, _, _ = core.route_dispatch(o32, wr, k, norm, 1.5, shared_gate_w=wsg, seq_of_token=seq,
+                                                       gather=o16, status=st)
+    # the fused kernel
+    x2 = x0.clone()
+    res = core.norm_route(x2, delta, nw, eps, wr, k, norm, 1.5, bf16=bf16, shared_gate_w=wsg, seq_of_token=seq,
+                          status=st)
+    assert res is not None
+    out32, out16, idx, w, sg, offs, sorted_token, pos, xs = res
+    assert int(st[0]) == 0
+    assert torch.equal(x1, x2)
+    if bf16:
+        assert out32 is None and float((out16.float() - o16.float()).abs().max()) <= 2.0 ** -7 * float(o16.float().abs().max())
+    else:
+        assert out16 is None and torch.allclose(out32, o32, rtol=1e-5, atol=1e-6)
+    # picks: equal, or the probabilities of the differing experts agree to rounding
+    probs = torch.softmax(o32.double() @ wr.double().T, dim=-1)
+    for t in range(T):
+        a, b = set(idx1[t].tolist()), set(idx[t].tolist())
+        if a != b:
+            diff = sorted(a ^ b)
+            assert a != {-1} and float(probs[t, diff].max() - probs[t, diff].min()) < 1e-5, (t, a, b)
+        else:
+            order = torch.argsort(idx[t]), torch.argsort(idx1[t])
+            assert torch.allclose(w[t][order[0]], w1[t][order[1]], rtol=1e-4, atol=1e-7)
+    assert torch.allclose(sg, sg1, rtol=1e-4, atol=1e-6)
+    total = int(offs[-1])
+    flat = idx.reshape(-1).cpu()
+    seen = set()
+    for pair in range(T * k):                                     # the inversion is a valid one
+        e, p = int(flat[pair]), int(pos[pair])
+        if e < 0:
+            assert p == -1
+            continue
+        assert int(offs[e]) <= p < int(offs[e + 1]) and p not in seen and int(sorted_token[p]) == pair // k
+        seen.add(p)
+    assert len(seen) == total
+    assert (xs is not None) == (bf16 and (H * 2) % 16 == 0)
+    if xs is not None:
+        assert torch.equal(xs[:total], out16[sorted_token[:total].long()])
+    assert int(core._tickets(DEV, 1).abs().sum()) == 0
