@@ -104,6 +104,32 @@ static inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
     return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// The same with thread-block clusters of `cluster_z` CTAs along grid.z (1: no clusters).
+template <typename... KArgs, typename... Args>
+static inline int launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     int cluster_z, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (cluster_z > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 1, attr[n].val.clusterDim.y = 1, attr[n].val.clusterDim.z = (unsigned)cluster_z;
+        n++;
+    }
+    if (g_pdl_enabled) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        n++;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Logical position -> (page, offset) of a paged, optionally ring-shaped, cache.
 //   ring:  positions wrap at `ring` (a multiple of the page size); 0 = no wrap
 //   table: the sequence's page list; page p holds `page_size` consecutive positions

@@ -55,7 +55,8 @@ struct Params {
     int w_rows_per_group;       // N, or 2 N for SWIGLU
     int splits;                 // K splits (>= 1), every split non-empty
     int kb_per_split;
-    float* partials;            // [splits][M][cols] float32, cols = N or 2 N
+    int cluster;                // 1: the splits of a tile are one cluster and add up through shared memory
+    float* partials;            // [splits][M][cols] float32, cols = N or 2 N (not with cluster)
     int* tickets;               // one per (grid.y, grid.x), zero before and after the launch
     int* status;
 };
@@ -93,6 +94,27 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
         : "memory");
+}
+// ---- thread-block clusters (the K splits of one tile) ----
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// address of the same shared-memory location in the CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa_cluster(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+    return v;
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
@@ -158,6 +180,8 @@ struct Cfg {
     static constexpr int TMEM_COLS_RAW = NW * BN;
     static constexpr int TMEM_COLS = TMEM_COLS_RAW < 32 ? 32 : TMEM_COLS_RAW;
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+    // the partial tile of a K split fits in the (then free) pipeline stages
+    static constexpr bool CLUSTER_OK = NW * BN * TILE_W * 4 <= STAGES * STAGE_BYTES;
 };
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
@@ -328,7 +352,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             const int cols = MODE == MODE_SWIGLU ? 2 * p.N : p.N;
             const float bias = (MODE == MODE_PLAIN && p.bias && n_ok) ? p.bias[n] : 0.f;
             const int rows_here = min(BN, row_end - row0);
-            if (p.splits == 1) {
+            if (p.cluster) {
+                // the K splits of a tile are the CTAs of one cluster: each leaves its partial tile in
+                // its own shared memory (the pipeline stages are free by now), as [acc][row][feature]
+                float* stage = reinterpret_cast<float*>(smem_raw + (base - smem_u32(smem_raw)));
+                const int f = q * 32 + lane;
+                for (int c0 = 0; c0 < rows_here; c0 += 16) {
+                    float a[16], b[16];
+                    __syncwarp();
+                    tmem_ld16(taddr + c0, a);
+                    if (MODE == MODE_SWIGLU) tmem_ld16(taddr + BN + c0, b);
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        if (c0 + j < rows_here) {
+                            stage[(c0 + j) * TILE_W + f] = a[j];
+                            if (MODE == MODE_SWIGLU) stage[(BN + c0 + j) * TILE_W + f] = b[j];
+                        }
+                    }
+                }
+            } else if (p.splits == 1) {
                 for (int c0 = 0; c0 < rows_here; c0 += 16) {      // trip count uniform per warp
                     float a[16], b[16];
                     __syncwarp();
@@ -378,27 +420,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     __threadfence();
                     if (n_ok) {
                         const size_t split_stride = (size_t)p.M * cols;
-                        for (int t = row0; t < row0 + rows_here; t++) {
-                            // all splits' values are requested before any is used: one memory latency
-                            // per row instead of one per split; the sum keeps the split order
-                            const float* src = p.partials + (size_t)t * cols + n;
-                            float va[MAX_SPLITS], vb[MAX_SPLITS];
+                        // RB rows at a time: the values of all their splits are requested before any
+                        // is used, so a block of rows costs one memory latency; each sum keeps the
+                        // split order
+                        constexpr int RB = MODE == MODE_SWIGLU ? 2 : 4;
+                        for (int t0 = row0; t0 < row0 + rows_here; t0 += RB) {
+                            float va[RB][MAX_SPLITS], vb[RB][MAX_SPLITS];
 #pragma unroll
-                            for (int s = 0; s < MAX_SPLITS; s++) {
-                                va[s] = s < p.splits ? __ldcg(src + s * split_stride) : 0.f;
-                                if (MODE == MODE_SWIGLU) vb[s] = s < p.splits ? __ldcg(src + s * split_stride + p.N) : 0.f;
-                            }
-                            float sa = 0.f, sb = 0.f;
+                            for (int r = 0; r < RB; r++) {
+                                const bool live = t0 + r < row0 + rows_here;
+                                const float* src = p.partials + (size_t)(t0 + r) * cols + n;
 #pragma unroll
-                            for (int s = 0; s < MAX_SPLITS; s++) {
-                                sa += va[s];
-                                if (MODE == MODE_SWIGLU) sb += vb[s];
+                                for (int s = 0; s < MAX_SPLITS; s++) {
+                                    const bool on = live && s < p.splits;
+                                    va[r][s] = on ? __ldcg(src + s * split_stride) : 0.f;
+                                    if (MODE == MODE_SWIGLU) vb[r][s] = on ? __ldcg(src + s * split_stride + p.N) : 0.f;
+                                }
                             }
-                            const float v = MODE == MODE_SWIGLU ? silu_mul(sa, sb) : sa + bias;
-                            if (p.out_bf16)
-                                ((__nv_bfloat16*)p.out)[(size_t)t * p.ldo + n] = __float2bfloat16_rn(v);
-                            else
-                                ((float*)p.out)[(size_t)t * p.ldo + n] = v;
+#pragma unroll
+                            for (int r = 0; r < RB; r++) {
+                                const int t = t0 + r;
+                                if (t >= row0 + rows_here) break;
+                                float sa = 0.f, sb = 0.f;
+#pragma unroll
+                                for (int s = 0; s < MAX_SPLITS; s++) {
+                                    sa += va[r][s];
+                                    if (MODE == MODE_SWIGLU) sb += vb[r][s];
+                                }
+                                const float v = MODE == MODE_SWIGLU ? silu_mul(sa, sb) : sa + bias;
+                                if (p.out_bf16)
+                                    ((__nv_bfloat16*)p.out)[(size_t)t * p.ldo + n] = __float2bfloat16_rn(v);
+                                else
+                                    ((float*)p.out)[(size_t)t * p.ldo + n] = v;
+                            }
                         }
                     }
                 }
@@ -407,6 +461,53 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     }
     tc_fence_before();
     __syncthreads();
+    if (p.cluster) {
+        // Every thread of every CTA of the cluster comes here (all waits above are bounded), so the
+        // two cluster barriers always complete.  Between them CTA r adds, for the rows r, r + S, ...
+        // of the tile, the S partial values in split order (reading its peers' shared memory) and
+        // writes the result; after the second barrier no peer reads this CTA's memory any more.
+        cluster_sync_all();
+        if (warp >= 2 && !s_abort) {
+            const uint32_t S = (uint32_t)p.splits, rank = cluster_ctarank();
+            const int f = (warp & 3) * 32 + lane, n = n0 + f;
+            const int rows_here = min(BN, row_end - row0);
+            const float bias = (MODE == MODE_PLAIN && p.bias && n < p.N) ? p.bias[n] : 0.f;
+            uint32_t peer[8];
+#pragma unroll
+            for (uint32_t s = 0; s < 8; s++) peer[s] = mapa_cluster(base, s < S ? s : 0);
+            for (int t0 = (int)rank; t0 < rows_here; t0 += 2 * (int)S) {
+                float va[2][8], vb[2][8];
+#pragma unroll
+                for (int r = 0; r < 2; r++) {
+                    const int t = t0 + r * (int)S;
+#pragma unroll
+                    for (uint32_t s = 0; s < 8; s++) {
+                        const bool on = t < rows_here && s < S;
+                        va[r][s] = on ? ld_cluster_f32(peer[s] + (uint32_t)(t * TILE_W + f) * 4u) : 0.f;
+                        if (MODE == MODE_SWIGLU)
+                            vb[r][s] = on ? ld_cluster_f32(peer[s] + (uint32_t)((BN + t) * TILE_W + f) * 4u) : 0.f;
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < 2; r++) {
+                    const int t = t0 + r * (int)S;
+                    if (t >= rows_here || n >= p.N) continue;
+                    float sa = 0.f, sb = 0.f;
+#pragma unroll
+                    for (int s = 0; s < 8; s++) {
+                        sa += va[r][s];
+                        if (MODE == MODE_SWIGLU) sb += vb[r][s];
+                    }
+                    const float v = MODE == MODE_SWIGLU ? silu_mul(sa, sb) : sa + bias;
+                    if (p.out_bf16)
+                        ((__nv_bfloat16*)p.out)[(size_t)(row0 + t) * p.ldo + n] = __float2bfloat16_rn(v);
+                    else
+                        ((float*)p.out)[(size_t)(row0 + t) * p.ldo + n] = v;
+                }
+            }
+        }
+        cluster_sync_all();
+    }
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem, C::TMEM_COLS);
@@ -444,8 +545,10 @@ bool make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, u
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+constexpr int MAX_CLUSTER = 8;   // portable cluster size
+
 template <int BN, int MODE>
-int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& p, dim3 grid, cudaStream_t stream) {
+int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, Params p, dim3 grid, cudaStream_t stream) {
     using C = Cfg<BN, MODE>;
     static bool configured = false;
     if (!configured) {
@@ -453,7 +556,10 @@ int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& p, dim3
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    return launch_pdl(gemm_tc_kernel<BN, MODE>, grid, dim3(192), (size_t)C::SMEM, stream, tmW, tmX, p);
+    p.cluster = (p.splits > 1 && p.splits <= MAX_CLUSTER && C::CLUSTER_OK) ? 1 : 0;
+    if (p.splits > 1 && !p.cluster && (!p.partials || !p.tickets)) return -1;
+    return launch_pdl_cluster(gemm_tc_kernel<BN, MODE>, grid, dim3(192), (size_t)C::SMEM, stream,
+                              p.cluster ? p.splits : 1, tmW, tmX, p);
 }
 
 }  // namespace
@@ -478,8 +584,8 @@ MOE_API int moe_gemm_tc(const void* X, int ldx, const void* W, int num_groups, i
     if (splits > kb_total) splits = kb_total;
     const int per = (kb_total + splits - 1) / splits;
     splits = (kb_total + per - 1) / per;
-    if (splits > 1 && (!partials || !tickets)) return -1;
     Params p;
+    p.cluster = 0;
     p.out = out, p.out_bf16 = out_bf16, p.ldo = ldo, p.bias = bias, p.group_offsets = group_offsets;
     p.num_groups = num_groups, p.M = M, p.N = N, p.K = K, p.w_rows_per_group = w_rows, p.splits = splits;
     p.kb_per_split = per, p.partials = partials, p.tickets = tickets, p.status = status;

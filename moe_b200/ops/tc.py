@@ -127,7 +127,9 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swiglu: bool
         else:
             # few tokens: the weight stream bounds the time; enough CTAs to keep every SM loading
             tiles = n_tiles * (max(1, -(-M // bn)) if not grouped else max(1, min(G, M)))
-            splits = max(1, min(16, (2 * num_sms(x.device)) // max(tiles, 1), -(-K // 64) // 4))
+            # (up to 8 splits add up through the shared memory of a cluster; more would go through
+            # partial sums in global memory)
+            splits = max(1, min(8, (2 * num_sms(x.device)) // max(tiles, 1), -(-K // 64) // 4))
     splits = L.moe_gemm_tc_plan(K, int(splits), M, bn, G, 1 if grouped else 0, core.ctypes.byref(gy))
     partials = tickets = None
     if splits > 1:

@@ -174,7 +174,8 @@ class RoutedExperts(Part):
             topk_idx, topk_w, sg, offsets, sorted_token, pos_of_pair, xs = core.route_dispatch(
                 h.f32, self.w_router, self.k, self.norm_topk, self.scale, shared_gate_w=self.w_sgate,
                 seq_of_token=getattr(batch, "seq_of_token", None),
-                gather=h.act if h.act.dtype == torch.bfloat16 else None, status=rt.status)
+                gather=h.act if h.act.dtype == torch.bfloat16 and T <= 16 else None, status=rt.status)
+            # (more tokens: the gather by that one block would take longer than a launch of its own)
         else:
             topk_idx, topk_w, sg = self.route(rt, h, batch)
             offsets = rt.empty((self.E + 1,), torch.int32)

@@ -27,7 +27,7 @@ def rel(got, ref):
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 200, 72), (13, 2056, 2048), (64, 384, 200), (100, 130, 1408),
                                     (300, 256, 512), (2, 6144, 2048)])
 @pytest.mark.parametrize("bn", [16, 64, 256])
-@pytest.mark.parametrize("splits", [1, 3])
+@pytest.mark.parametrize("splits", [1, 3, 12])    # up to 8: summed inside a cluster; more: through global memory
 def test_plain(tc, M, N, K, bn, splits):
     torch.manual_seed(M * 1000 + N + K)
     x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
@@ -44,7 +44,7 @@ def test_plain(tc, M, N, K, bn, splits):
 
 @pytest.mark.parametrize("M,I,K", [(5, 128, 64), (8, 1408, 2048), (70, 48, 96), (33, 200, 520)])
 @pytest.mark.parametrize("bn", [16, 128])
-@pytest.mark.parametrize("splits", [1, 4])
+@pytest.mark.parametrize("splits", [1, 4, 9])
 def test_swiglu(tc, M, I, K, bn, splits):
     torch.manual_seed(M + I)
     x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
