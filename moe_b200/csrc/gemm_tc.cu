@@ -160,10 +160,9 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
     return d;
 }
 
-template <int BN>
-__host__ __device__ constexpr uint32_t instr_desc() {
+__host__ __device__ constexpr uint32_t instr_desc(int n) {
     // c = f32 (1 << 4), a = bf16 (1 << 7), b = bf16 (1 << 10), both K-major, N >> 3 at 17, M >> 4 at 24
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TILE_W >> 4) << 24);
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TILE_W >> 4) << 24);
 }
 
 template <int BN, int MODE>
@@ -171,6 +170,7 @@ struct Cfg {
     static constexpr int NW = MODE == MODE_SWIGLU ? 2 : 1;
     static constexpr int W_BYTES = TILE_W * BK * 2;
     static constexpr int X_BYTES = BN * BK * 2;
+    static constexpr int XBOX = BN < 64 ? BN : 64;      // rows of one activation box
     static constexpr int STAGE_BYTES = NW * W_BYTES + X_BYTES;
     // few tokens: the weight stream bounds the time, and two CTAs per SM (each with fewer stages)
     // hide one CTA's set-up and epilogue behind the other's loads
@@ -265,6 +265,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     const int kb0 = split * p.kb_per_split;
     const int kb1 = min(kb_total, kb0 + p.kb_per_split);
     const int w_row = g * p.w_rows_per_group + n0;
+    // A tile with fewer than BN rows multiplies only as many tokens as it has (the MMA's N, in steps
+    // of 16) and loads only the 64-row boxes of activations that hold them.
+    constexpr int XBOX = C::XBOX;
+    const int n_eff = min(BN, (min(BN, row_end - row0) + 15) & ~15);
+    const int xchunks = (n_eff + XBOX - 1) / XBOX;
+    const uint32_t stage_tx = C::NW * C::W_BYTES + xchunks * XBOX * BK * 2;
+    auto load_x = [&](uint32_t st, int kb, uint32_t bar) {
+        for (int c = 0; c < xchunks; c++)
+            tma_load_2d(st + C::NW * C::W_BYTES + c * XBOX * BK * 2, &tmX, kb * BK, row0 + c * XBOX, bar);
+    };
 
     if (warp == 0) {
         // ---- producer ---------------------------------------------------------------------
@@ -277,13 +287,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 const int pre = min(C::STAGES, kb1 - kb0);
                 for (int i = 0; i < pre; i++) {
                     const uint32_t st = base + i * C::STAGE_BYTES;
-                    mbar_expect_tx(full_bar(i), C::STAGE_BYTES);
+                    mbar_expect_tx(full_bar(i), stage_tx);
                     tma_load_2d(st, &tmW, (kb0 + i) * BK, w_row, full_bar(i));
                     if (MODE == MODE_SWIGLU) tma_load_2d(st + C::W_BYTES, &tmW, (kb0 + i) * BK, w_row + p.N, full_bar(i));
                 }
                 pdl_sync();
-                for (int i = 0; i < pre; i++)
-                    tma_load_2d(base + i * C::STAGE_BYTES + C::NW * C::W_BYTES, &tmX, (kb0 + i) * BK, row0, full_bar(i));
+                for (int i = 0; i < pre; i++) load_x(base + i * C::STAGE_BYTES, kb0 + i, full_bar(i));
                 issued = pre;
                 kb_next = kb0 + pre;
             }
@@ -293,10 +302,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 ok = mbar_wait(empty_bar(s), ph ^ 1, &s_abort);
                 if (!ok) break;
                 const uint32_t st = base + s * C::STAGE_BYTES;
-                mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+                mbar_expect_tx(full_bar(s), stage_tx);
                 tma_load_2d(st, &tmW, kb * BK, w_row, full_bar(s));
                 if (MODE == MODE_SWIGLU) tma_load_2d(st + C::W_BYTES, &tmW, kb * BK, w_row + p.N, full_bar(s));
-                tma_load_2d(st + C::NW * C::W_BYTES, &tmX, kb * BK, row0, full_bar(s));
+                load_x(st, kb, full_bar(s));
             }
             if (!ok) {
                 atomicOr(p.status, ST_WAIT_TIMEOUT);
@@ -309,7 +318,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     } else if (warp == 1) {
         // ---- MMA issuer -------------------------------------------------------------------
         if (lane == 0) {
-            constexpr uint32_t idesc = instr_desc<BN>();
+            const uint32_t idesc = instr_desc(n_eff);
             bool ok = true;
             int it = 0;
             for (int kb = kb0; kb < kb1; kb++, it++) {
@@ -577,7 +586,7 @@ MOE_API int moe_gemm_tc(const void* X, int ldx, const void* W, int num_groups, i
     const int w_rows = mode == MODE_SWIGLU ? 2 * N : N;
     CUtensorMap tmW, tmX;
     if (!make_map(&tmW, W, (uint64_t)num_groups * w_rows, K, K, TILE_W)) return -1;
-    if (!make_map(&tmX, X, M, K, ldx, bn)) return -1;
+    if (!make_map(&tmX, X, M, K, ldx, bn < 64 ? bn : 64)) return -1;
     const int kb_total = (K + BK - 1) / BK;
     if (splits < 1) splits = 1;
     if (splits > MAX_SPLITS) splits = MAX_SPLITS;
