@@ -523,6 +523,224 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     }
 }
 
+// ---- the persistent form, for many tokens ------------------------------------------------------
+// One CTA per SM walks over the tiles (blockIdx.x, blockIdx.x + gridDim.x, ...).  The producer and
+// the MMA issuer run ahead across tile borders, and the accumulator in tensor memory is doubled,
+// so that the epilogue of one tile (tensor memory -> registers -> global memory) runs while the
+// tensor cores work on the next.  No K split here.  Tile order: all token tiles of one feature
+// tile first, so that CTAs running at the same time share weight tiles in L2.
+template <int BN, int MODE>
+struct PCfg {
+    static constexpr int NW = MODE == MODE_SWIGLU ? 2 : 1;
+    static constexpr int W_BYTES = TILE_W * BK * 2;
+    static constexpr int XBOX = 64;
+    static constexpr int STAGE_BYTES = NW * W_BYTES + BN * BK * 2;
+    static constexpr int STAGES_RAW = (196 * 1024) / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+    static constexpr int ACC_COLS = NW * BN;            // columns of one accumulator buffer
+    static constexpr int TMEM_COLS = 2 * ACC_COLS;      // 256 or 512: a power of two
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
+    static_assert(BN >= 64 && TMEM_COLS <= 512 && STAGES >= 2, "tile does not fit");
+};
+
+struct Tile {
+    int g, row0, row_end, n0;
+};
+
+// item -> tile.  prefix[i]: token tiles of the groups before i (grouped), in shared memory.
+template <int BN>
+__device__ __forceinline__ Tile tile_of(int item, int m_tiles, const Params& p, const int* prefix, const int* offs) {
+    Tile t;
+    const int nt = item / m_tiles, m = item % m_tiles;
+    t.n0 = nt * TILE_W;
+    if (!p.group_offsets) {
+        t.g = 0, t.row0 = m * BN, t.row_end = p.M;
+        return t;
+    }
+    int lo = 0, hi = p.num_groups;          // the last group whose first tile is <= m
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (prefix[mid] <= m) lo = mid; else hi = mid;
+    }
+    t.g = lo, t.row0 = offs[lo] + (m - prefix[lo]) * BN, t.row_end = offs[lo + 1];
+    return t;
+}
+
+template <int BN, int MODE>
+__global__ void __launch_bounds__(192)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                          const Params p) {
+    using C = PCfg<BN, MODE>;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ volatile int s_abort;
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_offs[MAX_SMEM_GROUPS + 1], s_prefix[MAX_SMEM_GROUPS + 1];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_sync();
+
+    // ---- the list of tiles ---------------------------------------------------------------------
+    int m_tiles = (p.M + BN - 1) / BN;
+    if (p.group_offsets) {
+        for (int i = threadIdx.x; i <= p.num_groups; i += blockDim.x) s_offs[i] = p.group_offsets[i];
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int run = 0;
+            for (int i = 0; i < p.num_groups; i++) {
+                s_prefix[i] = run;
+                run += (s_offs[i + 1] - s_offs[i] + BN - 1) / BN;
+            }
+            s_prefix[p.num_groups] = run;
+        }
+    }
+    if (threadIdx.x == 0) s_abort = 0;
+    __syncthreads();
+    if (p.group_offsets) m_tiles = s_prefix[p.num_groups];
+    const int items = m_tiles * ((p.N + TILE_W - 1) / TILE_W);
+
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar_base = base + C::STAGES * C::STAGE_BYTES;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (C::STAGES + s); };
+    auto acc_full = [&](int b) { return bar_base + 8u * (2 * C::STAGES + b); };
+    auto acc_empty = [&](int b) { return bar_base + 8u * (2 * C::STAGES + 2 + b); };
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; s++) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(acc_full(b), 1);
+            mbar_init(acc_empty(b), 4);      // one arrival per epilogue warp
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(&s_tmem), C::TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem;
+    const int kbs = (p.K + BK - 1) / BK;
+
+    if (warp == 0) {
+        // ---- producer: one ring of stages across all tiles ---------------------------------------
+        if (lane == 0) {
+            int issued = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+                const Tile t = tile_of<BN>(item, m_tiles, p, s_prefix, s_offs);
+                const int n_eff = min(BN, (min(BN, t.row_end - t.row0) + 15) & ~15);
+                const int xchunks = (n_eff + C::XBOX - 1) / C::XBOX;
+                const uint32_t stage_tx = C::NW * C::W_BYTES + xchunks * C::XBOX * BK * 2;
+                const int w_row = t.g * p.w_rows_per_group + t.n0;
+                for (int kb = 0; kb < kbs; kb++, issued++) {
+                    const int s = issued % C::STAGES;
+                    ok = mbar_wait(empty_bar(s), ((issued / C::STAGES) & 1) ^ 1, &s_abort);
+                    if (!ok) break;
+                    const uint32_t st = base + s * C::STAGE_BYTES;
+                    mbar_expect_tx(full_bar(s), stage_tx);
+                    tma_load_2d(st, &tmW, kb * BK, w_row, full_bar(s));
+                    if (MODE == MODE_SWIGLU) tma_load_2d(st + C::W_BYTES, &tmW, kb * BK, w_row + p.N, full_bar(s));
+                    for (int c = 0; c < xchunks; c++)
+                        tma_load_2d(st + C::NW * C::W_BYTES + c * C::XBOX * BK * 2, &tmX, kb * BK,
+                                    t.row0 + c * C::XBOX, full_bar(s));
+                }
+            }
+            if (!ok) {
+                atomicOr(p.status, ST_WAIT_TIMEOUT);
+                s_abort = 1;
+                for (int i = max(0, issued - C::STAGES); i < issued; i++)     // copies in flight must land
+                    mbar_wait(full_bar(i % C::STAGES), (i / C::STAGES) & 1, nullptr);
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer: accumulator buffer (tile & 1) -------------------------------------------
+        if (lane == 0) {
+            int consumed = 0, local = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; item < items && ok; item += gridDim.x, local++) {
+                const Tile t = tile_of<BN>(item, m_tiles, p, s_prefix, s_offs);
+                const int n_eff = min(BN, (min(BN, t.row_end - t.row0) + 15) & ~15);
+                const uint32_t idesc = instr_desc(n_eff);
+                const int b = local & 1;
+                ok = mbar_wait(acc_empty(b), ((local >> 1) & 1) ^ 1, &s_abort);   // the epilogue has drained it
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t acc_addr = tmem + b * C::ACC_COLS;
+                for (int kb = 0; kb < kbs; kb++, consumed++) {
+                    const int s = consumed % C::STAGES;
+                    ok = mbar_wait(full_bar(s), (consumed / C::STAGES) & 1, &s_abort);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t st = base + s * C::STAGE_BYTES;
+#pragma unroll
+                    for (int k4 = 0; k4 < BK / UMMA_K; k4++) {
+                        const uint32_t koff = k4 * UMMA_K * 2;
+                        const uint64_t bdesc = smem_desc(st + C::NW * C::W_BYTES + koff);
+                        const uint32_t acc = (kb > 0 || k4 > 0) ? 1u : 0u;
+                        umma_bf16(acc_addr, smem_desc(st + koff), bdesc, idesc, acc);
+                        if (MODE == MODE_SWIGLU)
+                            umma_bf16(acc_addr + BN, smem_desc(st + C::W_BYTES + koff), bdesc, idesc, acc);
+                    }
+                    umma_commit(empty_bar(s));
+                }
+                if (ok) umma_commit(acc_full(b));
+            }
+            if (!ok) {
+                atomicOr(p.status, ST_WAIT_TIMEOUT);
+                s_abort = 1;
+            }
+        }
+    } else {
+        // ---- epilogue ----------------------------------------------------------------------------
+        const int q = warp & 3;
+        int local = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < items && ok; item += gridDim.x, local++) {
+            const Tile t = tile_of<BN>(item, m_tiles, p, s_prefix, s_offs);
+            const int b = local & 1;
+            ok = mbar_wait(acc_full(b), (local >> 1) & 1, &s_abort);
+            if (!ok) break;
+            tc_fence_after();
+            const int n = t.n0 + q * 32 + lane;
+            const bool n_ok = n < p.N;
+            const uint32_t taddr = tmem + b * C::ACC_COLS + ((uint32_t)(q * 32) << 16);
+            const float bias = (MODE == MODE_PLAIN && p.bias && n_ok) ? p.bias[n] : 0.f;
+            const int rows_here = min(BN, t.row_end - t.row0);
+            for (int c0 = 0; c0 < rows_here; c0 += 16) {
+                float a[16], bb[16];
+                __syncwarp();
+                tmem_ld16(taddr + c0, a);
+                if (MODE == MODE_SWIGLU) tmem_ld16(taddr + BN + c0, bb);
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    const int r = t.row0 + c0 + j;
+                    if (n_ok && r < t.row_end) {
+                        const float v = MODE == MODE_SWIGLU ? silu_mul(a[j], bb[j]) : a[j] + bias;
+                        if (p.out_bf16)
+                            ((__nv_bfloat16*)p.out)[(size_t)r * p.ldo + n] = __float2bfloat16_rn(v);
+                        else
+                            ((float*)p.out)[(size_t)r * p.ldo + n] = v;
+                    }
+                }
+            }
+            // this warp has read its part of the buffer: the MMA issuer may overwrite it
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(b)) : "memory");
+        }
+        if (!ok && lane == 0) {
+            atomicOr(p.status, ST_WAIT_TIMEOUT);
+            s_abort = 1;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, C::TMEM_COLS);
+    }
+}
+
 // ---- host side ------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -571,6 +789,34 @@ int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, Params p, dim3 grid, 
                               p.cluster ? p.splits : 1, tmW, tmX, p);
 }
 
+int g_persistent = 1;
+
+int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            n = 0;
+        if (n <= 0) n = 1;
+    }
+    return n;
+}
+
+template <int BN, int MODE>
+int launch_persistent(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& p, int max_items,
+                      cudaStream_t stream) {
+    using C = PCfg<BN, MODE>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, MODE>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int ctas = max_items < sm_count() ? max_items : sm_count();
+    return launch_pdl(gemm_tc_persistent_kernel<BN, MODE>, dim3(ctas), dim3(192), (size_t)C::SMEM, stream, tmW, tmX, p);
+}
+
 }  // namespace
 
 // X: [M, K] bf16 with row pitch ldx; W: [G * w_rows, K] bf16 contiguous; out: [M, ldo].
@@ -600,6 +846,16 @@ MOE_API int moe_gemm_tc(const void* X, int ldx, const void* W, int num_groups, i
     p.kb_per_split = per, p.partials = partials, p.tickets = tickets, p.status = status;
     // token tiles: sum over groups of ceil(rows / bn) <= (non-empty groups) + floor(M / bn); CTAs past
     // the real count leave at once, but each still reserves its shared memory, so the bound is kept tight
+    if (splits == 1 && bn >= 128 && g_persistent && (!group_offsets || num_groups <= MAX_SMEM_GROUPS)) {
+        // many tokens: the persistent form (SwiGLU keeps two accumulators, so its widest tile is 128)
+        const int pbn = (mode == MODE_SWIGLU || bn == 128) ? 128 : 256;
+        const int mt = group_offsets ? (M < num_groups ? M : num_groups) + M / pbn : (M + pbn - 1) / pbn;
+        const long long max_items = (long long)mt * ((N + TILE_W - 1) / TILE_W);
+        const int cap = max_items > (1 << 30) ? (1 << 30) : (int)max_items;
+        if (mode == MODE_SWIGLU) return launch_persistent<128, MODE_SWIGLU>(tmW, tmX, p, cap, stream);
+        if (pbn == 128) return launch_persistent<128, MODE_PLAIN>(tmW, tmX, p, cap, stream);
+        return launch_persistent<256, MODE_PLAIN>(tmW, tmX, p, cap, stream);
+    }
     const int m_tiles = group_offsets ? (M < num_groups ? M : num_groups) + M / bn : (M + bn - 1) / bn;
     dim3 grid((N + TILE_W - 1) / TILE_W, m_tiles, splits);
     if (grid.y > 65535 || grid.z > 65535) return -1;
@@ -614,6 +870,9 @@ MOE_API int moe_gemm_tc(const void* X, int ldx, const void* W, int num_groups, i
 
 // Programmatic dependent launch on or off for the kernels of this library (on by default).
 MOE_API void moe_tc_set_pdl(int enabled) { g_pdl_enabled = enabled ? 1 : 0; }
+
+// The persistent form for many tokens on or off (on by default; off: one CTA per tile).
+MOE_API void moe_tc_set_persistent(int enabled) { g_persistent = enabled ? 1 : 0; }
 
 // How many K splits the kernel will really use for (K, splits asked), and its grid.y for tickets.
 MOE_API int moe_gemm_tc_plan(int K, int splits, int M, int bn, int num_groups, int grouped, int* grid_y) {

@@ -38,6 +38,10 @@ def lib():
 
         if os.environ.get("MOE_B200_PDL", "1") == "0":      # programmatic dependent launch off
             L.moe_tc_set_pdl(0)
+        L.moe_tc_set_persistent.argtypes = [c_int]
+        L.moe_tc_set_persistent.restype = None
+        if os.environ.get("MOE_B200_PERSISTENT", "1") == "0":   # one CTA per tile also for many tokens
+            L.moe_tc_set_persistent(0)
         _lib = L
     return _lib
 

@@ -60,7 +60,7 @@ def test_swiglu(tc, M, I, K, bn, splits):
 
 
 @pytest.mark.parametrize("swiglu", [False, True])
-@pytest.mark.parametrize("bn", [16, 32, 128])
+@pytest.mark.parametrize("bn", [16, 32, 128, 256])
 @pytest.mark.parametrize("splits", [1, 2])
 def test_grouped(tc, swiglu, bn, splits):
     G, N, K = 7, 160, 264
@@ -82,6 +82,48 @@ def test_grouped(tc, swiglu, bn, splits):
             ref[o:o + c] = a / (1 + torch.exp(-a)) * b
         else:
             ref[o:o + c] = xs @ w[g].double().T
+        o += c
+    assert int(st[0]) == 0 and rel(out, ref) < 2e-5
+
+
+@pytest.mark.parametrize("swiglu,bn", [(False, 256), (False, 128), (True, 128)])
+def test_many_tiles_per_cta(tc, swiglu, bn):
+    """More tiles than SMs: the persistent form walks several tiles per CTA, its stage ring wraps
+    across tile borders and both accumulator buffers are used again and again."""
+    M, N, K = 2304 + 40, 8192 + 72, 264
+    torch.manual_seed(bn)
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(2 * N if swiglu else N, K, device=DEV) * 0.1).to(torch.bfloat16)
+    out = torch.full((M, N), float("nan"), device=DEV)
+    st = status()
+    assert tc.gemm_tc(x, w, out, swiglu=swiglu, bn=bn, splits=1, status=st)
+    if swiglu:
+        a, b = x.double() @ w[:N].double().T, x.double() @ w[N:].double().T
+        ref = a / (1 + torch.exp(-a)) * b
+    else:
+        ref = x.double() @ w.double().T
+    assert int(st[0]) == 0 and rel(out, ref) < 2e-5
+
+
+def test_grouped_many_tiles_per_cta(tc):
+    """Sixty groups of uneven size (some empty), more tiles than SMs."""
+    G, N, K = 60, 1408, 200
+    rng = np.random.default_rng(5)
+    counts = rng.integers(0, 300, size=G)
+    counts[[3, 17, 59]] = 0
+    M = int(counts.sum())
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(G, 2 * N, K, device=DEV) * 0.1).to(torch.bfloat16)
+    offs = torch.tensor(np.concatenate([[0], np.cumsum(counts)]), dtype=torch.int32, device=DEV)
+    out = torch.full((M, N), float("nan"), device=DEV)
+    st = status()
+    assert tc.gemm_tc(x, w, out, swiglu=True, group_offsets=offs, bn=256, splits=1, status=st)
+    ref = torch.empty(M, N, dtype=torch.float64, device=DEV)
+    o = 0
+    for g, c in enumerate(counts.tolist()):
+        xs = x[o:o + c].double()
+        a, b = xs @ w[g, :N].double().T, xs @ w[g, N:].double().T
+        ref[o:o + c] = a / (1 + torch.exp(-a)) * b
         o += c
     assert int(st[0]) == 0 and rel(out, ref) < 2e-5
 
