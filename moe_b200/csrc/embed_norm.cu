@@ -41,7 +41,7 @@ MOE_API int moe_embed(const void* table, int table_dt, const int* tokens, float*
 __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, const float* __restrict__ w,
                                const int* __restrict__ rows, float* __restrict__ out32,
                                __nv_bfloat16* __restrict__ out16, int hidden, float eps, int write_back,
-                               int num_src_rows, int* status) {
+                               int num_src_rows, int* status, int vec) {
     extern __shared__ float row[];
     __shared__ float red[32];
     pdl_sync();
@@ -54,6 +54,32 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
     float* xr = x + (size_t)r * hidden;
     const float* dr = delta ? delta + (size_t)r * hidden : nullptr;
     float ss = 0.f;
+    if (vec) {   // rows of whole 16-byte units: four elements per access
+        for (int j = threadIdx.x; j < hidden / 4; j += blockDim.x) {
+            float4 v = reinterpret_cast<const float4*>(xr)[j];
+            if (dr) {
+                const float4 d = reinterpret_cast<const float4*>(dr)[j];
+                v.x += d.x, v.y += d.y, v.z += d.z, v.w += d.w;
+                if (write_back) reinterpret_cast<float4*>(xr)[j] = v;
+            }
+            reinterpret_cast<float4*>(row)[j] = v;
+            ss += v.x * v.x, ss += v.y * v.y, ss += v.z * v.z, ss += v.w * v.w;
+        }
+        ss = block_sum(ss, red);
+        const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
+        for (int j = threadIdx.x; j < hidden / 4; j += blockDim.x) {
+            const float4 v = reinterpret_cast<const float4*>(row)[j], g = reinterpret_cast<const float4*>(w)[j];
+            const float4 y = make_float4(v.x * scale * g.x, v.y * scale * g.y, v.z * scale * g.z, v.w * scale * g.w);
+            if (out32) reinterpret_cast<float4*>(out32 + (size_t)i * hidden)[j] = y;
+            if (out16) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y), hi = __floats2bfloat162_rn(y.z, y.w);
+                uint2 u;
+                u.x = *reinterpret_cast<unsigned*>(&lo), u.y = *reinterpret_cast<unsigned*>(&hi);
+                reinterpret_cast<uint2*>(out16 + (size_t)i * hidden)[j] = u;
+            }
+        }
+        return;
+    }
     for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
         float v = xr[j];
         if (dr) {
@@ -83,8 +109,10 @@ MOE_API int moe_rmsnorm(float* x, const float* delta, const float* w, const int*
         cudaError_t e = cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
+    const int vec = hidden % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)delta % 16 == 0 && (uintptr_t)w % 16 == 0 &&
+                    (uintptr_t)out32 % 16 == 0 && (uintptr_t)out16 % 8 == 0;
     return launch_pdl(rmsnorm_kernel, num_out_rows, threads, smem, stream, x, delta, w, rows, out32,
-                      (__nv_bfloat16*)out16, hidden, eps, write_back, num_src_rows, status);
+                      (__nv_bfloat16*)out16, hidden, eps, write_back, num_src_rows, status, vec);
 }
 
 // Ask for `bytes` at `p` in L2: weights that a later kernel of the step will stream, requested

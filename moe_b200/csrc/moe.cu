@@ -150,6 +150,80 @@ router_logits_tiled_kernel(const float* __restrict__ h, const WT* __restrict__ w
     }
 }
 
+// The product for a whole prompt, register-tiled: a block of 128 threads takes 128 tokens x 64
+// router rows and a slice of the hidden dimension; a thread holds 8 x 8 sums and walks its slice
+// in order, so that every operand fetched from shared memory feeds 8 multiply-adds.  The slices'
+// partial sums go to part[slice][token][row]; sum_slices_kernel adds them in slice order.
+// hidden must be a multiple of 8 and the slice length of 16.
+constexpr int ST = 128, SR = 64, SK = 16;
+template <typename WT>
+__global__ void __launch_bounds__(128)
+router_logits_sgemm_kernel(const float* __restrict__ h, const WT* __restrict__ wr, const WT* __restrict__ wsg,
+                           int num_tokens, int hidden, int num_experts, int rows, int kper,
+                           float* __restrict__ part) {
+    __shared__ __align__(16) float Xs[SK][ST + 4];
+    __shared__ __align__(16) float Ws[SK][SR + 4];
+    const int tid = threadIdx.x, tg = tid % 16, rg = tid / 16;
+    const int t0 = blockIdx.x * ST, r0 = blockIdx.z * SR;
+    const int k0 = blockIdx.y * kper, k1 = min(hidden, k0 + kper);
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[i][j] = 0.f;
+    const int xt = t0 + tid;                         // the token whose activations this thread stages
+    const int wrow = r0 + tid / 2, whalf = tid % 2;   // the router row and the half of the chunk it stages
+    const WT* wp = wrow < num_experts ? wr + (size_t)wrow * hidden : wsg;
+    for (int kk = k0; kk < k1; kk += SK) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (xt < num_tokens && kk + 4 * j < k1) v = *reinterpret_cast<const float4*>(h + (size_t)xt * hidden + kk + 4 * j);
+            Xs[4 * j + 0][tid] = v.x, Xs[4 * j + 1][tid] = v.y, Xs[4 * j + 2][tid] = v.z, Xs[4 * j + 3][tid] = v.w;
+        }
+        {
+            float wv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (wrow < rows && kk + whalf * 8 < k1) w_load8<WT>(wp + kk + whalf * 8, wv);
+#pragma unroll
+            for (int i = 0; i < 8; i++) Ws[whalf * 8 + i][tid / 2] = wv[i];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < SK; k++) {
+            const float4 a0 = *reinterpret_cast<const float4*>(&Xs[k][tg * 4]);
+            const float4 a1 = *reinterpret_cast<const float4*>(&Xs[k][64 + tg * 4]);
+            const float4 b0 = *reinterpret_cast<const float4*>(&Ws[k][rg * 4]);
+            const float4 b1 = *reinterpret_cast<const float4*>(&Ws[k][32 + rg * 4]);
+            const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+#pragma unroll
+                for (int j = 0; j < 8; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+    float* out = part + (size_t)blockIdx.y * num_tokens * rows;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int t = t0 + (i < 4 ? tg * 4 + i : 64 + tg * 4 + i - 4);
+        if (t >= num_tokens) continue;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int r = r0 + (j < 4 ? rg * 4 + j : 32 + rg * 4 + j - 4);
+            if (r < rows) out[(size_t)t * rows + r] = acc[i][j];
+        }
+    }
+}
+
+__global__ void sum_slices_kernel(const float* __restrict__ part, float* __restrict__ out, size_t n, int slices) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float s = 0.f;
+    for (int k = 0; k < slices; k++) s += part[(size_t)k * n + i];
+    out[i] = s;
+}
+
 // Softmax over all experts, top-k and weights of ONE token, by one warp.  `sc` is shared memory
 // of num_experts floats owned by the warp.
 __device__ __forceinline__ void route_token(const float* __restrict__ lg, float* sc, int lane, bool padding,
@@ -340,6 +414,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
     __syncthreads();
     const int first = blockIdx.y * blockDim.x + threadIdx.x, step = gridDim.y * blockDim.x;
     if (vec) {   // four columns per thread, 16-byte accesses
+#pragma unroll 2
         for (int c4 = first; c4 < hidden / 4; c4 += step) {
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 4
@@ -612,10 +687,32 @@ MOE_API int moe_norm_route(float* x, const float* delta, const float* norm_w, fl
     return launch_pdl(kernel, num_tokens, 1024, smem, stream, p);
 }
 
+// Slices of the hidden dimension the register-tiled kernel would use for this size (0: the size
+// goes to another kernel); it then wants slices * num_tokens * rows floats of scratch.
+static int router_slices(int num_tokens, int hidden, int rows, int* kper) {
+    if (num_tokens <= 256 || hidden % 8) return 0;
+    const long long blocks = (long long)((num_tokens + ST - 1) / ST) * ((rows + SR - 1) / SR);
+    int want = (int)((2 * 148 + blocks - 1) / blocks);
+    if (want < 1) want = 1;
+    if (want > hidden / 64) want = hidden / 64 > 0 ? hidden / 64 : 1;
+    int per = (hidden + want - 1) / want;
+    per = (per + SK - 1) / SK * SK;
+    *kper = per;
+    return (hidden + per - 1) / per;
+}
+
+MOE_API long long moe_router_scratch_floats(int num_tokens, int hidden, int num_experts, int has_gate_row) {
+    int kper = 0;
+    const int rows = num_experts + (has_gate_row ? 1 : 0);
+    return (long long)router_slices(num_tokens, hidden, rows, &kper) * num_tokens * rows;
+}
+
 // logits[t, r] = h[t] . W[r] for the router rows (and the shared-gate row, if wsg): num_tokens *
-// (num_experts + (wsg ? 1 : 0)) floats.
+// (num_experts + (wsg ? 1 : 0)) floats.  scratch: moe_router_scratch_floats floats (may be null:
+// a prompt then takes the slower kernel).
 MOE_API int moe_router_logits(const float* h, const void* wr, const void* wsg, int w_dt, int num_tokens, int hidden,
-                              int num_experts, float* logits, cudaStream_t stream) {
+                              int num_experts, float* logits, float* scratch, long long scratch_floats,
+                              cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (num_experts <= 0 || !logits) return (int)cudaErrorInvalidValue;
     const int rows = num_experts + (wsg ? 1 : 0);
@@ -627,7 +724,21 @@ MOE_API int moe_router_logits(const float* h, const void* wr, const void* wsg, i
 #define LOGITS(WT, ROWS, KSPLIT)                                                                          \
     launch_pdl(router_logits_kernel<WT, ROWS, KSPLIT>, dim3((rows + ROWS - 1) / ROWS, ty), ROWS * KSPLIT * 32, 0,   \
                stream, h, (const WT*)wr, (const WT*)wsg, num_tokens, hidden, num_experts, rows, vec_ok, logits)
-    if (num_tokens <= 64) {
+    int kper = 0;
+    const int slices = vec_ok ? router_slices(num_tokens, hidden, rows, &kper) : 0;
+    if (slices > 0 && scratch && scratch_floats >= (long long)slices * num_tokens * rows &&
+        (num_tokens + ST - 1) / ST <= 0x7fffffff && slices <= 65535 && (rows + SR - 1) / SR <= 65535) {
+        const dim3 g((num_tokens + ST - 1) / ST, slices, (rows + SR - 1) / SR);
+        if (w_dt == DT_F32)
+            router_logits_sgemm_kernel<float><<<g, 128, 0, stream>>>(h, (const float*)wr, (const float*)wsg, num_tokens,
+                                                                     hidden, num_experts, rows, kper, scratch);
+        else
+            router_logits_sgemm_kernel<__nv_bfloat16><<<g, 128, 0, stream>>>(
+                h, (const __nv_bfloat16*)wr, (const __nv_bfloat16*)wsg, num_tokens, hidden, num_experts, rows, kper,
+                scratch);
+        const size_t n = (size_t)num_tokens * rows;
+        sum_slices_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(scratch, logits, n, slices);
+    } else if (num_tokens <= 64) {
         if (w_dt == DT_F32) LOGITS(float, 2, 4); else LOGITS(__nv_bfloat16, 2, 4);
     } else if (vec_ok && (num_tokens + PT - 1) / PT <= 65535) {
         const dim3 tg((rows + 7) / 8, (num_tokens + PT - 1) / PT);
@@ -647,11 +758,13 @@ MOE_API int moe_router_logits(const float* h, const void* wr, const void* wsg, i
 // logits: scratch of num_tokens * (num_experts + (wsg ? 1 : 0)) floats.
 MOE_API int moe_router(const float* h, const void* wr, const void* wsg, int w_dt, const int* seq_of_token,
                        int num_tokens, int hidden, int num_experts, int top_k, int norm_topk, float scale,
-                       float* logits, int* topk_idx, float* topk_w, float* shared_gate, cudaStream_t stream) {
+                       float* logits, int* topk_idx, float* topk_w, float* shared_gate, float* scratch,
+                       long long scratch_floats, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (top_k <= 0 || top_k > num_experts || num_experts > 2048 || !logits) return (int)cudaErrorInvalidValue;
     if (wsg && !shared_gate) return (int)cudaErrorInvalidValue;
-    const int rc = moe_router_logits(h, wr, wsg, w_dt, num_tokens, hidden, num_experts, logits, stream);
+    const int rc = moe_router_logits(h, wr, wsg, w_dt, num_tokens, hidden, num_experts, logits, scratch,
+                                     scratch_floats, stream);
     if (rc) return rc;
     const int rows = num_experts + (wsg ? 1 : 0);
     const size_t smem = (size_t)4 * num_experts * sizeof(float);
@@ -703,7 +816,10 @@ MOE_API int moe_combine(const float* y, const int* pos_of_pair, const float* top
     const int vec = hidden % 4 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)out % 16 == 0 &&
                     (!shared || (uintptr_t)shared % 16 == 0);
     const int units = vec ? hidden / 4 : hidden;
-    const int by = max(1, min(64, (units + 127) / 128));
-    return launch_pdl(moe_combine_kernel, dim3(num_tokens, by), 128, (size_t)top_k * 8, stream, y, pos_of_pair, topk_w,
-                      top_k, shared, shared_gate, out, hidden, vec);
+    // few tokens: several small blocks a token, for parallelism; many: one block a token, whose
+    // threads each keep the loads of two columns in flight
+    const int threads = num_tokens >= 512 ? 256 : 128;
+    const int by = num_tokens >= 512 ? 1 : max(1, min(64, (units + 127) / 128));
+    return launch_pdl(moe_combine_kernel, dim3(num_tokens, by), threads, (size_t)top_k * 8, stream, y, pos_of_pair,
+                      topk_w, top_k, shared, shared_gate, out, hidden, vec);
 }

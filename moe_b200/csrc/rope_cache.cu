@@ -19,12 +19,15 @@ __global__ void rope_split_kernel(const float* __restrict__ qkv, const int* __re
     const float p = (float)pos[t];
     const int half = rot / 2;
     const int rot_heads = nh + nkv;   // heads that are rotated: queries then keys
+    // the token's angles once (all heads share them): cos[half], sin[half]
+    extern __shared__ float split_tab[];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(p * inv_freq[i], &split_tab[half + i], &split_tab[i]);
+    __syncthreads();
     // rotated part: one thread per (head, pair)
     for (int idx = threadIdx.x; idx < rot_heads * half; idx += blockDim.x) {
         const int h = idx / half, i = idx % half;
         const float* s = src + (size_t)h * hd;
-        float sn, cs;
-        sincosf(p * inv_freq[i], &sn, &cs);
+        const float cs = split_tab[i], sn = split_tab[half + i];
         const float a = s[i], b = s[i + half];
         OT* dst = h < nh ? q + ((size_t)t * nh + h) * hd : k + ((size_t)t * nkv + (h - nh)) * hd;
         st_f(dst + i, a * cs - b * sn);
@@ -51,11 +54,13 @@ MOE_API int moe_rope_split(const float* qkv, const int* pos, const float* inv_fr
     if (rot < 0 || rot > hd || (rot & 1)) return (int)cudaErrorInvalidValue;
     if (rot > 0 && !inv_freq) return (int)cudaErrorInvalidValue;
     const int threads = 256;
+    if (rot > 8192) return (int)cudaErrorInvalidValue;
+    const size_t smem = (size_t)rot * sizeof(float);
     if (out_dt == DT_F32)
-        rope_split_kernel<float><<<num_tokens, threads, 0, stream>>>(qkv, pos, inv_freq, nh, nkv, hd, rot, (float*)q,
-                                                                      (float*)k, (float*)v);
+        rope_split_kernel<float><<<num_tokens, threads, smem, stream>>>(qkv, pos, inv_freq, nh, nkv, hd, rot, (float*)q,
+                                                                         (float*)k, (float*)v);
     else
-        rope_split_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(
+        rope_split_kernel<__nv_bfloat16><<<num_tokens, threads, smem, stream>>>(
             qkv, pos, inv_freq, nh, nkv, hd, rot, (__nv_bfloat16*)q, (__nv_bfloat16*)k, (__nv_bfloat16*)v);
     return launch_status();
 }

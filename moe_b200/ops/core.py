@@ -38,8 +38,8 @@ def lib():
             "moe_rope_split": [P, P, P, I, I, I, I, I, P, P, P, I, P],
             "moe_kv_commit": [P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
             "moe_attention_generic": [P, P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],
-            "moe_router": [P, P, P, I, P, I, I, I, I, I, F, P, P, P, P, P],
-            "moe_router_logits": [P, P, P, I, I, I, I, P, P],
+            "moe_router": [P, P, P, I, P, I, I, I, I, I, F, P, P, P, P, P, LL, P],
+            "moe_router_logits": [P, P, P, I, I, I, I, P, P, LL, P],
             "moe_route_dispatch": [P, P, I, I, I, I, I, F, P, P, P, P, P, P, P, P, I, P, P],
             "moe_rope_commit": [P, P, P, I, I, I, I, I, P, P, P, I, P, P, P, I, I, I, I, P, P],
             "moe_attention_decode": [P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],
@@ -57,6 +57,8 @@ def lib():
             fn = getattr(L, name)
             fn.argtypes = argtypes
             fn.restype = c_int
+        L.moe_router_scratch_floats.argtypes = [I, I, I, I]
+        L.moe_router_scratch_floats.restype = LL
         L.moe_set_pdl.argtypes = [c_int]
         L.moe_set_pdl.restype = None
         if os.environ.get("MOE_B200_PDL", "1") == "0":      # programmatic dependent launch off
@@ -267,9 +269,11 @@ def router(h32, w_router, top_k, norm_topk, scale, topk_idx, topk_w, *, shared_g
             raise KernelError("router: the shared gate weight must have the router's dtype and width")
         _chk(shared_gate, "shared_gate", torch.float32)
     logits = torch.empty((T, E + (1 if shared_gate_w is not None else 0)), dtype=torch.float32, device=h32.device)
+    need = lib().moe_router_scratch_floats(T, H, E, 1 if shared_gate_w is not None else 0)
+    scratch = torch.empty((need,), dtype=torch.float32, device=h32.device) if need else None
     _ok(lib().moe_router(_p(h32), _p(w_router), _p(shared_gate_w), _dt(w_router), _p(seq_of_token), T, H, E, top_k,
                          1 if norm_topk else 0, float(scale), _p(logits), _p(topk_idx), _p(topk_w), _p(shared_gate),
-                         _stream()), "router")
+                         _p(scratch), need, _stream()), "router")
 
 
 _SMS = {}
@@ -459,7 +463,7 @@ def route_dispatch(h32, w_router, top_k, norm_topk, scale, *, shared_gate_w=None
     dev = h32.device
     rows = E + (1 if shared_gate_w is not None else 0)
     logits = torch.empty((T, rows), dtype=torch.float32, device=dev)
-    _ok(lib().moe_router_logits(_p(h32), _p(w_router), _p(shared_gate_w), _dt(w_router), T, H, E, _p(logits),
+    _ok(lib().moe_router_logits(_p(h32), _p(w_router), _p(shared_gate_w), _dt(w_router), T, H, E, _p(logits), None, 0,
                                 _stream()), "router_logits")
     P_ = T * top_k
     topk_idx = torch.empty((T, top_k), dtype=torch.int32, device=dev)
