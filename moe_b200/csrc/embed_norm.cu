@@ -34,6 +34,19 @@ MOE_API int moe_embed(const void* table, int table_dt, const int* tokens, float*
                       x, hidden, vocab, status);
 }
 
+// A delta that is still the output of routed experts, not yet combined: for token t,
+//   delta[t] = sum_j w[t, j] * y[pos[t, j]] + gate[t] * shared[t]
+// with the arithmetic (and its order) of moe_combine_kernel in moe.cu.  The norm that follows the
+// feed-forward forms it on the fly, which spares one pass over the stream.
+struct CombineSrc {
+    const float* y;        // null: no such delta
+    const int* pos;        // [T, top_k], -1: no expert
+    const float* w;        // [T, top_k]
+    int top_k;
+    const float* shared;   // [T, hidden] or null
+    const float* gate;     // [T] or null
+};
+
 // One block per output row i.  Source row r = rows ? rows[i] : i.
 //   v = x[r] (+ delta[r]);  if write_back: x[r] = v
 //   y = v * rsqrt(mean(v^2) + eps) * w;  out32[i] = y;  out16[i] = bf16(y)
@@ -41,7 +54,7 @@ MOE_API int moe_embed(const void* table, int table_dt, const int* tokens, float*
 __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, const float* __restrict__ w,
                                const int* __restrict__ rows, float* __restrict__ out32,
                                __nv_bfloat16* __restrict__ out16, int hidden, float eps, int write_back,
-                               int num_src_rows, int* status, int vec) {
+                               int num_src_rows, int* status, int vec, const CombineSrc cs) {
     extern __shared__ float row[];
     __shared__ float red[32];
     pdl_sync();
@@ -54,7 +67,34 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
     float* xr = x + (size_t)r * hidden;
     const float* dr = delta ? delta + (size_t)r * hidden : nullptr;
     float ss = 0.f;
-    if (vec) {   // rows of whole 16-byte units: four elements per access
+    if (cs.y) {   // (vec is set: the host refuses this form otherwise)
+        const float g = cs.gate ? cs.gate[r] : 1.0f;
+        for (int j = threadIdx.x; j < hidden / 4; j += blockDim.x) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+            for (int q = 0; q < cs.top_k; q++) {
+                const int p = cs.pos[(size_t)r * cs.top_k + q];
+                if (p >= 0) {
+                    const float4 yv = *reinterpret_cast<const float4*>(cs.y + (size_t)p * hidden + 4 * j);
+                    const float wq = cs.w[(size_t)r * cs.top_k + q];
+                    acc.x = fmaf(wq, yv.x, acc.x), acc.y = fmaf(wq, yv.y, acc.y);
+                    acc.z = fmaf(wq, yv.z, acc.z), acc.w = fmaf(wq, yv.w, acc.w);
+                }
+            }
+            if (cs.shared) {
+                const float4 sv = *reinterpret_cast<const float4*>(cs.shared + (size_t)r * hidden + 4 * j);
+                if (cs.gate)
+                    acc.x += g * sv.x, acc.y += g * sv.y, acc.z += g * sv.z, acc.w += g * sv.w;
+                else
+                    acc.x += sv.x, acc.y += sv.y, acc.z += sv.z, acc.w += sv.w;
+            }
+            float4 v = reinterpret_cast<const float4*>(xr)[j];
+            v.x += acc.x, v.y += acc.y, v.z += acc.z, v.w += acc.w;
+            if (write_back) reinterpret_cast<float4*>(xr)[j] = v;
+            reinterpret_cast<float4*>(row)[j] = v;
+            ss += v.x * v.x, ss += v.y * v.y, ss += v.z * v.z, ss += v.w * v.w;
+        }
+    } else if (vec) {   // rows of whole 16-byte units: four elements per access
         for (int j = threadIdx.x; j < hidden / 4; j += blockDim.x) {
             float4 v = reinterpret_cast<const float4*>(xr)[j];
             if (dr) {
@@ -65,6 +105,8 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
             reinterpret_cast<float4*>(row)[j] = v;
             ss += v.x * v.x, ss += v.y * v.y, ss += v.z * v.z, ss += v.w * v.w;
         }
+    }
+    if (vec) {
         ss = block_sum(ss, red);
         const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
         for (int j = threadIdx.x; j < hidden / 4; j += blockDim.x) {
@@ -98,9 +140,9 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
     }
 }
 
-MOE_API int moe_rmsnorm(float* x, const float* delta, const float* w, const int* rows, float* out32, void* out16,
-                        int num_out_rows, int num_src_rows, int hidden, float eps, int write_back, int* status,
-                        cudaStream_t stream) {
+static int rmsnorm_launch(float* x, const float* delta, const float* w, const int* rows, float* out32, void* out16,
+                          int num_out_rows, int num_src_rows, int hidden, float eps, int write_back, int* status,
+                          const CombineSrc& cs, cudaStream_t stream) {
     if (num_out_rows <= 0) return 0;
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     const size_t smem = (size_t)hidden * sizeof(float);
@@ -111,8 +153,30 @@ MOE_API int moe_rmsnorm(float* x, const float* delta, const float* w, const int*
     }
     const int vec = hidden % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)delta % 16 == 0 && (uintptr_t)w % 16 == 0 &&
                     (uintptr_t)out32 % 16 == 0 && (uintptr_t)out16 % 8 == 0;
+    if (cs.y && (!vec || delta || (uintptr_t)cs.y % 16 || (uintptr_t)cs.shared % 16 || cs.top_k < 0)) return -1;
     return launch_pdl(rmsnorm_kernel, num_out_rows, threads, smem, stream, x, delta, w, rows, out32,
-                      (__nv_bfloat16*)out16, hidden, eps, write_back, num_src_rows, status, vec);
+                      (__nv_bfloat16*)out16, hidden, eps, write_back, num_src_rows, status, vec, cs);
+}
+
+MOE_API int moe_rmsnorm(float* x, const float* delta, const float* w, const int* rows, float* out32, void* out16,
+                        int num_out_rows, int num_src_rows, int hidden, float eps, int write_back, int* status,
+                        cudaStream_t stream) {
+    CombineSrc none = {};
+    return rmsnorm_launch(x, delta, w, rows, out32, out16, num_out_rows, num_src_rows, hidden, eps, write_back, status,
+                          none, stream);
+}
+
+// The same with the delta still uncombined (see CombineSrc).  Returns -1, with nothing launched, if
+// the rows are not whole 16-byte units: the caller then combines first.
+MOE_API int moe_rmsnorm_combine(float* x, const float* y, const int* pos_of_pair, const float* topk_w, int top_k,
+                                const float* shared, const float* shared_gate, const float* w, const int* rows,
+                                float* out32, void* out16, int num_out_rows, int num_src_rows, int hidden, float eps,
+                                int write_back, int* status, cudaStream_t stream) {
+    if (!y || !pos_of_pair || !topk_w) return (int)cudaErrorInvalidValue;
+    CombineSrc cs;
+    cs.y = y, cs.pos = pos_of_pair, cs.w = topk_w, cs.top_k = top_k, cs.shared = shared, cs.gate = shared_gate;
+    return rmsnorm_launch(x, nullptr, w, rows, out32, out16, num_out_rows, num_src_rows, hidden, eps, write_back,
+                          status, cs, stream);
 }
 
 // Ask for `bytes` at `p` in L2: weights that a later kernel of the step will stream, requested

@@ -12,7 +12,7 @@ import torch
 from ..cache.kv import KVRequest, StateRequest
 from ..config.spec import ModelSpec
 from ..parts import block as block_mod
-from ..parts.base import Part, Runtime, TensorSpec, make_part
+from ..parts.base import Part, Runtime, TensorSpec, delta_for, make_part
 from ..weights.store import WeightStore
 
 
@@ -113,5 +113,6 @@ class DecoderModel:
             x, pending = self.blocks[e.layer].forward(rt, x, pending, batch, cache.view(e.cache), cache.state(e.cache))
         if batch.num_want == 0:
             return None
-        h = self.final_norm.forward(rt, x, delta=pending, rows=batch.want_rows, write_back=False)
+        h = self.final_norm.forward(rt, x, delta=delta_for(self.final_norm, pending, rt), rows=batch.want_rows,
+                                    write_back=False)
         return self.head.forward(rt, h)

@@ -33,6 +33,7 @@ def lib():
         sig = {
             "moe_embed": [P, I, P, P, I, I, I, P, P],
             "moe_rmsnorm": [P, P, P, P, P, P, I, I, I, F, I, P, P],
+            "moe_rmsnorm_combine": [P, P, P, P, I, P, P, P, P, P, P, I, I, I, F, I, P, P],
             "moe_add_inplace": [P, P, LL, P],
             "moe_gemm_generic": [P, I, I, P, I, P, I, LL, P, I, I, P, P, I, I, I, I, P, P],
             "moe_rope_split": [P, P, P, I, I, I, I, I, P, P, P, I, P],
@@ -165,6 +166,24 @@ def rmsnorm(x, weight, eps, *, delta=None, rows=None, out32=None, out16=None, wr
                 raise KernelError("rmsnorm: output shape")
     _ok(lib().moe_rmsnorm(_p(x), _p(delta), _p(weight), _p(rows), _p(out32), _p(out16), n_out, S, H, float(eps),
                           1 if (write_back and rows is None) else 0, _p(status), _stream()), "rmsnorm")
+
+
+def rmsnorm_combine(x, cd, weight, eps, *, rows=None, out32=None, out16=None, write_back=True, status=None) -> bool:
+    """``rmsnorm`` whose delta is still the uncombined output of routed experts (``cd``: y,
+    pos_of_pair, topk_w, top_k, shared, shared_gate): combined inside the norm's kernel.  False,
+    with nothing launched, if the rows are not whole 16-byte units."""
+    _chk(x, "x", torch.float32, 2), _chk(weight, "weight", torch.float32, 1), _chk(cd.y, "y", torch.float32, 2)
+    S, H = x.shape
+    n_out = S if rows is None else rows.numel()
+    if weight.numel() != H or cd.y.shape[1] != H or cd.pos_of_pair.numel() < S * cd.top_k:
+        raise KernelError("rmsnorm_combine: shapes")
+    code = lib().moe_rmsnorm_combine(_p(x), _p(cd.y), _p(cd.pos_of_pair), _p(cd.topk_w), cd.top_k, _p(cd.shared),
+                                     _p(cd.shared_gate), _p(weight), _p(rows), _p(out32), _p(out16), n_out, S, H,
+                                     float(eps), 1 if (write_back and rows is None) else 0, _p(status), _stream())
+    if code == -1:
+        return False
+    _ok(code, "rmsnorm_combine")
+    return True
 
 
 def add_inplace(a, b):

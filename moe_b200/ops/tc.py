@@ -6,6 +6,7 @@ no multiple of 8 elements, an unaligned pointer); the caller then uses the plain
 """
 from __future__ import annotations
 
+import os
 from ctypes import c_int, c_void_p
 from typing import Optional
 
@@ -133,7 +134,10 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swiglu: bool
             tiles = n_tiles * (max(1, -(-M // bn)) if not grouped else max(1, min(G, M)))
             # (up to 8 splits add up through the shared memory of a cluster; more would go through
             # partial sums in global memory)
-            splits = max(1, min(8, (2 * num_sms(x.device)) // max(tiles, 1), -(-K // 64) // 4))
+            # (measured: about 1.5 CTAs per SM is best up to 32 tokens, where all clusters of a
+            # launch then find room at once; 2 per SM at 64 tokens)
+            target = 3 * num_sms(x.device) // 2 if bn <= 32 else 2 * num_sms(x.device)
+            splits = max(1, min(8, target // max(tiles, 1), -(-K // 64) // 4))
     splits = L.moe_gemm_tc_plan(K, int(splits), M, bn, G, 1 if grouped else 0, core.ctypes.byref(gy))
     partials = tickets = None
     if splits > 1:

@@ -12,7 +12,10 @@ Interfaces by category
   mixer     forward(rt, h: Activations, batch, cache_view, state) -> delta [T, hidden] float32
             kv_request() -> KVRequest | None;  state_request() -> StateRequest | None
   ffn       forward(rt, h: Activations, batch) -> delta [T, hidden] float32;  wants32: bool
+            optional: forward_lazy(rt, h, batch) -> delta or LazyDelta;
+                      forward_prenorm(rt, x, delta, norm, batch) -> delta, LazyDelta, or None (not taken)
   block     forward(rt, x, pending, batch, cache_view, state) -> (x, pending)
+A pending delta may be a ``LazyDelta``; ``delta_for(norm, delta, rt)`` gives what a norm can take.
 """
 from __future__ import annotations
 
@@ -22,6 +25,25 @@ from typing import Any, Callable, Dict, Optional, Tuple
 import torch
 
 from ..config.spec import PartSpec
+
+
+class LazyDelta:
+    """A residual delta that is not computed yet.  A feed-forward may hand one to its block
+    (``forward_lazy`` / ``forward_prenorm``) instead of a tensor; the norm that adds it next either
+    knows its ``kind`` and forms it inside its own kernel (it then declares ``lazy_kinds``), or
+    gets the tensor from ``materialize``."""
+
+    kind = ""
+
+    def materialize(self, rt) -> torch.Tensor:
+        raise NotImplementedError
+
+
+def delta_for(norm, delta, rt):
+    """What ``norm`` can be given for ``delta``: the lazy form if the norm takes that kind, else the tensor."""
+    if isinstance(delta, LazyDelta) and delta.kind not in getattr(norm, "lazy_kinds", ()):
+        return delta.materialize(rt)
+    return delta
 
 
 @dataclass(frozen=True)

@@ -9,7 +9,7 @@ reads and writes the stream once instead of twice.
 from __future__ import annotations
 
 from ..config.spec import LayerSpec
-from .base import make_part, register_part
+from .base import delta_for, make_part, register_part
 
 
 class PreNormBlock:
@@ -28,7 +28,8 @@ class PreNormBlock:
     def forward(self, rt, x, pending, batch, cache_view, state):
         """x: [T, hidden] float32 stream; pending: a delta not yet added (or None).
         Returns (x, pending)."""
-        h = self.norm1.forward(rt, x, delta=pending, want32=getattr(self.mixer, "wants32", False))
+        h = self.norm1.forward(rt, x, delta=delta_for(self.norm1, pending, rt),
+                               want32=getattr(self.mixer, "wants32", False))
         delta = self.mixer.forward(rt, h, batch, cache_view, state)
         # a feed-forward may offer to run the norm before it itself (fused with its first
         # kernels); it returns None where it cannot, and nothing has happened then
@@ -38,7 +39,8 @@ class PreNormBlock:
             if out is not None:
                 return x, out
         h = self.norm2.forward(rt, x, delta=delta, want32=getattr(self.ffn, "wants32", False))
-        return x, self.ffn.forward(rt, h, batch)
+        # (its delta may come back uncombined, for the next norm to finish: base.LazyDelta)
+        return x, getattr(self.ffn, "forward_lazy", self.ffn.forward)(rt, h, batch)
 
 
 _BLOCKS = {"prenorm": PreNormBlock}

@@ -15,7 +15,7 @@ import torch
 
 from ..ops import core
 from ..ops.linear import grouped_linear, grouped_swiglu_linear, linear, swiglu_linear
-from .base import Activations, Part, TensorSpec, register_part
+from .base import Activations, LazyDelta, Part, TensorSpec, register_part
 
 
 def _fuse_rows(tensors):
@@ -47,6 +47,23 @@ class DenseSwiGLU(Part):
 
     def forward(self, rt, h, batch):
         return linear(rt, swiglu_linear(rt, h.act, self.w_gu), self.w_down)
+
+
+class CombineDelta(LazyDelta):
+    """The routed experts' outputs before the combine: delta[t] = sum_j w[t, j] * y[pos[t, j]] +
+    gate[t] * shared[t].  An RMS norm forms it inside its own kernel."""
+
+    kind = "expert_combine"
+
+    def __init__(self, y, pos_of_pair, topk_w, top_k, shared, shared_gate, tokens, hidden):
+        self.y, self.pos_of_pair, self.topk_w, self.top_k = y, pos_of_pair, topk_w, top_k
+        self.shared, self.shared_gate, self.tokens, self.hidden = shared, shared_gate, tokens, hidden
+
+    def materialize(self, rt):
+        out = rt.empty((self.tokens, self.hidden), torch.float32)
+        core.moe_combine(self.y, self.pos_of_pair, self.topk_w, self.top_k, out, shared=self.shared,
+                         shared_gate=self.shared_gate)
+        return out
 
 
 class RoutedExperts(Part):
@@ -127,6 +144,10 @@ class RoutedExperts(Part):
         return linear(rt, swiglu_linear(rt, h.act, self.ws_gu), self.ws_down)
 
     def forward(self, rt, h, batch):
+        return self._run(rt, h, batch, None).materialize(rt)
+
+    def forward_lazy(self, rt, h, batch):
+        """The same, the combine left to whoever adds the delta (see ``CombineDelta``)."""
         return self._run(rt, h, batch, None)
 
     def forward_prenorm(self, rt, x, delta, norm, batch):
@@ -192,9 +213,7 @@ class RoutedExperts(Part):
         if side is not None:
             torch.cuda.current_stream().wait_stream(side)
             ys.record_stream(torch.cuda.current_stream())
-        out = rt.empty((T, self.hidden), torch.float32)
-        core.moe_combine(y, pos_of_pair, topk_w, self.k, out, shared=ys, shared_gate=sg)
-        return out
+        return CombineDelta(y, pos_of_pair, topk_w, self.k, ys, sg, T, self.hidden)
 
 
 register_part("ffn", "dense_swiglu", DenseSwiGLU)

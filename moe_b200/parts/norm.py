@@ -4,12 +4,13 @@ from __future__ import annotations
 import torch
 
 from ..ops import core
-from .base import Activations, Part, TensorSpec, register_part
+from .base import Activations, LazyDelta, Part, TensorSpec, register_part
 
 
 class RMSNorm(Part):
     category, kind = "norm", "rmsnorm"
     graph_safe = True
+    lazy_kinds = ("expert_combine",)      # deltas this norm forms inside its own kernel
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -34,6 +35,13 @@ class RMSNorm(Part):
                 out32 = rt.empty((n, self.size), torch.float32)
         else:
             out32 = rt.empty((n, self.size), torch.float32)
+        if isinstance(delta, LazyDelta):
+            if delta.kind != "expert_combine" or not core.rmsnorm_combine(
+                    x, delta, self.weight, self.eps, rows=rows, out32=out32, out16=out16, write_back=write_back,
+                    status=rt.status):
+                delta = delta.materialize(rt)
+            else:
+                return Activations(act=out16 if rt.is_bf16 else out32, f32=out32)
         core.rmsnorm(x, self.weight, self.eps, delta=delta, rows=rows, out32=out32, out16=out16,
                      write_back=write_back, status=rt.status)
         return Activations(act=out16 if rt.is_bf16 else out32, f32=out32)

@@ -204,3 +204,50 @@ def test_norm_route_equals_rmsnorm_then_route_dispatch(core, E, k, H, norm, T, w
     if xs is not None:
         assert torch.equal(xs[:total], out16[sorted_token[:total].long()])
     assert int(core._tickets(DEV, 1).abs().sum()) == 0
+
+
+@pytest.mark.parametrize("T,H,E,k,rows", [(8, 2048, 60, 4, None), (5, 96, 6, 3, [4, 0, 2]), (300, 264, 9, 2, None),
+                                          (3, 100, 4, 4, None)])
+@pytest.mark.parametrize("bf16", [False, True])
+def test_rmsnorm_with_uncombined_delta_equals_combine_then_rmsnorm(core, T, H, E, k, rows, bf16):
+    """The norm that forms the routed experts' delta inside its own kernel against the combine
+    kernel followed by the plain norm: the same stream and the same normalised rows."""
+    from moe_b200.parts.feedforward import CombineDelta
+
+    torch.manual_seed(T + H)
+    x0 = torch.randn(T, H, device=DEV)
+    nw = 1.0 + 0.1 * torch.randn(H, device=DEV)
+    P = T * k
+    y = torch.randn(P, H, device=DEV)
+    pos = torch.randperm(P, device=DEV).to(torch.int32)
+    if T > 2:
+        pos[k] = -1                                               # a pair without an expert
+    w = torch.rand(T, k, device=DEV)
+    shared = torch.randn(T, H, device=DEV)
+    gate = torch.rand(T, device=DEV)
+    st = torch.zeros(4, dtype=torch.int32, device=DEV)
+    r = None if rows is None else torch.tensor(rows, dtype=torch.int32, device=DEV)
+    n = T if rows is None else len(rows)
+    outs = []
+    for fused in (False, True):
+        x = x0.clone()
+        o32 = torch.empty(n, H, device=DEV)
+        o16 = torch.empty(n, H, device=DEV, dtype=torch.bfloat16) if bf16 else None
+        cd = CombineDelta(y, pos, w.reshape(-1), k, shared, gate, T, H)
+        if fused:
+            assert core.rmsnorm_combine(x, cd, nw, 1e-6, rows=r, out32=o32, out16=o16, write_back=rows is None,
+                                        status=st) == (H % 4 == 0)
+            if H % 4:
+                return
+        else:
+            delta = torch.empty(T, H, device=DEV)
+            core.moe_combine(y, pos, w.reshape(-1), k, delta, shared=shared, shared_gate=gate)
+            core.rmsnorm(x, nw, 1e-6, delta=delta, rows=r, out32=o32, out16=o16, write_back=rows is None, status=st)
+        outs.append((x, o32, o16))
+    assert int(st[0]) == 0
+    assert torch.allclose(outs[0][0], outs[1][0], rtol=1e-6, atol=1e-6)
+    assert torch.allclose(outs[0][1], outs[1][1], rtol=1e-5, atol=1e-6)
+    if bf16:
+        assert float((outs[0][2].float() - outs[1][2].float()).abs().max()) <= 2.0 ** -7 * float(outs[0][2].float().abs().max())
+    if rows is not None:
+        assert torch.equal(outs[1][0], x0)                        # selected rows: the stream is left alone
