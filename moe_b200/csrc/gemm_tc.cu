@@ -56,6 +56,7 @@ struct Params {
     int splits;                 // K splits (>= 1), every split non-empty
     int kb_per_split;
     int cluster;                // 1: the splits of a tile are one cluster and add up through shared memory
+    int early_offsets;          // 1: group_offsets were written at least two kernels ago (see the kernel)
     float* partials;            // [splits][M][cols] float32, cols = N or 2 N (not with cluster)
     int* tickets;               // one per (grid.y, grid.x), zero before and after the launch
     int* status;
@@ -203,8 +204,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     // still runs.  Weights never depend on the predecessor, so an ungrouped product sets itself up
     // and starts streaming its weight tiles before it waits (in the producer, below); a grouped one
     // needs the group offsets the predecessor wrote, and waits here.
+    // A grouped one whose offsets are older than the predecessor (the second product of the routed
+    // experts: its offsets were written before the first) may do the same.
     const bool grouped = p.group_offsets != nullptr;
-    if (grouped) pdl_sync();
+    const bool wait_first = grouped && !p.early_offsets;
+    if (wait_first) pdl_sync();
 
     // ---- which rows of X this CTA owns -------------------------------------------------
     // (the offsets are fetched by all threads at once: a scan straight from global memory would
@@ -282,7 +286,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             int issued = 0;
             bool ok = true;
             int kb_next = kb0;
-            if (!grouped) {
+            if (!wait_first) {
                 // weight tiles of the first stages, then wait for the predecessor, then their activations
                 const int pre = min(C::STAGES, kb1 - kb0);
                 for (int i = 0; i < pre; i++) {
@@ -826,7 +830,7 @@ int launch_persistent(const CUtensorMap& tmW, const CUtensorMap& tmX, const Para
 // Returns 0, a CUDA error code, or -1 if the shape cannot be handled (the caller falls back).
 MOE_API int moe_gemm_tc(const void* X, int ldx, const void* W, int num_groups, int N, int K, int mode, void* out,
                         int out_bf16, int ldo, const float* bias, const int* group_offsets, int M, int bn, int splits,
-                        float* partials, int* tickets, int* status, cudaStream_t stream) {
+                        float* partials, int* tickets, int* status, int early_offsets, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K % 8 != 0 || ldx % 8 != 0 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return -1;
     const int w_rows = mode == MODE_SWIGLU ? 2 * N : N;
@@ -840,7 +844,7 @@ MOE_API int moe_gemm_tc(const void* X, int ldx, const void* W, int num_groups, i
     const int per = (kb_total + splits - 1) / splits;
     splits = (kb_total + per - 1) / per;
     Params p;
-    p.cluster = 0;
+    p.cluster = 0, p.early_offsets = (group_offsets && early_offsets) ? 1 : 0;
     p.out = out, p.out_bf16 = out_bf16, p.ldo = ldo, p.bias = bias, p.group_offsets = group_offsets;
     p.num_groups = num_groups, p.M = M, p.N = N, p.K = K, p.w_rows_per_group = w_rows, p.splits = splits;
     p.kb_per_split = per, p.partials = partials, p.tickets = tickets, p.status = status;

@@ -66,13 +66,15 @@ def grouped_swiglu_linear(rt, a: torch.Tensor, w_gate_up: torch.Tensor, group_of
     return act
 
 
-def grouped_linear(rt, a: torch.Tensor, w: torch.Tensor, group_offsets: torch.Tensor, num_rows: int) -> torch.Tensor:
-    """Rows [offsets[g], offsets[g+1]) of a use w[g] ([G, N, K]); returns float32 [num_rows, N]."""
+def grouped_linear(rt, a: torch.Tensor, w: torch.Tensor, group_offsets: torch.Tensor, num_rows: int,
+                   early_offsets: bool = False) -> torch.Tensor:
+    """Rows [offsets[g], offsets[g+1]) of a use w[g] ([G, N, K]); returns float32 [num_rows, N].
+    ``early_offsets``: see ``tc.gemm_tc``."""
     out = torch.empty((num_rows, w.shape[1]), dtype=torch.float32, device=a.device)
     if _use_tc(rt, a, w):
         from . import tc
 
-        if tc.gemm_tc(a, w, out, group_offsets=group_offsets, status=rt.status):
+        if tc.gemm_tc(a, w, out, group_offsets=group_offsets, status=rt.status, early_offsets=early_offsets):
             return out
     core.gemm_generic(a, w, out, group_offsets=group_offsets, status=rt.status)
     return out

@@ -23,7 +23,7 @@ def lib():
     if _lib is None:
         L = build.load("tc")
         P, I = c_void_p, c_int
-        L.moe_gemm_tc.argtypes = [P, I, P, I, I, I, I, P, I, I, P, P, I, I, I, P, P, P, P]
+        L.moe_gemm_tc.argtypes = [P, I, P, I, I, I, I, P, I, I, P, P, I, I, I, P, P, P, I, P]
         L.moe_gemm_tc.restype = c_int
         L.moe_gemm_tc_plan.argtypes = [I, I, I, I, I, I, P]
         L.moe_gemm_tc_plan.restype = c_int
@@ -103,11 +103,14 @@ def token_tile(rows_per_group: float) -> int:
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swiglu: bool = False,
             bias: Optional[torch.Tensor] = None, group_offsets: Optional[torch.Tensor] = None,
-            bn: Optional[int] = None, splits: Optional[int] = None, status=None) -> bool:
+            bn: Optional[int] = None, splits: Optional[int] = None, status=None, early_offsets: bool = False) -> bool:
     """out = x @ w[g].T (PLAIN) or silu(x @ gate.T) * (x @ up.T) (SwiGLU, w rows = gate then up).
 
     x: [M, K] bf16 (row pitch a multiple of 8); w: [N', K] or [G, N', K] bf16 contiguous;
-    out: [M, N] float32 or bfloat16 with N = N' (PLAIN) or N' / 2 (SwiGLU)."""
+    out: [M, N] float32 or bfloat16 with N = N' (PLAIN) or N' / 2 (SwiGLU).
+    ``early_offsets``: the caller vouches that ``group_offsets`` were written at least two kernels
+    before this one on the stream (not by its direct predecessor); the kernel then starts loading
+    weights while the predecessor still runs."""
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not x.is_cuda:
         return False
     G = w.shape[0] if w.dim() == 3 else 1
@@ -153,7 +156,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swiglu: bool
                          None if group_offsets is None else group_offsets.data_ptr(), M, bn, splits,
                          None if partials is None else partials.data_ptr(),
                          None if tickets is None else tickets.data_ptr(),
-                         None if status is None else status.data_ptr(), core._stream())
+                         None if status is None else status.data_ptr(), 1 if early_offsets else 0, core._stream())
     if code == -1:
         return False
     core._ok(code, "gemm_tc")

@@ -76,6 +76,8 @@ class Runtime:
         if getattr(self, "_side", None) is None:
             from ..ops import tc
 
+            # (default priority: a higher one was measured slower, the side branch then crowds out
+            # the routed experts' first product)
             self._side = torch.cuda.Stream(device=self.device)
             tc.register_side_stream(self._side)     # its products get a split-K workspace of their own
         return self._side

@@ -207,7 +207,8 @@ class RoutedExperts(Part):
         if self.trace is not None:
             self.trace.append((topk_idx.clone(), topk_w.clone()))
         act = grouped_swiglu_linear(rt, h.act, self.w_gu, offsets, sorted_token, P, gathered=xs)
-        y = grouped_linear(rt, act, self.w_down, offsets, P)
+        # (the offsets were written before the product above: the second product may start on its weights early)
+        y = grouped_linear(rt, act, self.w_down, offsets, P, early_offsets=True)
         if self.ws_gu is not None and side is None:
             ys = self._shared(rt, h)
         if side is not None:
