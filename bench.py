@@ -121,13 +121,13 @@ def run_ours(args):
     nums = model_numbers(cfg, layers)
     clocks = ClockSampler()
 
-    def decode_run(B, steps, warmup, sample_clocks=False):
+    def decode_run(B, steps, warmup, sample_clocks=False, prompt_len=PROMPT_LEN):
         """-> (ms per step, launches per step, h2d bytes per step, mean cache tokens, unique experts per layer)"""
-        eng = moe_b200.Engine(model, max_tokens=B * (-(-(PROMPT_LEN + steps + warmup + 8) // 64) * 64), max_slots=B)
+        eng = moe_b200.Engine(model, max_tokens=B * (-(-(prompt_len + steps + warmup + 8) // 64) * 64), max_slots=B)
         sampler = DeviceSampler(eng.cache.rng_states, eng.rt.device)
         greedy = SamplingParams()
         slots = [eng.new_sequence() for _ in range(B)]
-        prompts = [[(i * 7 + 13 + 31 * b) % V for i in range(PROMPT_LEN)] for b in range(B)]
+        prompts = [[(i * 7 + 13 + 31 * b) % V for i in range(prompt_len)] for b in range(B)]
         for b0 in range(0, B, 8):                       # prompts in groups, to bound the workspace
             eng.step(slots[b0:b0 + 8], prompts[b0:b0 + 8], [[] for _ in slots[b0:b0 + 8]])
 
@@ -160,7 +160,7 @@ def run_ours(args):
         clk = clocks.stop() if sample_clocks else None
         eng.rt.check()
         launches = (core.launches - l0) / steps
-        mean_len = PROMPT_LEN + warmup + 1 + steps / 2
+        mean_len = prompt_len + warmup + 1 + steps / 2
         h2d = (3 * B + 4 * B + 2 + B) * 4
         for s in slots:
             eng.release(s)
@@ -177,9 +177,10 @@ def run_ours(args):
     if args.sweep:
         # decode only, one line per batch size (not the benchmark record)
         for b in [int(v) for v in args.sweep.split(",")]:
-            m, _, _, mean_len, uniq, _ = decode_run(b, max(8, args.steps // 2), args.warmup)
+            m, _, _, mean_len, uniq, _ = decode_run(b, max(8, args.steps // 2), args.warmup,
+                                                    prompt_len=args.prompt_len or PROMPT_LEN)
             gbs = decode_bytes(b, mean_len, uniq) / (m / 1e3) / 1e9
-            print(json.dumps({"batch": b, "ms_per_step": round(m, 4), "tokens_per_s": round(b / (m / 1e3), 1),
+            print(json.dumps({"batch": b, "cache_tokens": int(mean_len), "ms_per_step": round(m, 4), "tokens_per_s": round(b / (m / 1e3), 1),
                               "hbm_frac": round(gbs / pk["hbm_gbs"], 4)}))
         return 0
 
@@ -304,6 +305,7 @@ def main():
                     help="run a few steps of one kind between cudaProfilerStart/Stop (for ncu "
                          "--profile-from-start off) and print no benchmark line")
     ap.add_argument("--batch", type=int, default=8, help="with --profile-step decode: sequences in the batch")
+    ap.add_argument("--prompt-len", type=int, default=0, help="with --sweep: tokens in each prompt (default 512)")
     ap.add_argument("--sweep", default=None, help="comma-separated batch sizes: print decode throughput for each "
                                                   "and no benchmark line")
     args = ap.parse_args()
