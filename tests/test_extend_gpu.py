@@ -170,6 +170,155 @@ def test_toy_architecture_with_a_stateful_mixer(tmp_path, dtype):
     assert [len(o.tokens) for o in out] == [4, 4]
 
 
+def register_toy_switch():
+    """A second toy architecture: a position encoding of its own (acting on the 32-bit projections
+    through ``apply``) and a feed-forward with routing of its own (each token goes to ONE of two
+    small experts, picked by the larger of two router logits)."""
+    import moe_b200
+    from moe_b200.config import Architecture, LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    from moe_b200.parts import Part, TensorSpec
+
+    class GrowingScale(Part):
+        """q_p *= 1 / (1 + a p), k_j *= (1 + a j): a score then carries (1 + a j) / (1 + a p)."""
+        category, kind = "position", "toy_growing_scale"
+
+        def __init__(self, spec):
+            super().__init__(spec)
+            self.a = float(self.params["a"])
+
+        def rotary_table(self):
+            return None, 0
+
+        def attention_scale(self):
+            return 1.0
+
+        def apply(self, rt, qkv32, nh, nkv, hd, positions):
+            f = (1.0 + self.a * positions.to(torch.float32)).unsqueeze(1)
+            qkv32[:, : nh * hd] /= f
+            qkv32[:, nh * hd: (nh + nkv) * hd] *= f
+
+    class SwitchFFN(Part):
+        category, kind = "ffn", "toy_switch"
+        wants32 = True
+
+        def __init__(self, spec):
+            super().__init__(spec)
+            self.hidden, self.size = int(self.params["hidden_size"]), int(self.params["size"])
+            self.trace = None
+
+        def tensors(self):
+            t = {"router.weight": TensorSpec((2, self.hidden))}
+            for e in range(2):
+                t[f"e{e}.up.weight"] = TensorSpec((self.size, self.hidden))
+                t[f"e{e}.down.weight"] = TensorSpec((self.hidden, self.size))
+            return t
+
+        def bind(self, tensors, rt):
+            super().bind(tensors, rt)
+            self.w = {k: v.float() for k, v in tensors.items()}
+
+        def forward(self, rt, h, batch):
+            n = h.f32
+            pick = (n @ self.w["router.weight"].T).argmax(dim=1)
+            if self.trace is not None:
+                self.trace.append(pick.clone())
+            out = torch.zeros_like(n)
+            for e in range(2):
+                rows = (pick == e).nonzero().flatten()
+                if rows.numel():
+                    out[rows] = torch.relu(n[rows] @ self.w[f"e{e}.up.weight"].T) @ self.w[f"e{e}.down.weight"].T
+            return out.contiguous()
+
+    moe_b200.register_part("position", "toy_growing_scale", GrowingScale)
+    moe_b200.register_part("ffn", "toy_switch", SwitchFFN)
+
+    def spec_of(c):
+        H, V = c["hidden_size"], c["vocab_size"]
+        norm = lambda p: PartSpec("rmsnorm", {"size": H, "eps": c["eps"]}, p)
+        attn = lambda p, position, window: PartSpec("gqa_attention", {
+            "hidden_size": H, "num_heads": c["heads"], "num_kv_heads": c["kv_heads"], "head_dim": c["head_dim"],
+            "qkv_bias": True, "window": window, "own_kv": True, "position": position}, p)
+        layers = (
+            LayerSpec("prenorm", norm("l0.n1."), attn("l0.attn.", {"kind": "toy_growing_scale", "a": c["a"]}, None),
+                      norm("l0.n2."), PartSpec("toy_switch", {"hidden_size": H, "size": c["ffn"]}, "l0.ffn.")),
+            LayerSpec("prenorm", norm("l1.n1."),
+                      attn("l1.attn.", {"kind": "rotary", "theta": c["theta"], "rotary_dim": c["head_dim"] // 2}, c["window"]),
+                      norm("l1.n2."), PartSpec("dense_swiglu", {"hidden_size": H, "size": c["ffn"]}, "l1.ffn.")),
+        )
+        return ModelSpec("ToySwitchForCausalLM", H, V, PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H}, "emb."),
+                         layers, (ScheduleEntry(0, 0, True), ScheduleEntry(1, 1, True)), norm("final."),
+                         PartSpec("lm_head", {"vocab_size": V, "hidden_size": H, "tied": False}, "head."))
+
+    moe_b200.register_architecture(Architecture("ToySwitchForCausalLM", dict, spec_of, dict))
+
+
+SWITCH = dict(architectures=["ToySwitchForCausalLM"], hidden_size=40, vocab_size=77, heads=4, kv_heads=2, head_dim=32,
+              ffn=24, eps=1e-5, theta=5e3, a=0.05, window=6)
+
+
+def switch_plain(w, tokens, picks):
+    """The second toy model, whole sequence, float64, with the engine's expert picks."""
+    c = SWITCH
+    T, nh, nkv, hd = len(tokens), c["heads"], c["kv_heads"], c["head_dim"]
+    pos = torch.arange(T)
+    x = w["emb.weight"][torch.tensor(tokens)].clone()
+
+    def qkv(p, n):
+        return [(n @ w[p + f"{m}_proj.weight"].T + w[p + f"{m}_proj.bias"]).reshape(T, heads, hd)
+                for m, heads in (("q", nh), ("k", nkv), ("v", nkv))]
+
+    # layer 0: the toy position encoding, then the switch feed-forward
+    q, k, v = qkv("l0.attn.", plain.rmsnorm(x, w["l0.n1.weight"], c["eps"]))
+    f = (1.0 + c["a"] * pos.double()).reshape(T, 1, 1)
+    x = x + plain.attention(q / f, k * f, v, None) @ w["l0.attn.o_proj.weight"].T
+    n = plain.rmsnorm(x, w["l0.n2.weight"], c["eps"])
+    out = torch.zeros_like(n)
+    for t in range(T):
+        e = int(picks[t])
+        out[t] = torch.relu(n[t] @ w[f"l0.ffn.e{e}.up.weight"].T) @ w[f"l0.ffn.e{e}.down.weight"].T
+    x = x + out
+    # layer 1: rotary on half of each head, a window of 6, a dense feed-forward
+    q, k, v = qkv("l1.attn.", plain.rmsnorm(x, w["l1.n1.weight"], c["eps"]))
+    rot = hd // 2
+    inv = plain.rope_inv_freq(c["theta"], rot)
+    part = lambda z: torch.cat([plain.rope(z[..., :rot], pos, inv), z[..., rot:]], dim=-1)   # the rest passes through
+    x = x + plain.attention(part(q), part(k), v, c["window"]) @ w["l1.attn.o_proj.weight"].T
+    x = x + plain.swiglu_mlp({kk.replace("l1.ffn.", "m."): vv for kk, vv in w.items()}, "m.",
+                             plain.rmsnorm(x, w["l1.n2.weight"], c["eps"]))
+    return plain.rmsnorm(x, w["final.weight"], c["eps"]) @ w["head.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_with_its_own_position_encoding_and_routing(tmp_path, dtype):
+    import moe_b200
+    from moe_b200.engine import Engine
+
+    register_toy_switch()
+    d = str(tmp_path / "switch")
+    moe_b200.write_random_model(d, SWITCH, seed=11, std=G.STD[dtype][1], dtype=dtype)
+    model = moe_b200.load_model(d, dtype=dtype)
+    eng = Engine(model, max_tokens=512, max_slots=2)
+    assert len(eng.cache.groups) == 2                      # all keys for layer 0, a ring for layer 1's window
+    ffn = model.blocks[0].ffn
+    _, w = plain.read_model(d)
+    reqs = {f"r{i}": helpers.random_tokens(77, n, 80 + i) for i, n in enumerate([9, 26, 2, 15])}
+    whole = {}
+    for rid, toks in reqs.items():
+        ffn.trace = []
+        s = eng.new_sequence()
+        got = eng.step([s], [toks], [list(range(len(toks)))]).cpu()
+        eng.release(s)
+        picks, ffn.trace = ffn.trace[0].cpu().tolist(), None
+        assert helpers.max_rel_err(got, switch_plain(w, toks, picks)) < G.tol(dtype), rid
+        whole[rid] = got
+    tail = helpers.replay_tail(eng, reqs, 4)
+    batched = helpers.replay_batches(eng, reqs, 2)
+    for rid in reqs:
+        assert helpers.max_rel_err(tail[rid], whole[rid]) < G.tol_cut(dtype), rid
+        assert helpers.max_rel_err(batched[rid], whole[rid]) < G.tol_cut(dtype), rid
+    assert eng.cache.ledger.slots.num_held == 0
+
+
 def test_unknown_part_kind_is_a_clear_error():
     from moe_b200.config.spec import PartSpec
     from moe_b200.parts import make_part
