@@ -1,10 +1,11 @@
 """Host-side bookkeeping of the cache: who holds which slot and which pages.
 
-Nothing here touches the device, so it is tested on the CPU.  A *slot* belongs
-to one sequence from its first step until it is released; a *page* holds
-``PAGE_TOKENS`` consecutive positions of one sequence for every layer of one
-cache group.  Page 0 of every pool is never handed out: padding rows of a batch
-point at it.
+The bookkeeping itself is C++ (``csrc/host_runtime.cpp``, built with the host
+compiler alone, so it is tested on the CPU); the classes here are its Python
+face.  A *slot* belongs to one sequence from its first step until it is
+released; a *page* holds ``PAGE_TOKENS`` consecutive positions of one sequence
+for every layer of one cache group.  Page 0 of every pool is never handed out:
+padding rows of a batch point at it.
 
 The reference keeps one flat array of ``ctx`` positions per layer and sequence
 (src/model.rs:140-153) and a pool of sessions in its server (src/serve.rs:419-443);
@@ -12,8 +13,13 @@ the split into slots and pages is this library's own.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Tuple
+import ctypes
+from ctypes import POINTER, c_char_p, c_int, c_longlong, c_void_p
+from typing import List, Sequence, Tuple
+
+import numpy as np
+
+from ..ops import build
 
 PAGE_TOKENS = 64
 
@@ -22,77 +28,116 @@ class CacheError(RuntimeError):
     pass
 
 
+_lib = None
+_IP = POINTER(c_int)
+
+
+def host_lib():
+    """The host runtime library (built on first use)."""
+    global _lib
+    if _lib is None:
+        L = build.load("host")
+        P, I, LL = c_void_p, c_int, c_longlong
+        sig = {
+            "moe_host_page_tokens": ([], I),
+            "moe_slotpool_new": ([I], P), "moe_slotpool_delete": ([P], None), "moe_slotpool_acquire": ([P], I),
+            "moe_slotpool_release": ([P, I], I), "moe_slotpool_is_held": ([P, I], I), "moe_slotpool_num_free": ([P], I),
+            "moe_pagepool_new": ([I], P), "moe_pagepool_delete": ([P], None), "moe_pagepool_alloc": ([P, I, _IP], I),
+            "moe_pagepool_free": ([P, _IP, I], I), "moe_pagepool_num_free": ([P], I),
+            "moe_ledger_new": ([I, I, _IP, _IP], P), "moe_ledger_delete": ([P], None), "moe_ledger_acquire": ([P], I),
+            "moe_ledger_release": ([P, I], I), "moe_ledger_is_held": ([P, I], I), "moe_ledger_length": ([P, I], I),
+            "moe_ledger_count": ([P, I, I], I), "moe_ledger_pages": ([P, I, I, _IP, I], I),
+            "moe_ledger_extend": ([P, I, I, _IP, I], I), "moe_ledger_truncate": ([P, I, I], I),
+            "moe_ledger_tokens_held": ([P], LL),
+            "moe_ledger_reserve": ([P, I, _IP, _IP, _IP, _IP, _IP, I, LL], I),
+            "moe_pack_step": ([_IP, LL, I, _IP, _IP, _IP, _IP, _IP, _IP, _IP, _IP], LL),
+            "moe_pack_decode": ([_IP, I, I, _IP, _IP, _IP, I, I, _IP, _IP, I], I),
+        }
+        for name, (args, res) in sig.items():
+            fn = getattr(L, name)
+            fn.argtypes, fn.restype = args, res
+        L.moe_host_error.argtypes, L.moe_host_error.restype = [], c_char_p
+        if L.moe_host_page_tokens() != PAGE_TOKENS:
+            raise RuntimeError("the host runtime was built for another page size")
+        _lib = L
+    return _lib
+
+
+def _raise(code: int):
+    msg = host_lib().moe_host_error().decode()
+    raise (ValueError if code == -2 else CacheError)(msg)
+
+
+def _ok(code: int) -> int:
+    if code < 0:
+        _raise(code)
+    return code
+
+
+def ints(values: Sequence[int]):
+    """A C array of ints (and its length) for the host runtime."""
+    n = len(values)
+    return (c_int * max(n, 1))(*values), n
+
+
 class SlotPool:
     """Slots 0 .. n-1; each is free or held by exactly one sequence."""
 
     def __init__(self, num_slots: int):
-        if num_slots <= 0:
-            raise CacheError("a cache needs at least one slot")
         self.num_slots = num_slots
-        self._free: List[int] = list(range(num_slots - 1, -1, -1))   # pop() hands out the lowest first
-        self._held = [False] * num_slots
+        self._h = host_lib().moe_slotpool_new(num_slots)
+        if not self._h:
+            _raise(-1)
+
+    def __del__(self):
+        if getattr(self, "_h", None) and _lib is not None:
+            _lib.moe_slotpool_delete(self._h)
+            self._h = None
 
     def acquire(self) -> int:
-        if not self._free:
-            raise CacheError(f"all {self.num_slots} slots are in use")
-        s = self._free.pop()
-        self._held[s] = True
-        return s
+        return _ok(_lib.moe_slotpool_acquire(self._h))
 
     def release(self, slot: int) -> None:
-        if not 0 <= slot < self.num_slots:
-            raise CacheError(f"slot {slot} does not exist")
-        if not self._held[slot]:
-            raise CacheError(f"slot {slot} is not held (released twice?)")
-        self._held[slot] = False
-        self._free.append(slot)
+        _ok(_lib.moe_slotpool_release(self._h, slot))
 
     def is_held(self, slot: int) -> bool:
-        return 0 <= slot < self.num_slots and self._held[slot]
+        return bool(_lib.moe_slotpool_is_held(self._h, slot))
 
     @property
     def num_free(self) -> int:
-        return len(self._free)
+        return _lib.moe_slotpool_num_free(self._h)
 
     @property
     def num_held(self) -> int:
-        return self.num_slots - len(self._free)
+        return self.num_slots - self.num_free
 
 
 class PagePool:
     """Pages 1 .. n-1 of one cache group (page 0 is the scratch page)."""
 
     def __init__(self, num_pages: int):
-        if num_pages < 2:
-            raise CacheError("a page pool needs the scratch page and at least one more")
         self.num_pages = num_pages
-        self._free: List[int] = list(range(num_pages - 1, 0, -1))
-        self._held = [False] * num_pages
+        self._h = host_lib().moe_pagepool_new(num_pages)
+        if not self._h:
+            _raise(-1)
+
+    def __del__(self):
+        if getattr(self, "_h", None) and _lib is not None:
+            _lib.moe_pagepool_delete(self._h)
+            self._h = None
 
     def alloc(self, n: int) -> List[int]:
-        if n > len(self._free):
-            raise CacheError(
-                f"the cache is full: {n} more pages of {PAGE_TOKENS} tokens wanted, {len(self._free)} free "
-                f"of {self.num_pages - 1}"
-            )
-        out = [self._free.pop() for _ in range(n)]
-        for p in out:
-            self._held[p] = True
-        return out
+        out = (c_int * max(n, 1))()
+        got = _ok(_lib.moe_pagepool_alloc(self._h, n, out))
+        return list(out[:got])
 
     def free(self, pages: List[int]) -> None:
-        for p in pages:
-            if not 0 < p < self.num_pages:
-                raise CacheError(f"page {p} does not exist")
-            if not self._held[p]:
-                raise CacheError(f"page {p} is not held (freed twice?)")
-        for p in pages:
-            self._held[p] = False
-            self._free.append(p)
+        arr, n = ints(pages)
+        _ok(_lib.moe_pagepool_free(self._h, arr, n))
 
     @property
     def num_free(self) -> int:
-        return len(self._free)
+        return _lib.moe_pagepool_num_free(self._h)
 
 
 def pages_for(length: int, ring_pages: int = 0) -> int:
@@ -101,79 +146,127 @@ def pages_for(length: int, ring_pages: int = 0) -> int:
     return min(n, ring_pages) if ring_pages else n
 
 
-@dataclass
-class GroupLedger:
-    """Pages of one cache group, per slot."""
+class _LedgerSlots:
+    def __init__(self, led: "CacheLedger"):
+        self._led = led
+        self.num_slots = led.num_slots
 
-    pool: PagePool
-    ring_pages: int                      # 0: grows with the sequence
-    pages: Dict[int, List[int]] = field(default_factory=dict)
+    def is_held(self, slot: int) -> bool:
+        return bool(_lib.moe_ledger_is_held(self._led._h, slot))
+
+    @property
+    def num_free(self) -> int:
+        return _lib.moe_ledger_count(self._led._h, 0, 0)
+
+    @property
+    def num_held(self) -> int:
+        return _lib.moe_ledger_count(self._led._h, 1, 0)
+
+
+class _GroupPool:
+    def __init__(self, led: "CacheLedger", group: int):
+        self._led, self._g = led, group
+
+    @property
+    def num_free(self) -> int:
+        return _lib.moe_ledger_count(self._led._h, 2, self._g)
+
+    @property
+    def num_pages(self) -> int:
+        return _lib.moe_ledger_count(self._led._h, 3, self._g)
+
+
+class _GroupPages:
+    def __init__(self, led: "CacheLedger", group: int):
+        self._led, self._g = led, group
+
+    def __getitem__(self, slot: int) -> List[int]:
+        n = _ok(_lib.moe_ledger_pages(self._led._h, self._g, slot, None, 0))
+        out = (c_int * max(n, 1))()
+        _ok(_lib.moe_ledger_pages(self._led._h, self._g, slot, out, n))
+        return list(out[:n])
+
+
+class GroupLedger:
+    """Pages of one cache group, per slot: a view of the ledger."""
+
+    def __init__(self, led: "CacheLedger", group: int, ring_pages: int):
+        self.pool = _GroupPool(led, group)
+        self.ring_pages = ring_pages                     # 0: grows with the sequence
+        self.pages = _GroupPages(led, group)
+
+
+class _Lengths:
+    def __init__(self, led: "CacheLedger"):
+        self._led = led
+
+    def __getitem__(self, slot: int) -> int:
+        n = _lib.moe_ledger_length(self._led._h, slot)
+        if n < 0:
+            raise KeyError(slot)
+        return n
+
+    def __contains__(self, slot) -> bool:
+        return bool(_lib.moe_ledger_is_held(self._led._h, slot))
 
 
 class CacheLedger:
     """Slots, lengths and pages of every group: the host's view of the cache."""
 
     def __init__(self, num_slots: int, group_pages: List[int], group_ring_pages: List[int]):
-        self.slots = SlotPool(num_slots)
-        self.groups = [GroupLedger(PagePool(n), r) for n, r in zip(group_pages, group_ring_pages)]
-        self.length: Dict[int, int] = {}
+        gp, n = ints(group_pages)
+        gr, _ = ints(group_ring_pages)
+        self.num_slots = num_slots
+        self._h = host_lib().moe_ledger_new(num_slots, n, gp, gr)
+        if not self._h:
+            _raise(-1)
+        self.slots = _LedgerSlots(self)
+        self.groups = [GroupLedger(self, g, r) for g, r in enumerate(group_ring_pages)]
+        self.length = _Lengths(self)
+
+    def __del__(self):
+        if getattr(self, "_h", None) and _lib is not None:
+            _lib.moe_ledger_delete(self._h)
+            self._h = None
 
     def acquire(self) -> int:
-        s = self.slots.acquire()
-        self.length[s] = 0
-        for g in self.groups:
-            g.pages[s] = []
-        return s
+        return _ok(_lib.moe_ledger_acquire(self._h))
 
     def release(self, slot: int) -> None:
-        if not self.slots.is_held(slot):
-            raise CacheError(f"slot {slot} is not held (released twice?)")
-        for g in self.groups:
-            g.pool.free(g.pages.pop(slot))
-        del self.length[slot]
-        self.slots.release(slot)
+        _ok(_lib.moe_ledger_release(self._h, slot))
 
     def extend(self, slot: int, new_length: int) -> List[Tuple[int, int, int, int]]:
         """Make room for ``new_length`` tokens in ``slot``.
 
         Returns the page-table entries that changed as (group, slot, index, page).
         Either every group gets its pages or none does."""
-        if not self.slots.is_held(slot):
-            raise CacheError(f"slot {slot} is not held")
-        if new_length < self.length[slot]:
-            raise CacheError("extend cannot shrink a sequence; use truncate")
-        wants = []
-        for g in self.groups:
-            need = pages_for(new_length, g.ring_pages) - len(g.pages[slot])
-            if need > g.pool.num_free:
-                raise CacheError(
-                    f"the cache is full: slot {slot} needs {need} more pages of {PAGE_TOKENS} tokens, "
-                    f"{g.pool.num_free} free"
-                )
-            wants.append(max(need, 0))
-        updates = []
-        for gi, (g, need) in enumerate(zip(self.groups, wants)):
-            if need:
-                base = len(g.pages[slot])
-                new = g.pool.alloc(need)
-                g.pages[slot].extend(new)
-                updates.extend((gi, slot, base + i, p) for i, p in enumerate(new))
-        self.length[slot] = new_length
-        return updates
+        cap = len(self.groups) * (pages_for(max(new_length, 0)) + 1)
+        out = (c_int * (4 * max(cap, 1)))()
+        n = _ok(_lib.moe_ledger_extend(self._h, slot, new_length, out, cap))
+        return [tuple(out[4 * i:4 * i + 4]) for i in range(n)]
+
+    def reserve(self, slots: Sequence[int], counts: Sequence[int], table_caps: Sequence[int],
+                max_tokens: int = 0) -> Tuple[List[int], np.ndarray]:
+        """Room for a whole step: sequence ``slots[i]`` brings ``counts[i]`` more tokens.  All or
+        nothing.  Returns (each sequence's length before the step, the changed page-table entries
+        as an int32 array [n, 4] of (group, slot, index, page))."""
+        B = len(slots)
+        sl, _ = ints(slots)
+        ct, _ = ints(counts)
+        caps, _ = ints(table_caps)
+        cap = len(self.groups) * sum(max(n, 0) // PAGE_TOKENS + 2 for n in counts)
+        starts = (c_int * max(B, 1))()
+        upd = np.empty((max(cap, 1), 4), dtype=np.int32)
+        n = _ok(_lib.moe_ledger_reserve(self._h, B, sl, ct, caps, starts, upd.ctypes.data_as(_IP), cap, max_tokens))
+        if n > cap:
+            raise CacheError("internal: more page-table updates than a step can make")
+        return list(starts[:B]), upd[:n]
 
     def truncate(self, slot: int, new_length: int) -> None:
         """Forget everything at or after ``new_length`` (src/model.rs:176-189).  Pages are
         kept; a ring group can only go back while the kept prefix is still inside it."""
-        if not self.slots.is_held(slot):
-            raise CacheError(f"slot {slot} is not held")
-        cur = self.length[slot]
-        if new_length > cur:
-            raise CacheError("truncate cannot lengthen a sequence")
-        for g in self.groups:
-            if g.ring_pages and new_length < cur and cur > g.ring_pages * PAGE_TOKENS:
-                raise CacheError("a windowed cache that has wrapped cannot be rewound")
-        self.length[slot] = new_length
+        _ok(_lib.moe_ledger_truncate(self._h, slot, new_length))
 
     def tokens_held(self) -> int:
         """Tokens the live sequences hold, each rounded up to whole pages."""
-        return sum(pages_for(n) * PAGE_TOKENS for n in self.length.values())
+        return _lib.moe_ledger_tokens_held(self._h)

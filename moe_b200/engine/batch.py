@@ -7,6 +7,7 @@ and copied once.
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass
 from typing import List, Optional, Sequence, Tuple
 
@@ -44,41 +45,31 @@ def layout(num_tokens: int, num_seqs: int, num_want: int) -> List[Tuple[str, int
 
 def fill_host(buf: np.ndarray, slots: Sequence[int], starts: Sequence[int], tokens: Sequence[Sequence[int]],
               want: Sequence[Sequence[int]]) -> dict:
-    """Write the step's index arrays into ``buf`` (int32); return name -> (offset, length)
-    plus the host-side facts."""
+    """Write the step's index arrays into ``buf`` (int32, C-contiguous); return name ->
+    (offset, length) plus the host-side facts.  The packing itself is the host runtime's
+    ``moe_pack_step`` (``csrc/host_runtime.cpp``)."""
+    from ..cache.allocator import _IP, _ok, host_lib, ints
+
+    L = host_lib()
     B = len(slots)
     counts = [len(t) for t in tokens]
-    T = sum(counts)
-    W = sum(len(w) for w in want)
-    offs, o = {}, 0
-    for name, n in layout(T, B, W):
-        offs[name] = (o, n)
-        o += n
-    if o > buf.size:
-        raise ValueError("staging buffer too small")
-    v = {k: buf[a:a + n] for k, (a, n) in offs.items()}
-    cu = 0
-    wi = 0
-    for s in range(B):
-        n = counts[s]
-        v["token_ids"][cu:cu + n] = tokens[s]
-        v["seq_of_token"][cu:cu + n] = s
-        v["pos"][cu:cu + n] = np.arange(starts[s], starts[s] + n, dtype=np.int32)
-        v["cu_seqlens"][s] = cu
-        v["slots"][s] = slots[s]
-        v["seq_start"][s] = starts[s]
-        v["seq_end"][s] = starts[s] + n
-        for w in want[s]:
-            if not 0 <= w < n:
-                raise ValueError(f"wanted place {w} is not among the {n} tokens of this step")
-            v["want_rows"][wi] = cu + w
-            wi += 1
-        cu += n
-    v["cu_seqlens"][B] = cu
-    if W == 0:
-        v["want_rows"][0] = 0
-    facts = dict(
-        num_tokens=T, num_seqs=B, num_want=W, max_new=max(counts), max_end=max(s + n for s, n in zip(starts, counts)),
-        all_decode=all(n == 1 for n in counts), all_fresh=all(s == 0 for s in starts),
-    )
-    return {"offsets": offs, "used": o, "facts": facts}
+    flat = np.fromiter((x for t in tokens for x in t), dtype=np.int32, count=sum(counts))
+    wflat = np.fromiter((x for w in want for x in w), dtype=np.int32, count=sum(len(w) for w in want))
+    sl, _ = ints(slots)
+    st, _ = ints(starts)
+    ct, _ = ints(counts)
+    wc, _ = ints([len(w) for w in want])
+    offs = (ctypes.c_int * 8)()
+    facts = (ctypes.c_int * 7)()
+    used = L.moe_pack_step(buf.ctypes.data_as(_IP), buf.size, B, sl, st, ct, flat.ctypes.data_as(_IP), wc,
+                           wflat.ctypes.data_as(_IP), offs, facts)
+    _ok(int(used))
+    T, _, W = facts[0], facts[1], facts[2]
+    names = [n for n, _ in layout(T, B, W)]
+    sizes = [n for _, n in layout(T, B, W)]
+    return {
+        "offsets": {n: (offs[i], sizes[i]) for i, n in enumerate(names)},
+        "used": int(used),
+        "facts": dict(num_tokens=T, num_seqs=B, num_want=W, max_new=facts[3], max_end=facts[4],
+                      all_decode=bool(facts[5]), all_fresh=bool(facts[6])),
+    }

@@ -20,7 +20,9 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
-from ..cache.allocator import CacheError, pages_for
+import ctypes
+
+from ..cache.allocator import _IP, CacheError, _ok, host_lib, ints
 from ..cache.kv import KVCache
 from ..models.decoder import DecoderModel
 from ..ops import core
@@ -45,6 +47,7 @@ class _DecodeGraph:
             o += 3 * size
         self.used = o
         self.offsets = offs
+        self._upd_off_c, _ = ints(self.upd_off)
         self.host = torch.zeros(o, dtype=torch.int32).pin_memory()
         self.dev = torch.zeros(o, dtype=torch.int32, device=engine.rt.device)
         views = {k: self.dev[a:a + n] for k, (a, n) in offs.items()}
@@ -55,35 +58,18 @@ class _DecodeGraph:
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
 
-    def fill(self, engine: "Engine", slots, starts, tokens, updates) -> None:
+    def fill(self, engine: "Engine", slots, starts, tokens, updates: np.ndarray) -> None:
+        """Pack the step into the pinned buffer (``moe_pack_decode`` of the host runtime) and start its copy."""
         if self.busy:
             self.event.synchronize()
             self.busy = False
-        B, S = len(slots), self.size
-        h = self.host.numpy()
-        v = {k: h[a:a + n] for k, (a, n) in self.offsets.items()}
-        pad = engine.cache.padding_slot
-        v["token_ids"][:B] = tokens
-        v["token_ids"][B:] = 0
-        v["seq_of_token"][:B] = np.arange(B, dtype=np.int32)
-        v["seq_of_token"][B:] = -1
-        v["pos"][:B] = starts
-        v["pos"][B:] = 0
-        v["cu_seqlens"][:B + 1] = np.arange(B + 1, dtype=np.int32)
-        v["cu_seqlens"][B + 1:] = B
-        v["slots"][:B] = slots
-        v["slots"][B:] = pad
-        v["seq_start"][:B] = starts
-        v["seq_start"][B:] = 0
-        v["seq_end"][:B] = np.asarray(starts, dtype=np.int32) + 1
-        v["seq_end"][B:] = 1
-        v["want_rows"][:] = np.arange(S, dtype=np.int32)
-        for gi, o in enumerate(self.upd_off):
-            u = h[o:o + 3 * S].reshape(S, 3)
-            u[:, 0], u[:, 1], u[:, 2] = pad, 0, 0          # no-op: the padding row's first entry stays 0
-            mine = [(s, i, p) for g, s, i, p in updates if g == gi]
-            if mine:
-                u[:len(mine)] = np.asarray(mine, dtype=np.int32)
+        sl, B = ints(slots)
+        st, _ = ints(starts)
+        tk, _ = ints(tokens)
+        upd = np.ascontiguousarray(updates, dtype=np.int32)
+        _ok(host_lib().moe_pack_decode(ctypes.cast(self.host.data_ptr(), _IP), self.size, B, sl, st, tk,
+                                       engine.cache.padding_slot, len(self.upd_off), self._upd_off_c,
+                                       upd.ctypes.data_as(_IP), int(upd.shape[0])))
         self.dev.copy_(self.host, non_blocking=True)
         self.event.record()
         self.busy = True
@@ -136,6 +122,7 @@ class Engine:
         self.use_graphs = graph_safe if use_graphs is None else (use_graphs and graph_safe)
         self._routed = [p for p in parts if hasattr(p, "trace")]
         self._graphs: Dict[int, _DecodeGraph] = {}
+        self._table_caps = [0 if g.ring_pages else g.max_pages_per_seq for g in self.cache.groups]
 
     # ---- sequences -----------------------------------------------------------------
     def new_sequence(self) -> int:
@@ -159,33 +146,11 @@ class Engine:
         return self._stage_host.numpy(), self._stage_dev
 
     # ---- the step ----------------------------------------------------------------------
-    def _reserve(self, slots: Sequence[int], counts: Sequence[int]) -> List[Tuple[int, int, int, int]]:
-        """Give every sequence room for its new tokens, or change nothing and raise."""
-        led = self.cache.ledger
-        if len(set(slots)) != len(slots):
-            raise ValueError("a slot appears twice in one step")
-        need = [0] * len(led.groups)
-        for s, n in zip(slots, counts):
-            if not led.slots.is_held(s):
-                raise CacheError(f"slot {s} is not held")
-            if n <= 0:
-                raise ValueError("every sequence of a step brings at least one token")
-            for gi, g in enumerate(led.groups):
-                need[gi] += max(0, pages_for(led.length[s] + n, g.ring_pages) - len(g.pages[s]))
-        for gi, g in enumerate(led.groups):
-            if need[gi] > g.pool.num_free:
-                raise CacheError(
-                    f"the cache is full: this step needs {need[gi]} more pages of 64 tokens, "
-                    f"{g.pool.num_free} are free (max_tokens = {self.cache.max_tokens})"
-                )
-            if not g.ring_pages:
-                for s, n in zip(slots, counts):
-                    if pages_for(led.length[s] + n) > self.cache.groups[gi].max_pages_per_seq:
-                        raise CacheError("a sequence would outgrow the page table")
-        updates = []
-        for s, n in zip(slots, counts):
-            updates.extend(led.extend(s, led.length[s] + n))
-        return updates
+    def _reserve(self, slots: Sequence[int], counts: Sequence[int]) -> Tuple[List[int], np.ndarray]:
+        """Give every sequence room for its new tokens, or change nothing and raise.  Returns each
+        sequence's length before the step and the page-table entries that changed, [n, 4] of
+        (group, slot, index, page).  (``moe_ledger_reserve`` of the host runtime.)"""
+        return self.cache.ledger.reserve(slots, counts, self._table_caps, self.cache.max_tokens)
 
     def _bucket(self, B: int) -> Optional[int]:
         for b in GRAPH_BUCKETS:
@@ -215,8 +180,7 @@ class Engine:
             for i in w:
                 if not 0 <= i < n:
                     raise ValueError(f"wanted place {i} is not among the {n} tokens of this step")
-        starts = [self.cache.length(s) if self.cache.ledger.slots.is_held(s) else 0 for s in slots]
-        updates = self._reserve(slots, counts)
+        starts, updates = self._reserve(slots, counts)
         self.steps_run += 1
 
         # ---- one token each: replay the bucket's graph -----------------------------------
@@ -237,7 +201,7 @@ class Engine:
 
         # ---- the general step -----------------------------------------------------------------
         T, W = sum(counts), sum(len(w) for w in want)
-        n_upd = len(updates)
+        n_upd = int(updates.shape[0])
         host, dev = self._staging(3 * T + 4 * B + 2 + max(W, 1) + 3 * n_upd)
         info = fill_host(host, slots, starts, tokens, want)
         used = info["used"]
@@ -245,11 +209,11 @@ class Engine:
         if n_upd:
             o = used
             for gi in range(len(self.cache.groups)):
-                mine = [(s, i, p) for g, s, i, p in updates if g == gi]
-                if mine:
-                    host[o:o + 3 * len(mine)] = np.asarray(mine, dtype=np.int32).reshape(-1)
-                    upd_off[gi] = (o, len(mine))
-                    o += 3 * len(mine)
+                mine = updates[updates[:, 0] == gi, 1:]
+                if mine.shape[0]:
+                    host[o:o + 3 * mine.shape[0]] = mine.reshape(-1)
+                    upd_off[gi] = (o, int(mine.shape[0]))
+                    o += 3 * mine.shape[0]
             used = o
         dev[:used].copy_(self._stage_host[:used], non_blocking=True)
         self._stage_event.record()

@@ -1,7 +1,9 @@
-"""Compiling the CUDA sources for sm_100a and loading the result.
+"""Compiling the native sources and loading the result.
 
-Each *library* is a set of ``.cu`` files from ``moe_b200/csrc`` linked into one
-shared object with plain C entry points, loaded with ``ctypes``.  A library is
+Each *library* is a set of files from ``moe_b200/csrc`` linked into one shared
+object with plain C entry points, loaded with ``ctypes``: ``.cu`` files are
+compiled by ``nvcc`` for sm_100a, ``.cpp`` files (the host runtime, which needs
+no CUDA and is tested on machines without a GPU) by the host C++ compiler.  A library is
 compiled the first time it is asked for (one ``nvcc`` per file, in parallel, a
 progress line every few seconds) and afterwards only when a source, a header or
 a flag changed.  The objects live beside the sources in ``csrc/_build``; when
@@ -33,7 +35,10 @@ LIBRARIES: Dict[str, List[str]] = {
              "moe.cu", "sampling.cu"],
     # tcgen05 / TMA kernels of the bfloat16 path; a float32 model never builds or loads them
     "tc": ["gemm_tc.cu", "attention_prefill.cu"],
+    # host side of a step (cache ledger, step packing): plain C++, no CUDA
+    "host": ["host_runtime.cpp"],
 }
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall"]
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
@@ -48,6 +53,14 @@ def find_nvcc() -> str:
         if cand and os.path.isfile(cand) and os.access(cand, os.X_OK):
             return cand
     raise BuildError("nvcc not found (looked at $NVCC, PATH and /usr/local/cuda/bin); the kernels cannot be built")
+
+
+def find_cxx() -> str:
+    for cand in (os.environ.get("CXX"), "g++", "c++", "clang++"):
+        path = shutil.which(cand) if cand else None
+        if path:
+            return path
+    raise BuildError("no C++ compiler found (looked at $CXX, g++, c++, clang++); the host runtime cannot be built")
 
 
 def _build_dir() -> str:
@@ -83,11 +96,14 @@ def _say(msg: str) -> None:
     print(f"[moe_b200] {msg}", file=sys.stderr, flush=True)
 
 
-def _compile_one(nvcc: str, src: str, obj: str, extra: List[str]) -> None:
-    cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, *extra, "-I", CSRC, "-c", os.path.join(CSRC, src), "-o", obj]
+def _compile_one(compiler: str, src: str, obj: str, extra: List[str]) -> None:
+    if src.endswith(".cpp"):
+        cmd = [compiler, *CXX_FLAGS, *extra, "-I", CSRC, "-c", os.path.join(CSRC, src), "-o", obj]
+    else:
+        cmd = [compiler, *ARCH_FLAGS, *NVCC_FLAGS, *extra, "-I", CSRC, "-c", os.path.join(CSRC, src), "-o", obj]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
-        raise BuildError(f"nvcc failed on {src}:\n{r.stdout}\n{r.stderr}")
+        raise BuildError(f"{os.path.basename(compiler)} failed on {src}:\n{r.stdout}\n{r.stderr}")
 
 
 def build(name: str, verbose: bool = True) -> str:
@@ -104,8 +120,9 @@ def build(name: str, verbose: bool = True) -> str:
         with open(stamp) as f:
             if f.read().strip() == want:
                 return so
-    nvcc = find_nvcc()
-    if verbose:
+    host_only = all(s.endswith(".cpp") for s in sources)
+    nvcc = find_cxx() if host_only else find_nvcc()
+    if verbose and not host_only:
         _say(f"compiling kernel library '{name}' ({len(sources)} files) for sm_100a ...")
     t0 = time.time()
     objs = [os.path.join(out_dir, f"{name}_{os.path.splitext(s)[0]}.{want}.o") for s in sources]
@@ -126,7 +143,7 @@ def build(name: str, verbose: bool = True) -> str:
         for f in futures:
             f.result()
     tmp = so + f".{os.getpid()}.tmp"
-    link = [nvcc, *ARCH_FLAGS, "-shared", "-o", tmp, *objs]
+    link = [nvcc, "-shared", "-o", tmp, *objs] if host_only else [nvcc, *ARCH_FLAGS, "-shared", "-o", tmp, *objs]
     r = subprocess.run(link, capture_output=True, text=True)
     if r.returncode != 0:
         raise BuildError(f"linking {name} failed:\n{r.stdout}\n{r.stderr}")
@@ -138,7 +155,7 @@ def build(name: str, verbose: bool = True) -> str:
             os.remove(o)
         except OSError:
             pass
-    if verbose:
+    if verbose and not host_only:
         _say(f"kernel library '{name}' ready in {time.time() - t0:.0f} s")
     return so
 
