@@ -38,6 +38,10 @@ A27B = dict(
     max_position_embeddings=8192,
 )
 FULL_LAYERS = 24
+# the larger shape of the same architecture (Qwen2-57B-A14B): only with --sweep, to see other sizes
+A57B = dict(A27B, num_hidden_layers=28, hidden_size=3584, num_attention_heads=28, num_key_value_heads=4,
+            num_experts=64, num_experts_per_tok=8, moe_intermediate_size=2560, shared_expert_intermediate_size=20480,
+            intermediate_size=18944)
 CONTEXT, PROMPT_LEN, PREFILL_TOKENS = 4096, 512, 2048
 
 
@@ -112,8 +116,8 @@ def run_ours(args):
     from moe_b200.sampling.sampler import DeviceSampler
 
     pk = peaks()
-    cfg = dict(A27B)
-    layers = args.layers or FULL_LAYERS
+    cfg = dict(A57B if (args.sweep and args.shape == "57b") else A27B)
+    layers = args.layers or cfg["num_hidden_layers"]
     cfg["num_hidden_layers"] = layers
     torch.cuda.set_device(0)
     model = moe_b200.random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
@@ -305,6 +309,7 @@ def main():
                     help="run a few steps of one kind between cudaProfilerStart/Stop (for ncu "
                          "--profile-from-start off) and print no benchmark line")
     ap.add_argument("--batch", type=int, default=8, help="with --profile-step decode: sequences in the batch")
+    ap.add_argument("--shape", choices=["a2.7b", "57b"], default="a2.7b", help="with --sweep: the layer sizes")
     ap.add_argument("--prompt-len", type=int, default=0, help="with --sweep: tokens in each prompt (default 512)")
     ap.add_argument("--sweep", default=None, help="comma-separated batch sizes: print decode throughput for each "
                                                   "and no benchmark line")
