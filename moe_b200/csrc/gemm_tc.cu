@@ -18,9 +18,13 @@
 //   SWIGLU   W holds gate rows [0, I) and up rows [I, 2I) per group; two accumulators;
 //            out[t, j] = silu(gate) * up  (reference: src/model.rs:26-35)
 // Groups (routed experts): rows of X are partitioned by group_offsets[G + 1]; group g
-// uses the weight slab g.  Split K: each split writes float32 partial sums to scratch;
-// the CTA that arrives last at the tile's ticket adds them in split order (so the sum
-// does not depend on arrival order) and runs the epilogue.
+// uses the weight slab g.  Split K (few tokens, where the weight stream needs every SM):
+// up to 8 splits of a tile form a thread-block cluster; each leaves its float32 partial
+// tile in its own shared memory and CTA r of the cluster adds rows r, r + S, ... in split
+// order, reading its peers through distributed shared memory.  More than 8 splits write
+// their partials to scratch, and the CTA that arrives last at the tile's ticket adds them
+// in split order.  Either way the sum does not depend on arrival order.
+// Many tokens take the persistent form further down (gemm_tc_persistent_kernel).
 //
 // Every wait on a barrier is bounded.  A wait that runs out sets ST_WAIT_TIMEOUT in the
 // status word and the CTA drains, frees its tensor memory and returns.
