@@ -251,3 +251,43 @@ def test_rmsnorm_with_uncombined_delta_equals_combine_then_rmsnorm(core, T, H, E
         assert float((outs[0][2].float() - outs[1][2].float()).abs().max()) <= 2.0 ** -7 * float(outs[0][2].float().abs().max())
     if rows is not None:
         assert torch.equal(outs[1][0], x0)                        # selected rows: the stream is left alone
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window,where,seen", [(None, 0, True), (None, 299, True), (None, "self", True),
+                                                (100, 201, True), (100, 200, False), (100, "self", True)])
+def test_fused_decode_attention_finds_one_key_among_hundreds(core, dt, window, where, seen):
+    """Random keys would hide a key that is skipped or taken twice.  Here every cached key is zero
+    except ONE, which points along the query, and only its value is non-zero: the output is about
+    0.9 if that key is seen and 0 if not.  The key sits at the sequence's first position, at its
+    last cached one, at the window's first position, just before the window, or it is the step's
+    own key (which the fused kernel takes from the q/k/v row, not from the cache)."""
+    from moe_b200.cache import KVCache, KVRequest
+
+    nh, nkv, hd, p = 2, 1, 64, 300                               # the new token's position
+    cache = KVCache({0: KVRequest(nkv, hd, window)}, {0: None}, 1024, 2, dt, DEV)
+    view, grp = cache.view(0), cache.groups[0]
+    slot = cache.acquire()
+    G.give_pages(cache, slot, p + 1)
+    batch = G.make_batch(DEV, [slot], [p], [1])
+    u = torch.zeros(hd, device=DEV)
+    u[5] = 8.0
+    qkv = torch.zeros(1, (nh + 2 * nkv) * hd, device=DEV)
+    qkv[0, :hd] = u                                              # head 0 asks for u; head 1 asks for nothing
+    if where == "self":
+        qkv[0, nh * hd:(nh + 1) * hd] = u                        # the step's own key ...
+        qkv[0, (nh + 1) * hd:] = 1.0                             # ... and value
+    else:
+        r = where % grp.ring if grp.ring else where
+        page = int(grp.table[slot, r // 64])
+        view.k[page, 0, r % 64] = u.to(dt)
+        view.v[page, 0, r % 64] = 1.0
+    out = torch.full((1, nh * hd), 7.0, device=DEV, dtype=dt)
+    st = torch.zeros(4, dtype=torch.int32, device=DEV)
+    assert core.attention_decode_fused(qkv, None, 0, view, batch, out, nh=nh, window=window, scale=1.0 / 8.0, status=st)
+    assert int(st[0]) == 0
+    n = min(window, p + 1) if window else p + 1                  # keys the query sees
+    want = float(torch.exp(torch.tensor(8.0)) / (torch.exp(torch.tensor(8.0)) + n - 1)) if seen else 0.0
+    head0, head1 = out[0, :hd].float(), out[0, hd:].float()
+    assert float((head0 - want).abs().max()) < 1e-2, (float(head0[0]), want)
+    assert float((head1 - (1.0 / n if seen else 0.0)).abs().max()) < 1e-3      # head 1: a plain mean of the values
