@@ -535,8 +535,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 // One CTA per SM walks over the tiles (blockIdx.x, blockIdx.x + gridDim.x, ...).  The producer and
 // the MMA issuer run ahead across tile borders, and the accumulator in tensor memory is doubled,
 // so that the epilogue of one tile (tensor memory -> registers -> global memory) runs while the
-// tensor cores work on the next.  No K split here.  Tile order: all token tiles of one feature
-// tile first, so that CTAs running at the same time share weight tiles in L2.
+// tensor cores work on the next.  No K split here.  Tile order: see tile_of (what is read more
+// than once should be read by CTAs that run at the same time, so that it comes from L2).
 template <int BN, int MODE>
 struct PCfg {
     static constexpr int NW = MODE == MODE_SWIGLU ? 2 : 1;
@@ -559,12 +559,17 @@ struct Tile {
 template <int BN>
 __device__ __forceinline__ Tile tile_of(int item, int m_tiles, const Params& p, const int* prefix, const int* offs) {
     Tile t;
-    const int nt = item / m_tiles, m = item % m_tiles;
-    t.n0 = nt * TILE_W;
     if (!p.group_offsets) {
-        t.g = 0, t.row0 = m * BN, t.row_end = p.M;
+        // all token tiles of one feature tile first: CTAs running together share weight tiles in L2
+        const int nt = item / m_tiles, m = item % m_tiles;
+        t.n0 = nt * TILE_W, t.g = 0, t.row0 = m * BN, t.row_end = p.M;
         return t;
     }
+    // grouped: all feature tiles of one token tile first.  A group's weights are read once anyway;
+    // its activations are read by every feature tile, and stay in L2 only if those run together
+    const int n_tiles = (p.N + TILE_W - 1) / TILE_W;
+    const int m = item / n_tiles;
+    t.n0 = (item % n_tiles) * TILE_W;
     int lo = 0, hi = p.num_groups;          // the last group whose first tile is <= m
     while (hi - lo > 1) {
         const int mid = (lo + hi) >> 1;
