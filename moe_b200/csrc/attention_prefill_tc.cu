@@ -1,0 +1,478 @@
+// Attention of whole prompts on the 5th-generation tensor cores (tcgen05), head sizes 64 and 128.
+//
+// Same formulas as attention_prefill.cu (reference: src/model.rs:794-827): causal, optional window
+// [p + 1 - w, p], scale 1/sqrt(d), kv head = head / (heads / kv_heads); scores, running maximum
+// and sum, and the output accumulator are float32; P enters the second product as two bfloat16
+// terms (head and remainder), i.e. with 16 bits.
+//
+// One CTA takes 128 query rows of one (sequence, head) and walks the key tiles of 128 that the
+// causal window allows:
+//
+//   warp 0      TMA producer: Q once, then K and V tiles through a ring of two stages
+//   warp 1      MMA issuer: S = Q K^T (operands in shared memory, S in tensor memory, two
+//               buffers), then O_tile = P V with P read from tensor memory and V as the
+//               MN-major operand
+//   warps 2-5   one thread per query row: reads its row of S from tensor memory (no cross-thread
+//               reduction), masks, keeps the running maximum and sum, writes P (two bfloat16
+//               terms) back to tensor memory, and adds each O_tile to its float32 output row
+//
+// S of tile j + 1 is issued before the softmax of tile j has finished, so the tensor cores work
+// on the next scores meanwhile.  Every barrier wait is bounded (ST_WAIT_TIMEOUT).
+#include <cuda.h>
+
+#include <mutex>
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int QT = 128, KT = 128;
+constexpr uint32_t WAIT_LIMIT = 1u << 24;
+// tensor-memory columns: two score buffers, the product of one tile, P's two terms
+constexpr uint32_t COL_S = 0, COL_O = 256, COL_PHI = 384, COL_PLO = 448, TMEM_COLS = 512;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false if the barrier did not complete in time or another role gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// D (tensor memory) = A (shared memory) x B (shared memory)
+__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// D (tensor memory) = A (tensor memory) x B (shared memory)
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(r[0]),
+                 "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Shared-memory descriptors, 128-byte swizzle, version 1 (sm_100).  A tile is stored as chunks of
+// 64 elements (128 bytes) of every row, 128 rows per chunk (16 KB), as TMA writes them.
+//   K-major (Q and K: the contraction runs along a row): groups of 8 rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+    return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+//   MN-major (V: the contraction runs down the rows, the output dimension along a row): blocks of
+//   64 output elements are one chunk (16 KB) apart, groups of 8 contraction rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr) {
+    return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)(16384 >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// c = f32, a = b = bf16; bit 16: B is MN-major; N >> 3 at 17; M = 128 (>> 4 at 24)
+__host__ __device__ constexpr uint32_t instr_desc(int n, int b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(128 >> 4) << 24);
+}
+__device__ __forceinline__ float ex2_approx(float x) {     // 2^x; 0 for -inf
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(192)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                       const __grid_constant__ CUtensorMap tmV, __nv_bfloat16* __restrict__ out,
+                       const int* __restrict__ cu_seqlens, int num_seqs, int nh, int nkv, int window, float scale_log2,
+                       int* status) {
+    constexpr int CH = HD / 64;                      // 128-byte chunks of a row
+    constexpr int TILE_BYTES = CH * 128 * 128;       // a 128-row operand tile
+    constexpr int STAGE_BYTES = 2 * TILE_BYTES;      // K, then V
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ int s_seq, s_tile;
+    __shared__ volatile int s_abort;
+    __shared__ uint32_t s_tmem;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // which (sequence, query tile): tiles are numbered sequence by sequence
+    if (threadIdx.x == 0) {
+        int tile = blockIdx.x, seq = -1;
+        for (int s = 0; s < num_seqs; s++) {
+            const int tiles = (cu_seqlens[s + 1] - cu_seqlens[s] + QT - 1) / QT;
+            if (tile < tiles) {
+                seq = s;
+                break;
+            }
+            tile -= tiles;
+        }
+        s_seq = seq, s_tile = tile, s_abort = 0;
+    }
+    __syncthreads();
+    const int seq = s_seq;
+    if (seq < 0) return;
+    const int tok0 = cu_seqlens[seq], len = cu_seqlens[seq + 1] - tok0;
+    const int q_tile = (len + QT - 1) / QT - 1 - s_tile;        // heavier tiles (later rows) first
+    const int q0 = q_tile * QT;
+    const int head = blockIdx.y, kvh = head / (nh / nkv);
+    const int q_last = min(q0 + QT, len) - 1;
+    const int kv_lo = window > 0 ? max(0, q0 + 1 - window) / KT : 0;
+    const int n_tiles = q_last / KT - kv_lo + 1;
+
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t sQ = base;
+    auto sK = [&](int st) { return base + TILE_BYTES + st * STAGE_BYTES; };
+    auto sV = [&](int st) { return base + TILE_BYTES + st * STAGE_BYTES + TILE_BYTES; };
+    const uint32_t bars = base + TILE_BYTES + 2 * STAGE_BYTES;
+    const uint32_t q_full = bars;
+    auto kv_full = [&](int st) { return bars + 8u * (1 + st); };
+    auto kv_empty = [&](int st) { return bars + 8u * (3 + st); };
+    auto s_full = [&](int b) { return bars + 8u * (5 + b); };
+    auto s_empty = [&](int b) { return bars + 8u * (7 + b); };
+    const uint32_t p_full = bars + 8u * 9, pv_done = bars + 8u * 10, o_empty = bars + 8u * 11;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int i = 0; i < 2; i++) {
+            mbar_init(kv_full(i), 1);
+            mbar_init(kv_empty(i), 1);
+            mbar_init(s_full(i), 1);
+            mbar_init(s_empty(i), 4);        // one arrival per softmax warp
+        }
+        mbar_init(p_full, 4);
+        mbar_init(pv_done, 1);
+        mbar_init(o_empty, 4);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(&s_tmem), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem;
+
+    if (warp == 0) {
+        // ---- producer ------------------------------------------------------------------------------
+        if (lane == 0) {
+            mbar_expect_tx(q_full, TILE_BYTES);
+            for (int c = 0; c < CH; c++) tma_load_3d(sQ + c * 16384, &tmQ, c * 64, head, tok0 + q0, q_full);
+            bool ok = true;
+            int it = 0;
+            for (; it < n_tiles; it++) {
+                const int st = it & 1;
+                ok = mbar_wait(kv_empty(st), ((it >> 1) & 1) ^ 1, &s_abort);
+                if (!ok) break;
+                const int j0 = tok0 + (kv_lo + it) * KT;
+                mbar_expect_tx(kv_full(st), STAGE_BYTES);
+                for (int c = 0; c < CH; c++) {
+                    tma_load_3d(sK(st) + c * 16384, &tmK, c * 64, kvh, j0, kv_full(st));
+                    tma_load_3d(sV(st) + c * 16384, &tmV, c * 64, kvh, j0, kv_full(st));
+                }
+            }
+            if (!ok) {
+                atomicOr(status, ST_WAIT_TIMEOUT);
+                s_abort = 1;
+                for (int i = max(0, it - 2); i < it; i++)       // copies in flight must land
+                    mbar_wait(kv_full(i & 1), (i >> 1) & 1, &s_abort);
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer ----------------------------------------------------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = instr_desc(KT, 0), idesc_pv = instr_desc(HD, 1);
+            bool ok = mbar_wait(q_full, 0, &s_abort);
+            auto issue_s = [&](int it) {           // scores of tile `it` into buffer it & 1
+                const int b = it & 1;
+                if (!mbar_wait(kv_full(b), (it >> 1) & 1, &s_abort)) return false;
+                if (!mbar_wait(s_empty(b), ((it >> 1) & 1) ^ 1, &s_abort)) return false;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ks++) {
+                    const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
+                    umma_ss(tmem + COL_S + b * KT, desc_k_major(sQ + off), desc_k_major(sK(b) + off), idesc_s, ks > 0);
+                }
+                umma_commit(s_full(b));
+                return true;
+            };
+            if (ok) ok = issue_s(0);
+            for (int it = 0; it < n_tiles && ok; it++) {
+                if (it + 1 < n_tiles) ok = issue_s(it + 1);
+                if (!ok) break;
+                ok = mbar_wait(p_full, it & 1, &s_abort) && mbar_wait(o_empty, (it & 1) ^ 1, &s_abort);
+                if (!ok) break;
+                tc_fence_after();
+                const int st = it & 1;
+#pragma unroll
+                for (int half = 0; half < 2; half++) {
+#pragma unroll
+                    for (int ks = 0; ks < KT / 16; ks++)         // 16 keys per step: 8 columns of packed P
+                        umma_ts(tmem + COL_O, tmem + (half ? COL_PLO : COL_PHI) + ks * 8, desc_mn_major(sV(st) + ks * 2048),
+                                idesc_pv, (half | ks) != 0);
+                }
+                umma_commit(pv_done);
+                umma_commit(kv_empty(st));
+            }
+            if (!ok) {
+                atomicOr(status, ST_WAIT_TIMEOUT);
+                s_abort = 1;
+            }
+        }
+    } else {
+        // ---- one thread per query row ----------------------------------------------------------------
+        const int qd = warp & 3;                               // tensor-memory lane group of this warp
+        const uint32_t lane_base = (uint32_t)(qd * 32) << 16;
+        const int row = q0 + qd * 32 + lane;                   // position of this thread's query
+        float o[HD];
+#pragma unroll
+        for (int d = 0; d < HD; d++) o[d] = 0.f;
+        float m = -INFINITY, l = 0.f;
+        bool ok = true;
+        auto add_product = [&]() {                             // o += O_tile, then the tile may be overwritten
+            tc_fence_after();
+#pragma unroll
+            for (int c0 = 0; c0 < HD; c0 += 16) {
+                float t[16];
+                tmem_ld16(tmem + COL_O + lane_base + c0, t);
+#pragma unroll
+                for (int i = 0; i < 16; i++) o[c0 + i] += t[i];
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(o_empty);
+        };
+        for (int it = 0; it < n_tiles; it++) {
+            const int b = it & 1;
+            ok = mbar_wait(s_full(b), (it >> 1) & 1, &s_abort);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t ts = tmem + COL_S + b * KT + lane_base;
+            const int j0 = (kv_lo + it) * KT;
+            // a tile strictly below the diagonal, inside the window and inside the sequence needs no mask
+            const bool full = j0 + KT - 1 <= q0 && j0 + KT <= len && (window <= 0 || j0 >= q0 + QT - window);
+            auto tile_softmax = [&](auto masked_tag) -> bool {
+                constexpr bool MASKED = decltype(masked_tag)::value;
+                auto visible = [&](int j) { return j <= row && j < len && (window <= 0 || j >= row + 1 - window); };
+                // pass 1: the row's maximum (of the raw scores: the scale is positive)
+                float mx = -INFINITY;
+#pragma unroll
+                for (int c0 = 0; c0 < KT; c0 += 16) {
+                    float s[16];
+                    tmem_ld16(ts + c0, s);
+#pragma unroll
+                    for (int i = 0; i < 16; i++)
+                        if (!MASKED || visible(j0 + c0 + i)) mx = fmaxf(mx, s[i]);
+                }
+                mx *= scale_log2;
+                // The running maximum only has to keep the exponentials in range: it moves when the
+                // tile's maximum exceeds it by more than 8 (a factor 256), which spares most rescalings.
+                float m_new = m, alpha = 1.f;
+                if (mx > m + 8.f || m == -INFINITY) {
+                    m_new = fmaxf(m, mx);
+                    alpha = (m == -INFINITY) ? 0.f : ex2_approx(m - m_new);
+                }
+                // the previous tile's product belongs to the old maximum: add it, then rescale
+                if (it > 0) {
+                    if (!mbar_wait(pv_done, (it - 1) & 1, &s_abort)) return false;
+                    add_product();
+                }
+                if (alpha != 1.f) {
+#pragma unroll
+                    for (int d = 0; d < HD; d++) o[d] *= alpha;
+                }
+                // pass 2: P in two bfloat16 terms, into tensor memory (two keys per 32-bit column)
+                const float neg_m = m_new == -INFINITY ? 0.f : -m_new;     // no key seen yet: every p is 0 anyway
+                float rs = 0.f;
+#pragma unroll
+                for (int c0 = 0; c0 < KT; c0 += 16) {
+                    float s[16];
+                    tmem_ld16(ts + c0, s);
+                    uint32_t hi[8], lo[8];
+#pragma unroll
+                    for (int i = 0; i < 16; i += 2) {
+                        float x0 = fmaf(s[i], scale_log2, neg_m), x1 = fmaf(s[i + 1], scale_log2, neg_m);
+                        if (MASKED) {
+                            if (!visible(j0 + c0 + i)) x0 = -INFINITY;
+                            if (!visible(j0 + c0 + i + 1)) x1 = -INFINITY;
+                        }
+                        const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+                        rs += p0 + p1;
+                        const uint32_t h = pack_bf16(p0, p1);
+                        hi[i / 2] = h;
+                        lo[i / 2] = pack_bf16(p0 - __uint_as_float(h << 16), p1 - __uint_as_float(h & 0xffff0000u));
+                    }
+                    tmem_st8(tmem + COL_PHI + lane_base + c0 / 2, hi);
+                    tmem_st8(tmem + COL_PLO + lane_base + c0 / 2, lo);
+                }
+                l = l * alpha + rs;
+                m = m_new;
+                return true;
+            };
+            ok = full ? tile_softmax(std::false_type{}) : tile_softmax(std::true_type{});
+            if (!ok) break;
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(s_empty(b));       // the scores have been read
+                mbar_arrive(p_full);           // P is in place
+            }
+        }
+        if (ok && n_tiles > 0) {
+            ok = mbar_wait(pv_done, (n_tiles - 1) & 1, &s_abort);
+            if (ok) add_product();
+        }
+        if (!ok) {
+            if (lane == 0) {
+                atomicOr(status, ST_WAIT_TIMEOUT);
+                s_abort = 1;
+            }
+        } else if (row < len) {
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            uint4* dst = reinterpret_cast<uint4*>(out + ((size_t)(tok0 + row) * nh + head) * HD);
+#pragma unroll
+            for (int d = 0; d < HD; d += 8) {
+                uint4 v;
+                v.x = pack_bf16(o[d] * inv, o[d + 1] * inv), v.y = pack_bf16(o[d + 2] * inv, o[d + 3] * inv);
+                v.z = pack_bf16(o[d + 4] * inv, o[d + 5] * inv), v.w = pack_bf16(o[d + 6] * inv, o[d + 7] * inv);
+                dst[d / 8] = v;
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
+// ---- host side -------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)sym;
+    });
+    return fn;
+}
+
+// bf16 [tokens, heads, hd] contiguous; box = 64 elements of one head for 128 tokens, 128-byte swizzle
+bool make_map(CUtensorMap* map, const void* ptr, int tokens, int heads, int hd) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)heads, (cuuint64_t)tokens};
+    cuuint64_t strides[2] = {(cuuint64_t)hd * 2, (cuuint64_t)heads * hd * 2};
+    cuuint32_t box[3] = {64, 1, 128};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int HD>
+int launch(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, void* out, const int* cu_seqlens,
+           int num_seqs, int num_tokens, int nh, int nkv, int window, float scale, int* status, cudaStream_t stream) {
+    constexpr int TILE_BYTES = (HD / 64) * 128 * 128;
+    const int smem = 5 * TILE_BYTES + 1024 + 128;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid((num_tokens + QT - 1) / QT + num_seqs, nh);
+    attn_prefill_tc_kernel<HD><<<grid, 192, smem, stream>>>(tmQ, tmK, tmV, (__nv_bfloat16*)out, cu_seqlens, num_seqs, nh,
+                                                            nkv, window, scale * 1.4426950408889634f, status);
+    return launch_status();
+}
+
+}  // namespace
+
+// q: [T, nh, hd], k, v: [T, nkv, hd], out: [T, nh * hd], all bfloat16, 16-byte aligned; sequences
+// start at position 0.  Returns -1 (nothing launched) for a head size or an alignment this kernel
+// does not take: the caller then uses moe_attention_prefill_bf16.
+MOE_API int moe_attention_prefill_tc(const void* q, const void* k, const void* v, void* out, const int* cu_seqlens,
+                                     int num_seqs, int num_tokens, int nh, int nkv, int hd, int window, float scale,
+                                     int* status, cudaStream_t stream) {
+    if (num_tokens <= 0) return 0;
+    if (nkv <= 0 || nh % nkv != 0 || nh > 65535) return (int)cudaErrorInvalidValue;
+    if (hd != 64 && hd != 128) return -1;
+    if ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15) != 0) return -1;
+    CUtensorMap tmQ, tmK, tmV;
+    if (!make_map(&tmQ, q, num_tokens, nh, hd) || !make_map(&tmK, k, num_tokens, nkv, hd) ||
+        !make_map(&tmV, v, num_tokens, nkv, hd))
+        return -1;
+    if (hd == 64)
+        return launch<64>(tmQ, tmK, tmV, out, cu_seqlens, num_seqs, num_tokens, nh, nkv, window, scale, status, stream);
+    return launch<128>(tmQ, tmK, tmV, out, cu_seqlens, num_seqs, num_tokens, nh, nkv, window, scale, status, stream);
+}

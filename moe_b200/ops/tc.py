@@ -33,6 +33,8 @@ def lib():
 
         L.moe_attention_prefill_bf16.argtypes = [P, P, P, P, P, I, I, I, I, I, I, c_float, P]
         L.moe_attention_prefill_bf16.restype = c_int
+        L.moe_attention_prefill_tc.argtypes = [P, P, P, P, P, I, I, I, I, I, I, c_float, P, P]
+        L.moe_attention_prefill_tc.restype = c_int
         L.moe_tc_set_pdl.argtypes = [c_int]
         L.moe_tc_set_pdl.restype = None
         import os
@@ -164,11 +166,19 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swiglu: bool
 
 
 def attention_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, batch, out: torch.Tensor, *, nh: int, nkv: int,
-                      hd: int, window, scale: float) -> bool:
+                      hd: int, window, scale: float, status=None) -> bool:
     """Causal (optionally windowed) attention of whole prompts on the tensor cores; every
-    sequence of ``batch`` must start at position 0.  False if the head size is not taken."""
+    sequence of ``batch`` must start at position 0.  False if the head size is not taken.
+    Head sizes 64 and 128 run on tcgen05 (``attention_prefill_tc.cu``), 16 and 32 on mma.sync."""
     if q.dtype != torch.bfloat16 or hd not in (16, 32, 64, 128):
         return False
+    if hd in (64, 128) and status is not None and os.environ.get("MOE_B200_ATTN_TC", "1") != "0":
+        code = lib().moe_attention_prefill_tc(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                              batch.cu_seqlens.data_ptr(), batch.num_seqs, batch.num_tokens, nh, nkv,
+                                              hd, int(window or 0), float(scale), status.data_ptr(), core._stream())
+        if code != -1:
+            core._ok(code, "attention_prefill_tc")
+            return True
     code = lib().moe_attention_prefill_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
                                             batch.cu_seqlens.data_ptr(), batch.num_seqs, batch.num_tokens, nh, nkv,
                                             hd, int(window or 0), float(scale), core._stream())

@@ -115,7 +115,7 @@ class GQAttention(Part):
                 from ..ops import tc
 
                 done = tc.attention_prefill(q, k_new, v_new, batch, ctx, nh=self.nh, nkv=self.nkv, hd=self.hd,
-                                            window=self.window, scale=self.scale)
+                                            window=self.window, scale=self.scale, status=rt.status)
             if not done:
                 # keys of earlier steps from the cache, keys of this step from its own buffers
                 core.attention_generic(q, k_new, v_new, cache_view, batch, ctx, nh=self.nh, window=self.window,

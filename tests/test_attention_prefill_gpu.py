@@ -1,6 +1,6 @@
-"""The tensor-core prefill attention against the plain attention function: unequal sequences in
-one batch, grouped heads, windows whose edge falls inside and across key tiles, a far key that
-must dominate."""
+"""The tensor-core prefill attention kernels (tcgen05 for head sizes 64 and 128, mma.sync for
+16 ... 128) against the plain attention function: unequal sequences in one batch, grouped heads,
+windows whose edge falls inside and across key tiles, a far key that must dominate."""
 import math
 
 import pytest
@@ -21,23 +21,30 @@ def tc():
     return t
 
 
-def run(tc, q, k, v, lens, nh, nkv, hd, window):
+def run(tc, q, k, v, lens, nh, nkv, hd, window, kernel="mma"):
+    """kernel "tcgen05": the status word is given, so head sizes 64 and 128 take the tcgen05 kernel;
+    "mma": no status word, the mma.sync kernel."""
     batch = G.make_batch(DEV, list(range(len(lens))), [0] * len(lens), lens)
     out = torch.full((sum(lens), nh * hd), float("nan"), device=DEV, dtype=torch.bfloat16)
-    assert tc.attention_prefill(q, k, v, batch, out, nh=nh, nkv=nkv, hd=hd, window=window, scale=1.0 / math.sqrt(hd))
+    st = torch.zeros(4, dtype=torch.int32, device=DEV) if kernel == "tcgen05" else None
+    assert tc.attention_prefill(q, k, v, batch, out, nh=nh, nkv=nkv, hd=hd, window=window, scale=1.0 / math.sqrt(hd),
+                                status=st)
+    assert st is None or int(st[0]) == 0
     return out
 
 
-@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (3, 1, 32), (6, 3, 64), (2, 2, 128), (5, 1, 128)])
-@pytest.mark.parametrize("window", [None, 1, 8, 64, 100])
-def test_against_plain(tc, nh, nkv, hd, window):
+@pytest.mark.parametrize("kernel,nh,nkv,hd", [("mma", 4, 2, 16), ("mma", 3, 1, 32), ("mma", 6, 3, 64), ("mma", 2, 2, 128),
+                                              ("mma", 5, 1, 128), ("tcgen05", 6, 3, 64), ("tcgen05", 2, 2, 128),
+                                              ("tcgen05", 5, 1, 128)])
+@pytest.mark.parametrize("window", [None, 1, 8, 64, 100, 128, 200])
+def test_against_plain(tc, kernel, nh, nkv, hd, window):
     torch.manual_seed(hd + (window or 0))
-    lens = [1, 63, 64, 65, 200, 7]
+    lens = [1, 63, 64, 65, 200, 7, 127, 128, 129, 300]
     T = sum(lens)
     q = torch.randn(T, nh, hd, device=DEV).to(torch.bfloat16)
     k = torch.randn(T, nkv, hd, device=DEV).to(torch.bfloat16)
     v = torch.randn(T, nkv, hd, device=DEV).to(torch.bfloat16)
-    out = run(tc, q, k, v, lens, nh, nkv, hd, window).double().cpu()
+    out = run(tc, q, k, v, lens, nh, nkv, hd, window, kernel).double().cpu()
     o = 0
     for n in lens:
         ref = plain.attention(q[o:o + n].double().cpu(), k[o:o + n].double().cpu(), v[o:o + n].double().cpu(), window)
@@ -47,7 +54,8 @@ def test_against_plain(tc, nh, nkv, hd, window):
     assert torch.isfinite(out).all()
 
 
-def test_a_far_key_among_hundreds_and_the_windows_edge(tc):
+@pytest.mark.parametrize("kernel", ["mma", "tcgen05"])
+def test_a_far_key_among_hundreds_and_the_windows_edge(tc, kernel):
     """One key is made to stand out (query and key scaled): without a window the last query must
     return that key's value; with a window the key counts exactly while it is inside."""
     nh = nkv = 1
@@ -63,9 +71,9 @@ def test_a_far_key_among_hundreds_and_the_windows_edge(tc):
     q[far + 99, 0] = 40.0 * u
     q[far + 100, 0] = 40.0 * u
     qd, kd, vd = (t.to(DEV).to(torch.bfloat16) for t in (q, k, v))
-    full = run(tc, qd, kd, vd, [n], nh, nkv, hd, None).float().cpu()
+    full = run(tc, qd, kd, vd, [n], nh, nkv, hd, None, kernel).float().cpu()
     assert torch.allclose(full[n - 1], vd[far, 0].float().cpu(), atol=2e-2)
-    win = run(tc, qd, kd, vd, [n], nh, nkv, hd, 100).float().cpu()
+    win = run(tc, qd, kd, vd, [n], nh, nkv, hd, 100, kernel).float().cpu()
     # position far + 99 still sees `far` (window 100 includes itself); far + 100 no longer does
     assert torch.allclose(win[far + 99], vd[far, 0].float().cpu(), atol=2e-2)
     assert not torch.allclose(win[far + 100], vd[far, 0].float().cpu(), atol=0.2)
