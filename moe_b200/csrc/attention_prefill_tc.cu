@@ -315,16 +315,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 constexpr bool MASKED = decltype(masked_tag)::value;
                 auto visible = [&](int j) { return j <= row && j < len && (window <= 0 || j >= row + 1 - window); };
                 // pass 1: the row's maximum (of the raw scores: the scale is positive)
-                float mx = -INFINITY;
+                float mx0 = -INFINITY, mx1 = -INFINITY;         // two chains instead of one
 #pragma unroll
                 for (int c0 = 0; c0 < KT; c0 += 16) {
                     float s[16];
                     tmem_ld16(ts + c0, s);
 #pragma unroll
-                    for (int i = 0; i < 16; i++)
-                        if (!MASKED || visible(j0 + c0 + i)) mx = fmaxf(mx, s[i]);
+                    for (int i = 0; i < 16; i += 2) {
+                        if (!MASKED || visible(j0 + c0 + i)) mx0 = fmaxf(mx0, s[i]);
+                        if (!MASKED || visible(j0 + c0 + i + 1)) mx1 = fmaxf(mx1, s[i + 1]);
+                    }
                 }
-                mx *= scale_log2;
+                const float mx = fmaxf(mx0, mx1) * scale_log2;
                 // The running maximum only has to keep the exponentials in range: it moves when the
                 // tile's maximum exceeds it by more than 8 (a factor 256), which spares most rescalings.
                 float m_new = m, alpha = 1.f;
@@ -343,7 +345,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 }
                 // pass 2: P in two bfloat16 terms, into tensor memory (two keys per 32-bit column)
                 const float neg_m = m_new == -INFINITY ? 0.f : -m_new;     // no key seen yet: every p is 0 anyway
-                float rs = 0.f;
+                float rs = 0.f, rs1 = 0.f;
 #pragma unroll
                 for (int c0 = 0; c0 < KT; c0 += 16) {
                     float s[16];
@@ -357,7 +359,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                             if (!visible(j0 + c0 + i + 1)) x1 = -INFINITY;
                         }
                         const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
-                        rs += p0 + p1;
+                        rs += p0, rs1 += p1;
                         const uint32_t h = pack_bf16(p0, p1);
                         hi[i / 2] = h;
                         lo[i / 2] = pack_bf16(p0 - __uint_as_float(h << 16), p1 - __uint_as_float(h & 0xffff0000u));
@@ -365,7 +367,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                     tmem_st8(tmem + COL_PHI + lane_base + c0 / 2, hi);
                     tmem_st8(tmem + COL_PLO + lane_base + c0 / 2, lo);
                 }
-                l = l * alpha + rs;
+                l = l * alpha + (rs + rs1);
                 m = m_new;
                 return true;
             };
