@@ -13,8 +13,9 @@
 //               buffers), then O_tile = P V with P read from tensor memory and V as the
 //               MN-major operand
 //   warps 2-5   one thread per query row: reads its row of S from tensor memory (no cross-thread
-//               reduction), masks, keeps the running maximum and sum, writes P (two bfloat16
-//               terms) back to tensor memory, and adds each O_tile to its float32 output row
+//               reduction), masks, keeps the running maximum and sum, and writes P (two bfloat16
+//               terms) back to tensor memory.  The output row accumulates in tensor memory over
+//               all tiles; its thread rescales it there when the running maximum moves
 //
 // S of tile j + 1 is issued before the softmax of tile j has finished, so the tensor cores work
 // on the next scores meanwhile.  Every barrier wait is bounded (ST_WAIT_TIMEOUT).
@@ -29,7 +30,7 @@ namespace {
 
 constexpr int QT = 128, KT = 128;
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
-// tensor-memory columns: two score buffers, the product of one tile, P's two terms
+// tensor-memory columns: two score buffers, the output rows, P's two terms
 constexpr uint32_t COL_S = 0, COL_O = 256, COL_PHI = 384, COL_PLO = 448, TMEM_COLS = 512;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -97,21 +98,35 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
-    uint32_t r[16];
+// 32 columns of this thread's lane, without the wait: the registers are valid after tmem_ld_wait()
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, float* v) {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]), "=f"(v[8]),
+          "=f"(v[9]), "=f"(v[10]), "=f"(v[11]), "=f"(v[12]), "=f"(v[13]), "=f"(v[14]), "=f"(v[15]), "=f"(v[16]),
+          "=f"(v[17]), "=f"(v[18]), "=f"(v[19]), "=f"(v[20]), "=f"(v[21]), "=f"(v[22]), "=f"(v[23]), "=f"(v[24]),
+          "=f"(v[25]), "=f"(v[26]), "=f"(v[27]), "=f"(v[28]), "=f"(v[29]), "=f"(v[30]), "=f"(v[31])
+        : "r"(taddr)
+        : "memory");
 }
-__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(r[0]),
-                 "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
-                 : "memory");
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]), "f"(v[8]),
+        "f"(v[9]), "f"(v[10]), "f"(v[11]), "f"(v[12]), "f"(v[13]), "f"(v[14]), "f"(v[15]), "f"(v[16]), "f"(v[17]),
+        "f"(v[18]), "f"(v[19]), "f"(v[20]), "f"(v[21]), "f"(v[22]), "f"(v[23]), "f"(v[24]), "f"(v[25]), "f"(v[26]),
+        "f"(v[27]), "f"(v[28]), "f"(v[29]), "f"(v[30]), "f"(v[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -192,7 +207,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     auto kv_empty = [&](int st) { return bars + 8u * (3 + st); };
     auto s_full = [&](int b) { return bars + 8u * (5 + b); };
     auto s_empty = [&](int b) { return bars + 8u * (7 + b); };
-    const uint32_t p_full = bars + 8u * 9, pv_done = bars + 8u * 10, o_empty = bars + 8u * 11;
+    const uint32_t p_full = bars + 8u * 9, pv_done = bars + 8u * 10;
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
@@ -204,7 +219,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         }
         mbar_init(p_full, 4);
         mbar_init(pv_done, 1);
-        mbar_init(o_empty, 4);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) tmem_alloc(smem_u32(&s_tmem), TMEM_COLS);
@@ -260,7 +274,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             for (int it = 0; it < n_tiles && ok; it++) {
                 if (it + 1 < n_tiles) ok = issue_s(it + 1);
                 if (!ok) break;
-                ok = mbar_wait(p_full, it & 1, &s_abort) && mbar_wait(o_empty, (it & 1) ^ 1, &s_abort);
+                ok = mbar_wait(p_full, it & 1, &s_abort);
                 if (!ok) break;
                 tc_fence_after();
                 const int st = it & 1;
@@ -269,7 +283,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 #pragma unroll
                     for (int ks = 0; ks < KT / 16; ks++)         // 16 keys per step: 8 columns of packed P
                         umma_ts(tmem + COL_O, tmem + (half ? COL_PLO : COL_PHI) + ks * 8, desc_mn_major(sV(st) + ks * 2048),
-                                idesc_pv, (half | ks) != 0);
+                                idesc_pv, (it | half | ks) != 0);       // the output row accumulates over all tiles
                 }
                 umma_commit(pv_done);
                 umma_commit(kv_empty(st));
@@ -281,27 +295,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         }
     } else {
         // ---- one thread per query row ----------------------------------------------------------------
+        // The output row stays in tensor memory: the P V products of all tiles accumulate there, and
+        // a thread touches it only when its running maximum moves (rarely, see below) and at the end.
         const int qd = warp & 3;                               // tensor-memory lane group of this warp
         const uint32_t lane_base = (uint32_t)(qd * 32) << 16;
         const int row = q0 + qd * 32 + lane;                   // position of this thread's query
-        float o[HD];
-#pragma unroll
-        for (int d = 0; d < HD; d++) o[d] = 0.f;
+        const uint32_t to = tmem + COL_O + lane_base;
         float m = -INFINITY, l = 0.f;
         bool ok = true;
-        auto add_product = [&]() {                             // o += O_tile, then the tile may be overwritten
-            tc_fence_after();
-#pragma unroll
-            for (int c0 = 0; c0 < HD; c0 += 16) {
-                float t[16];
-                tmem_ld16(tmem + COL_O + lane_base + c0, t);
-#pragma unroll
-                for (int i = 0; i < 16; i++) o[c0 + i] += t[i];
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(o_empty);
-        };
         for (int it = 0; it < n_tiles; it++) {
             const int b = it & 1;
             ok = mbar_wait(s_full(b), (it >> 1) & 1, &s_abort);
@@ -314,16 +315,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             auto tile_softmax = [&](auto masked_tag) -> bool {
                 constexpr bool MASKED = decltype(masked_tag)::value;
                 auto visible = [&](int j) { return j <= row && j < len && (window <= 0 || j >= row + 1 - window); };
+                float s[2][32];                                  // the next 32 scores are requested while these are used
                 // pass 1: the row's maximum (of the raw scores: the scale is positive)
-                float mx0 = -INFINITY, mx1 = -INFINITY;         // two chains instead of one
+                float mx0 = -INFINITY, mx1 = -INFINITY;
+                tmem_ld32_issue(ts, s[0]);
 #pragma unroll
-                for (int c0 = 0; c0 < KT; c0 += 16) {
-                    float s[16];
-                    tmem_ld16(ts + c0, s);
+                for (int c = 0; c < KT / 32; c++) {
+                    tmem_ld_wait();
+                    if (c + 1 < KT / 32) tmem_ld32_issue(ts + (c + 1) * 32, s[(c + 1) & 1]);
 #pragma unroll
-                    for (int i = 0; i < 16; i += 2) {
-                        if (!MASKED || visible(j0 + c0 + i)) mx0 = fmaxf(mx0, s[i]);
-                        if (!MASKED || visible(j0 + c0 + i + 1)) mx1 = fmaxf(mx1, s[i + 1]);
+                    for (int i = 0; i < 32; i += 2) {
+                        if (!MASKED || visible(j0 + c * 32 + i)) mx0 = fmaxf(mx0, s[c & 1][i]);
+                        if (!MASKED || visible(j0 + c * 32 + i + 1)) mx1 = fmaxf(mx1, s[c & 1][i + 1]);
                     }
                 }
                 const float mx = fmaxf(mx0, mx1) * scale_log2;
@@ -332,31 +335,39 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 float m_new = m, alpha = 1.f;
                 if (mx > m + 8.f || m == -INFINITY) {
                     m_new = fmaxf(m, mx);
-                    alpha = (m == -INFINITY) ? 0.f : ex2_approx(m - m_new);
+                    alpha = (m == -INFINITY) ? 1.f : ex2_approx(m - m_new);     // nothing accumulated yet: nothing to rescale
                 }
-                // the previous tile's product belongs to the old maximum: add it, then rescale
-                if (it > 0) {
-                    if (!mbar_wait(pv_done, (it - 1) & 1, &s_abort)) return false;
-                    add_product();
-                }
+                tmem_ld32_issue(ts, s[0]);                       // pass 2's first scores, on their way meanwhile
+                // the products so far belong to the old maximum: wait for the last one, rescale the row
+                if (it > 0 && !mbar_wait(pv_done, (it - 1) & 1, &s_abort)) return false;
                 if (alpha != 1.f) {
+                    tc_fence_after();
+                    tmem_ld_wait();
 #pragma unroll
-                    for (int d = 0; d < HD; d++) o[d] *= alpha;
+                    for (int c = 0; c < HD / 32; c++) {
+                        float t[32];
+                        tmem_ld32_issue(to + c * 32, t);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; i++) t[i] *= alpha;
+                        tmem_st32(to + c * 32, t);
+                    }
+                    tmem_ld32_issue(ts, s[0]);
                 }
                 // pass 2: P in two bfloat16 terms, into tensor memory (two keys per 32-bit column)
                 const float neg_m = m_new == -INFINITY ? 0.f : -m_new;     // no key seen yet: every p is 0 anyway
                 float rs = 0.f, rs1 = 0.f;
 #pragma unroll
-                for (int c0 = 0; c0 < KT; c0 += 16) {
-                    float s[16];
-                    tmem_ld16(ts + c0, s);
-                    uint32_t hi[8], lo[8];
+                for (int c = 0; c < KT / 32; c++) {
+                    tmem_ld_wait();
+                    if (c + 1 < KT / 32) tmem_ld32_issue(ts + (c + 1) * 32, s[(c + 1) & 1]);
+                    uint32_t hi[16], lo[16];
 #pragma unroll
-                    for (int i = 0; i < 16; i += 2) {
-                        float x0 = fmaf(s[i], scale_log2, neg_m), x1 = fmaf(s[i + 1], scale_log2, neg_m);
+                    for (int i = 0; i < 32; i += 2) {
+                        float x0 = fmaf(s[c & 1][i], scale_log2, neg_m), x1 = fmaf(s[c & 1][i + 1], scale_log2, neg_m);
                         if (MASKED) {
-                            if (!visible(j0 + c0 + i)) x0 = -INFINITY;
-                            if (!visible(j0 + c0 + i + 1)) x1 = -INFINITY;
+                            if (!visible(j0 + c * 32 + i)) x0 = -INFINITY;
+                            if (!visible(j0 + c * 32 + i + 1)) x1 = -INFINITY;
                         }
                         const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
                         rs += p0, rs1 += p1;
@@ -364,8 +375,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                         hi[i / 2] = h;
                         lo[i / 2] = pack_bf16(p0 - __uint_as_float(h << 16), p1 - __uint_as_float(h & 0xffff0000u));
                     }
-                    tmem_st8(tmem + COL_PHI + lane_base + c0 / 2, hi);
-                    tmem_st8(tmem + COL_PLO + lane_base + c0 / 2, lo);
+                    tmem_st16(tmem + COL_PHI + lane_base + c * 16, hi);
+                    tmem_st16(tmem + COL_PLO + lane_base + c * 16, lo);
                 }
                 l = l * alpha + (rs + rs1);
                 m = m_new;
@@ -378,27 +389,33 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(s_empty(b));       // the scores have been read
-                mbar_arrive(p_full);           // P is in place
+                mbar_arrive(p_full);           // P is in place, and the output row is rescaled
             }
         }
-        if (ok && n_tiles > 0) {
-            ok = mbar_wait(pv_done, (n_tiles - 1) & 1, &s_abort);
-            if (ok) add_product();
-        }
+        if (ok) ok = mbar_wait(pv_done, (n_tiles - 1) & 1, &s_abort);
         if (!ok) {
             if (lane == 0) {
                 atomicOr(status, ST_WAIT_TIMEOUT);
                 s_abort = 1;
             }
-        } else if (row < len) {
+        } else {
+            tc_fence_after();
             const float inv = l > 0.f ? 1.f / l : 0.f;
-            uint4* dst = reinterpret_cast<uint4*>(out + ((size_t)(tok0 + row) * nh + head) * HD);
+            uint4* dst = reinterpret_cast<uint4*>(out + ((size_t)(tok0 + min(row, len - 1)) * nh + head) * HD);
 #pragma unroll
-            for (int d = 0; d < HD; d += 8) {
-                uint4 v;
-                v.x = pack_bf16(o[d] * inv, o[d + 1] * inv), v.y = pack_bf16(o[d + 2] * inv, o[d + 3] * inv);
-                v.z = pack_bf16(o[d + 4] * inv, o[d + 5] * inv), v.w = pack_bf16(o[d + 6] * inv, o[d + 7] * inv);
-                dst[d / 8] = v;
+            for (int c = 0; c < HD / 32; c++) {
+                float t[32];
+                tmem_ld32_issue(to + c * 32, t);               // (every lane of the warp takes part in the load)
+                tmem_ld_wait();
+                if (row < len) {
+#pragma unroll
+                    for (int d = 0; d < 32; d += 8) {
+                        uint4 v;
+                        v.x = pack_bf16(t[d] * inv, t[d + 1] * inv), v.y = pack_bf16(t[d + 2] * inv, t[d + 3] * inv);
+                        v.z = pack_bf16(t[d + 4] * inv, t[d + 5] * inv), v.w = pack_bf16(t[d + 6] * inv, t[d + 7] * inv);
+                        dst[(c * 32 + d) / 8] = v;
+                    }
+                }
             }
         }
     }
