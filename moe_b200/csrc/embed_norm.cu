@@ -179,20 +179,6 @@ MOE_API int moe_rmsnorm_combine(float* x, const float* y, const int* pos_of_pair
                           status, cs, stream);
 }
 
-// Ask for `bytes` at `p` in L2: weights that a later kernel of the step will stream, requested
-// while the step is in a phase that leaves the memory system idle.  Changes no result.
-__global__ void l2_prefetch_kernel(const char* __restrict__ p, size_t bytes) {
-    for (size_t off = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 128; off < bytes;
-         off += (size_t)gridDim.x * blockDim.x * 128)
-        prefetch_l2(p + off);
-}
-
-MOE_API int moe_l2_prefetch(const void* p, long long bytes, int blocks, cudaStream_t stream) {
-    if (bytes <= 0) return 0;
-    l2_prefetch_kernel<<<blocks < 1 ? 1 : blocks, 256, 0, stream>>>((const char*)p, (size_t)bytes);
-    return launch_status();
-}
-
 // Programmatic dependent launch on or off for every kernel of this library (on by default).
 MOE_API void moe_set_pdl(int enabled) { g_pdl_enabled = enabled ? 1 : 0; }
 

@@ -46,7 +46,6 @@ def lib():
             "moe_attention_decode": [P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],
             "moe_attention_decode_fused": [P, P, I, P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],
             "moe_norm_route": [P, P, P, F, I, I, P, P, P, P, I, I, I, I, F, P, P, P, P, P, P, P, P, P, P, P],
-            "moe_l2_prefetch": [P, LL, I, P],
             "moe_align": [P, I, I, I, P, P, P, P, P],
             "moe_swiglu": [P, P, I, LL, I, P],
             "moe_combine": [P, P, P, I, P, P, P, I, I, P],
@@ -322,14 +321,6 @@ def attention_decode(q, view, batch, out, *, nh, window, scale, status):
                                    g.table.stride(0), g.ring, g.page_size, g.num_pages, T, nh, g.num_kv_heads,
                                    g.head_dim, int(window or 0), float(scale), nsplit, _p(status), _stream()),
         "attention_decode")
-
-
-def l2_prefetch(t: torch.Tensor) -> None:
-    """Ask for a tensor (weights a later kernel will stream) in L2; changes no result."""
-    idx = t.device.index or 0
-    if idx not in _SMS:
-        _SMS[idx] = torch.cuda.get_device_properties(t.device).multi_processor_count
-    _ok(lib().moe_l2_prefetch(_p(t), t.numel() * t.element_size(), 2 * _SMS[idx], _stream()), "l2_prefetch")
 
 
 _TICKETS = {}

@@ -87,11 +87,8 @@ class RoutedExperts(Part):
         # Set to a list to record every routing decision as (expert ids [T, k], weights [T, k]);
         # the reference's State::trace does the same per token and layer (src/model.rs:157, 943-950).
         self.trace = None
-        # measured on a B200: asking for the shared expert's weights in L2 during the norm delays
-        # the shared expert behind the routed ones and loses more than it gains (off); the fused
-        # norm + router + dispatch launch wins up to 8 tokens and loses from 16 on, where its
-        # single gathering block is the bottleneck
-        self.prefetch_shared = os.environ.get("MOE_B200_PREFETCH", "0") != "0"
+        # measured on a B200: the fused norm + router + dispatch launch wins up to 8 tokens and loses
+        # from 16 on, where its single gathering block is the bottleneck
         self.fused_norm_tokens = int(os.environ.get("MOE_B200_NORM_ROUTE_MAX", "8"))
 
     def tensors(self):
@@ -156,16 +153,6 @@ class RoutedExperts(Part):
         not allow it (the block then runs the norm itself and calls ``forward``)."""
         if getattr(norm, "kind", None) != "rmsnorm" or x.shape[0] > self.fused_norm_tokens or self.E > 256:
             return None
-        if self.ws_gu is not None and self.prefetch_shared:
-            # the step is bound by latency until the routed experts begin: meanwhile the shared
-            # expert's weights are asked into L2 on the second stream, so that its products do not
-            # share the memory bandwidth with the routed ones
-            main = torch.cuda.current_stream()
-            side = rt.side_stream()
-            side.wait_stream(main)
-            with torch.cuda.stream(side):
-                core.l2_prefetch(self.ws_gu)
-                core.l2_prefetch(self.ws_down)
         routed = core.norm_route(x, delta, norm.weight, norm.eps, self.w_router, self.k, self.norm_topk, self.scale,
                                  bf16=rt.is_bf16, shared_gate_w=self.w_sgate,
                                  seq_of_token=getattr(batch, "seq_of_token", None), status=rt.status)
