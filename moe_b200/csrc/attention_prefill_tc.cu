@@ -12,10 +12,10 @@
 //   warp 1      MMA issuer: S = Q K^T (operands in shared memory, S in tensor memory, two
 //               buffers), then O_tile = P V with P read from tensor memory and V as the
 //               MN-major operand
-//   warps 2-5   one thread per query row: reads its row of S from tensor memory (no cross-thread
-//               reduction), masks, keeps the running maximum and sum, and writes P (two bfloat16
-//               terms) back to tensor memory.  The output row accumulates in tensor memory over
-//               all tiles; its thread rescales it there when the running maximum moves
+//   warps 2-9   two threads per query row (half of the columns each): read the scores from tensor
+//               memory, mask, keep the running maximum and sum, and write P (two bfloat16 terms)
+//               back to tensor memory.  The output row accumulates in tensor memory over all
+//               tiles; its threads rescale it there when the running maximum moves
 //
 // S of tile j + 1 is issued before the softmax of tile j has finished, so the tensor cores work
 // on the next scores meanwhile.  Every barrier wait is bounded (ST_WAIT_TIMEOUT).
@@ -159,7 +159,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 template <int HD>
-__global__ void __launch_bounds__(192)
+__global__ void __launch_bounds__(320)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                        const __grid_constant__ CUtensorMap tmV, __nv_bfloat16* __restrict__ out,
                        const int* __restrict__ cu_seqlens, int num_seqs, int nh, int nkv, int window, float scale_log2,
@@ -171,6 +171,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     __shared__ int s_seq, s_tile;
     __shared__ volatile int s_abort;
     __shared__ uint32_t s_tmem;
+    __shared__ float x_max[2][2][QT], x_sum[2][QT];      // what the two threads of a row tell each other
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     // which (sequence, query tile): tiles are numbered sequence by sequence
@@ -203,21 +204,27 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     auto sV = [&](int st) { return base + TILE_BYTES + st * STAGE_BYTES + TILE_BYTES; };
     const uint32_t bars = base + TILE_BYTES + 2 * STAGE_BYTES;
     const uint32_t q_full = bars;
-    auto kv_full = [&](int st) { return bars + 8u * (1 + st); };
-    auto kv_empty = [&](int st) { return bars + 8u * (3 + st); };
+    auto k_full = [&](int st) { return bars + 8u * (1 + st); };
+    auto k_empty = [&](int st) { return bars + 8u * (3 + st); };
+    auto v_full = [&](int st) { return bars + 8u * (15 + st); };
+    auto v_empty = [&](int st) { return bars + 8u * (17 + st); };
     auto s_full = [&](int b) { return bars + 8u * (5 + b); };
     auto s_empty = [&](int b) { return bars + 8u * (7 + b); };
     const uint32_t p_full = bars + 8u * 9, pv_done = bars + 8u * 10;
+    auto x_bar = [&](int q) { return bars + 8u * (11 + q); };
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
         for (int i = 0; i < 2; i++) {
-            mbar_init(kv_full(i), 1);
-            mbar_init(kv_empty(i), 1);
+            mbar_init(k_full(i), 1);
+            mbar_init(k_empty(i), 1);
+            mbar_init(v_full(i), 1);
+            mbar_init(v_empty(i), 1);
             mbar_init(s_full(i), 1);
-            mbar_init(s_empty(i), 4);        // one arrival per softmax warp
+            mbar_init(s_empty(i), 8);        // one arrival per softmax warp
         }
-        mbar_init(p_full, 4);
+        mbar_init(p_full, 8);
+        for (int i = 0; i < 4; i++) mbar_init(x_bar(i), 2);      // the two warps that share 32 rows
         mbar_init(pv_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -232,24 +239,40 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         if (lane == 0) {
             mbar_expect_tx(q_full, TILE_BYTES);
             for (int c = 0; c < CH; c++) tma_load_3d(sQ + c * 16384, &tmQ, c * 64, head, tok0 + q0, q_full);
+            // Keys and values have rings of their own: a key tile is free again as soon as its
+            // scores are computed, a value tile only after P V.  The keys run one tile ahead of
+            // the values, as the MMA issuer asks for them (scores of tile j + 1 before P V of tile j).
             bool ok = true;
-            int it = 0;
-            for (; it < n_tiles; it++) {
+            int nk = 0, nv = 0;                         // tiles whose keys / values have been requested
+            auto load_k = [&](int it) {
                 const int st = it & 1;
-                ok = mbar_wait(kv_empty(st), ((it >> 1) & 1) ^ 1, &s_abort);
-                if (!ok) break;
-                const int j0 = tok0 + (kv_lo + it) * KT;
-                mbar_expect_tx(kv_full(st), STAGE_BYTES);
-                for (int c = 0; c < CH; c++) {
-                    tma_load_3d(sK(st) + c * 16384, &tmK, c * 64, kvh, j0, kv_full(st));
-                    tma_load_3d(sV(st) + c * 16384, &tmV, c * 64, kvh, j0, kv_full(st));
-                }
+                if (!mbar_wait(k_empty(st), ((it >> 1) & 1) ^ 1, &s_abort)) return false;
+                mbar_expect_tx(k_full(st), TILE_BYTES);
+                for (int c = 0; c < CH; c++)
+                    tma_load_3d(sK(st) + c * 16384, &tmK, c * 64, kvh, tok0 + (kv_lo + it) * KT, k_full(st));
+                nk = it + 1;
+                return true;
+            };
+            auto load_v = [&](int it) {
+                const int st = it & 1;
+                if (!mbar_wait(v_empty(st), ((it >> 1) & 1) ^ 1, &s_abort)) return false;
+                mbar_expect_tx(v_full(st), TILE_BYTES);
+                for (int c = 0; c < CH; c++)
+                    tma_load_3d(sV(st) + c * 16384, &tmV, c * 64, kvh, tok0 + (kv_lo + it) * KT, v_full(st));
+                nv = it + 1;
+                return true;
+            };
+            ok = load_k(0);
+            for (int it = 0; it < n_tiles && ok; it++) {
+                if (it + 1 < n_tiles) ok = load_k(it + 1);
+                if (ok) ok = load_v(it);
             }
             if (!ok) {
                 atomicOr(status, ST_WAIT_TIMEOUT);
                 s_abort = 1;
-                for (int i = max(0, it - 2); i < it; i++)       // copies in flight must land
-                    mbar_wait(kv_full(i & 1), (i >> 1) & 1, &s_abort);
+                for (int i = max(0, nk - 2); i < nk; i++)       // copies in flight must land
+                    mbar_wait(k_full(i & 1), (i >> 1) & 1, &s_abort);
+                for (int i = max(0, nv - 2); i < nv; i++) mbar_wait(v_full(i & 1), (i >> 1) & 1, &s_abort);
             }
         }
     } else if (warp == 1) {
@@ -259,7 +282,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             bool ok = mbar_wait(q_full, 0, &s_abort);
             auto issue_s = [&](int it) {           // scores of tile `it` into buffer it & 1
                 const int b = it & 1;
-                if (!mbar_wait(kv_full(b), (it >> 1) & 1, &s_abort)) return false;
+                if (!mbar_wait(k_full(b), (it >> 1) & 1, &s_abort)) return false;
                 if (!mbar_wait(s_empty(b), ((it >> 1) & 1) ^ 1, &s_abort)) return false;
                 tc_fence_after();
 #pragma unroll
@@ -268,16 +291,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                     umma_ss(tmem + COL_S + b * KT, desc_k_major(sQ + off), desc_k_major(sK(b) + off), idesc_s, ks > 0);
                 }
                 umma_commit(s_full(b));
+                umma_commit(k_empty(b));           // the key tile is free when these MMAs have read it
                 return true;
             };
             if (ok) ok = issue_s(0);
             for (int it = 0; it < n_tiles && ok; it++) {
                 if (it + 1 < n_tiles) ok = issue_s(it + 1);
                 if (!ok) break;
-                ok = mbar_wait(p_full, it & 1, &s_abort);
+                const int st = it & 1;
+                ok = mbar_wait(v_full(st), (it >> 1) & 1, &s_abort) && mbar_wait(p_full, it & 1, &s_abort);
                 if (!ok) break;
                 tc_fence_after();
-                const int st = it & 1;
 #pragma unroll
                 for (int half = 0; half < 2; half++) {
 #pragma unroll
@@ -286,7 +310,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                                 idesc_pv, (it | half | ks) != 0);       // the output row accumulates over all tiles
                 }
                 umma_commit(pv_done);
-                umma_commit(kv_empty(st));
+                umma_commit(v_empty(st));
             }
             if (!ok) {
                 atomicOr(status, ST_WAIT_TIMEOUT);
@@ -294,13 +318,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             }
         }
     } else {
-        // ---- one thread per query row ----------------------------------------------------------------
-        // The output row stays in tensor memory: the P V products of all tiles accumulate there, and
-        // a thread touches it only when its running maximum moves (rarely, see below) and at the end.
+        // ---- two threads per query row ---------------------------------------------------------------
+        // Warps w and w + 4 share the tensor-memory lanes of 32 rows; each takes one half of the
+        // columns (of the scores, of P and of the output row).  They exchange the half-row maxima
+        // through shared memory once per tile (a bounded wait on an mbarrier, not a bar.sync: a
+        // thread that gives up must not leave its partner waiting).  The output row stays in tensor
+        // memory: the P V products of all tiles accumulate there, and its threads touch it only
+        // when the running maximum moves (rarely, see below) and at the end.
         const int qd = warp & 3;                               // tensor-memory lane group of this warp
+        const int half = (warp - 2) >> 2;                      // which half of the columns
+        const int r = qd * 32 + lane;                          // row of the tile
         const uint32_t lane_base = (uint32_t)(qd * 32) << 16;
-        const int row = q0 + qd * 32 + lane;                   // position of this thread's query
-        const uint32_t to = tmem + COL_O + lane_base;
+        const int row = q0 + r;                                // position of this thread's query
+        const uint32_t to = tmem + COL_O + lane_base + half * (HD / 2);
         float m = -INFINITY, l = 0.f;
         bool ok = true;
         for (int it = 0; it < n_tiles; it++) {
@@ -308,28 +338,33 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             ok = mbar_wait(s_full(b), (it >> 1) & 1, &s_abort);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t ts = tmem + COL_S + b * KT + lane_base;
-            const int j0 = (kv_lo + it) * KT;
+            const uint32_t ts = tmem + COL_S + b * KT + lane_base + half * (KT / 2);
+            const int j0 = (kv_lo + it) * KT, jh = j0 + half * (KT / 2);
             // a tile strictly below the diagonal, inside the window and inside the sequence needs no mask
             const bool full = j0 + KT - 1 <= q0 && j0 + KT <= len && (window <= 0 || j0 >= q0 + QT - window);
             auto tile_softmax = [&](auto masked_tag) -> bool {
                 constexpr bool MASKED = decltype(masked_tag)::value;
                 auto visible = [&](int j) { return j <= row && j < len && (window <= 0 || j >= row + 1 - window); };
-                float s[2][32];                                  // the next 32 scores are requested while these are used
-                // pass 1: the row's maximum (of the raw scores: the scale is positive)
+                float s[2][32];                                  // this thread's 64 scores
+                // pass 1: the maximum of the half row (of the raw scores: the scale is positive)
                 float mx0 = -INFINITY, mx1 = -INFINITY;
                 tmem_ld32_issue(ts, s[0]);
+                tmem_ld32_issue(ts + 32, s[1]);
+                tmem_ld_wait();
 #pragma unroll
-                for (int c = 0; c < KT / 32; c++) {
-                    tmem_ld_wait();
-                    if (c + 1 < KT / 32) tmem_ld32_issue(ts + (c + 1) * 32, s[(c + 1) & 1]);
+                for (int c = 0; c < 2; c++) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-                        if (!MASKED || visible(j0 + c * 32 + i)) mx0 = fmaxf(mx0, s[c & 1][i]);
-                        if (!MASKED || visible(j0 + c * 32 + i + 1)) mx1 = fmaxf(mx1, s[c & 1][i + 1]);
+                        if (!MASKED || visible(jh + c * 32 + i)) mx0 = fmaxf(mx0, s[c][i]);
+                        if (!MASKED || visible(jh + c * 32 + i + 1)) mx1 = fmaxf(mx1, s[c][i + 1]);
                     }
                 }
-                const float mx = fmaxf(mx0, mx1) * scale_log2;
+                // ... and of the whole row
+                x_max[b][half][r] = fmaxf(mx0, mx1);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(x_bar(qd));
+                if (!mbar_wait(x_bar(qd), it & 1, &s_abort)) return false;
+                const float mx = fmaxf(x_max[b][0][r], x_max[b][1][r]) * scale_log2;
                 // The running maximum only has to keep the exponentials in range: it moves when the
                 // tile's maximum exceeds it by more than 8 (a factor 256), which spares most rescalings.
                 float m_new = m, alpha = 1.f;
@@ -337,14 +372,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                     m_new = fmaxf(m, mx);
                     alpha = (m == -INFINITY) ? 1.f : ex2_approx(m - m_new);     // nothing accumulated yet: nothing to rescale
                 }
-                tmem_ld32_issue(ts, s[0]);                       // pass 2's first scores, on their way meanwhile
                 // the products so far belong to the old maximum: wait for the last one, rescale the row
                 if (it > 0 && !mbar_wait(pv_done, (it - 1) & 1, &s_abort)) return false;
                 if (alpha != 1.f) {
                     tc_fence_after();
-                    tmem_ld_wait();
 #pragma unroll
-                    for (int c = 0; c < HD / 32; c++) {
+                    for (int c = 0; c < HD / 64; c++) {
                         float t[32];
                         tmem_ld32_issue(to + c * 32, t);
                         tmem_ld_wait();
@@ -352,22 +385,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                         for (int i = 0; i < 32; i++) t[i] *= alpha;
                         tmem_st32(to + c * 32, t);
                     }
-                    tmem_ld32_issue(ts, s[0]);
                 }
                 // pass 2: P in two bfloat16 terms, into tensor memory (two keys per 32-bit column)
                 const float neg_m = m_new == -INFINITY ? 0.f : -m_new;     // no key seen yet: every p is 0 anyway
                 float rs = 0.f, rs1 = 0.f;
 #pragma unroll
-                for (int c = 0; c < KT / 32; c++) {
-                    tmem_ld_wait();
-                    if (c + 1 < KT / 32) tmem_ld32_issue(ts + (c + 1) * 32, s[(c + 1) & 1]);
+                for (int c = 0; c < 2; c++) {
                     uint32_t hi[16], lo[16];
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-                        float x0 = fmaf(s[c & 1][i], scale_log2, neg_m), x1 = fmaf(s[c & 1][i + 1], scale_log2, neg_m);
+                        float x0 = fmaf(s[c][i], scale_log2, neg_m), x1 = fmaf(s[c][i + 1], scale_log2, neg_m);
                         if (MASKED) {
-                            if (!visible(j0 + c * 32 + i)) x0 = -INFINITY;
-                            if (!visible(j0 + c * 32 + i + 1)) x1 = -INFINITY;
+                            if (!visible(jh + c * 32 + i)) x0 = -INFINITY;
+                            if (!visible(jh + c * 32 + i + 1)) x1 = -INFINITY;
                         }
                         const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
                         rs += p0, rs1 += p1;
@@ -375,8 +405,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                         hi[i / 2] = h;
                         lo[i / 2] = pack_bf16(p0 - __uint_as_float(h << 16), p1 - __uint_as_float(h & 0xffff0000u));
                     }
-                    tmem_st16(tmem + COL_PHI + lane_base + c * 16, hi);
-                    tmem_st16(tmem + COL_PLO + lane_base + c * 16, lo);
+                    tmem_st16(tmem + COL_PHI + lane_base + half * (KT / 4) + c * 16, hi);
+                    tmem_st16(tmem + COL_PLO + lane_base + half * (KT / 4) + c * 16, lo);
                 }
                 l = l * alpha + (rs + rs1);
                 m = m_new;
@@ -392,6 +422,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 mbar_arrive(p_full);           // P is in place, and the output row is rescaled
             }
         }
+        // the row's sum: the two halves, in a fixed order
+        if (ok) {
+            x_sum[half][r] = l;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(x_bar(qd));
+            ok = mbar_wait(x_bar(qd), n_tiles & 1, &s_abort);
+        }
         if (ok) ok = mbar_wait(pv_done, (n_tiles - 1) & 1, &s_abort);
         if (!ok) {
             if (lane == 0) {
@@ -400,10 +437,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             }
         } else {
             tc_fence_after();
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            uint4* dst = reinterpret_cast<uint4*>(out + ((size_t)(tok0 + min(row, len - 1)) * nh + head) * HD);
+            const float lsum = x_sum[0][r] + x_sum[1][r];
+            const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+            uint4* dst = reinterpret_cast<uint4*>(out + ((size_t)(tok0 + min(row, len - 1)) * nh + head) * HD +
+                                                  half * (HD / 2));
 #pragma unroll
-            for (int c = 0; c < HD / 32; c++) {
+            for (int c = 0; c < HD / 64; c++) {
                 float t[32];
                 tmem_ld32_issue(to + c * 32, t);               // (every lane of the warp takes part in the load)
                 tmem_ld_wait();
@@ -462,7 +501,7 @@ template <int HD>
 int launch(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, void* out, const int* cu_seqlens,
            int num_seqs, int num_tokens, int nh, int nkv, int window, float scale, int* status, cudaStream_t stream) {
     constexpr int TILE_BYTES = (HD / 64) * 128 * 128;
-    const int smem = 5 * TILE_BYTES + 1024 + 128;
+    const int smem = 5 * TILE_BYTES + 1024 + 192;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -470,7 +509,7 @@ int launch(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tm
         configured = true;
     }
     dim3 grid((num_tokens + QT - 1) / QT + num_seqs, nh);
-    attn_prefill_tc_kernel<HD><<<grid, 192, smem, stream>>>(tmQ, tmK, tmV, (__nv_bfloat16*)out, cu_seqlens, num_seqs, nh,
+    attn_prefill_tc_kernel<HD><<<grid, 320, smem, stream>>>(tmQ, tmK, tmV, (__nv_bfloat16*)out, cu_seqlens, num_seqs, nh,
                                                             nkv, window, scale * 1.4426950408889634f, status);
     return launch_status();
 }
