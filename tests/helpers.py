@@ -27,7 +27,17 @@ CONFIG_B = dict(
     vocab_size=384, rope_theta=1e6, rms_norm_eps=1e-5, use_sliding_window=True, sliding_window=8,
     max_window_layers=1, tie_word_embeddings=True, max_position_embeddings=4096, eos_token_id=[7, 383],
 )
-CONFIGS = {"A": CONFIG_A, "B": CONFIG_B}
+# heads of 64 (the tcgen05 prompt attention and the fastest decode kernels take this size), grouped
+# 2:1, a window of 70 that crosses a page of 64 on the second layer, sizes that are no power of two
+CONFIG_C = dict(
+    architectures=["Qwen2MoeForCausalLM"], model_type="qwen2_moe",
+    num_hidden_layers=2, hidden_size=160, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+    num_experts=5, num_experts_per_tok=2, moe_intermediate_size=40, shared_expert_intermediate_size=72,
+    norm_topk_prob=False, decoder_sparse_step=1, mlp_only_layers=[], intermediate_size=96,
+    vocab_size=300, rope_theta=5e4, rms_norm_eps=1e-6, use_sliding_window=True, sliding_window=70,
+    max_window_layers=1, tie_word_embeddings=False, max_position_embeddings=4096, eos_token_id=299,
+)
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C}
 
 
 class ModelFolders:

@@ -11,12 +11,14 @@ import helpers
 pytestmark = pytest.mark.gpu
 
 CASES = [(n, dt, std) for n in ("A", "B") for dt in ("float32", "bfloat16") for std in G.STD[dt]]
+CASES += [("C", dt, G.STD[dt][-1]) for dt in ("float32", "bfloat16")]
 LENGTHS = [5, 9, 12, 40, 77, 1, 33]
 
 
 def requests_for(name):
     V = helpers.CONFIGS[name]["vocab_size"]
-    return {f"r{i}": helpers.random_tokens(V, n, 100 + i) for i, n in enumerate(LENGTHS)}
+    lengths = LENGTHS + ([150, 260] if name == "C" else [])      # C: prompts of more than one 128-key tile
+    return {f"r{i}": helpers.random_tokens(V, n, 100 + i) for i, n in enumerate(lengths)}
 
 
 @pytest.mark.parametrize("name,dtype,std", CASES)
@@ -46,7 +48,7 @@ def test_last_32_tokens_one_by_one_equal_whole(model_dirs, name, dtype, std):
 @pytest.mark.parametrize("name,dtype,std", CASES)
 def test_unequal_batches_one_after_another_equal_whole(model_dirs, name, dtype, std):
     # 3 slots for 7 requests: every slot is given back and used again
-    d, eng = G.engine_for(model_dirs, name, dtype, std, max_tokens=64 * 6, max_slots=3)
+    d, eng = G.engine_for(model_dirs, name, dtype, std, max_tokens=64 * (12 if name == "C" else 6), max_slots=3)
     reqs = requests_for(name)
     whole = helpers.replay_whole(eng, reqs)
     batched = helpers.replay_batches(eng, reqs, 3)
