@@ -113,6 +113,9 @@ class KVCache:
                 self._states[cid] = torch.zeros((max_slots + 1, *req.shape), dtype=req.dtype, device=device)
         # sampler state: one xorshift64* word per slot
         self.rng_states = torch.zeros(max_slots + 1, dtype=torch.int64, device=device)
+        # the token sampled last for the sequence of each slot: the next step's input can be read
+        # from here on the device (token id -1) before the host has seen it
+        self.last_token = torch.zeros(max_slots + 1, dtype=torch.int32, device=device)
 
     # ---- views -----------------------------------------------------------------
     def view(self, cache_id: int) -> Optional[CacheView]:

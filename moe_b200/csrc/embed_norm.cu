@@ -8,12 +8,20 @@
 
 // x[t, :] = table[token[t], :]; a token id outside [0, vocab) sets ST_BAD_TOKEN
 // and reads row 0 (the reference wraps modulo the vocabulary, src/model.rs:664).
+// A token id of -1 stands for "the token sampled last for this row's sequence": it is read from
+// last_token[slot of the sequence] (written by the sampling kernel), so a decode step can be
+// launched before the host knows the previous step's tokens.
 template <typename WT>
 __global__ void embed_kernel(const WT* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ x,
-                             int hidden, int vocab, int* status) {
+                             int hidden, int vocab, int* status, const int* __restrict__ last_token,
+                             const int* __restrict__ seq_of_token, const int* __restrict__ slots) {
     pdl_sync();
     const int t = blockIdx.x;
     int tok = tokens[t];
+    if (tok == -1 && last_token) {
+        const int s = seq_of_token[t];
+        tok = s >= 0 ? last_token[slots[s]] : 0;      // a padding row: any valid row
+    }
     if (tok < 0 || tok >= vocab) {
         if (threadIdx.x == 0) atomicOr(status, ST_BAD_TOKEN);
         tok = 0;
@@ -24,14 +32,16 @@ __global__ void embed_kernel(const WT* __restrict__ table, const int* __restrict
 }
 
 MOE_API int moe_embed(const void* table, int table_dt, const int* tokens, float* x, int num_tokens, int hidden,
-                      int vocab, int* status, cudaStream_t stream) {
+                      int vocab, int* status, const int* last_token, const int* seq_of_token, const int* slots,
+                      cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
+    if (last_token && (!seq_of_token || !slots)) return (int)cudaErrorInvalidValue;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (table_dt == DT_F32)
         return launch_pdl(embed_kernel<float>, num_tokens, threads, 0, stream, (const float*)table, tokens, x, hidden,
-                          vocab, status);
+                          vocab, status, last_token, seq_of_token, slots);
     return launch_pdl(embed_kernel<__nv_bfloat16>, num_tokens, threads, 0, stream, (const __nv_bfloat16*)table, tokens,
-                      x, hidden, vocab, status);
+                      x, hidden, vocab, status, last_token, seq_of_token, slots);
 }
 
 // A delta that is still the output of routed experts, not yet combined: for token t,

@@ -33,6 +33,8 @@ class StepBatch:
     max_end: int = 0             # longest sequence after the step
     all_decode: bool = False     # every sequence brings exactly one token
     all_fresh: bool = False      # every sequence starts at position 0
+    # per-slot table of the tokens sampled last; if given, a token id of -1 is read from it
+    last_token: Optional[torch.Tensor] = None
 
 
 def layout(num_tokens: int, num_seqs: int, num_want: int) -> List[Tuple[str, int]]:

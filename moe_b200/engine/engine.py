@@ -29,6 +29,7 @@ from ..ops import core
 from .batch import StepBatch, fill_host, layout
 
 GRAPH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+LAST_TOKEN = -1      # as a token id (with ``from_last``): the token sampled last for the sequence
 
 
 class _DecodeGraph:
@@ -52,7 +53,7 @@ class _DecodeGraph:
         self.dev = torch.zeros(o, dtype=torch.int32, device=engine.rt.device)
         views = {k: self.dev[a:a + n] for k, (a, n) in offs.items()}
         self.batch = StepBatch(**views, num_tokens=size, num_seqs=size, num_want=size, max_new=1, max_end=0,
-                               all_decode=True, all_fresh=False)
+                               all_decode=True, all_fresh=False, last_token=engine.cache.last_token)
         self.event = torch.cuda.Event()
         self.busy = False
         self.graph: Optional[torch.cuda.CUDAGraph] = None
@@ -123,6 +124,7 @@ class Engine:
         self._routed = [p for p in parts if hasattr(p, "trace")]
         self._graphs: Dict[int, _DecodeGraph] = {}
         self._table_caps = [0 if g.ring_pages else g.max_pages_per_seq for g in self.cache.groups]
+        self._results: List[Tuple[torch.Tensor, torch.cuda.Event]] = []     # pinned buffers for sampled tokens
 
     # ---- sequences -----------------------------------------------------------------
     def new_sequence(self) -> int:
@@ -159,8 +161,13 @@ class Engine:
         return None
 
     def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
-             want: Optional[Sequence[Sequence[int]]] = None, check: bool = True) -> Optional[torch.Tensor]:
+             want: Optional[Sequence[Sequence[int]]] = None, check: bool = True,
+             from_last: bool = False) -> Optional[torch.Tensor]:
         """Run ``tokens[i]`` for the sequence in ``slots[i]``; return logits at ``want[i]``.
+
+        With ``from_last`` a token id of ``LAST_TOKEN`` (-1) stands for the token that the
+        sampler picked last for that sequence; it is read on the device, so the step can be
+        launched before the host has seen that token.
 
         ``want[i]`` lists places among ``tokens[i]`` (0 = its first token of this
         step); by default the last place of each sequence.  The result is a float32
@@ -185,7 +192,8 @@ class Engine:
 
         # ---- one token each: replay the bucket's graph -----------------------------------
         if (self.use_graphs and all(n == 1 for n in counts) and all(len(w) == 1 for w in want)
-                and not any(p.trace is not None for p in self._routed)):
+                and not any(p.trace is not None for p in self._routed)
+                and (from_last or min(t[0] for t in tokens) >= 0)):
             size = self._bucket(B)
             if size is not None:
                 g = self._graphs.get(size)
@@ -221,7 +229,7 @@ class Engine:
         for gi, (o, n) in upd_off.items():
             core.table_update(self.cache.groups[gi].table, dev[o:o + 3 * n], n)
         views = {k: dev[a:a + n] for k, (a, n) in info["offsets"].items()}
-        batch = StepBatch(**views, **info["facts"])
+        batch = StepBatch(**views, **info["facts"], last_token=self.cache.last_token if from_last else None)
         self.last_batch = batch
         self.last_rows = B
         logits = self.model.forward(batch, self.cache)
@@ -229,15 +237,32 @@ class Engine:
             self.rt.check()
         return logits
 
-    def step_and_sample(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], sampler, params,
-                        histories=None) -> List[int]:
-        """One step, then one sampled token per sequence from the logits at its last
-        place; tokens come back to the host (one small copy, which also carries the
-        device status word)."""
-        logits = self.step(slots, tokens, None, check=False)
+    def begin_step_and_sample(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], sampler, params,
+                              histories=None, from_last: bool = False):
+        """Launch one step and the sampling of one token per sequence from the logits at its last
+        place, and start the copy of those tokens (and of the device status word) to pinned host
+        memory.  Nothing waits for the device; ``finish_step_and_sample`` does.  A token id of
+        ``LAST_TOKEN`` (with ``from_last``) is the token sampled last for that sequence, so the next
+        step can be begun before this one is finished."""
+        logits = self.step(slots, tokens, None, check=False, from_last=from_last)
         B = len(slots)
         picked = sampler.sample(logits, self.last_batch.slots[:B], params, histories)
-        host = torch.cat([picked, self.rt.status[:1]]).cpu()
-        if int(host[-1]):
+        host, event = self._results.pop() if self._results else (
+            torch.empty(self.cache.max_slots + 2, dtype=torch.int32).pin_memory(), torch.cuda.Event())
+        host[:B + 1].copy_(torch.cat([picked, self.rt.status[:1]]), non_blocking=True)
+        event.record()
+        return host, event, B
+
+    def finish_step_and_sample(self, handle) -> List[int]:
+        host, event, B = handle
+        event.synchronize()
+        out = host[:B + 1].tolist()
+        self._results.append((host, event))
+        if out[-1]:
             self.rt.check()
-        return host[:-1].tolist()
+        return out[:-1]
+
+    def step_and_sample(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], sampler, params,
+                        histories=None) -> List[int]:
+        """One step, then one sampled token per sequence; the tokens come back to the host."""
+        return self.finish_step_and_sample(self.begin_step_and_sample(slots, tokens, sampler, params, histories))

@@ -15,6 +15,15 @@ another until every request is served.  Results come back in request order.
 The loop only decides; it drives a *stepper* (``EngineStepper`` in production, a
 fake in the CPU tests) with four methods: ``new_sequence``, ``release``,
 ``seed`` and ``step_and_sample``.
+
+A stepper may split ``step_and_sample`` into ``begin`` (launch, no waiting) and
+``finish`` (the tokens).  The loop then works one step ahead: it begins step k+1
+before it has finished step k, for the sequences that go on whatever token step k
+gives them (by the counts: length and context), and feeds them ``LAST_TOKEN``,
+which the device replaces by the token it sampled in step k.  The host's work for a
+step is thereby hidden behind the device's.  A sequence that stops at step k for a
+reason the counts do not show (end-of-sequence, the caller) has a row in step k+1
+whose result is dropped.  The results are the same as without looking ahead.
 """
 from __future__ import annotations
 
@@ -23,6 +32,8 @@ from dataclasses import dataclass, field
 from typing import Callable, List, Optional, Sequence
 
 from ..sampling.params import SamplingParams
+
+LAST_TOKEN = -1      # fed for "the token sampled last for this sequence" when a step is begun ahead
 
 LENGTH, EOS, CALLER, CONTEXT = "length", "eos", "caller", "context"
 
@@ -56,7 +67,7 @@ class EngineStepper:
         from ..sampling.sampler import DeviceSampler
 
         self.engine = engine
-        self.sampler = DeviceSampler(engine.cache.rng_states, engine.rt.device)
+        self.sampler = DeviceSampler(engine.cache.rng_states, engine.rt.device, engine.cache.last_token)
 
     def new_sequence(self) -> int:
         return self.engine.new_sequence()
@@ -67,19 +78,30 @@ class EngineStepper:
     def seed(self, slots, seeds) -> None:
         self.sampler.seed(slots, seeds)
 
+    def begin(self, slots, tokens, histories, params: SamplingParams, from_last: bool = False):
+        return self.engine.begin_step_and_sample(slots, tokens, self.sampler, params, histories, from_last)
+
+    def finish(self, handle) -> List[int]:
+        return self.engine.finish_step_and_sample(handle)
+
     def step_and_sample(self, slots, tokens, histories, params: SamplingParams) -> List[int]:
-        return self.engine.step_and_sample(slots, tokens, self.sampler, params, histories)
+        return self.finish(self.begin(slots, tokens, histories, params))
 
 
 def generate(stepper, prompts: Sequence[Sequence[int]], max_tokens: int = 128,
              sampling: Optional[SamplingParams] = None, eos: Sequence[int] = (), batch_size: Optional[int] = None,
              ctx: Optional[int] = None, on_token: Optional[Callable[[int, int], bool]] = None,
-             stats: Optional[GenerationStats] = None) -> List[GenerationResult]:
+             stats: Optional[GenerationStats] = None, lookahead: Optional[bool] = None) -> List[GenerationResult]:
     """Generate up to ``max_tokens`` tokens after each prompt.
 
     ``on_token(request_index, token)`` sees every emitted token and returns False to
     stop that request (stop reason Caller).  ``ctx`` bounds a sequence's length in the
-    cache (stop reason Context).  Request i samples with seed ``sampling.seed + i``."""
+    cache (stop reason Context).  Request i samples with seed ``sampling.seed + i``.
+    ``lookahead`` (default: on if the stepper has ``begin``/``finish``) begins each step
+    before the one before it is finished; it is off with a repeat penalty, whose history
+    the host must know."""
+    from ..cache.allocator import CacheError
+
     sampling = (sampling or SamplingParams()).validate()
     eos = set(int(e) for e in eos)
     n = len(prompts)
@@ -92,6 +114,10 @@ def generate(stepper, prompts: Sequence[Sequence[int]], max_tokens: int = 128,
     batch_size = batch_size or n
     stats = stats if stats is not None else GenerationStats()
     clock = time.perf_counter
+    split = hasattr(stepper, "begin") and hasattr(stepper, "finish")
+    look = split and (lookahead is None or lookahead) and sampling.repeat_penalty == 1.0
+    if lookahead and not look:
+        raise ValueError("lookahead needs a stepper with begin/finish and no repeat penalty")
 
     for b0 in range(0, n, batch_size):
         ids = list(range(b0, min(n, b0 + batch_size)))
@@ -99,15 +125,16 @@ def generate(stepper, prompts: Sequence[Sequence[int]], max_tokens: int = 128,
         try:
             stepper.seed([slot[i] for i in ids], [sampling.seed + i for i in ids])
             history = {i: list(prompts[i]) for i in ids}
-            length = {i: len(prompts[i]) for i in ids}      # tokens in the cache after the next step
+            alive = set(ids)
 
-            def commit(i: int, tok: int) -> bool:
-                """Judge the token sampled for request i; True if the request goes on."""
+            def commit(i: int, tok: int, cached: int) -> bool:
+                """Judge the token sampled for request i, whose sequence then holds ``cached`` tokens
+                in the cache; True if the request goes on."""
                 r = results[i]
                 if tok in eos:
                     r.stop = EOS
                     return False
-                if ctx is not None and length[i] >= ctx:
+                if ctx is not None and cached >= ctx:
                     r.stop = CONTEXT
                     return False
                 history[i].append(tok)
@@ -120,32 +147,52 @@ def generate(stepper, prompts: Sequence[Sequence[int]], max_tokens: int = 128,
                     return False
                 return True
 
+            def launch(who, toks, cached, from_last):
+                """Begin a step; ``cached[i]`` is the length of i's sequence in the cache after it."""
+                sl, hs = [slot[i] for i in who], [history[i] for i in who]
+                if split:
+                    return who, stepper.begin(sl, toks, hs, sampling, from_last), cached
+                return who, stepper.step_and_sample(sl, toks, hs, sampling), cached
+
             t0 = clock()
-            first = stepper.step_and_sample([slot[i] for i in ids], [list(prompts[i]) for i in ids],
-                                            [history[i] for i in ids], sampling)
-            stats.prefill_seconds += clock() - t0
-            stats.prefill_tokens += sum(len(prompts[i]) for i in ids)
-            live = []
-            for i, tok in zip(ids, first):
-                if commit(i, int(tok)):
-                    live.append(i)
-                else:
-                    stepper.release(slot.pop(i))
-            t0 = clock()
-            while live:
-                pend = [[results[i].tokens[-1]] for i in live]
-                nxt = stepper.step_and_sample([slot[i] for i in live], pend, [history[i] for i in live], sampling)
-                stats.decode_steps += 1
-                stats.decode_tokens += len(live)
-                still = []
-                for i, tok in zip(live, nxt):
-                    length[i] += 1
-                    results[i].steps += 1
-                    if commit(i, int(tok)):
-                        still.append(i)
-                    else:
+            flights = [launch(ids, [list(prompts[i]) for i in ids], {i: len(prompts[i]) for i in ids}, False)]
+            prefill = True
+            while flights:
+                if look and len(flights) == 1:
+                    # who goes on whatever the step in flight gives them: one more token fits both
+                    # the request's budget and the context
+                    who, _, cached = flights[0]
+                    ahead = [i for i in who if i in alive and len(results[i].tokens) + 1 < max_tokens
+                             and (ctx is None or cached[i] < ctx)]
+                    if ahead:
+                        try:
+                            flights.append(launch(ahead, [[LAST_TOKEN]] * len(ahead),
+                                                  {i: cached[i] + 1 for i in ahead}, True))
+                        except CacheError:
+                            pass        # no room for all of them: wait for the tokens, some may stop
+                who, handle, cached = flights.pop(0)
+                picked = stepper.finish(handle) if split else handle
+                if prefill:
+                    stats.prefill_seconds += clock() - t0
+                    stats.prefill_tokens += sum(len(prompts[i]) for i in ids)
+                    t0 = clock()
+                elif any(i in alive for i in who):
+                    stats.decode_steps += 1
+                for i, tok in zip(who, picked):
+                    if i not in alive:
+                        continue            # stopped while this step was already in flight
+                    if not prefill:
+                        results[i].steps += 1
+                        stats.decode_tokens += 1
+                    if not commit(i, int(tok), cached[i]):
+                        alive.discard(i)
                         stepper.release(slot.pop(i))
-                live = still
+                prefill = False
+                if not flights:
+                    live = [i for i in who if i in alive]
+                    if live:
+                        flights.append(launch(live, [[results[i].tokens[-1]] for i in live],
+                                              {i: cached[i] + 1 for i in live}, False))
             stats.decode_seconds += clock() - t0
         finally:
             for s in slot.values():

@@ -107,7 +107,7 @@ class DecoderModel:
         """Run the batch's tokens through every scheduled layer, appending to the cache;
         return float32 logits [len(want_rows), vocab], or None if no row is wanted."""
         rt = self.rt
-        x = self.embedding.forward(rt, batch.token_ids, batch.num_tokens)
+        x = self.embedding.forward(rt, batch.token_ids, batch.num_tokens, batch)
         pending = None
         for e in self.spec.schedule:
             x, pending = self.blocks[e.layer].forward(rt, x, pending, batch, cache.view(e.cache), cache.state(e.cache))

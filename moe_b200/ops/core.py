@@ -31,7 +31,7 @@ def lib():
         L = build.load("core")
         P, I, F, LL = c_void_p, c_int, c_float, c_longlong
         sig = {
-            "moe_embed": [P, I, P, P, I, I, I, P, P],
+            "moe_embed": [P, I, P, P, I, I, I, P, P, P, P, P],
             "moe_rmsnorm": [P, P, P, P, P, P, I, I, I, F, I, P, P],
             "moe_rmsnorm_combine": [P, P, P, P, I, P, P, P, P, P, P, I, I, I, F, I, P, P],
             "moe_add_inplace": [P, P, LL, P],
@@ -49,7 +49,7 @@ def lib():
             "moe_align": [P, I, I, I, P, P, P, P, P],
             "moe_swiglu": [P, P, I, LL, I, P],
             "moe_combine": [P, P, P, I, P, P, P, I, I, P],
-            "moe_sample": [P, I, I, P, P, P, I, F, I, F, F, P, P],
+            "moe_sample": [P, I, I, P, P, P, I, F, I, F, F, P, P, P, LL, I, P],
             "moe_seed_rng": [P, P, P, I, P],
             "moe_table_update": [P, I, P, I, P],
         }
@@ -132,13 +132,18 @@ def check_status(status: torch.Tensor):
 
 
 # --------------------------------------------------------------------------- kernels
-def embed(table, token_ids, out, status):
+def embed(table, token_ids, out, status, last_token=None, seq_of_token=None, slots=None):
+    """out[t] = table[token_ids[t]]; with ``last_token`` (a per-slot table the sampler fills) a token
+    id of -1 stands for the token sampled last for the row's sequence."""
     _chk(table, "table", dims=2), _chk(token_ids, "token_ids", torch.int32, 1), _chk(out, "out", torch.float32, 2)
     T, H = out.shape
     if token_ids.numel() < T or table.shape[1] != H:
         raise KernelError("embed: shape mismatch")
-    _ok(lib().moe_embed(_p(table), _dt(table), _p(token_ids), _p(out), T, H, table.shape[0], _p(status), _stream()),
-        "embed")
+    if last_token is not None:
+        _chk(last_token, "last_token", torch.int32, 1), _chk(seq_of_token, "seq_of_token", torch.int32, 1)
+        _chk(slots, "slots", torch.int32, 1)
+    _ok(lib().moe_embed(_p(table), _dt(table), _p(token_ids), _p(out), T, H, table.shape[0], _p(status),
+                        _p(last_token), _p(seq_of_token), _p(slots), _stream()), "embed")
 
 
 def rmsnorm(x, weight, eps, *, delta=None, rows=None, out32=None, out16=None, write_back=True, status=None):
@@ -386,17 +391,34 @@ def moe_combine(y, pos_of_pair, topk_w, top_k, out, *, shared=None, shared_gate=
                           _stream()), "moe_combine")
 
 
-def sample(logits, slots, rng_states, out_tokens, *, temp=0.0, top_k=0, top_p=1.0, repeat_penalty=1.0, history=None):
+_sample_ws = {}
+
+
+def sample(logits, slots, rng_states, out_tokens, *, temp=0.0, top_k=0, top_p=1.0, repeat_penalty=1.0, history=None,
+           last_token=None, kernel=None):
+    """One token per row of ``logits``.  ``kernel="global"`` takes the kernel that works over global
+    memory whatever the vocabulary (otherwise only a vocabulary too large for a cluster's shared
+    memory does)."""
     _chk(logits, "logits", torch.float32, 2), _chk(out_tokens, "out_tokens", torch.int32, 1)
     R, V = logits.shape
     if temp > 0:
         _chk(slots, "slots", torch.int32, 1), _chk(rng_states, "rng_states", torch.int64, 1)
+    if last_token is not None:
+        _chk(last_token, "last_token", torch.int32, 1), _chk(slots, "slots", torch.int32, 1)
+        if slots.numel() < R:
+            raise KernelError("sample: fewer slots than rows")
     hl = 0
     if history is not None:
         _chk(history, "history", torch.int32, 2)
         hl = history.shape[1]
+    if out_tokens.numel() < R:
+        raise KernelError("sample: fewer places for tokens than rows")
+    ws = _sample_ws.get(logits.device)
+    if ws is None or ws.numel() < 2 * R:       # zeroed once; the kernels leave it zeroed
+        ws = _sample_ws[logits.device] = torch.zeros(max(2 * R, 512), dtype=torch.int64, device=logits.device)
     _ok(lib().moe_sample(_p(logits), R, V, _p(slots), _p(rng_states), _p(history), hl, float(temp), int(top_k),
-                         float(top_p), float(repeat_penalty), _p(out_tokens), _stream()), "sample")
+                         float(top_p), float(repeat_penalty), _p(out_tokens), _p(last_token), _p(ws), ws.numel() * 8,
+                         1 if kernel == "global" else 0, _stream()), "sample")
 
 
 def seed_rng(rng_states, slots, seeds):

@@ -29,9 +29,15 @@ class TokenEmbedding(Part):
         super().bind(tensors, rt)
         self.weight = tensors["weight"].contiguous()
 
-    def forward(self, rt, token_ids, num_tokens):
+    def forward(self, rt, token_ids, num_tokens, batch=None):
+        """With a batch that carries ``last_token`` (the per-slot table of the tokens sampled last),
+        a token id of -1 is read from there."""
         x = rt.empty((num_tokens, self.hidden), torch.float32)
-        core.embed(self.weight, token_ids, x, rt.status)
+        last = getattr(batch, "last_token", None)
+        if last is not None:
+            core.embed(self.weight, token_ids, x, rt.status, last, batch.seq_of_token, batch.slots)
+        else:
+            core.embed(self.weight, token_ids, x, rt.status)
         return x
 
 

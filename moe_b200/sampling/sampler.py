@@ -16,9 +16,10 @@ from .params import SamplingParams
 
 
 class DeviceSampler:
-    def __init__(self, rng_states: torch.Tensor, device):
+    def __init__(self, rng_states: torch.Tensor, device, last_token: Optional[torch.Tensor] = None):
         self.rng_states = rng_states
         self.device = device
+        self.last_token = last_token     # per-slot table that also receives every sampled token
 
     def seed(self, slots: Sequence[int], seeds: Sequence[int]) -> None:
         """state = seed * 0x9e3779b97f4a7c15 | 1 for each slot (src/sample.rs:7-9)."""
@@ -48,5 +49,6 @@ class DeviceSampler:
         if params.repeat_penalty != 1.0 and histories is not None:
             hist = self.history_tensor(histories, params.repeat_window)
         core.sample(logits, slots, self.rng_states, out, temp=params.temp, top_k=params.top_k, top_p=params.top_p,
-                    repeat_penalty=params.repeat_penalty if hist is not None else 1.0, history=hist)
+                    repeat_penalty=params.repeat_penalty if hist is not None else 1.0, history=hist,
+                    last_token=self.last_token)
         return out

@@ -167,3 +167,100 @@ def test_slots_are_returned_when_a_step_raises():
 def test_empty_prompt_is_refused():
     with pytest.raises(ValueError):
         generate(FakeStepper(), [[1], []], max_tokens=2)
+
+
+# ---- one step ahead ---------------------------------------------------------------------------------
+class AheadStepper(FakeStepper):
+    """A stepper with ``begin``/``finish``: the loop may begin a step before it has finished the one
+    before and feed LAST_TOKEN, which is replaced here, as on the device, by the token sampled last
+    for that slot.  ``room`` bounds the tokens held, to make a step begun ahead fail for lack of room."""
+
+    def __init__(self, num_slots=4, room=None):
+        super().__init__(num_slots)
+        self.last: Dict[int, int] = {}
+        self.room = room
+        self.open = 0                      # steps begun and not finished
+        self.most_open = 0
+        self.refused = 0
+
+    def begin(self, slots, tokens, histories, params, from_last=False):
+        from moe_b200.cache.allocator import CacheError
+        from moe_b200.engine.generate import LAST_TOKEN
+
+        if self.room is not None and sum(len(v) for v in self.fed.values()) + sum(len(t) for t in tokens) > self.room:
+            self.refused += 1
+            raise CacheError("the cache is full")
+        real = []
+        for s, t in zip(slots, tokens):
+            if list(t) == [LAST_TOKEN]:
+                assert from_last, "LAST_TOKEN fed without from_last"
+                real.append([self.last[s]])
+            else:
+                assert all(x >= 0 for x in t)
+                real.append(list(t))
+        # the host's history lags by the token still in flight: compare what it does know
+        for s, t, h in zip(slots, real, histories):
+            known = self.fed[s] + t
+            assert list(h) == known[:len(h)] and len(known) - len(h) in (0, 1)
+        out = FakeStepper.step_and_sample(self, slots, real, [self.fed[s] + t for s, t in zip(slots, real)], params)
+        for s, tok in zip(slots, out):
+            self.last[s] = tok
+        self.open += 1
+        self.most_open = max(self.most_open, self.open)
+        return out
+
+    def finish(self, handle):
+        self.open -= 1
+        return handle
+
+    def step_and_sample(self, slots, tokens, histories, params):
+        return self.finish(self.begin(slots, tokens, histories, params))
+
+
+def same(a, b):
+    assert [(r.tokens, r.stop, r.steps, r.prompt_tokens) for r in a] == [(r.tokens, r.stop, r.steps, r.prompt_tokens)
+                                                                         for r in b]
+
+
+@pytest.mark.parametrize("n", [1, 2, 3, 9])
+def test_one_step_ahead_gives_the_same_results(n):
+    full, _ = expected(PROMPTS[0], 8)
+    for kw in (dict(), dict(eos={full[2]}), dict(ctx=9), dict(batch_size=2), dict(eos={next_token(PROMPTS[1])})):
+        a, b = AheadStepper(), FakeStepper()
+        sa, sb = GenerationStats(), GenerationStats()
+        same(generate(a, PROMPTS[:4], max_tokens=n, stats=sa, **kw), generate(b, PROMPTS[:4], max_tokens=n, stats=sb, **kw))
+        assert sa.decode_tokens == sb.decode_tokens and sa.prefill_tokens == sb.prefill_tokens
+        assert not a.fed and a.open == 0 and (a.most_open == 2 or n == 1)
+        same(generate(AheadStepper(), PROMPTS[:4], max_tokens=n, lookahead=False, **kw),
+             generate(FakeStepper(), PROMPTS[:4], max_tokens=n, **kw))
+
+
+def test_one_step_ahead_with_a_callback_that_halts():
+    def make():
+        seen = []
+
+        def cb(i, tok):
+            seen.append(i)
+            return not (i == 1 and seen.count(1) == 3)
+        return cb
+
+    same(generate(AheadStepper(), PROMPTS[:3], max_tokens=6, on_token=make()),
+         generate(FakeStepper(), PROMPTS[:3], max_tokens=6, on_token=make()))
+
+
+def test_a_step_begun_ahead_that_finds_no_room_is_begun_again_when_the_tokens_are_known():
+    # room for the prompts and 3 more tokens each: the last step ahead is refused, then fits
+    # because request 0 has stopped by then
+    full, _ = expected(PROMPTS[0], 8)
+    st = AheadStepper(room=sum(len(p) for p in PROMPTS[:2]) + 5)
+    res = generate(st, PROMPTS[:2], max_tokens=5, eos={full[2]})
+    same(res, generate(FakeStepper(), PROMPTS[:2], max_tokens=5, eos={full[2]}))
+    assert st.refused >= 1 and not st.fed
+
+
+def test_repeat_penalty_turns_looking_ahead_off():
+    st = AheadStepper()
+    generate(st, PROMPTS[:2], max_tokens=4, sampling=SamplingParams(temp=0.7, repeat_penalty=1.3))
+    assert st.most_open == 1
+    with pytest.raises(ValueError):
+        generate(AheadStepper(), PROMPTS[:2], max_tokens=4, sampling=SamplingParams(repeat_penalty=1.3), lookahead=True)

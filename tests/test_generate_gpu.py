@@ -96,6 +96,38 @@ def test_seeded_temperature_sampling_workload_b(model_dirs, dtype):
                 assert tok in inside, f"request {i}, token {j}"
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_one_step_ahead_gives_the_same_tokens(model_dirs, dtype):
+    """The loop begins each step before it has read the tokens of the one before (the device feeds
+    itself the token it sampled); the results must be those of the loop that waits: greedy and seeded
+    sampling, an end-of-sequence token that the counts cannot foresee, a context limit, a callback,
+    and batches in a row whose slots are used again while a step of the batch before is still queued."""
+    import moe_b200
+
+    d, eng = G.engine_for(model_dirs, "B", dtype, std=0.2, max_tokens=64 * 4, max_slots=3)
+    prompts = [helpers.random_tokens(384, n, 70 + n) for n in (1, 7, 16, 23, 3, 64, 65)]
+    for kw in (dict(), dict(temp=0.8, top_p=0.9, seed=3), dict(temp=1.1, top_k=5, seed=9)):
+        wait = moe_b200.generate(eng, prompts, max_tokens=14, eos=(), batch_size=3, lookahead=False, **kw)
+        s1, s2 = moe_b200.GenerationStats(), moe_b200.GenerationStats()
+        ahead = moe_b200.generate(eng, prompts, max_tokens=14, eos=(), batch_size=3, lookahead=True, stats=s1, **kw)
+        assert [(o.tokens, o.stop, o.steps) for o in ahead] == [(o.tokens, o.stop, o.steps) for o in wait]
+        eos = [wait[1].tokens[3], wait[5].tokens[0]]
+        a = moe_b200.generate(eng, prompts, max_tokens=14, eos=eos, batch_size=3, ctx=70, lookahead=True, stats=s2, **kw)
+        b = moe_b200.generate(eng, prompts, max_tokens=14, eos=eos, batch_size=3, ctx=70, lookahead=False, **kw)
+        assert [(o.tokens, o.stop, o.steps) for o in a] == [(o.tokens, o.stop, o.steps) for o in b]
+        assert a[1].stop == "eos" and a[5].tokens == [] and a[6].stop == "context"
+        assert eng.cache.ledger.slots.num_held == 0
+        halt = lambda i, tok: not (i == 2 and tok == wait[2].tokens[4])
+        a = moe_b200.generate(eng, prompts, max_tokens=14, eos=(), batch_size=3, on_token=halt, lookahead=True, **kw)
+        b = moe_b200.generate(eng, prompts, max_tokens=14, eos=(), batch_size=3, on_token=halt, lookahead=False, **kw)
+        assert [(o.tokens, o.stop) for o in a] == [(o.tokens, o.stop) for o in b] and a[2].stop == "caller"
+    # a token id of -1 that was not asked for is still an error
+    s = eng.new_sequence()
+    with pytest.raises(Exception):
+        eng.step([s], [[-1]])
+    eng.release(s)
+
+
 def test_command_line_run_info_bench(model_dirs, tmp_path):
     d = model_dirs.get("A", "bfloat16", seed=1, std=0.08)
     env = dict(os.environ, PYTHONPATH=ROOT)
