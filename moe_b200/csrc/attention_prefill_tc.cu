@@ -174,9 +174,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     __shared__ float x_max[2][2][QT], x_sum[2][QT];      // what the two threads of a row tell each other
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    // which (sequence, query tile): tiles are numbered sequence by sequence
+    // which (sequence, query tile, head): tiles are numbered sequence by sequence, and the heads of a
+    // tile follow one another, so that the heaviest tiles of ALL heads are handed out first (with the
+    // heads outermost, the last heads' heaviest tiles would start late and finish alone)
     if (threadIdx.x == 0) {
-        int tile = blockIdx.x, seq = -1;
+        int tile = blockIdx.x / nh, seq = -1;
         for (int s = 0; s < num_seqs; s++) {
             const int tiles = (cu_seqlens[s + 1] - cu_seqlens[s] + QT - 1) / QT;
             if (tile < tiles) {
@@ -193,7 +195,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     const int tok0 = cu_seqlens[seq], len = cu_seqlens[seq + 1] - tok0;
     const int q_tile = (len + QT - 1) / QT - 1 - s_tile;        // heavier tiles (later rows) first
     const int q0 = q_tile * QT;
-    const int head = blockIdx.y, kvh = head / (nh / nkv);
+    const int head = blockIdx.x % nh, kvh = head / (nh / nkv);
     const int q_last = min(q0 + QT, len) - 1;
     const int kv_lo = window > 0 ? max(0, q0 + 1 - window) / KT : 0;
     const int n_tiles = q_last / KT - kv_lo + 1;
@@ -508,7 +510,7 @@ int launch(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tm
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid((num_tokens + QT - 1) / QT + num_seqs, nh);
+    dim3 grid(((num_tokens + QT - 1) / QT + num_seqs) * nh);
     attn_prefill_tc_kernel<HD><<<grid, 320, smem, stream>>>(tmQ, tmK, tmV, (__nv_bfloat16*)out, cu_seqlens, num_seqs, nh,
                                                             nkv, window, scale * 1.4426950408889634f, status);
     return launch_status();
