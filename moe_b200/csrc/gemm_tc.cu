@@ -128,6 +128,43 @@ __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
 __device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
 }
+// ---- a pair of CTAs on one tile (cta_group::2) ----
+// Both CTAs of the pair run these; allocation and release are mirrored in the two tensor memories.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+// A tile load whose bytes are counted by a barrier of the pair's first CTA (bar: an address in the
+// cluster's shared window, from mapa_cluster).  The data go to this CTA's own shared memory.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+// D[256, N] (+)= A[256, 16] B[N, 16]^T over the pair: each CTA holds 128 rows of A and N / 2 rows of B
+// at the same shared-memory offsets, and gets its 128 rows of D in its own tensor memory.
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// When the pair's MMAs so far are done, arrive on the barrier at this offset in both CTAs.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(both) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
@@ -165,9 +202,9 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
     return d;
 }
 
-__host__ __device__ constexpr uint32_t instr_desc(int n) {
+__host__ __device__ constexpr uint32_t instr_desc(int n, int m = TILE_W) {
     // c = f32 (1 << 4), a = bf16 (1 << 7), b = bf16 (1 << 10), both K-major, N >> 3 at 17, M >> 4 at 24
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TILE_W >> 4) << 24);
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 template <int BN, int MODE>
@@ -556,20 +593,20 @@ struct Tile {
 };
 
 // item -> tile.  prefix[i]: token tiles of the groups before i (grouped), in shared memory.
-template <int BN>
+template <int BN, int TW = TILE_W>
 __device__ __forceinline__ Tile tile_of(int item, int m_tiles, const Params& p, const int* prefix, const int* offs) {
     Tile t;
     if (!p.group_offsets) {
         // all token tiles of one feature tile first: CTAs running together share weight tiles in L2
         const int nt = item / m_tiles, m = item % m_tiles;
-        t.n0 = nt * TILE_W, t.g = 0, t.row0 = m * BN, t.row_end = p.M;
+        t.n0 = nt * TW, t.g = 0, t.row0 = m * BN, t.row_end = p.M;
         return t;
     }
     // grouped: all feature tiles of one token tile first.  A group's weights are read once anyway;
     // its activations are read by every feature tile, and stay in L2 only if those run together
-    const int n_tiles = (p.N + TILE_W - 1) / TILE_W;
+    const int n_tiles = (p.N + TW - 1) / TW;
     const int m = item / n_tiles;
-    t.n0 = (item % n_tiles) * TILE_W;
+    t.n0 = (item % n_tiles) * TW;
     int lo = 0, hi = p.num_groups;          // the last group whose first tile is <= m
     while (hi - lo > 1) {
         const int mid = (lo + hi) >> 1;
@@ -754,6 +791,214 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
     }
 }
 
+
+// ---- the persistent form on pairs of CTAs ------------------------------------------------------
+// Two CTAs of a cluster (two SMs) share one tile of 256 features x BN tokens: each loads its own 128
+// weight rows and HALF of the tile's tokens, the first CTA issues tcgen05.mma.cta_group::2, which reads
+// both shared memories, and each CTA finds its 128 features of the result in its own tensor memory.
+// A CTA thus brings 16 + 16 KB a stage into shared memory for the work that 16 + 32 KB bring without
+// pairing, which is what bounds the single-CTA form for many tokens (L2 to shared memory).
+//   full[s]      in the first CTA: its expect_tx arrival, bytes of both CTAs' loads
+//   empty[s]     in each CTA: the MMA issuer's commit, multicast to both
+//   acc_full[b]  in each CTA: likewise
+//   acc_empty[b] in the first CTA: 4 epilogue warps of each CTA
+template <int BN, int MODE>
+struct PairCfg {
+    static constexpr int NW = MODE == MODE_SWIGLU ? 2 : 1;
+    static constexpr int W_BYTES = TILE_W * BK * 2;
+    static constexpr int XBOX = 64;
+    static constexpr int X_ROWS = ((BN / 2 + XBOX - 1) / XBOX) * XBOX;      // this CTA's half of the tokens
+    static constexpr int STAGE_BYTES = NW * W_BYTES + X_ROWS * BK * 2;
+    static constexpr int STAGES_RAW = (196 * 1024) / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+    static constexpr int ACC_COLS = NW * BN;
+    static constexpr int TMEM_COLS = 2 * ACC_COLS;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
+    static_assert(BN >= 128 && TMEM_COLS <= 512 && STAGES >= 2, "tile does not fit");
+};
+
+template <int BN, int MODE>
+__global__ void __launch_bounds__(192)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const Params p) {
+    using C = PairCfg<BN, MODE>;
+    constexpr int PAIR_W = 2 * TILE_W;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ volatile int s_abort;
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_offs[MAX_SMEM_GROUPS + 1], s_prefix[MAX_SMEM_GROUPS + 1];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();        // 0: the CTA that issues the MMAs
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    pdl_sync();
+
+    int m_tiles = (p.M + BN - 1) / BN;
+    if (p.group_offsets) {
+        for (int i = threadIdx.x; i <= p.num_groups; i += blockDim.x) s_offs[i] = p.group_offsets[i];
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int run = 0;
+            for (int i = 0; i < p.num_groups; i++) {
+                s_prefix[i] = run;
+                run += (s_offs[i + 1] - s_offs[i] + BN - 1) / BN;
+            }
+            s_prefix[p.num_groups] = run;
+        }
+    }
+    if (threadIdx.x == 0) s_abort = 0;
+    __syncthreads();
+    if (p.group_offsets) m_tiles = s_prefix[p.num_groups];
+    const int items = m_tiles * ((p.N + PAIR_W - 1) / PAIR_W);
+
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar_base = base + C::STAGES * C::STAGE_BYTES;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (C::STAGES + s); };
+    auto acc_full = [&](int b) { return bar_base + 8u * (2 * C::STAGES + b); };
+    auto acc_empty = [&](int b) { return bar_base + 8u * (2 * C::STAGES + 2 + b); };
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; s++) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(acc_full(b), 1);
+            mbar_init(acc_empty(b), 8);      // one arrival per epilogue warp of both CTAs
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc_pair(smem_u32(&s_tmem), C::TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();          // the other CTA's barriers exist before anything arrives on them
+    tc_fence_after();
+    const uint32_t tmem = s_tmem;
+    const int kbs = (p.K + BK - 1) / BK;
+
+    if (warp == 0) {
+        // ---- producer (in both CTAs): own weight rows, own half of the tokens --------------------
+        if (lane == 0) {
+            int issued = 0;
+            bool ok = true;
+            for (int item = pair; item < items && ok; item += pairs) {
+                const Tile t = tile_of<BN, PAIR_W>(item, m_tiles, p, s_prefix, s_offs);
+                const int n_eff = min(BN, (min(BN, t.row_end - t.row0) + 15) & ~15);
+                const int half = n_eff >> 1;
+                const int xchunks = (half + C::XBOX - 1) / C::XBOX;
+                const uint32_t cta_tx = C::NW * C::W_BYTES + xchunks * C::XBOX * BK * 2;
+                const int w_row = t.g * p.w_rows_per_group + t.n0 + (int)rank * TILE_W;
+                const int x_row = t.row0 + (int)rank * half;
+                for (int kb = 0; kb < kbs; kb++, issued++) {
+                    const int s = issued % C::STAGES;
+                    ok = mbar_wait(empty_bar(s), ((issued / C::STAGES) & 1) ^ 1, &s_abort);
+                    if (!ok) break;
+                    const uint32_t st = base + s * C::STAGE_BYTES;
+                    const uint32_t bar = mapa_cluster(full_bar(s), 0);
+                    if (rank == 0) mbar_expect_tx(full_bar(s), 2 * cta_tx);
+                    tma_load_2d_pair(st, &tmW, kb * BK, w_row, bar);
+                    if (MODE == MODE_SWIGLU) tma_load_2d_pair(st + C::W_BYTES, &tmW, kb * BK, w_row + p.N, bar);
+                    for (int c = 0; c < xchunks; c++)
+                        tma_load_2d_pair(st + C::NW * C::W_BYTES + c * C::XBOX * BK * 2, &tmX, kb * BK,
+                                         x_row + c * C::XBOX, bar);
+                }
+            }
+            if (!ok) {
+                atomicOr(p.status, ST_WAIT_TIMEOUT);
+                s_abort = 1;
+                if (rank == 0)
+                    for (int i = max(0, issued - C::STAGES); i < issued; i++)     // copies in flight must land
+                        mbar_wait(full_bar(i % C::STAGES), (i / C::STAGES) & 1, nullptr);
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer (first CTA only): accumulator buffer (tile & 1) ---------------------------
+        if (lane == 0 && rank == 0) {
+            int consumed = 0, local = 0;
+            bool ok = true;
+            for (int item = pair; item < items && ok; item += pairs, local++) {
+                const Tile t = tile_of<BN, PAIR_W>(item, m_tiles, p, s_prefix, s_offs);
+                const int n_eff = min(BN, (min(BN, t.row_end - t.row0) + 15) & ~15);
+                const uint32_t idesc = instr_desc(n_eff, PAIR_W);
+                const int b = local & 1;
+                ok = mbar_wait(acc_empty(b), ((local >> 1) & 1) ^ 1, &s_abort);   // both epilogues have drained it
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t acc_addr = tmem + b * C::ACC_COLS;
+                for (int kb = 0; kb < kbs; kb++, consumed++) {
+                    const int s = consumed % C::STAGES;
+                    ok = mbar_wait(full_bar(s), (consumed / C::STAGES) & 1, &s_abort);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t st = base + s * C::STAGE_BYTES;
+#pragma unroll
+                    for (int k4 = 0; k4 < BK / UMMA_K; k4++) {
+                        const uint32_t koff = k4 * UMMA_K * 2;
+                        const uint64_t bdesc = smem_desc(st + C::NW * C::W_BYTES + koff);
+                        const uint32_t acc = (kb > 0 || k4 > 0) ? 1u : 0u;
+                        umma_bf16_pair(acc_addr, smem_desc(st + koff), bdesc, idesc, acc);
+                        if (MODE == MODE_SWIGLU)
+                            umma_bf16_pair(acc_addr + BN, smem_desc(st + C::W_BYTES + koff), bdesc, idesc, acc);
+                    }
+                    umma_commit_pair(empty_bar(s));
+                }
+                if (ok) umma_commit_pair(acc_full(b));
+            }
+            if (!ok) {
+                atomicOr(p.status, ST_WAIT_TIMEOUT);
+                s_abort = 1;
+            }
+        }
+    } else {
+        // ---- epilogue (in both CTAs): this CTA's 128 features of the tile ----------------------------
+        const int q = warp & 3;
+        int local = 0;
+        bool ok = true;
+        for (int item = pair; item < items && ok; item += pairs, local++) {
+            const Tile t = tile_of<BN, PAIR_W>(item, m_tiles, p, s_prefix, s_offs);
+            const int b = local & 1;
+            ok = mbar_wait(acc_full(b), (local >> 1) & 1, &s_abort);
+            if (!ok) break;
+            tc_fence_after();
+            const int n = t.n0 + (int)rank * TILE_W + q * 32 + lane;
+            const bool n_ok = n < p.N;
+            const uint32_t taddr = tmem + b * C::ACC_COLS + ((uint32_t)(q * 32) << 16);
+            const float bias = (MODE == MODE_PLAIN && p.bias && n_ok) ? p.bias[n] : 0.f;
+            const int rows_here = min(BN, t.row_end - t.row0);
+            for (int c0 = 0; c0 < rows_here; c0 += 16) {
+                float a[16], bb[16];
+                __syncwarp();
+                tmem_ld16(taddr + c0, a);
+                if (MODE == MODE_SWIGLU) tmem_ld16(taddr + BN + c0, bb);
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    const int r = t.row0 + c0 + j;
+                    if (n_ok && r < t.row_end) {
+                        const float v = MODE == MODE_SWIGLU ? silu_mul(a[j], bb[j]) : a[j] + bias;
+                        if (p.out_bf16)
+                            ((__nv_bfloat16*)p.out)[(size_t)r * p.ldo + n] = __float2bfloat16_rn(v);
+                        else
+                            ((float*)p.out)[(size_t)r * p.ldo + n] = v;
+                    }
+                }
+            }
+            // this warp has read its part of the buffer; the issuer waits for all eight warps of the pair
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa_cluster(acc_empty(b), 0));
+        }
+        if (!ok && lane == 0) {
+            atomicOr(p.status, ST_WAIT_TIMEOUT);
+            s_abort = 1;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();          // neither CTA frees tensor memory or leaves while the other may still use it
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem, C::TMEM_COLS);
+    }
+}
+
 // ---- host side ------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -830,6 +1075,31 @@ int launch_persistent(const CUtensorMap& tmW, const CUtensorMap& tmX, const Para
     return launch_pdl(gemm_tc_persistent_kernel<BN, MODE>, dim3(ctas), dim3(192), (size_t)C::SMEM, stream, tmW, tmX, p);
 }
 
+int g_pair = 0;
+
+template <int BN, int MODE>
+int launch_pair(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& p, int max_items, cudaStream_t stream) {
+    using C = PairCfg<BN, MODE>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             C::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int most = sm_count() / 2;
+    const int pairs = max_items < most ? max_items : most;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs), cfg.blockDim = dim3(192), cfg.dynamicSmemBytes = (size_t)C::SMEM, cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = g_pdl_enabled ? 2 : 1;
+    return (int)cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<BN, MODE>, tmW, tmX, p);
+}
+
 }  // namespace
 
 // X: [M, K] bf16 with row pitch ldx; W: [G * w_rows, K] bf16 contiguous; out: [M, ldo].
@@ -865,6 +1135,14 @@ MOE_API int moe_gemm_tc(const void* X, int ldx, const void* W, int num_groups, i
         const int mt = group_offsets ? (M < num_groups ? M : num_groups) + M / pbn : (M + pbn - 1) / pbn;
         const long long max_items = (long long)mt * ((N + TILE_W - 1) / TILE_W);
         const int cap = max_items > (1 << 30) ? (1 << 30) : (int)max_items;
+        if (g_pair && sm_count() >= 2) {
+            // pairs of CTAs on tiles of 256 features: half the activation traffic into shared memory
+            const long long pair_items = (long long)mt * ((N + 2 * TILE_W - 1) / (2 * TILE_W));
+            const int pcap = pair_items > (1 << 30) ? (1 << 30) : (int)pair_items;
+            if (mode == MODE_SWIGLU) return launch_pair<128, MODE_SWIGLU>(tmW, tmX, p, pcap, stream);
+            if (pbn == 128) return launch_pair<128, MODE_PLAIN>(tmW, tmX, p, pcap, stream);
+            return launch_pair<256, MODE_PLAIN>(tmW, tmX, p, pcap, stream);
+        }
         if (mode == MODE_SWIGLU) return launch_persistent<128, MODE_SWIGLU>(tmW, tmX, p, cap, stream);
         if (pbn == 128) return launch_persistent<128, MODE_PLAIN>(tmW, tmX, p, cap, stream);
         return launch_persistent<256, MODE_PLAIN>(tmW, tmX, p, cap, stream);
@@ -886,6 +1164,10 @@ MOE_API void moe_tc_set_pdl(int enabled) { g_pdl_enabled = enabled ? 1 : 0; }
 
 // The persistent form for many tokens on or off (on by default; off: one CTA per tile).
 MOE_API void moe_tc_set_persistent(int enabled) { g_persistent = enabled ? 1 : 0; }
+
+// Pairs of CTAs (cta_group::2) for the persistent form on or off (off by default: measured equal or
+// slower than single CTAs at the sizes tried, so what bounds those is not the activation traffic).
+MOE_API void moe_tc_set_pair(int enabled) { g_pair = enabled ? 1 : 0; }
 
 // How many K splits the kernel will really use for (K, splits asked), and its grid.y for tickets.
 MOE_API int moe_gemm_tc_plan(int K, int splits, int M, int bn, int num_groups, int grouped, int* grid_y) {

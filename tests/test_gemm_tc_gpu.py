@@ -16,6 +16,15 @@ def tc():
     return t
 
 
+@pytest.fixture(autouse=True, params=["pairs", "single"])
+def pairing(request, tc):
+    """Many tokens take pairs of CTAs on tiles of 256 features (cta_group::2), or, switched off, one
+    CTA per tile of 128: every test runs both ways."""
+    tc.lib().moe_tc_set_pair(1 if request.param == "pairs" else 0)
+    yield
+    tc.lib().moe_tc_set_pair(0)
+
+
 def status():
     return torch.zeros(4, dtype=torch.int32, device=DEV)
 
