@@ -190,6 +190,21 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
     for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
 }
 
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+
 // Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes,
 // groups of 8 rows 1024 bytes apart (SBO), descriptor version 1 (sm_100), layout type 2.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
@@ -568,6 +583,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     }
 }
 
+constexpr int EPI_GROUPS = 4;                        // epilogue warps per quarter of the accumulator's lanes
+constexpr int P_THREADS = 64 + 128 * EPI_GROUPS;     // producer warp, MMA warp, epilogue warps
+
+// What one epilogue warp of a persistent kernel does with a finished tile: feature n (this lane's row
+// of the accumulator at taddr), tokens row0 + [c_lo, c_hi).  The persistent kernels have EPI_GROUPS
+// epilogue warps for each quarter of the accumulator's lanes, which share the tile's tokens:
+// the epilogue is a chain of tensor-memory loads (each waited for) and scattered stores, and with
+// four warps it took twice as long as the tile's MMAs.
+template <int BN, int MODE>
+__device__ __forceinline__ void epilogue_part(const Params& p, uint32_t taddr, int n, int row0, int row_end, int c_lo,
+                                              int c_hi) {
+    const bool n_ok = n < p.N;
+    const float bias = (MODE == MODE_PLAIN && p.bias && n_ok) ? p.bias[n] : 0.f;
+    for (int c0 = c_lo; c0 < c_hi; c0 += 32) {
+        float a[32], bb[32];
+        __syncwarp();
+        tmem_ld32(taddr + c0, a);
+        if (MODE == MODE_SWIGLU) tmem_ld32(taddr + BN + c0, bb);
+        if (p.out_bf16) {
+            __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)(row0 + c0) * p.ldo + n;
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+                if (n_ok && row0 + c0 + j < row_end)
+                    o[(size_t)j * p.ldo] = __float2bfloat16_rn(MODE == MODE_SWIGLU ? silu_mul(a[j], bb[j]) : a[j] + bias);
+        } else {
+            float* o = (float*)p.out + (size_t)(row0 + c0) * p.ldo + n;
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+                if (n_ok && row0 + c0 + j < row_end)
+                    o[(size_t)j * p.ldo] = MODE == MODE_SWIGLU ? silu_mul(a[j], bb[j]) : a[j] + bias;
+        }
+    }
+}
+
 // ---- the persistent form, for many tokens ------------------------------------------------------
 // One CTA per SM walks over the tiles (blockIdx.x, blockIdx.x + gridDim.x, ...).  The producer and
 // the MMA issuer run ahead across tile borders, and the accumulator in tensor memory is doubled,
@@ -617,7 +666,7 @@ __device__ __forceinline__ Tile tile_of(int item, int m_tiles, const Params& p, 
 }
 
 template <int BN, int MODE>
-__global__ void __launch_bounds__(192)
+__global__ void __launch_bounds__(P_THREADS)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                           const Params p) {
     using C = PCfg<BN, MODE>;
@@ -660,7 +709,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(acc_full(b), 1);
-            mbar_init(acc_empty(b), 4);      // one arrival per epilogue warp
+            mbar_init(acc_empty(b), 4 * EPI_GROUPS);      // one arrival per epilogue warp
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -741,8 +790,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
             }
         }
     } else {
-        // ---- epilogue ----------------------------------------------------------------------------
-        const int q = warp & 3;
+        // ---- epilogue: warps 2...; warp (q, h) takes lanes 32 q.. and part h of the tile's tokens --------
+        const int q = warp & 3, h = (warp - 2) >> 2;
         int local = 0;
         bool ok = true;
         for (int item = blockIdx.x; item < items && ok; item += gridDim.x, local++) {
@@ -751,28 +800,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
             ok = mbar_wait(acc_full(b), (local >> 1) & 1, &s_abort);
             if (!ok) break;
             tc_fence_after();
-            const int n = t.n0 + q * 32 + lane;
-            const bool n_ok = n < p.N;
             const uint32_t taddr = tmem + b * C::ACC_COLS + ((uint32_t)(q * 32) << 16);
-            const float bias = (MODE == MODE_PLAIN && p.bias && n_ok) ? p.bias[n] : 0.f;
             const int rows_here = min(BN, t.row_end - t.row0);
-            for (int c0 = 0; c0 < rows_here; c0 += 16) {
-                float a[16], bb[16];
-                __syncwarp();
-                tmem_ld16(taddr + c0, a);
-                if (MODE == MODE_SWIGLU) tmem_ld16(taddr + BN + c0, bb);
-#pragma unroll
-                for (int j = 0; j < 16; j++) {
-                    const int r = t.row0 + c0 + j;
-                    if (n_ok && r < t.row_end) {
-                        const float v = MODE == MODE_SWIGLU ? silu_mul(a[j], bb[j]) : a[j] + bias;
-                        if (p.out_bf16)
-                            ((__nv_bfloat16*)p.out)[(size_t)r * p.ldo + n] = __float2bfloat16_rn(v);
-                        else
-                            ((float*)p.out)[(size_t)r * p.ldo + n] = v;
-                    }
-                }
-            }
+            const int part = ((rows_here + 32 * EPI_GROUPS - 1) / (32 * EPI_GROUPS)) * 32;      // a multiple of 32
+            epilogue_part<BN, MODE>(p, taddr, t.n0 + q * 32 + lane, t.row0, t.row_end, min(rows_here, h * part),
+                                    min(rows_here, (h + 1) * part));
             // this warp has read its part of the buffer: the MMA issuer may overwrite it
             tc_fence_before();
             __syncwarp();
@@ -801,7 +833,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
 //   full[s]      in the first CTA: its expect_tx arrival, bytes of both CTAs' loads
 //   empty[s]     in each CTA: the MMA issuer's commit, multicast to both
 //   acc_full[b]  in each CTA: likewise
-//   acc_empty[b] in the first CTA: 4 epilogue warps of each CTA
+//   acc_empty[b] in the first CTA: the epilogue warps of both CTAs
 template <int BN, int MODE>
 struct PairCfg {
     static constexpr int NW = MODE == MODE_SWIGLU ? 2 : 1;
@@ -818,7 +850,7 @@ struct PairCfg {
 };
 
 template <int BN, int MODE>
-__global__ void __launch_bounds__(192)
+__global__ void __launch_bounds__(P_THREADS)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const Params p) {
     using C = PairCfg<BN, MODE>;
     constexpr int PAIR_W = 2 * TILE_W;
@@ -862,7 +894,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(acc_full(b), 1);
-            mbar_init(acc_empty(b), 8);      // one arrival per epilogue warp of both CTAs
+            mbar_init(acc_empty(b), 8 * EPI_GROUPS);     // one arrival per epilogue warp of both CTAs
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -948,8 +980,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             }
         }
     } else {
-        // ---- epilogue (in both CTAs): this CTA's 128 features of the tile ----------------------------
-        const int q = warp & 3;
+        // ---- epilogue (in both CTAs): this CTA's 128 features of the tile; warps as in the single form --
+        const int q = warp & 3, h = (warp - 2) >> 2;
         int local = 0;
         bool ok = true;
         for (int item = pair; item < items && ok; item += pairs, local++) {
@@ -958,29 +990,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             ok = mbar_wait(acc_full(b), (local >> 1) & 1, &s_abort);
             if (!ok) break;
             tc_fence_after();
-            const int n = t.n0 + (int)rank * TILE_W + q * 32 + lane;
-            const bool n_ok = n < p.N;
             const uint32_t taddr = tmem + b * C::ACC_COLS + ((uint32_t)(q * 32) << 16);
-            const float bias = (MODE == MODE_PLAIN && p.bias && n_ok) ? p.bias[n] : 0.f;
             const int rows_here = min(BN, t.row_end - t.row0);
-            for (int c0 = 0; c0 < rows_here; c0 += 16) {
-                float a[16], bb[16];
-                __syncwarp();
-                tmem_ld16(taddr + c0, a);
-                if (MODE == MODE_SWIGLU) tmem_ld16(taddr + BN + c0, bb);
-#pragma unroll
-                for (int j = 0; j < 16; j++) {
-                    const int r = t.row0 + c0 + j;
-                    if (n_ok && r < t.row_end) {
-                        const float v = MODE == MODE_SWIGLU ? silu_mul(a[j], bb[j]) : a[j] + bias;
-                        if (p.out_bf16)
-                            ((__nv_bfloat16*)p.out)[(size_t)r * p.ldo + n] = __float2bfloat16_rn(v);
-                        else
-                            ((float*)p.out)[(size_t)r * p.ldo + n] = v;
-                    }
-                }
-            }
-            // this warp has read its part of the buffer; the issuer waits for all eight warps of the pair
+            const int part = ((rows_here + 32 * EPI_GROUPS - 1) / (32 * EPI_GROUPS)) * 32;
+            epilogue_part<BN, MODE>(p, taddr, t.n0 + (int)rank * TILE_W + q * 32 + lane, t.row0, t.row_end,
+                                    min(rows_here, h * part), min(rows_here, (h + 1) * part));
+            // this warp has read its part of the buffer; the issuer waits for all epilogue warps of the pair
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(mapa_cluster(acc_empty(b), 0));
@@ -1072,7 +1087,7 @@ int launch_persistent(const CUtensorMap& tmW, const CUtensorMap& tmX, const Para
         configured = true;
     }
     const int ctas = max_items < sm_count() ? max_items : sm_count();
-    return launch_pdl(gemm_tc_persistent_kernel<BN, MODE>, dim3(ctas), dim3(192), (size_t)C::SMEM, stream, tmW, tmX, p);
+    return launch_pdl(gemm_tc_persistent_kernel<BN, MODE>, dim3(ctas), dim3(P_THREADS), (size_t)C::SMEM, stream, tmW, tmX, p);
 }
 
 int g_pair = 0;
@@ -1090,7 +1105,7 @@ int launch_pair(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& p,
     const int most = sm_count() / 2;
     const int pairs = max_items < most ? max_items : most;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * pairs), cfg.blockDim = dim3(192), cfg.dynamicSmemBytes = (size_t)C::SMEM, cfg.stream = stream;
+    cfg.gridDim = dim3(2 * pairs), cfg.blockDim = dim3(P_THREADS), cfg.dynamicSmemBytes = (size_t)C::SMEM, cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
