@@ -98,7 +98,7 @@ __device__ __forceinline__ void rotated_chunk(const float* __restrict__ src, int
         if (d < rot) {
             const int i = d < half ? d : d - half;
             const float a = src[i], b = src[i + half], cs = ang[i], sn = ang[half + i];
-            v = d < half ? a * cs - b * sn : a * sn + b * cs;
+            v = d < half ? rot_lo(a, b, cs, sn) : rot_hi(a, b, cs, sn);
         } else {
             v = src[d];
         }

@@ -130,6 +130,16 @@ static inline int launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 b
     return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// The rotation of one pair (a at i, b at i + half) by the angle whose cosine and sine are cs, sn:
+// products and sums rounded one by one, as the reference's plain 32-bit code does (no fused
+// multiply-add), and the same in every kernel that rotates, so that they agree to the bit.
+__device__ __forceinline__ float rot_lo(float a, float b, float cs, float sn) {
+    return __fsub_rn(__fmul_rn(a, cs), __fmul_rn(b, sn));
+}
+__device__ __forceinline__ float rot_hi(float a, float b, float cs, float sn) {
+    return __fadd_rn(__fmul_rn(a, sn), __fmul_rn(b, cs));
+}
+
 // Logical position -> (page, offset) of a paged, optionally ring-shaped, cache.
 //   ring:  positions wrap at `ring` (a multiple of the page size); 0 = no wrap
 //   table: the sequence's page list; page p holds `page_size` consecutive positions

@@ -36,7 +36,7 @@ def lib():
             "moe_rmsnorm_combine": [P, P, P, P, I, P, P, P, P, P, P, I, I, I, F, I, P, P],
             "moe_add_inplace": [P, P, LL, P],
             "moe_gemm_generic": [P, I, I, P, I, P, I, LL, P, I, I, P, P, I, I, I, I, P, P],
-            "moe_rope_split": [P, P, P, I, I, I, I, I, P, P, P, I, P],
+            "moe_rope_split": [P, P, P, I, I, I, I, I, P, P, P, I, P, P, P, P, P, P, I, I, I, I, P, P],
             "moe_kv_commit": [P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
             "moe_attention_generic": [P, P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],
             "moe_router": [P, P, P, I, P, I, I, I, I, I, F, P, P, P, P, P, LL, P],
@@ -235,7 +235,11 @@ def gemm_generic(a, w, out, *, bias=None, a_rows=None, group_offsets=None, statu
                                _stream()), "gemm_generic")
 
 
-def rope_split(qkv, pos, inv_freq, nh, nkv, hd, rot, q, k, v):
+def rope_split(qkv, pos, inv_freq, nh, nkv, hd, rot, q, k, v, commit=None, status=None):
+    """Rotate and split a step's projections.  ``commit=(view, batch)``: also append the keys and
+    values to that cache layer in the same launch (only for a step whose attention reads nothing
+    from the cache); returns False if this was asked for and the sizes do not allow it (nothing is
+    launched then), else True."""
     _chk(qkv, "qkv", torch.float32, 2), _chk(pos, "pos", torch.int32, 1)
     T = qkv.shape[0]
     if qkv.shape[1] != (nh + 2 * nkv) * hd:
@@ -248,8 +252,22 @@ def rope_split(qkv, pos, inv_freq, nh, nkv, hd, rot, q, k, v):
         _chk(inv_freq, "inv_freq", torch.float32, 1)
         if inv_freq.numel() < rot // 2:
             raise KernelError("rope_split: inv_freq too short")
+    if commit is not None:
+        view, batch = commit
+        g = view.group
+        if k.dtype != g.dtype or g.num_kv_heads != nkv or g.head_dim != hd:
+            raise KernelError("rope_split: the cache layer differs from the keys in dtype or shape")
+        code = lib().moe_rope_split(_p(qkv), _p(pos), _p(inv_freq) if rot else None, T, nh, nkv, hd, rot, _p(q),
+                                    _p(k), _p(v), _dt(q), _p(view.k), _p(view.v), _p(batch.seq_of_token),
+                                    _p(batch.seq_end), _p(batch.slots), _p(g.table), g.table.stride(0), g.ring,
+                                    g.page_size, g.num_pages, _p(status), _stream())
+        if code == -1:
+            return False
+        _ok(code, "rope_split")
+        return True
     _ok(lib().moe_rope_split(_p(qkv), _p(pos), _p(inv_freq) if rot else None, T, nh, nkv, hd, rot, _p(q), _p(k), _p(v),
-                             _dt(q), _stream()), "rope_split")
+                             _dt(q), None, None, None, None, None, None, 0, 0, 0, 0, None, _stream()), "rope_split")
+    return True
 
 
 def kv_commit(k_new, v_new, view, batch, status):

@@ -103,7 +103,12 @@ class GQAttention(Part):
         q = rt.empty((T, self.nh, self.hd))
         k_new = rt.empty((T, max(nkv, 1), self.hd))
         v_new = rt.empty((T, max(nkv, 1), self.hd))
-        core.rope_split(qkv, batch.pos, table, self.nh, nkv, self.hd, rot, q, k_new, v_new)
+        # whole prompts read nothing from the cache, so their keys and values may go there at once
+        early = batch.all_fresh and self.own_kv and not batch.all_decode
+        committed = early and core.rope_split(qkv, batch.pos, table, self.nh, nkv, self.hd, rot, q, k_new, v_new,
+                                              commit=(cache_view, batch), status=rt.status)
+        if not committed:
+            core.rope_split(qkv, batch.pos, table, self.nh, nkv, self.hd, rot, q, k_new, v_new)
         if batch.all_decode:
             # a layer that reads another layer's cache: queries only
             core.attention_decode(q, cache_view, batch, ctx, nh=self.nh, window=self.window, scale=self.scale,
@@ -120,7 +125,7 @@ class GQAttention(Part):
                 # keys of earlier steps from the cache, keys of this step from its own buffers
                 core.attention_generic(q, k_new, v_new, cache_view, batch, ctx, nh=self.nh, window=self.window,
                                        scale=self.scale, use_local=self.own_kv, status=rt.status)
-            if self.own_kv:
+            if self.own_kv and not committed:
                 core.kv_commit(k_new, v_new, cache_view, batch, rt.status)
         return linear(rt, ctx, self.wo)
 

@@ -113,7 +113,45 @@ def test_gemm_generic_grouped_with_gather(core, dt):
     assert int(st[0]) & 16
 
 
-@pytest.mark.parametrize("nh,nkv,hd,rot", [(3, 1, 32, 32), (4, 2, 16, 16), (5, 5, 48, 48), (2, 1, 64, 32), (2, 2, 16, 0)])
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,rot,window", [(4, 2, 16, 16, None), (3, 1, 32, 16, 70), (2, 2, 128, 128, 130)])
+def test_rope_split_with_commit_equals_rope_split_then_kv_commit(core, dt, nh, nkv, hd, rot, window):
+    """Whole prompts of unequal lengths (one longer than the window's ring) and a padding row: the
+    launch that also appends to the cache leaves the cache as the separate launch does."""
+    from moe_b200.cache import KVCache, KVRequest
+
+    lens = [1, 63, 200, 65]
+    B, T = len(lens), sum(lens) + 1
+    torch.manual_seed(hd)
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, device=DEV)
+    inv = plain.rope_inv_freq(1e4, rot).to(DEV)
+    st = status()
+    results = []
+    for fused in (False, True):
+        cache = KVCache({0: KVRequest(nkv, hd, window)}, {0: None}, 2048, B, dt, DEV)
+        view = cache.view(0)
+        slots = [cache.acquire() for _ in range(B)]
+        for s, n in zip(slots, lens):
+            G.give_pages(cache, s, n)
+        batch = G.make_batch(DEV, slots + [cache.padding_slot], [0] * (B + 1), lens + [1])
+        batch.seq_of_token[T - 1] = -1
+        q = torch.zeros(T, nh, hd, device=DEV, dtype=dt)
+        k = torch.zeros(T, nkv, hd, device=DEV, dtype=dt)
+        v = torch.zeros(T, nkv, hd, device=DEV, dtype=dt)
+        if fused:
+            assert core.rope_split(qkv, batch.pos, inv, nh, nkv, hd, rot, q, k, v, commit=(view, batch), status=st)
+        else:
+            core.rope_split(qkv, batch.pos, inv, nh, nkv, hd, rot, q, k, v)
+            core.kv_commit(k, v, view, batch, st)
+        results.append((q.clone(), k.clone(), v.clone(), view.group.storage.clone()))
+    assert int(st[0]) == 0
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
+    assert float(results[1][3].abs().sum()) > 0 and float(results[1][3][:, :, 0].abs().sum()) == 0.0   # not the scratch page
+
+
+@pytest.mark.parametrize("nh,nkv,hd,rot", [(3, 1, 32, 32), (4, 2, 16, 16), (5, 5, 48, 48), (2, 1, 64, 32), (2, 2, 16, 0),
+                                           (2, 1, 20, 12)])
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
 def test_rope_split(core, nh, nkv, hd, rot, dt):
     T = 11
