@@ -235,6 +235,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = s_tmem;
+    // the set-up above needed nothing of the predecessor's (the sequence lengths are a step's input);
+    // its queries, keys and values are read from here on
+    pdl_sync();
 
     if (warp == 0) {
         // ---- producer ------------------------------------------------------------------------------
@@ -511,9 +514,8 @@ int launch(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tm
         configured = true;
     }
     dim3 grid(((num_tokens + QT - 1) / QT + num_seqs) * nh);
-    attn_prefill_tc_kernel<HD><<<grid, 320, smem, stream>>>(tmQ, tmK, tmV, (__nv_bfloat16*)out, cu_seqlens, num_seqs, nh,
-                                                            nkv, window, scale * 1.4426950408889634f, status);
-    return launch_status();
+    return launch_pdl(attn_prefill_tc_kernel<HD>, grid, 320, (size_t)smem, stream, tmQ, tmK, tmV, (__nv_bfloat16*)out,
+                      cu_seqlens, num_seqs, nh, nkv, window, scale * 1.4426950408889634f, status);
 }
 
 }  // namespace

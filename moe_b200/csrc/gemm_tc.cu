@@ -1197,6 +1197,7 @@ MOE_API int moe_gemm_tc_plan(int K, int splits, int M, int bn, int num_groups, i
 // dst[i, :] = src[rows[i], :] for bf16 rows of `width` elements (expert dispatch before the grouped product)
 __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ rows,
                                    __nv_bfloat16* __restrict__ dst, int width, int src_rows, int* status) {
+    pdl_sync();
     const int i = blockIdx.x;
     int r = rows[i];
     if (r < 0 || r >= src_rows) {
@@ -1211,6 +1212,6 @@ MOE_API int moe_gather_rows_bf16(const void* src, const int* rows, void* dst, in
                                  int* status, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (width % 8) return (int)cudaErrorInvalidValue;
-    gather_rows_kernel<<<n, 128, 0, stream>>>((const __nv_bfloat16*)src, rows, (__nv_bfloat16*)dst, width, src_rows, status);
-    return launch_status();
+    return launch_pdl(gather_rows_kernel, n, 128, 0, stream, (const __nv_bfloat16*)src, rows, (__nv_bfloat16*)dst,
+                      width, src_rows, status);
 }

@@ -163,6 +163,7 @@ router_logits_sgemm_kernel(const float* __restrict__ h, const WT* __restrict__ w
                            float* __restrict__ part) {
     __shared__ __align__(16) float Xs[SK][ST + 4];
     __shared__ __align__(16) float Ws[SK][SR + 4];
+    pdl_sync();
     const int tid = threadIdx.x, tg = tid % 16, rg = tid / 16;
     const int t0 = blockIdx.x * ST, r0 = blockIdx.z * SR;
     const int k0 = blockIdx.y * kper, k1 = min(hidden, k0 + kper);
@@ -291,18 +292,36 @@ __device__ __forceinline__ void route_token(const float* __restrict__ lg, float*
     }
 }
 
-// One warp per token.
+// One warp per token.  With `part` (the partial sums of router_logits_sgemm_kernel, `slices` of
+// them) the warp first adds its token's slices in slice order and writes the logits, which spares
+// the launch of sum_slices_kernel.
 __global__ void __launch_bounds__(128)
-router_topk_kernel(const float* __restrict__ logits, const int* __restrict__ seq_of_token, int num_tokens,
-                   int num_experts, int rows, int top_k, int norm_topk, float scale, int* __restrict__ topk_idx,
-                   float* __restrict__ topk_w, float* __restrict__ shared_gate) {
-    extern __shared__ float sc_all[];   // 4 warps x num_experts
+router_topk_kernel(float* __restrict__ logits, const float* __restrict__ part, int slices,
+                   const int* __restrict__ seq_of_token, int num_tokens, int num_experts, int rows, int top_k,
+                   int norm_topk, float scale, int* __restrict__ topk_idx, float* __restrict__ topk_w,
+                   float* __restrict__ shared_gate) {
+    extern __shared__ float sc_all[];   // per warp: rows logits, num_experts scores, top_k weights
+    pdl_sync();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * 4 + warp;
     if (t >= num_tokens) return;
-    route_token(logits + (size_t)t * rows, sc_all + (size_t)warp * num_experts, lane,
-                seq_of_token && seq_of_token[t] < 0, num_experts, rows, top_k, norm_topk, scale,
-                topk_idx + (size_t)t * top_k, topk_w + (size_t)t * top_k, shared_gate ? shared_gate + t : nullptr);
+    float* lg = sc_all + (size_t)warp * (rows + num_experts + top_k);
+    const size_t n = (size_t)num_tokens * rows;
+    for (int r = lane; r < rows; r += 32) {
+        float s;
+        if (part) {
+            s = 0.f;
+            for (int k = 0; k < slices; k++) s += part[(size_t)k * n + (size_t)t * rows + r];
+            logits[(size_t)t * rows + r] = s;
+        } else {
+            s = logits[(size_t)t * rows + r];
+        }
+        lg[r] = s;
+    }
+    __syncwarp();
+    route_token(lg, lg + rows, lane, seq_of_token && seq_of_token[t] < 0, num_experts, rows, top_k, norm_topk, scale,
+                topk_idx + (size_t)t * top_k, topk_w + (size_t)t * top_k, shared_gate ? shared_gate + t : nullptr,
+                lg + rows + num_experts);
 }
 
 // Inverting the (token, expert) table, by one block.  pairs = tokens * top_k entries of topk_idx
@@ -351,6 +370,7 @@ __global__ void __launch_bounds__(1024)
 moe_align_kernel(const int* __restrict__ topk_idx, int pairs, int top_k, int num_experts, int* __restrict__ offsets,
                  int* __restrict__ sorted_token, int* __restrict__ pos_of_pair, int* status) {
     extern __shared__ int sm[];   // counts[E], cursor[E]
+    pdl_sync();
     align_block(topk_idx, pairs, top_k, num_experts, sm, sm + num_experts, offsets, sorted_token, pos_of_pair, status);
 }
 
@@ -710,9 +730,12 @@ MOE_API long long moe_router_scratch_floats(int num_tokens, int hidden, int num_
 // logits[t, r] = h[t] . W[r] for the router rows (and the shared-gate row, if wsg): num_tokens *
 // (num_experts + (wsg ? 1 : 0)) floats.  scratch: moe_router_scratch_floats floats (may be null:
 // a prompt then takes the slower kernel).
-MOE_API int moe_router_logits(const float* h, const void* wr, const void* wsg, int w_dt, int num_tokens, int hidden,
+// *left_in_slices (if given): the sgemm kernel's partial sums are left in scratch, to be added by the
+// caller's next kernel; set to the number of slices, or to 0 if the logits are complete.
+static int router_logits_impl(const float* h, const void* wr, const void* wsg, int w_dt, int num_tokens, int hidden,
                               int num_experts, float* logits, float* scratch, long long scratch_floats,
-                              cudaStream_t stream) {
+                              int* left_in_slices, cudaStream_t stream) {
+    if (left_in_slices) *left_in_slices = 0;
     if (num_tokens <= 0) return 0;
     if (num_experts <= 0 || !logits) return (int)cudaErrorInvalidValue;
     const int rows = num_experts + (wsg ? 1 : 0);
@@ -729,13 +752,18 @@ MOE_API int moe_router_logits(const float* h, const void* wr, const void* wsg, i
     if (slices > 0 && scratch && scratch_floats >= (long long)slices * num_tokens * rows &&
         (num_tokens + ST - 1) / ST <= 0x7fffffff && slices <= 65535 && (rows + SR - 1) / SR <= 65535) {
         const dim3 g((num_tokens + ST - 1) / ST, slices, (rows + SR - 1) / SR);
+        int e;
         if (w_dt == DT_F32)
-            router_logits_sgemm_kernel<float><<<g, 128, 0, stream>>>(h, (const float*)wr, (const float*)wsg, num_tokens,
-                                                                     hidden, num_experts, rows, kper, scratch);
+            e = launch_pdl(router_logits_sgemm_kernel<float>, g, 128, 0, stream, h, (const float*)wr, (const float*)wsg,
+                           num_tokens, hidden, num_experts, rows, kper, scratch);
         else
-            router_logits_sgemm_kernel<__nv_bfloat16><<<g, 128, 0, stream>>>(
-                h, (const __nv_bfloat16*)wr, (const __nv_bfloat16*)wsg, num_tokens, hidden, num_experts, rows, kper,
-                scratch);
+            e = launch_pdl(router_logits_sgemm_kernel<__nv_bfloat16>, g, 128, 0, stream, h, (const __nv_bfloat16*)wr,
+                           (const __nv_bfloat16*)wsg, num_tokens, hidden, num_experts, rows, kper, scratch);
+        if (e) return e;
+        if (left_in_slices) {
+            *left_in_slices = slices;
+            return 0;
+        }
         const size_t n = (size_t)num_tokens * rows;
         sum_slices_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(scratch, logits, n, slices);
     } else if (num_tokens <= 64) {
@@ -755,6 +783,13 @@ MOE_API int moe_router_logits(const float* h, const void* wr, const void* wsg, i
     return launch_status();
 }
 
+MOE_API int moe_router_logits(const float* h, const void* wr, const void* wsg, int w_dt, int num_tokens, int hidden,
+                              int num_experts, float* logits, float* scratch, long long scratch_floats,
+                              cudaStream_t stream) {
+    return router_logits_impl(h, wr, wsg, w_dt, num_tokens, hidden, num_experts, logits, scratch, scratch_floats,
+                              nullptr, stream);
+}
+
 // logits: scratch of num_tokens * (num_experts + (wsg ? 1 : 0)) floats.
 MOE_API int moe_router(const float* h, const void* wr, const void* wsg, int w_dt, const int* seq_of_token,
                        int num_tokens, int hidden, int num_experts, int top_k, int norm_topk, float scale,
@@ -763,24 +798,28 @@ MOE_API int moe_router(const float* h, const void* wr, const void* wsg, int w_dt
     if (num_tokens <= 0) return 0;
     if (top_k <= 0 || top_k > num_experts || num_experts > 2048 || !logits) return (int)cudaErrorInvalidValue;
     if (wsg && !shared_gate) return (int)cudaErrorInvalidValue;
-    const int rc = moe_router_logits(h, wr, wsg, w_dt, num_tokens, hidden, num_experts, logits, scratch,
-                                     scratch_floats, stream);
+    int slices = 0;
+    const int rc = router_logits_impl(h, wr, wsg, w_dt, num_tokens, hidden, num_experts, logits, scratch,
+                                      scratch_floats, &slices, stream);
     if (rc) return rc;
     const int rows = num_experts + (wsg ? 1 : 0);
-    const size_t smem = (size_t)4 * num_experts * sizeof(float);
-    router_topk_kernel<<<(num_tokens + 3) / 4, 128, smem, stream>>>(logits, seq_of_token, num_tokens, num_experts, rows,
-                                                                   top_k, norm_topk, scale, topk_idx, topk_w,
-                                                                   shared_gate);
-    return launch_status();
+    const size_t smem = (size_t)4 * (rows + num_experts + top_k) * sizeof(float);
+    if (smem > 48 * 1024) {
+        const cudaError_t e = cudaFuncSetAttribute(router_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return launch_pdl(router_topk_kernel, (num_tokens + 3) / 4, 128, smem, stream, logits,
+                      (const float*)(slices ? scratch : nullptr), slices, seq_of_token, num_tokens, num_experts, rows,
+                      top_k, norm_topk, scale, topk_idx, topk_w, shared_gate);
 }
 
 MOE_API int moe_align(const int* topk_idx, int num_tokens, int top_k, int num_experts, int* offsets,
                       int* sorted_token, int* pos_of_pair, int* status, cudaStream_t stream) {
     if (num_experts > 4096) return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)num_experts * 2 * sizeof(int);
-    moe_align_kernel<<<1, 1024, smem, stream>>>(topk_idx, num_tokens * top_k, top_k, num_experts, offsets,
-                                               sorted_token, pos_of_pair, status);
-    return launch_status();
+    return launch_pdl(moe_align_kernel, 1, 1024, smem, stream, topk_idx, num_tokens * top_k, top_k, num_experts,
+                      offsets, sorted_token, pos_of_pair, status);
 }
 
 // logits -> picks, weights, shared gate, inverted table and (optionally) gathered activations, one
