@@ -130,6 +130,25 @@ static inline int launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 b
     return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// ---- thread-block clusters -------------------------------------------------------------------
+__device__ __forceinline__ unsigned cl_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// all threads of all CTAs of the cluster; orders shared-memory writes before it against reads after
+__device__ __forceinline__ void cl_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// the 32-bit word at the same shared-memory address in CTA `rank` of the cluster
+__device__ __forceinline__ unsigned cl_peer_u32(const void* local, unsigned rank) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(local);
+    unsigned pa, v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(pa) : "r"(a), "r"(rank));
+    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(pa) : "memory");
+    return v;
+}
+
 // The rotation of one pair (a at i, b at i + half) by the angle whose cosine and sine are cs, sn:
 // products and sums rounded one by one, as the reference's plain 32-bit code does (no fused
 // multiply-add), and the same in every kernel that rotates, so that they agree to the bit.

@@ -477,6 +477,8 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
 // (as rmsnorm_kernel), forms the token's router logits from the 32-bit normalised row in shared
 // memory (one warp per router row) and picks its experts; the block that finishes last inverts
 // the table and gathers the picked tokens' activations (as route_dispatch_kernel).
+int g_norm_route_cluster = 1;
+
 struct NormRouteParams {
     float* x;                 // [T, hidden] stream, updated in place if delta
     const float* delta;       // pending sum or null
@@ -501,6 +503,7 @@ struct NormRouteParams {
     int* ticket;              // one int, zero before and after
     int* status;
     int vec_ok;
+    int cluster;              // 1: the tokens' blocks are one cluster (at most 8 tokens), see the kernel
 };
 
 template <typename WT>
@@ -508,14 +511,15 @@ __global__ void __launch_bounds__(1024) norm_route_kernel(const NormRouteParams 
     extern __shared__ __align__(16) float nr_smem[];
     __shared__ float red[32];
     __shared__ int s_last;
-    const int t = blockIdx.x, H = p.hidden, E = p.num_experts;
+    __shared__ int s_mine[64];                         // this token's picks, for the other blocks of a cluster
+    const int t = blockIdx.x + blockIdx.z, H = p.hidden, E = p.num_experts;      // (a cluster lies along z)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     {
         // the weights do not depend on the predecessor: they are asked into L2 before the wait
         // (the blocks share the router's lines among them)
         const size_t line = 128, w_bytes = (size_t)E * H * sizeof(WT);
-        for (size_t off = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * line; off < w_bytes;
-             off += (size_t)gridDim.x * blockDim.x * line)
+        for (size_t off = ((size_t)t * blockDim.x + threadIdx.x) * line; off < w_bytes;
+             off += (size_t)p.num_tokens * blockDim.x * line)
             prefetch_l2((const char*)p.wr + off);
         for (size_t off = threadIdx.x * line; off < (size_t)H * sizeof(float); off += blockDim.x * line)
             prefetch_l2((const char*)p.norm_w + off);
@@ -598,6 +602,76 @@ __global__ void __launch_bounds__(1024) norm_route_kernel(const NormRouteParams 
                     p.topk_idx + (size_t)t * p.top_k, p.topk_w + (size_t)t * p.top_k,
                     p.shared_gate ? p.shared_gate + t : nullptr, wk);
 
+    if (p.cluster) {
+        // ---- one cluster: every block learns all picks through distributed shared memory, inverts
+        // the table for itself (in pair order, so the result does not depend on timing) and writes
+        // the gathered rows of ITS token from the row it still holds; block 0 writes the tables
+        __syncthreads();
+        for (int j = threadIdx.x; j < p.top_k; j += blockDim.x) s_mine[j] = p.topk_idx[(size_t)t * p.top_k + j];
+        cl_sync();
+        for (int i = threadIdx.x; i < pairs; i += blockDim.x)
+            picks[i] = (int)cl_peer_u32(&s_mine[i % p.top_k], (unsigned)(i / p.top_k));
+        __syncthreads();
+        for (int e = threadIdx.x; e < E; e += blockDim.x) {
+            int c = 0;
+            for (int i = 0; i < pairs; i++) c += picks[i] == e;
+            counts[e] = c;
+        }
+        for (int i = threadIdx.x; i < pairs; i += blockDim.x)
+            if (picks[i] != -1 && (picks[i] < 0 || picks[i] >= E)) atomicOr(p.status, ST_BAD_EXPERT);
+        __syncthreads();
+        int* start = counts + E;
+        if (warp == 0) {   // exclusive scan of the counts, 32 experts at a time
+            int run = 0;
+            for (int e0 = 0; e0 < E; e0 += 32) {
+                const int e = e0 + lane;
+                const int c = e < E ? counts[e] : 0;
+                int inc = c;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int n = __shfl_up_sync(0xffffffffu, inc, o);
+                    if (lane >= o) inc += n;
+                }
+                if (e < E) {
+                    start[e] = run + inc - c;
+                    if (t == 0) p.offsets[e] = run + inc - c;
+                }
+                run += __shfl_sync(0xffffffffu, inc, 31);
+            }
+            if (lane == 0) {
+                if (t == 0) p.offsets[E] = run;
+                s_last = run;
+            }
+        }
+        __syncthreads();
+        const int total = s_last;
+        for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+            const int e = picks[i];
+            int q = -1;
+            if (e >= 0 && e < E) {
+                q = start[e];
+                for (int j = 0; j < i; j++) q += picks[j] == e;      // pairs of the same expert before this one
+                if (t == 0) p.sorted_token[q] = i / p.top_k;
+            }
+            sorted[i] = q;                                          // here: the place of pair i
+            if (t == 0) p.pos_of_pair[i] = q;
+        }
+        if (t == 0)
+            for (int i = total + threadIdx.x; i < pairs; i += blockDim.x) p.sorted_token[i] = 0;
+        __syncthreads();
+        if (p.xs) {
+            for (int j = 0; j < p.top_k; j++) {
+                const int q = sorted[t * p.top_k + j];
+                if (q < 0) continue;
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.xs) + (size_t)q * H;
+                for (int c = threadIdx.x * 2; c < H; c += blockDim.x * 2)
+                    *reinterpret_cast<__nv_bfloat162*>(dst + c) = __floats2bfloat162_rn(row[c], row[c + 1]);
+            }
+        }
+        cl_sync();      // no block leaves while another may still read its picks
+        return;
+    }
+
     // ---- the block that finishes last inverts the table and gathers ----------------------------
     __threadfence();
     __syncthreads();
@@ -671,6 +745,9 @@ __global__ void __launch_bounds__(1024) norm_route_kernel(const NormRouteParams 
 
 }  // namespace
 
+// The cluster form of norm_route_kernel (up to 8 tokens) on or off (on by default).
+MOE_API void moe_set_norm_route_cluster(int enabled) { g_norm_route_cluster = enabled ? 1 : 0; }
+
 // The norm before a routed feed-forward, the router and the dispatch of a step of few tokens, one
 // launch (see norm_route_kernel).  Returns -1, with nothing launched, for sizes it does not take
 // (more than 64 tokens, 256 experts or 4096 (token, expert) pairs, or a row too long for shared
@@ -704,6 +781,9 @@ MOE_API int moe_norm_route(float* x, const float* delta, const float* norm_w, fl
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
+    // up to 8 tokens: one cluster, no ticket, no second reading of what other blocks wrote
+    p.cluster = (num_tokens <= 8 && top_k <= 64 && hidden % 2 == 0 && g_norm_route_cluster) ? 1 : 0;
+    if (p.cluster) return launch_pdl_cluster(kernel, dim3(1, 1, num_tokens), 1024, smem, stream, num_tokens, p);
     return launch_pdl(kernel, num_tokens, 1024, smem, stream, p);
 }
 

@@ -63,6 +63,10 @@ def lib():
         L.moe_set_pdl.restype = None
         if os.environ.get("MOE_B200_PDL", "1") == "0":      # programmatic dependent launch off
             L.moe_set_pdl(0)
+        L.moe_set_norm_route_cluster.argtypes = [c_int]
+        L.moe_set_norm_route_cluster.restype = None
+        if os.environ.get("MOE_B200_NORM_ROUTE_CLUSTER", "1") == "0":   # ticket form also for few tokens
+            L.moe_set_norm_route_cluster(0)
         _lib = L
     return _lib
 
