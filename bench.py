@@ -269,10 +269,30 @@ def profile_step(args):
     import moe_b200
 
     cfg = dict(A27B)
-    cfg["num_hidden_layers"] = args.layers or 2
-    model = moe_b200.random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
     V = cfg["vocab_size"]
-    if args.profile_step == "decode":
+    if args.profile_step == "sample":
+        # the sampling kernels alone, on random logits of the model's vocabulary: greedy, then a
+        # temperature with top-p, then with top-k too
+        from moe_b200.ops import core
+
+        B = args.batch
+        logits = torch.randn(B, V, device="cuda:0") * 2
+        slots = torch.arange(B, dtype=torch.int32, device="cuda:0")
+        rng = torch.arange(1, B + 2, dtype=torch.int64, device="cuda:0") * 0x9E3779B97F4A7C15 % (1 << 62) | 1
+        out = torch.zeros(B, dtype=torch.int32, device="cuda:0")
+        last = torch.zeros(B + 1, dtype=torch.int32, device="cuda:0")
+
+        def run(i):
+            core.sample(logits, slots, rng, out, last_token=last)
+            core.sample(logits, slots, rng, out, temp=0.8, top_p=0.95, last_token=last)
+            core.sample(logits, slots, rng, out, temp=0.8, top_k=40, top_p=0.95, last_token=last)
+        model = None
+    else:
+        cfg["num_hidden_layers"] = args.layers or 2
+        model = moe_b200.random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+    if args.profile_step == "sample":
+        pass
+    elif args.profile_step == "decode":
         B = args.batch
         eng = moe_b200.Engine(model, max_tokens=B * 1024, max_slots=B, use_graphs=False)
         slots = [eng.new_sequence() for _ in range(B)]
@@ -305,7 +325,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (reported in config)")
-    ap.add_argument("--profile-step", choices=["decode", "prefill"], default=None,
+    ap.add_argument("--profile-step", choices=["decode", "prefill", "sample"], default=None,
                     help="run a few steps of one kind between cudaProfilerStart/Stop (for ncu "
                          "--profile-from-start off) and print no benchmark line")
     ap.add_argument("--batch", type=int, default=8, help="with --profile-step decode: sequences in the batch")
