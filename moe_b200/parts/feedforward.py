@@ -90,6 +90,11 @@ class RoutedExperts(Part):
         # measured on a B200: the fused norm + router + dispatch launch wins up to 8 tokens and loses
         # from 16 on, where its single gathering block is the bottleneck
         self.fused_norm_tokens = int(os.environ.get("MOE_B200_NORM_ROUTE_MAX", "8"))
+        # up to this many tokens one block picks, inverts and gathers (one launch after the logits);
+        # beyond, a warp per token picks and the inversion and the gather are launches of their own
+        # (measured on a B200, ms a decode step at 16 / 32 / 64 tokens: 4.65 / 5.89 / 7.38 with one
+        # block up to 64 tokens, 4.48 / 5.75 / 7.07 with one block up to 8)
+        self.route_dispatch_tokens = int(os.environ.get("MOE_B200_ROUTE_DISPATCH_MAX", "8"))
 
     def tensors(self):
         t = {"gate.weight": TensorSpec((self.E, self.hidden))}
@@ -177,7 +182,7 @@ class RoutedExperts(Part):
                 ys = self._shared(rt, h)
         if routed is not None:
             topk_idx, topk_w, sg, offsets, sorted_token, pos_of_pair, xs = routed
-        elif few:
+        elif few and T <= self.route_dispatch_tokens:
             # pick, table inversion and gather in one launch after the logits
             topk_idx, topk_w, sg, offsets, sorted_token, pos_of_pair, xs = core.route_dispatch(
                 h.f32, self.w_router, self.k, self.norm_topk, self.scale, shared_gate_w=self.w_sgate,
