@@ -44,7 +44,9 @@ constexpr uint32_t WAIT_LIMIT = 1u << 24;
 constexpr int MAX_SMEM_GROUPS = 256;
 constexpr int MAX_SPLITS = 16;
 
-enum { MODE_PLAIN = 0, MODE_SWIGLU = 1 };
+// MODE_SWIGLU_IL (persistent form only): gate and up rows of the same 16 features alternate within a
+// 128-row weight tile (see gemm_tc_persistent_kernel), so that SwiGLU needs ONE accumulator.
+enum { MODE_PLAIN = 0, MODE_SWIGLU = 1, MODE_SWIGLU_IL = 2 };
 
 struct Params {
     void* out;
@@ -98,6 +100,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4,
+                                            uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar)
         : "memory");
 }
 // ---- thread-block clusters (the K splits of one tile) ----
@@ -617,6 +626,33 @@ __device__ __forceinline__ void epilogue_part(const Params& p, uint32_t taddr, i
     }
 }
 
+// The same for MODE_SWIGLU_IL: lanes 0..15 of this warp's quarter hold the gate rows of 16 features,
+// lanes 16..31 the up rows of the same features.  Of each pair of tokens the lower lanes take the
+// first (they get `up` from lane + 16), the upper lanes the second (they get `gate` from lane - 16).
+template <int BN>
+__device__ __forceinline__ void epilogue_part_il(const Params& p, uint32_t taddr, int f, bool upper, int row0,
+                                                 int row_end, int c_lo, int c_hi) {
+    const bool n_ok = f < p.N;
+    for (int c0 = c_lo; c0 < c_hi; c0 += 32) {
+        float a[32];
+        __syncwarp();
+        tmem_ld32(taddr + c0, a);
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+            const float send = upper ? a[j] : a[j + 1];
+            const float recv = __shfl_xor_sync(0xffffffffu, send, 16);
+            const float v = upper ? silu_mul(recv, a[j + 1]) : silu_mul(a[j], recv);
+            const int r = row0 + c0 + j + (upper ? 1 : 0);
+            if (n_ok && r < row_end) {
+                if (p.out_bf16)
+                    ((__nv_bfloat16*)p.out)[(size_t)r * p.ldo + f] = __float2bfloat16_rn(v);
+                else
+                    ((float*)p.out)[(size_t)r * p.ldo + f] = v;
+            }
+        }
+    }
+}
+
 // ---- the persistent form, for many tokens ------------------------------------------------------
 // One CTA per SM walks over the tiles (blockIdx.x, blockIdx.x + gridDim.x, ...).  The producer and
 // the MMA issuer run ahead across tile borders, and the accumulator in tensor memory is doubled,
@@ -627,12 +663,13 @@ template <int BN, int MODE>
 struct PCfg {
     static constexpr int NW = MODE == MODE_SWIGLU ? 2 : 1;
     static constexpr int W_BYTES = TILE_W * BK * 2;
-    static constexpr int XBOX = 64;
+    static constexpr int XBOX = 64;      // activation rows of one copy: only as many copies as hold a tile's tokens
     static constexpr int STAGE_BYTES = NW * W_BYTES + BN * BK * 2;
     static constexpr int STAGES_RAW = (196 * 1024) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int ACC_COLS = NW * BN;            // columns of one accumulator buffer
-    static constexpr int TMEM_COLS = 2 * ACC_COLS;      // 256 or 512: a power of two
+    static constexpr int NBUF = 2;                      // a tile's epilogue runs under the next tile's MMAs
+    static constexpr int TMEM_COLS = NBUF * ACC_COLS;   // 256 or 512: a power of two
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
     static_assert(BN >= 64 && TMEM_COLS <= 512 && STAGES >= 2, "tile does not fit");
 };
@@ -670,6 +707,8 @@ __global__ void __launch_bounds__(P_THREADS)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                           const Params p) {
     using C = PCfg<BN, MODE>;
+    // features of a tile: 128, or 64 where gate and up rows share the tile's 128 rows
+    constexpr int TW = MODE == MODE_SWIGLU_IL ? TILE_W / 2 : TILE_W;
     extern __shared__ uint8_t smem_raw[];
     __shared__ volatile int s_abort;
     __shared__ uint32_t s_tmem;
@@ -694,7 +733,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
     if (threadIdx.x == 0) s_abort = 0;
     __syncthreads();
     if (p.group_offsets) m_tiles = s_prefix[p.num_groups];
-    const int items = m_tiles * ((p.N + TILE_W - 1) / TILE_W);
+    const int items = m_tiles * ((p.N + TW - 1) / TW);
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t bar_base = base + C::STAGES * C::STAGE_BYTES;
@@ -707,7 +746,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
         }
-        for (int b = 0; b < 2; b++) {
+        for (int b = 0; b < C::NBUF; b++) {
             mbar_init(acc_full(b), 1);
             mbar_init(acc_empty(b), 4 * EPI_GROUPS);      // one arrival per epilogue warp
         }
@@ -726,7 +765,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
             int issued = 0;
             bool ok = true;
             for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
-                const Tile t = tile_of<BN>(item, m_tiles, p, s_prefix, s_offs);
+                const Tile t = tile_of<BN, TW>(item, m_tiles, p, s_prefix, s_offs);
                 const int n_eff = min(BN, (min(BN, t.row_end - t.row0) + 15) & ~15);
                 const int xchunks = (n_eff + C::XBOX - 1) / C::XBOX;
                 const uint32_t stage_tx = C::NW * C::W_BYTES + xchunks * C::XBOX * BK * 2;
@@ -737,7 +776,13 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
                     if (!ok) break;
                     const uint32_t st = base + s * C::STAGE_BYTES;
                     mbar_expect_tx(full_bar(s), stage_tx);
-                    tma_load_2d(st, &tmW, kb * BK, w_row, full_bar(s));
+                    if (MODE == MODE_SWIGLU_IL) {
+                        // tmW is five-dimensional here, (k, row of 16, gate|up, block of 16 features, group):
+                        // one box is four times [16 gate rows, the 16 up rows of the same features]
+                        tma_load_5d(st, &tmW, kb * BK, 0, 0, t.n0 / 16, t.g, full_bar(s));
+                    } else {
+                        tma_load_2d(st, &tmW, kb * BK, w_row, full_bar(s));
+                    }
                     if (MODE == MODE_SWIGLU) tma_load_2d(st + C::W_BYTES, &tmW, kb * BK, w_row + p.N, full_bar(s));
                     for (int c = 0; c < xchunks; c++)
                         tma_load_2d(st + C::NW * C::W_BYTES + c * C::XBOX * BK * 2, &tmX, kb * BK,
@@ -757,11 +802,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
             int consumed = 0, local = 0;
             bool ok = true;
             for (int item = blockIdx.x; item < items && ok; item += gridDim.x, local++) {
-                const Tile t = tile_of<BN>(item, m_tiles, p, s_prefix, s_offs);
+                const Tile t = tile_of<BN, TW>(item, m_tiles, p, s_prefix, s_offs);
                 const int n_eff = min(BN, (min(BN, t.row_end - t.row0) + 15) & ~15);
                 const uint32_t idesc = instr_desc(n_eff);
-                const int b = local & 1;
-                ok = mbar_wait(acc_empty(b), ((local >> 1) & 1) ^ 1, &s_abort);   // the epilogue has drained it
+                const int b = local % C::NBUF;
+                ok = mbar_wait(acc_empty(b), ((local / C::NBUF) & 1) ^ 1, &s_abort);   // the epilogue has drained it
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t acc_addr = tmem + b * C::ACC_COLS;
@@ -795,16 +840,20 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
         int local = 0;
         bool ok = true;
         for (int item = blockIdx.x; item < items && ok; item += gridDim.x, local++) {
-            const Tile t = tile_of<BN>(item, m_tiles, p, s_prefix, s_offs);
-            const int b = local & 1;
-            ok = mbar_wait(acc_full(b), (local >> 1) & 1, &s_abort);
+            const Tile t = tile_of<BN, TW>(item, m_tiles, p, s_prefix, s_offs);
+            const int b = local % C::NBUF;
+            ok = mbar_wait(acc_full(b), (local / C::NBUF) & 1, &s_abort);
             if (!ok) break;
             tc_fence_after();
             const uint32_t taddr = tmem + b * C::ACC_COLS + ((uint32_t)(q * 32) << 16);
             const int rows_here = min(BN, t.row_end - t.row0);
             const int part = ((rows_here + 32 * EPI_GROUPS - 1) / (32 * EPI_GROUPS)) * 32;      // a multiple of 32
-            epilogue_part<BN, MODE>(p, taddr, t.n0 + q * 32 + lane, t.row0, t.row_end, min(rows_here, h * part),
-                                    min(rows_here, (h + 1) * part));
+            if (MODE == MODE_SWIGLU_IL)
+                epilogue_part_il<BN>(p, taddr, t.n0 + q * 16 + (lane & 15), (lane & 16) != 0, t.row0, t.row_end,
+                                     min(rows_here, h * part), min(rows_here, (h + 1) * part));
+            else
+                epilogue_part<BN, MODE>(p, taddr, t.n0 + q * 32 + lane, t.row0, t.row_end, min(rows_here, h * part),
+                                        min(rows_here, (h + 1) * part));
             // this warp has read its part of the buffer: the MMA issuer may overwrite it
             tc_fence_before();
             __syncwarp();
@@ -1045,6 +1094,22 @@ bool make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, u
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// W [G][2 I][K] (gate rows, then up rows), I a multiple of 16, seen as (k, row of 16, gate|up, block
+// of 16 features, group): a box of 64 x 16 x 2 x 4 x 1 is, four times, 16 gate rows followed by the 16
+// up rows of the same features: a 128-row tile of 64 features in one copy.  Blocks past I / 16 read
+// as zeros.
+bool make_map_gate_up(CUtensorMap* map, const void* ptr, uint64_t groups, uint64_t inter, uint64_t K) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn || inter % 16) return false;
+    cuuint64_t dims[5] = {K, 16, 2, inter / 16, groups};
+    cuuint64_t strides[4] = {K * 2, inter * K * 2, 16 * K * 2, 2 * inter * K * 2};
+    cuuint32_t box[5] = {(cuuint32_t)BK, 16, 2, 4, 1};
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(ptr), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 constexpr int MAX_CLUSTER = 8;   // portable cluster size
 
 template <int BN, int MODE>
@@ -1091,6 +1156,7 @@ int launch_persistent(const CUtensorMap& tmW, const CUtensorMap& tmX, const Para
 }
 
 int g_pair = 0;
+int g_swiglu_il = 1;
 
 template <int BN, int MODE>
 int launch_pair(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& p, int max_items, cudaStream_t stream) {
@@ -1158,6 +1224,22 @@ MOE_API int moe_gemm_tc(const void* X, int ldx, const void* W, int num_groups, i
             if (pbn == 128) return launch_pair<128, MODE_PLAIN>(tmW, tmX, p, pcap, stream);
             return launch_pair<256, MODE_PLAIN>(tmW, tmX, p, pcap, stream);
         }
+        if (mode == MODE_SWIGLU && g_swiglu_il) {
+            // one accumulator of up to 256 tokens for 64 features (gate and up rows interleaved by the
+            // load), instead of two of 128 tokens for 128 features: half the MMA instructions where a
+            // group has between 129 and 256 tokens, and room for two accumulator buffers all the same.
+            // (Measured equal to the two-accumulator form on a B200: what bounds these products is the
+            // weight stream from DRAM, not MMA instructions, copies or bytes into shared memory.)
+            CUtensorMap tmG;
+            const int ibn = bn >= 256 ? 256 : 128;
+            if (make_map_gate_up(&tmG, W, (uint64_t)num_groups, (uint64_t)N, (uint64_t)K)) {
+                const int imt = group_offsets ? (M < num_groups ? M : num_groups) + M / ibn : (M + ibn - 1) / ibn;
+                const long long il_items = (long long)imt * ((N + TILE_W / 2 - 1) / (TILE_W / 2));
+                const int icap = il_items > (1 << 30) ? (1 << 30) : (int)il_items;
+                if (ibn == 256) return launch_persistent<256, MODE_SWIGLU_IL>(tmG, tmX, p, icap, stream);
+                return launch_persistent<128, MODE_SWIGLU_IL>(tmG, tmX, p, icap, stream);
+            }
+        }
         if (mode == MODE_SWIGLU) return launch_persistent<128, MODE_SWIGLU>(tmW, tmX, p, cap, stream);
         if (pbn == 128) return launch_persistent<128, MODE_PLAIN>(tmW, tmX, p, cap, stream);
         return launch_persistent<256, MODE_PLAIN>(tmW, tmX, p, cap, stream);
@@ -1179,6 +1261,9 @@ MOE_API void moe_tc_set_pdl(int enabled) { g_pdl_enabled = enabled ? 1 : 0; }
 
 // The persistent form for many tokens on or off (on by default; off: one CTA per tile).
 MOE_API void moe_tc_set_persistent(int enabled) { g_persistent = enabled ? 1 : 0; }
+
+// The one-accumulator SwiGLU form of the persistent kernel on or off (on by default).
+MOE_API void moe_tc_set_swiglu_interleaved(int enabled) { g_swiglu_il = enabled ? 1 : 0; }
 
 // Pairs of CTAs (cta_group::2) for the persistent form on or off (off by default: measured equal or
 // slower than single CTAs at the sizes tried, so what bounds those is not the activation traffic).

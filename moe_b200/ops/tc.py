@@ -45,6 +45,10 @@ def lib():
         L.moe_tc_set_persistent.restype = None
         if os.environ.get("MOE_B200_PERSISTENT", "1") == "0":   # one CTA per tile also for many tokens
             L.moe_tc_set_persistent(0)
+        L.moe_tc_set_swiglu_interleaved.argtypes = [c_int]
+        L.moe_tc_set_swiglu_interleaved.restype = None
+        if os.environ.get("MOE_B200_SWIGLU_IL", "1") == "0":    # many tokens: SwiGLU with two accumulators
+            L.moe_tc_set_swiglu_interleaved(0)
         L.moe_tc_set_pair.argtypes = [c_int]
         L.moe_tc_set_pair.restype = None
         if os.environ.get("MOE_B200_PAIR", "0") == "1":         # pairs of CTAs (cta_group::2) for many tokens

@@ -16,13 +16,16 @@ def tc():
     return t
 
 
-@pytest.fixture(autouse=True, params=["pairs", "single"])
+@pytest.fixture(autouse=True, params=["pairs", "single", "two-accumulators"])
 def pairing(request, tc):
     """Many tokens take pairs of CTAs on tiles of 256 features (cta_group::2), or, switched off, one
-    CTA per tile of 128: every test runs both ways."""
+    CTA per tile; SwiGLU for many tokens has one accumulator (gate and up rows interleaved by the
+    loads) or, switched off, two: every test runs all ways."""
     tc.lib().moe_tc_set_pair(1 if request.param == "pairs" else 0)
+    tc.lib().moe_tc_set_swiglu_interleaved(0 if request.param == "two-accumulators" else 1)
     yield
     tc.lib().moe_tc_set_pair(0)
+    tc.lib().moe_tc_set_swiglu_interleaved(1)
 
 
 def status():
