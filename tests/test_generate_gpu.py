@@ -128,6 +128,19 @@ def test_one_step_ahead_gives_the_same_tokens(model_dirs, dtype):
     eng.release(s)
 
 
+def test_one_step_ahead_over_many_pages(model_dirs):
+    """140 tokens after prompts that end just before, at and after a page border: every new page of
+    the cache is reserved for a step that is begun before the step before it has been read."""
+    import moe_b200
+
+    d, eng = G.engine_for(model_dirs, "A", "bfloat16", max_tokens=64 * 12, max_slots=3)
+    prompts = [helpers.random_tokens(256, n, 90 + n) for n in (63, 64, 65)]
+    wait = moe_b200.generate(eng, prompts, max_tokens=140, eos=(), lookahead=False, temp=0.9, seed=2)
+    ahead = moe_b200.generate(eng, prompts, max_tokens=140, eos=(), lookahead=True, temp=0.9, seed=2)
+    assert [o.tokens for o in ahead] == [o.tokens for o in wait] and all(len(o.tokens) == 140 for o in ahead)
+    assert eng.cache.ledger.slots.num_held == 0
+
+
 def test_command_line_run_info_bench(model_dirs, tmp_path):
     d = model_dirs.get("A", "bfloat16", seed=1, std=0.08)
     env = dict(os.environ, PYTHONPATH=ROOT)
