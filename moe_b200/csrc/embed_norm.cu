@@ -67,8 +67,59 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
                                int num_src_rows, int* status, int vec, const CombineSrc cs) {
     extern __shared__ float row[];
     __shared__ float red[32];
-    pdl_sync();
     const int i = blockIdx.x;
+    // The experts' combine with one 16-byte unit a thread: what does not come from the predecessor
+    // (the stream, the picks' places and weights, the gate and the norm's weight were all written
+    // at least two kernels ago) is read before the wait, so that only the experts' rows are left.
+    if (cs.y && !rows && hidden / 4 <= (int)blockDim.x && cs.top_k <= 8) {
+        const int j = threadIdx.x;
+        const bool mine = j < hidden / 4;
+        int pq[8];
+        float wq[8];
+#pragma unroll
+        for (int q = 0; q < 8; q++) {
+            pq[q] = q < cs.top_k ? cs.pos[(size_t)i * cs.top_k + q] : -1;
+            wq[q] = q < cs.top_k ? cs.w[(size_t)i * cs.top_k + q] : 0.f;
+        }
+        const float g = cs.gate ? cs.gate[i] : 1.0f;
+        float* xr = x + (size_t)i * hidden;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f), nw = v;
+        if (mine) v = reinterpret_cast<const float4*>(xr)[j], nw = reinterpret_cast<const float4*>(w)[j];
+        pdl_sync();
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (mine) {
+#pragma unroll
+            for (int q = 0; q < 8; q++)
+                if (pq[q] >= 0) {
+                    const float4 yv = *reinterpret_cast<const float4*>(cs.y + (size_t)pq[q] * hidden + 4 * j);
+                    acc.x = fmaf(wq[q], yv.x, acc.x), acc.y = fmaf(wq[q], yv.y, acc.y);
+                    acc.z = fmaf(wq[q], yv.z, acc.z), acc.w = fmaf(wq[q], yv.w, acc.w);
+                }
+            if (cs.shared) {
+                const float4 sv = *reinterpret_cast<const float4*>(cs.shared + (size_t)i * hidden + 4 * j);
+                if (cs.gate)
+                    acc.x += g * sv.x, acc.y += g * sv.y, acc.z += g * sv.z, acc.w += g * sv.w;
+                else
+                    acc.x += sv.x, acc.y += sv.y, acc.z += sv.z, acc.w += sv.w;
+            }
+            v.x += acc.x, v.y += acc.y, v.z += acc.z, v.w += acc.w;
+            if (write_back) reinterpret_cast<float4*>(xr)[j] = v;
+        }
+        const float ss1 = block_sum(mine ? v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w : 0.f, red);
+        const float scale = 1.0f / sqrtf(ss1 / (float)hidden + eps);
+        if (mine) {
+            const float4 y = make_float4(v.x * scale * nw.x, v.y * scale * nw.y, v.z * scale * nw.z, v.w * scale * nw.w);
+            if (out32) reinterpret_cast<float4*>(out32 + (size_t)i * hidden)[j] = y;
+            if (out16) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y), hi = __floats2bfloat162_rn(y.z, y.w);
+                uint2 u;
+                u.x = *reinterpret_cast<unsigned*>(&lo), u.y = *reinterpret_cast<unsigned*>(&hi);
+                reinterpret_cast<uint2*>(out16 + (size_t)i * hidden)[j] = u;
+            }
+        }
+        return;
+    }
+    pdl_sync();
     int r = rows ? rows[i] : i;
     if (r < 0 || r >= num_src_rows) {
         if (threadIdx.x == 0) atomicOr(status, ST_BAD_ROW);
