@@ -35,7 +35,7 @@ LAST_TOKEN = -1      # as a token id (with ``from_last``): the token sampled las
 class _DecodeGraph:
     """Static buffers and the captured graph of one batch-size bucket."""
 
-    def __init__(self, engine: "Engine", size: int):
+    def __init__(self, engine: "Engine", size: int, max_end: int = 0):
         self.size = size
         ngroups = len(engine.cache.groups)
         offs, o = {}, 0
@@ -52,7 +52,8 @@ class _DecodeGraph:
         self.host = torch.zeros(o, dtype=torch.int32).pin_memory()
         self.dev = torch.zeros(o, dtype=torch.int32, device=engine.rt.device)
         views = {k: self.dev[a:a + n] for k, (a, n) in offs.items()}
-        self.batch = StepBatch(**views, num_tokens=size, num_seqs=size, num_want=size, max_new=1, max_end=0,
+        # max_end: the longest sequence this graph will see (kernels size their grids by it)
+        self.batch = StepBatch(**views, num_tokens=size, num_seqs=size, num_want=size, max_new=1, max_end=max_end,
                                all_decode=True, all_fresh=False, last_token=engine.cache.last_token)
         self.event = torch.cuda.Event()
         self.busy = False
@@ -122,7 +123,7 @@ class Engine:
         graph_safe = all(getattr(p, "graph_safe", False) for p in parts)
         self.use_graphs = graph_safe if use_graphs is None else (use_graphs and graph_safe)
         self._routed = [p for p in parts if hasattr(p, "trace")]
-        self._graphs: Dict[int, _DecodeGraph] = {}
+        self._graphs: Dict[Tuple[int, int], _DecodeGraph] = {}
         self._table_caps = [0 if g.ring_pages else g.max_pages_per_seq for g in self.cache.groups]
         self._results: List[Tuple[torch.Tensor, torch.cuda.Event]] = []     # pinned buffers for sampled tokens
 
@@ -196,9 +197,11 @@ class Engine:
                 and (from_last or min(t[0] for t in tokens) >= 0)):
             size = self._bucket(B)
             if size is not None:
-                g = self._graphs.get(size)
+                # one graph per (batch bucket, bucket of the longest sequence: powers of two from 256)
+                reach = max(256, 1 << max(starts).bit_length())
+                g = self._graphs.get((size, reach))
                 if g is None:
-                    g = self._graphs[size] = _DecodeGraph(self, size)
+                    g = self._graphs[(size, reach)] = _DecodeGraph(self, size, reach)
                 g.fill(self, slots, starts, [t[0] for t in tokens], updates)
                 logits = g.run(self)
                 self.last_batch = g.batch

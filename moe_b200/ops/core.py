@@ -324,14 +324,19 @@ def router(h32, w_router, top_k, norm_topk, scale, topk_idx, topk_w, *, shared_g
 _SMS = {}
 
 
-def decode_splits(device, num_tokens: int, nkv: int) -> int:
-    """Key splits of the decode attention: about eight small CTAs per SM (each is a chain of
-    dependent loads, so many must be in flight)."""
+def decode_splits(device, num_tokens: int, nkv: int, max_end: int = 0) -> int:
+    """Key splits of the decode attention: about four small CTAs per SM (each is a chain of
+    dependent loads, so many must be in flight), but no more than leave each of a CTA's four warps
+    a tile of 32 keys of the longest sequence (``max_end``, 0 if unknown): with a short context and
+    one sequence, 32 splits of one tile each cost more in the merge than they gain."""
     idx = torch.device(device).index or 0
     if idx not in _SMS:
         _SMS[idx] = torch.cuda.get_device_properties(device).multi_processor_count
     per_sm = int(os.environ.get("MOE_B200_DECODE_CTAS", "4"))
-    return max(1, min(32, (per_sm * _SMS[idx]) // max(1, num_tokens * nkv)))
+    n = max(1, min(32, (per_sm * _SMS[idx]) // max(1, num_tokens * nkv)))
+    if max_end > 0:
+        n = min(n, max(1, -(-max_end // 32) // 4))
+    return n
 
 
 def attention_decode(q, view, batch, out, *, nh, window, scale, status):
@@ -341,7 +346,7 @@ def attention_decode(q, view, batch, out, *, nh, window, scale, status):
     T = batch.num_tokens
     if q.dtype != g.dtype or out.dtype != q.dtype:
         raise KernelError("attention: dtypes of queries, cache and output must agree")
-    nsplit = decode_splits(q.device, T, g.num_kv_heads)
+    nsplit = decode_splits(q.device, T, g.num_kv_heads, getattr(batch, "max_end", 0))
     partial = torch.empty(T * nh * nsplit * (g.head_dim + 2), dtype=torch.float32, device=q.device)
     _ok(lib().moe_attention_decode(_p(q), _p(view.k), _p(view.v), _p(out), _p(partial), _dt(q),
                                    _p(batch.seq_of_token), _p(batch.pos), _p(batch.slots), _p(g.table),
@@ -375,7 +380,7 @@ def attention_decode_fused(qkv, inv_freq, rot, view, batch, out, *, nh, window, 
         raise KernelError("attention_decode_fused: shapes or dtypes do not fit the cache")
     if rot:
         _chk(inv_freq, "inv_freq", torch.float32, 1)
-    nsplit = decode_splits(qkv.device, T, g.num_kv_heads)
+    nsplit = decode_splits(qkv.device, T, g.num_kv_heads, getattr(batch, "max_end", 0))
     partial = torch.empty(T * nh * nsplit * (g.head_dim + 2), dtype=torch.float32, device=qkv.device)
     tickets = _tickets(qkv.device, T * g.num_kv_heads)
     code = lib().moe_attention_decode_fused(_p(qkv), _p(inv_freq) if rot else None, rot, _p(view.k), _p(view.v),
