@@ -149,7 +149,12 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swiglu: bool
             # partial sums in global memory)
             # (measured: about 1.5 CTAs per SM is best up to 32 tokens, where all clusters of a
             # launch then find room at once; 2 per SM at 64 tokens)
-            target = 3 * num_sms(x.device) // 2 if bn <= 32 else 2 * num_sms(x.device)
+            # (a single sequence, i.e. one row, or up to four rows of routed experts: one CTA per SM;
+            # 1.76 -> 1.70 ms a step at batch 1, while two sequences and more lose by it)
+            one = M == 1 if not grouped else M <= 4
+            target = num_sms(x.device) if one else 3 * num_sms(x.device) // 2 if bn <= 32 else 2 * num_sms(x.device)
+            if "MOE_B200_SPLIT_TARGET" in os.environ:      # for measurements
+                target = int(os.environ["MOE_B200_SPLIT_TARGET"])
             splits = max(1, min(8, target // max(tiles, 1), -(-K // 64) // 4))
     splits = L.moe_gemm_tc_plan(K, int(splits), M, bn, G, 1 if grouped else 0, core.ctypes.byref(gy))
     partials = tickets = None
