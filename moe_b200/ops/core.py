@@ -71,7 +71,15 @@ def lib():
     return _lib
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream() -> int:
+    """The current stream's handle.  (``torch.cuda.current_stream()`` builds a Python object on
+    every call, which with hundreds of launches a step is milliseconds of host time.)"""
+    if _raw_stream is not None and _raw_device is not None:
+        return _raw_stream(_raw_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -324,6 +332,9 @@ def router(h32, w_router, top_k, norm_topk, scale, topk_idx, topk_w, *, shared_g
 _SMS = {}
 
 
+_DECODE_CTAS = None
+
+
 def decode_splits(device, num_tokens: int, nkv: int, max_end: int = 0) -> int:
     """Key splits of the decode attention: about four small CTAs per SM (each is a chain of
     dependent loads, so many must be in flight), but no more than leave each of a CTA's four warps
@@ -332,7 +343,10 @@ def decode_splits(device, num_tokens: int, nkv: int, max_end: int = 0) -> int:
     idx = torch.device(device).index or 0
     if idx not in _SMS:
         _SMS[idx] = torch.cuda.get_device_properties(device).multi_processor_count
-    per_sm = int(os.environ.get("MOE_B200_DECODE_CTAS", "4"))
+    global _DECODE_CTAS
+    if _DECODE_CTAS is None:
+        _DECODE_CTAS = int(os.environ.get("MOE_B200_DECODE_CTAS", "4"))
+    per_sm = _DECODE_CTAS
     n = max(1, min(32, (per_sm * _SMS[idx]) // max(1, num_tokens * nkv)))
     if max_end > 0:
         n = min(n, max(1, -(-max_end // 32) // 4))

@@ -57,6 +57,10 @@ def lib():
     return _lib
 
 
+_SPLIT_TARGET = int(os.environ.get("MOE_B200_SPLIT_TARGET", "0"))      # read once: the environment is slow to ask
+_ATTN_TC = os.environ.get("MOE_B200_ATTN_TC", "1") != "0"
+
+
 def num_sms(device) -> int:
     global _NUM_SMS
     if _NUM_SMS is None:
@@ -89,18 +93,20 @@ _workspaces = {}
 def workspace(device) -> Workspace:
     """The scratch of the calling stream: products on the side stream (``Runtime.side_stream``)
     have a workspace of their own, since they may run beside products on the main stream."""
-    side = torch.cuda.current_stream(device) in _side_streams
-    key = (torch.device(device).index or 0, side)
+    side = core._stream() in _side_handles
+    key = (device.index or 0 if isinstance(device, torch.device) else torch.device(device).index or 0, side)
     if key not in _workspaces:
         _workspaces[key] = Workspace(device)
     return _workspaces[key]
 
 
 _side_streams = set()
+_side_handles = set()       # their raw handles: asking torch for the current Stream object is slow
 
 
 def register_side_stream(stream) -> None:
     _side_streams.add(stream)
+    _side_handles.add(stream.cuda_stream)
 
 
 def token_tile(rows_per_group: float) -> int:
@@ -153,8 +159,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swiglu: bool
             # 1.76 -> 1.70 ms a step at batch 1, while two sequences and more lose by it)
             one = M == 1 if not grouped else M <= 4
             target = num_sms(x.device) if one else 3 * num_sms(x.device) // 2 if bn <= 32 else 2 * num_sms(x.device)
-            if "MOE_B200_SPLIT_TARGET" in os.environ:      # for measurements
-                target = int(os.environ["MOE_B200_SPLIT_TARGET"])
+            if _SPLIT_TARGET:                              # for measurements
+                target = _SPLIT_TARGET
             splits = max(1, min(8, target // max(tiles, 1), -(-K // 64) // 4))
     splits = L.moe_gemm_tc_plan(K, int(splits), M, bn, G, 1 if grouped else 0, core.ctypes.byref(gy))
     partials = tickets = None
@@ -185,7 +191,7 @@ def attention_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, batch, 
     Head sizes 64 and 128 run on tcgen05 (``attention_prefill_tc.cu``), 16 and 32 on mma.sync."""
     if q.dtype != torch.bfloat16 or hd not in (16, 32, 64, 128):
         return False
-    if hd in (64, 128) and status is not None and os.environ.get("MOE_B200_ATTN_TC", "1") != "0":
+    if hd in (64, 128) and status is not None and _ATTN_TC:
         code = lib().moe_attention_prefill_tc(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
                                               batch.cu_seqlens.data_ptr(), batch.num_seqs, batch.num_tokens, nh, nkv,
                                               hd, int(window or 0), float(scale), status.data_ptr(), core._stream())
