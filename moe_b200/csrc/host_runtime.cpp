@@ -370,6 +370,50 @@ MOE_API long long moe_pack_step(int* buf, long long cap, int B, const int* slots
     return o;
 }
 
+// A step of whole prompts (every sequence starts at position 0, the logits of each last token are
+// wanted), padded for a captured graph to `tp` token rows and `bb` sequences: rows past the tokens
+// belong to no sequence (seq_of_token -1, position 0, token 0), sequences past B are empty and sit in
+// the padding slot.  Layout: token_ids[tp] seq_of_token[tp] pos[tp] cu_seqlens[bb + 1] slots[bb]
+// seq_start[bb] seq_end[bb] want_rows[bb], then per cache group `upd_cap` page-table updates at
+// upd_off[g], padded as in moe_pack_decode.
+MOE_API int moe_pack_prompt(int* buf, int tp, int bb, int B, const int* slots, const int* counts, const int* tokens,
+                            int pad_slot, int num_groups, const int* upd_off, int upd_cap, const int* updates,
+                            int num_updates) {
+    if (B > bb || B < 0) return fail(ERR_VALUE, "more sequences than the bucket holds");
+    long long T = 0;
+    for (int i = 0; i < B; i++) {
+        if (counts[i] <= 0) return fail(ERR_VALUE, "every sequence of a step brings at least one token");
+        T += counts[i];
+    }
+    if (T > tp) return fail(ERR_VALUE, "more tokens than the bucket holds");
+    int* tok = buf;
+    int *sot = tok + tp, *pos = sot + tp, *cu = pos + tp, *sl = cu + bb + 1, *st = sl + bb, *en = st + bb;
+    int* wr = en + bb;
+    int at = 0;
+    for (int i = 0; i < bb; i++) {
+        const int n = i < B ? counts[i] : 0;
+        for (int j = 0; j < n; j++) tok[at + j] = tokens[at + j], sot[at + j] = i, pos[at + j] = j;
+        cu[i] = at, sl[i] = i < B ? slots[i] : pad_slot, st[i] = 0, en[i] = n;
+        wr[i] = n > 0 ? at + n - 1 : 0;
+        at += n;
+    }
+    cu[bb] = at;
+    for (int t = at; t < tp; t++) tok[t] = 0, sot[t] = -1, pos[t] = 0;
+    for (int g = 0; g < num_groups; g++) {
+        int* u = buf + upd_off[g];
+        int n = 0;
+        for (int k = 0; k < num_updates; k++) {
+            const int* e = updates + 4 * k;
+            if (e[0] != g) continue;
+            if (n >= upd_cap) return fail(ERR_VALUE, "more page-table updates than the bucket holds");
+            u[3 * n] = e[1], u[3 * n + 1] = e[2], u[3 * n + 2] = e[3];
+            n++;
+        }
+        for (; n < upd_cap; n++) u[3 * n] = pad_slot, u[3 * n + 1] = 0, u[3 * n + 2] = 0;
+    }
+    return 0;
+}
+
 // A step of one token per sequence, padded to `size` rows for a captured graph: rows past B belong
 // to no sequence (seq_of_token -1, the padding slot, position 0).  After the eight arrays of
 // moe_pack_step (each `size` long, cu_seqlens size + 1) come, per cache group, `size` page-table

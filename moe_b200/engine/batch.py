@@ -35,6 +35,10 @@ class StepBatch:
     all_fresh: bool = False      # every sequence starts at position 0
     # per-slot table of the tokens sampled last; if given, a token id of -1 is read from it
     last_token: Optional[torch.Tensor] = None
+    # a step of several tokens a sequence with rows that belong to no sequence (a padded graph): a
+    # mixer must leave something finite in those rows of its output, as rows of a tile are multiplied
+    # by weights of exactly zero, and 0 x NaN is NaN
+    has_padding: bool = False
 
 
 def layout(num_tokens: int, num_seqs: int, num_want: int) -> List[Tuple[str, int]]:

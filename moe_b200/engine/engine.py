@@ -21,6 +21,7 @@ import numpy as np
 import torch
 
 import ctypes
+import os
 
 from ..cache.allocator import _IP, CacheError, _ok, host_lib, ints
 from ..cache.kv import KVCache
@@ -29,6 +30,10 @@ from ..ops import core
 from .batch import StepBatch, fill_host, layout
 
 GRAPH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+# Short prompts are bound by the host's launches (hundreds of kernels a step), so they too are replayed
+# from graphs, padded to these numbers of token rows and of sequences.
+PROMPT_TOKEN_BUCKETS = (64, 128, 256, 512)
+PROMPT_SEQ_BUCKETS = (1, 2, 4, 8)
 LAST_TOKEN = -1      # as a token id (with ``from_last``): the token sampled last for the sequence
 
 
@@ -101,6 +106,70 @@ class _DecodeGraph:
         return self.logits
 
 
+class _PromptGraph:
+    """Static buffers and the captured graph of a step of whole prompts (every sequence from
+    position 0, the logits of each last token), padded to ``tokens`` rows and ``seqs`` sequences."""
+
+    def __init__(self, engine: "Engine", tokens: int, seqs: int):
+        self.tokens, self.seqs = tokens, seqs
+        ngroups = len(engine.cache.groups)
+        offs, o = {}, 0
+        for name, n in layout(tokens, seqs, seqs):
+            offs[name] = (o, n)
+            o += n
+        self.upd_cap = -(-tokens // 64) + seqs          # most pages a group can hand out in such a step
+        self.upd_off = []
+        for _ in range(ngroups):
+            self.upd_off.append(o)
+            o += 3 * self.upd_cap
+        self._upd_off_c, _ = ints(self.upd_off)
+        self.host = torch.zeros(o, dtype=torch.int32).pin_memory()
+        self.dev = torch.zeros(o, dtype=torch.int32, device=engine.rt.device)
+        views = {k: self.dev[a:a + n] for k, (a, n) in offs.items()}
+        self.batch = StepBatch(**views, num_tokens=tokens, num_seqs=seqs, num_want=seqs, max_new=tokens,
+                               max_end=tokens, all_decode=False, all_fresh=True, has_padding=True)
+        self.event = torch.cuda.Event()
+        self.busy = False
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+
+    def fill(self, engine: "Engine", slots, counts, tokens, updates: np.ndarray) -> None:
+        """Pack the step (``moe_pack_prompt`` of the host runtime) and start its copy."""
+        if self.busy:
+            self.event.synchronize()
+            self.busy = False
+        sl, B = ints(slots)
+        ct, _ = ints(counts)
+        flat = np.fromiter((x for t in tokens for x in t), dtype=np.int32, count=sum(counts))
+        upd = np.ascontiguousarray(updates, dtype=np.int32)
+        _ok(host_lib().moe_pack_prompt(ctypes.cast(self.host.data_ptr(), _IP), self.tokens, self.seqs, B, sl, ct,
+                                       flat.ctypes.data_as(_IP), engine.cache.padding_slot, len(self.upd_off),
+                                       self._upd_off_c, self.upd_cap, upd.ctypes.data_as(_IP), int(upd.shape[0])))
+        self.dev.copy_(self.host, non_blocking=True)
+        self.event.record()
+        self.busy = True
+
+    def run(self, engine: "Engine") -> torch.Tensor:
+        def body():
+            for gi, o in enumerate(self.upd_off):
+                core.table_update(engine.cache.groups[gi].table, self.dev[o:o + 3 * self.upd_cap], self.upd_cap)
+            return engine.model.forward(self.batch, engine.cache)
+
+        if self.graph is None:
+            body()      # lazy builds and workspaces outside the capture; the step may run twice (same keys, same places)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            l0 = core.launches
+            with torch.cuda.graph(g):
+                self.logits = body()
+            self.launches = core.launches - l0
+            self.graph = g
+        else:
+            core.launches += self.launches
+        self.graph.replay()
+        return self.logits
+
+
 class Engine:
     def __init__(self, model: DecoderModel, max_tokens: int, max_slots: Optional[int] = None,
                  use_graphs: Optional[bool] = None):
@@ -123,7 +192,9 @@ class Engine:
         graph_safe = all(getattr(p, "graph_safe", False) for p in parts)
         self.use_graphs = graph_safe if use_graphs is None else (use_graphs and graph_safe)
         self._routed = [p for p in parts if hasattr(p, "trace")]
+        self.prompt_graphs = os.environ.get("MOE_B200_PROMPT_GRAPHS", "1") != "0"
         self._graphs: Dict[Tuple[int, int], _DecodeGraph] = {}
+        self._prompt_graphs: Dict[Tuple[int, int], _PromptGraph] = {}
         self._table_caps = [0 if g.ring_pages else g.max_pages_per_seq for g in self.cache.groups]
         self._results: List[Tuple[torch.Tensor, torch.cuda.Event]] = []     # pinned buffers for sampled tokens
 
@@ -209,6 +280,25 @@ class Engine:
                 if check:
                     self.rt.check()
                 return logits[:B]
+
+        # ---- short whole prompts, last logits wanted: replay the bucket's graph ------------------
+        T = sum(counts)
+        if (self.use_graphs and self.prompt_graphs and T <= PROMPT_TOKEN_BUCKETS[-1] and B <= PROMPT_SEQ_BUCKETS[-1]
+                and not any(starts) and all(len(w) == 1 and w[0] == n - 1 for w, n in zip(want, counts))
+                and not from_last
+                and not any(p.trace is not None for p in self._routed)):
+            tb = next(b for b in PROMPT_TOKEN_BUCKETS if b >= T)
+            sb = next(b for b in PROMPT_SEQ_BUCKETS if b >= B)
+            g = self._prompt_graphs.get((tb, sb))
+            if g is None:
+                g = self._prompt_graphs[(tb, sb)] = _PromptGraph(self, tb, sb)
+            g.fill(self, slots, counts, tokens, updates)
+            logits = g.run(self)
+            self.last_batch = g.batch
+            self.last_rows = B
+            if check:
+                self.rt.check()
+            return logits[:B]
 
         # ---- the general step -----------------------------------------------------------------
         T, W = sum(counts), sum(len(w) for w in want)

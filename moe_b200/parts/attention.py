@@ -88,6 +88,8 @@ class GQAttention(Part):
         if table is None and hasattr(self.position, "apply"):
             self.position.apply(rt, qkv, self.nh, nkv, self.hd, batch.pos)
         ctx = rt.empty((T, self.nh * self.hd))
+        if getattr(batch, "has_padding", False) and not batch.all_decode:
+            ctx.zero_()      # rows of no sequence are written by no attention kernel
         if batch.all_decode and self.own_kv:
             # one token per sequence: rotation, append, attention split along the keys and the
             # merge in ONE launch where the head size allows it

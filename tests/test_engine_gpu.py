@@ -90,6 +90,34 @@ def test_long_decoding(model_dirs, name, dtype):
     assert cut < G.tol_cut(dtype), f"first wrong place {first_bad(one_by_one, whole, G.tol_cut(dtype))}"
 
 
+@pytest.mark.parametrize("name,dtype", [(n, dt) for n in ("A", "B", "C") for dt in ("float32", "bfloat16")])
+def test_short_prompts_replayed_from_padded_graphs_equal_the_step_launched_kernel_by_kernel(model_dirs, name, dtype):
+    """Whole prompts whose last logits are wanted run from a graph padded to a bucket of token rows
+    and of sequences: the logits, and the cache they leave (seen through a decode step), are those
+    of the same step without graphs.  Lengths just below, at and above a bucket's and a page's edge."""
+    import moe_b200
+
+    vocab = helpers.CONFIGS[name]["vocab_size"]
+    d, eng = G.engine_for(model_dirs, name, dtype, max_tokens=64 * 24, max_slots=8)
+    model = eng.model
+    plain_eng = moe_b200.Engine(model, max_tokens=64 * 24, max_slots=8, use_graphs=False)
+    for lens in ([5], [63], [64, 1], [65, 3, 17], [127, 128, 2, 40], [200, 9, 64, 30, 31, 7, 1, 100]):
+        prompts = [helpers.random_tokens(vocab, n, 11 + n) for n in lens]
+        nxt = [[(7 * n + 1) % vocab] for n in lens]
+        out = []
+        for e in (eng, plain_eng):
+            slots = [e.new_sequence() for _ in lens]
+            first = e.step(slots, prompts).float().cpu()
+            second = e.step(slots, nxt).float().cpu()
+            for s in slots:
+                e.release(s)
+            out.append((first, second))
+        assert eng._prompt_graphs, "the prompt step did not take a graph"
+        for a, b in zip(out[0], out[1]):
+            assert torch.isfinite(a).all()
+            assert helpers.max_rel_err(a, b) < G.tol_cut(dtype), lens
+
+
 def test_a_reused_slot_never_shows_what_it_held_before(model_dirs):
     """The same request on a fresh engine and on one whose slot and pages held other sequences."""
     import moe_b200
