@@ -15,7 +15,8 @@ from . import config as _config  # registers architectures
 from . import parts as _parts    # registers parts
 from .config import ConfigError, parse_config, read_config_json, register_architecture  # noqa: F401
 from .parts import Runtime, register_part  # noqa: F401
-from .weights import SafetensorsStore, TensorDictStore, WeightError, random_tensors, write_random_model  # noqa: F401
+from .weights import (RandomStore, SafetensorsStore, TensorDictStore, WeightError, random_tensors,  # noqa: F401
+                      write_random_model)
 
 __version__ = "0.1.0"
 
@@ -43,7 +44,8 @@ def load_model(model_dir: str, dtype="bfloat16", device="cuda"):
 
 def random_model(config: Union[Dict[str, Any], Any], seed: int = 0, dtype="bfloat16", device="cuda",
                  std: float = 0.02):
-    """A model with random weights drawn on ``device`` (no files written)."""
+    """A model with random weights drawn on ``device`` (no files written), part by part: at no
+    time is more held than the model itself and the tensors of the part being bound."""
     from .models import DecoderModel
 
     if isinstance(config, dict):
@@ -54,9 +56,7 @@ def random_model(config: Union[Dict[str, Any], Any], seed: int = 0, dtype="bfloa
         arch, typed = _config.lookup(_arch_of(config)), config
     spec = arch.model_spec(typed)
     dt = _dtype(dtype)
-    store = TensorDictStore(random_tensors(spec, seed, std, dt, device))
-    model = DecoderModel(spec, store, Runtime(device, dt), check=False)
-    store.tensors.clear()
+    model = DecoderModel(spec, RandomStore(spec, seed, std, dt, device), Runtime(device, dt), check=False)
     model.config = typed
     return model
 

@@ -47,7 +47,7 @@ def host_lib():
             "moe_ledger_new": ([I, I, _IP, _IP], P), "moe_ledger_delete": ([P], None), "moe_ledger_acquire": ([P], I),
             "moe_ledger_release": ([P, I], I), "moe_ledger_is_held": ([P, I], I), "moe_ledger_length": ([P, I], I),
             "moe_ledger_count": ([P, I, I], I), "moe_ledger_pages": ([P, I, I, _IP, I], I),
-            "moe_ledger_extend": ([P, I, I, _IP, I], I), "moe_ledger_truncate": ([P, I, I], I),
+            "moe_ledger_extend": ([P, I, I, _IP, I], I), "moe_ledger_truncate": ([P, I, I, _IP], I),
             "moe_ledger_tokens_held": ([P], LL),
             "moe_ledger_reserve": ([P, I, _IP, _IP, _IP, _IP, _IP, I, LL], I),
             "moe_pack_step": ([_IP, LL, I, _IP, _IP, _IP, _IP, _IP, _IP, _IP, _IP], LL),
@@ -263,10 +263,13 @@ class CacheLedger:
             raise CacheError("internal: more page-table updates than a step can make")
         return list(starts[:B]), upd[:n]
 
-    def truncate(self, slot: int, new_length: int) -> None:
+    def truncate(self, slot: int, new_length: int, windows: Sequence[int] = ()) -> None:
         """Forget everything at or after ``new_length`` (src/model.rs:176-189).  Pages are
-        kept; a ring group can only go back while the kept prefix is still inside it."""
-        _ok(_lib.moe_ledger_truncate(self._h, slot, new_length))
+        kept; a ring group that has wrapped can only go back while it still holds the keys that the
+        token at ``new_length`` looks back on (``windows``: each group's window, 0 for none; without
+        it any rewind of a wrapped ring is refused)."""
+        w = ints(list(windows))[0] if len(windows) else None
+        _ok(_lib.moe_ledger_truncate(self._h, slot, new_length, w))
 
     def tokens_held(self) -> int:
         """Tokens the live sequences hold, each rounded up to whole pages."""

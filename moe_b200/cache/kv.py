@@ -141,4 +141,9 @@ class KVCache:
         return self.ledger.length[slot]
 
     def truncate(self, slot: int, new_length: int) -> None:
-        self.ledger.truncate(slot, new_length)
+        """Forget the tokens of ``slot`` from ``new_length`` on.  Keys and values are simply written
+        over by what comes next; state of fixed size cannot be taken back, so a cache that holds any
+        refuses a rewind (a mixer that wants it has to keep snapshots of its own)."""
+        if self._states and new_length < self.length(slot):
+            raise CacheError("this model keeps per-sequence state of fixed size, which cannot be rewound")
+        self.ledger.truncate(slot, new_length, [g.window or 0 for g in self.groups])

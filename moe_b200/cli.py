@@ -4,13 +4,15 @@
     moe run   <model> --prompts FILE        one list of ids a line = one batch of unequal prompts
     moe bench <model> [--prompt-len N] [--tokens N] [--batch N]
     moe info  <model>
+    moe run|bench|info --random CONFIG.json [--seed N]     random weights instead of a folder
 
 Options keep the reference's names, meanings and defaults where it has them
 (``--ids``, ``-n/--tokens`` [128], ``--ctx``, ``--temp`` [0], ``--top-p`` [0.95],
 ``--top-k`` [0], ``--repeat-penalty`` [1.0], ``--seed`` [0], ``--prompts``,
 ``--no-stream``, ``--stats``, ``--prompt-len`` [32], bench ``--tokens`` [16]).
 Added here: ``--dtype bfloat16|float32`` [bfloat16], ``--batch N``,
-``--max-tokens N`` (cache size).  Prompts are token ids; there is no tokenizer.
+``--max-tokens N`` (cache size), ``--random CONFIG.json`` (with ``--seed``),
+``--peak-gbs F`` (bench: the bandwidth its roofline line is a percentage of).  Prompts are token ids; there is no tokenizer.
 Arguments are parsed as the reference does: ``--k v``, ``--k=v``, short aliases
 ``-n -o -h -V``, and a fixed list of boolean flags.
 """
@@ -29,7 +31,7 @@ USAGE
   moe info  <model>                  show the architecture and its footprint
   moe bench <model> [options]        measure prefill and decode throughput
 
-<model> is a folder with config.json and *.safetensors.
+<model> is a folder with config.json and *.safetensors (or give --random CONFIG.json).
 
 RUN OPTIONS
       --ids 1,2,3           prompt as token ids
@@ -52,7 +54,11 @@ BENCH OPTIONS
       --tokens N            decode steps to time          [16]
       --batch N             sequences decoded together    [1]
 
+      --peak-gbs F          memory bandwidth the roofline line is a percentage of   [7700]
+
 GLOBAL
+      --random CONFIG.json  instead of <model>: random weights of this configuration, drawn on
+                            the GPU from --seed (the sampler's seed and the weights' are one option)
       --dtype NAME          bfloat16 | float32            [bfloat16]
       --max-tokens N        tokens the cache can hold     [what the run needs]
   -h, --help                this message
@@ -123,56 +129,86 @@ def human(n: int) -> str:
     return f"{n} B" if i == 0 else f"{v:.2f} {units[i]}"
 
 
-def _load(path: str, opt):
+def _load(path: str, opt, device="cuda"):
+    """The model of the command: a folder, or with ``--random CONFIG.json`` random weights of that
+    configuration drawn on the device from ``--seed`` (nothing is written)."""
     import moe_b200
 
+    dtype = opt.get("dtype", "bfloat16")
     try:
-        return moe_b200.load_model(path, dtype=opt.get("dtype", "bfloat16"))
+        if "random" in opt:
+            with open(opt["random"], encoding="utf-8") as f:
+                cfg = json.load(f)
+            return moe_b200.random_model(cfg, seed=_num(opt, "seed", 0, int), dtype=dtype, device=device)
+        return moe_b200.load_model(path, dtype=dtype, device=device)
     except (moe_b200.ConfigError, moe_b200.WeightError, ValueError, OSError) as e:
         fail(e)
 
 
+def _grouped(descriptions: List[str], total: int, what: str) -> List[str]:
+    """Equal descriptions once, with the number of parts that have them."""
+    seen: Dict[str, int] = {}
+    for d in descriptions:
+        seen[d] = seen.get(d, 0) + 1
+    return [f"  {what:<10} {d}" + ("" if n == total else f"   ({n} of {total})") for d, n in seen.items()]
+
+
 def summary(model) -> str:
-    """The reference's ``Spec::summary`` (src/spec.rs:341-376), from the model's parts."""
+    """The reference's ``Spec::summary`` (src/spec.rs:341-376): what the model is made of, in the
+    words of its own parts (``Part.describe``); nothing here knows a kind of part."""
     spec = model.spec
-    mixers = [b.mixer for b in model.blocks]
-    m0 = mixers[0]
-    lines = [spec.architecture, f"  layers {len(spec.layers)}  hidden {spec.hidden_size}  vocab {spec.vocab_size}"]
-    lines.append(f"  attention  GQA({m0.nh} q / {m0.nkv} kv heads, head_dim={m0.hd})")
-    pos = m0.position
-    lines.append(f"  rope       theta {getattr(pos, 'theta', 0):.0f}")
-    wins = [m.window for m in mixers]
-    local = [w for w in wins if w]
-    if local:
-        where = "every layer" if len(local) == len(wins) else f"{len(local)} of {len(wins)} layers"
-        lines.append(f"  window     {max(local)} on {where}")
-    ffns = [b.ffn for b in model.blocks]
-    routed = [f for f in ffns if f.kind == "routed_experts"]
-    if routed:
-        f = routed[0]
-        lines.append(f"  ffn        {f.E} experts, top-{f.k}, softmax gate"
-                     + (f", shared expert {f.shared_size}" if f.shared_size else "")
-                     + (f", {len(ffns) - len(routed)} dense layers" if len(routed) != len(ffns) else ""))
-    else:
-        lines.append("  ffn        dense")
+    n = len(model.blocks)
+    lines = [spec.architecture, f"  layers {n}  hidden {spec.hidden_size}  vocab {spec.vocab_size}"]
+    if len(spec.schedule) != n or any(e.layer != i for i, e in enumerate(spec.schedule)):
+        lines.append("  schedule   " + " ".join(
+            f"{e.layer}" + ("" if e.writes_cache and e.cache == e.layer else f"[cache {e.cache}{'' if e.writes_cache else ', read'}]")
+            for e in spec.schedule))
+    by_category: Dict[str, List[str]] = {}
+    for b in model.blocks:
+        for part in b.parts():
+            by_category.setdefault(part.category, []).append(part.describe())
+    for category, found in by_category.items():
+        lines += _grouped(found, len(found), category)
+    lines.append(f"  {'output':<10} {model.head.describe()}")
     return "\n".join(lines)
 
 
+def step_bytes(model, live_lengths: List[int]) -> Tuple[float, float]:
+    """Bytes that a step of one token for each of the live sequences has to read: every weight it
+    uses once (``Part.step_elements``; a layer that the schedule runs twice is read twice), and
+    the keys and values of the live sequences (a window bounds them).  -> (weights, cache)"""
+    esize = 2 if model.rt.is_bf16 else 4
+    B = len(live_lengths)
+    weights = model.embedding.step_elements(B) + model.final_norm.step_elements(B) + model.head.step_elements(B)
+    cache = 0.0
+    for e in model.spec.schedule:
+        blk = model.blocks[e.layer]
+        weights += sum(p.step_elements(B) for p in blk.parts())
+        req = blk.mixer.kv_request()
+        if req is not None:
+            per_pos = 2 * req.num_kv_heads * req.head_dim * esize
+            cache += per_pos * sum(min(n, req.window) if req.window else n for n in live_lengths)
+    return weights * esize, cache
+
+
 def cmd_info(path: str, opt) -> None:
-    model = _load(path, opt)
+    model = _load(path, opt, device="cpu")
     from .models.decoder import expected_tensors
 
     exp = expected_tensors(model.spec)
     esize = 2 if model.rt.is_bf16 else 4
     total = sum(_numel(t.shape) for t in exp.values()) * esize
-    experts = sum(_numel(t.shape) for n, t in exp.items() if ".mlp.experts." in n) * esize
+    experts = sum(_numel(t.shape) for t in exp.values() if t.sparse) * esize
     print(summary(model))
     print(f"\nweights    {len(exp)} tensors, {human(total)}")
     print(f"  dense    {human(total - experts)}")
     print(f"  experts  {human(experts)} ({100.0 * experts / max(total, 1):.0f}%)")
     kv = sum(2 * r.num_kv_heads * r.head_dim for r in model.kv_requests().values() if r) * esize * 1024
     print(f"kv cache   {human(kv)} per 1k tokens")
-    print(f"source     {path} (safetensors)")
+    state = sum(_numel(r.shape) * 4 for r in model.state_requests().values() if r)
+    if state:
+        print(f"state      {human(state)} per sequence")
+    print(f"source     {'random weights of ' + opt['random'] if 'random' in opt else path + ' (safetensors)'}")
 
 
 def _numel(shape) -> int:
@@ -271,6 +307,12 @@ def cmd_bench(path: str, opt) -> None:
     print(f"\nprefill  {plen * B} tok in {pf:.3f}s   {plen * B / max(pf, 1e-9):.1f} tok/s")
     print(f"decode   {n * B} tok in {dc:.3f}s   {n * B / max(dc, 1e-9):.2f} tok/s   {1000.0 * dc / max(n, 1):.2f} ms/step")
     print(f"batch    {B}   dtype {opt.get('dtype', 'bfloat16')}   kv cache {human(engine.cache.bytes())}")
+    # what a decode step has to read, against the memory bandwidth given (B200 HBM3e nominal by default)
+    wb, cb = step_bytes(model, [plen + n // 2] * B)
+    peak = _num(opt, "peak-gbs", 7700.0, float)
+    gbs = (wb + cb) / max(dc / max(n, 1), 1e-12) / 1e9
+    print(f"roofline {human(int(wb))} weights + {human(int(cb))} cache a step   {gbs:.0f} GB/s   "
+          f"{100.0 * gbs / peak:.1f}% of {peak:.0f} GB/s")
 
 
 def main(argv=None) -> int:
@@ -285,7 +327,7 @@ def main(argv=None) -> int:
         return 0
     if cmd not in ("run", "info", "bench"):
         fail(f"unknown command '{cmd}' (try --help)")
-    if not pos:
-        fail(f"{cmd}: name a model folder")
-    {"run": cmd_run, "info": cmd_info, "bench": cmd_bench}[cmd](pos[0], opt)
+    if not pos and "random" not in opt:
+        fail(f"{cmd}: name a model folder (or --random CONFIG.json)")
+    {"run": cmd_run, "info": cmd_info, "bench": cmd_bench}[cmd](pos[0] if pos else "", opt)
     return 0

@@ -536,7 +536,11 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, f
     dim3 grid(nsplit, nkv, num_tokens);
     const int group = nh / nkv;
     const int row_bytes = hd * (int)sizeof(T);
-    const bool fast = page_size % 32 == 0 && (ring % 32 == 0) &&
+    // the fast kernel reads q 16 bytes at a time: a q that is not 16-byte aligned (a view into the
+    // middle of a buffer) takes the row-per-lane kernel, which reads it element by element.  Both
+    // kernels read cache rows 16 bytes at a time; the entry points refuse a cache that is not aligned so.
+    const bool aligned = ((uintptr_t)q % 16) == 0;
+    const bool fast = aligned && page_size % 32 == 0 && (ring % 32 == 0) &&
                       (row_bytes == 64 || row_bytes == 128 || row_bytes == 256 || row_bytes == 512);
     if (fused && !fast) return -1;
     const FusedArgs fa = fused ? *fused : FusedArgs{};
@@ -568,9 +572,9 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, f
         }
     } else {
         const size_t smem = ((size_t)GHS * hd + (size_t)WARPS * GHS * (hd + 2)) * sizeof(float);
-        launch_pdl(attn_decode_rows_kernel<T>, grid, WARPS * 32, smem, stream, (const T*)q, (const T*)k_cache,
-                   (const T*)v_cache, partial, seq_of_token, pos, slots, tables, table_stride, ring, page_size,
-                   num_pages, nh, nkv, hd, window, scale, status);
+        rc = launch_pdl(attn_decode_rows_kernel<T>, grid, WARPS * 32, smem, stream, (const T*)q, (const T*)k_cache,
+                        (const T*)v_cache, partial, seq_of_token, pos, slots, tables, table_stride, ring, page_size,
+                        num_pages, nh, nkv, hd, window, scale, status);
     }
 #undef FAST
 #undef FAST_G
@@ -617,8 +621,11 @@ MOE_API int moe_attention_decode(const void* q, const void* k_cache, const void*
                                  int num_tokens, int nh, int nkv, int hd, int window, float scale, int nsplit,
                                  int* status, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
-    if (hd % 16 != 0 || hd > MAX_HD || hd <= 0 || nkv <= 0 || nh % nkv != 0 || nsplit < 1 || nsplit > 65535 ||
-        nkv > 65535 || num_tokens > 65535)
+    if (hd % 16 != 0 || hd > MAX_HD || hd <= 0 || nkv <= 0 || nh <= 0 || nh > 65535 || nh % nkv != 0 || nsplit < 1 ||
+        nsplit > 65535 || nkv > 65535 || num_tokens > 65535 || !q || !k_cache || !v_cache || !out || !partial)
+        return (int)cudaErrorInvalidValue;
+    // cache rows are read 16 bytes at a time; q and out at least by whole elements
+    if (((uintptr_t)k_cache | (uintptr_t)v_cache) % 16 || ((uintptr_t)q | (uintptr_t)out) % (dt == DT_F32 ? 4 : 2))
         return (int)cudaErrorInvalidValue;
     if (dt == DT_F32)
         return launch<float>(q, k_cache, v_cache, out, partial, seq_of_token, pos, slots, tables, table_stride, ring,
@@ -662,7 +669,17 @@ float* noalloc_scratch() {
 }  // namespace
 
 MOE_API long long moe_attention_decode_noalloc_need(int num_tokens, int num_heads, int head_dim, int nsplit) {
-    return (long long)num_tokens * num_heads * nsplit * (head_dim + 2);
+    // each factor is bounded (65535, 65535, 65535, MAX_HD + 2) only by the entry point's own checks, so the
+    // product is formed step by step and reported as "too many" (-1) once it leaves what the array could hold
+    if (num_tokens <= 0 || num_heads <= 0 || head_dim <= 0 || nsplit <= 0) return -1;
+    const long long cap = (long long)MOE_NOALLOC_SCRATCH_FLOATS * 4;
+    long long n = num_tokens;
+    n *= num_heads;
+    if (n > cap) return -1;
+    n *= nsplit;
+    if (n > cap) return -1;
+    n *= (long long)head_dim + 2;
+    return n;
 }
 
 MOE_API const char* moe_noalloc_strerror(int code) {
@@ -683,12 +700,19 @@ MOE_API int moe_attention_decode_noalloc(const void* q, const void* k_cache, con
                                          int num_tokens, int num_heads, int num_kv_heads, int head_dim, int window,
                                          float scale, int nsplit, int* status, cudaStream_t stream) {
     if (num_tokens <= 0) return MOE_NOALLOC_OK;
-    if (head_dim % 16 != 0 || head_dim > MAX_HD || head_dim <= 0 || num_kv_heads <= 0 ||
-        num_heads % num_kv_heads != 0 || nsplit < 1 || nsplit > 65535 || num_kv_heads > 65535 || num_tokens > 65535 ||
-        (dt != DT_F32 && dt != DT_BF16))
+    if (head_dim % 16 != 0 || head_dim > MAX_HD || head_dim <= 0 || num_kv_heads <= 0 || num_heads <= 0 ||
+        num_heads > 65535 || num_heads % num_kv_heads != 0 || nsplit < 1 || nsplit > 65535 || num_kv_heads > 65535 ||
+        num_tokens > 65535 || (dt != DT_F32 && dt != DT_BF16))
         return MOE_NOALLOC_BAD_ARGUMENT;
-    if (moe_attention_decode_noalloc_need(num_tokens, num_heads, head_dim, nsplit) > MOE_NOALLOC_SCRATCH_FLOATS)
-        return MOE_NOALLOC_TOO_LARGE;
+    const long long need = moe_attention_decode_noalloc_need(num_tokens, num_heads, head_dim, nsplit);
+    if (need < 0 || need > MOE_NOALLOC_SCRATCH_FLOATS) return MOE_NOALLOC_TOO_LARGE;
+    // Missing or misaligned memory is refused here, on the host, so that it never reaches the device: the
+    // cache is read 16 bytes at a time by every kernel; q and out must at least be aligned to their
+    // elements (a q that is not 16-byte aligned is served by the slower kernel that reads it element by
+    // element).
+    if (!q || !k_cache || !v_cache || !out || !seq_of_token || !pos || !slots || !tables) return MOE_NOALLOC_BAD_ARGUMENT;
+    if (((uintptr_t)k_cache | (uintptr_t)v_cache) % 16 || ((uintptr_t)q | (uintptr_t)out) % (dt == DT_F32 ? 4 : 2))
+        return MOE_NOALLOC_BAD_ARGUMENT;
     float* scratch = noalloc_scratch();
     if (!scratch) return MOE_NOALLOC_NO_DEVICE;
     if (dt == DT_F32)

@@ -19,8 +19,15 @@
 //     more is refused with MOE_NOALLOC_TOO_LARGE and launches nothing; moe_noalloc_strerror
 //     gives the message.
 //   * The first call on a device looks up the device address of the array (one
-//     cudaGetSymbolAddress with that device current; no allocation).  Make that first call
-//     before any stream capture begins on the device.
+//     cudaGetSymbolAddress with that device current).  The CUDA runtime may load this
+//     library's device code lazily: that first lookup, and the first launch of each kernel
+//     variant (one per element type, head size and "more than one query head per kv head"),
+//     can make the driver place code and this array in device memory and synchronise.  So
+//     warm up: make one call per variant you will use, on each device, before the region in
+//     which nothing may be allocated and before any stream capture begins on the device.
+//   * k_cache and v_cache must be 16-byte aligned; q and out aligned to their element type.
+//     Anything else, zero or negative head counts included, is refused with
+//     MOE_NOALLOC_BAD_ARGUMENT before anything is launched.
 //   * No cudaMalloc, cudaFree or other allocating routine is called, by this library or through it.
 //   * All calls on a device share the one array, and it keeps whatever the previous call left.
 //     The kernels write every record they later read, so nothing has to be cleared between

@@ -253,17 +253,26 @@ MOE_API int moe_ledger_extend(void* p, int slot, int new_length, int* updates, i
     return L.grow(slot, new_length, updates, cap, 0);
 }
 
-// Forget everything at or after new_length (src/model.rs:176-189).  Pages are kept; a ring that
-// has wrapped cannot be rewound.
-MOE_API int moe_ledger_truncate(void* p, int slot, int new_length) {
+// Forget everything at or after new_length (src/model.rs:176-189).  Pages are kept.  A ring holds
+// the last `ring` positions only: once it has wrapped, a rewind is possible only while the keys that
+// the token at new_length will look back on, [new_length + 1 - window, new_length), are still in it.
+// windows[g]: the window of group g (0 or a null array: unknown, any rewind of a wrapped ring is refused).
+MOE_API int moe_ledger_truncate(void* p, int slot, int new_length, const int* windows) {
     Ledger& L = *static_cast<Ledger*>(p);
     if (!L.slots.is_held(slot)) return fail(ERR_CACHE, "slot " + std::to_string(slot) + " is not held");
     const int cur = L.length[slot];
     if (new_length > cur) return fail(ERR_CACHE, "truncate cannot lengthen a sequence");
     if (new_length < 0) return fail(ERR_VALUE, "negative length");
-    for (const auto& g : L.groups)
-        if (g.ring_pages && new_length < cur && cur > g.ring_pages * PAGE_TOKENS)
-            return fail(ERR_CACHE, "a windowed cache that has wrapped cannot be rewound");
+    for (size_t gi = 0; gi < L.groups.size(); gi++) {
+        const auto& g = L.groups[gi];
+        const int ring = g.ring_pages * PAGE_TOKENS;
+        if (!g.ring_pages || new_length == cur || cur <= ring) continue;
+        const int w = windows ? windows[gi] : 0;
+        const int oldest_needed = w > 0 ? std::max(0, new_length + 1 - w) : 0;
+        if (w <= 0 || oldest_needed < cur - ring)
+            return fail(ERR_CACHE, "a windowed cache no longer holds the keys before position " +
+                                       std::to_string(new_length) + ": it cannot be rewound that far");
+    }
     L.length[slot] = new_length;
     return 0;
 }

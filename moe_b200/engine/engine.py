@@ -15,6 +15,7 @@ get no expert and change no result.
 """
 from __future__ import annotations
 
+from collections import OrderedDict
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -23,7 +24,7 @@ import torch
 import ctypes
 import os
 
-from ..cache.allocator import _IP, CacheError, _ok, host_lib, ints
+from ..cache.allocator import _IP, PAGE_TOKENS, CacheError, _ok, host_lib, ints
 from ..cache.kv import KVCache
 from ..models.decoder import DecoderModel
 from ..ops import core
@@ -34,11 +35,101 @@ GRAPH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 # from graphs, padded to these numbers of token rows and of sequences.
 PROMPT_TOKEN_BUCKETS = (64, 128, 256, 512)
 PROMPT_SEQ_BUCKETS = (1, 2, 4, 8)
+MAX_GRAPHS = 48      # captured steps an engine keeps; the one used longest ago goes first
 LAST_TOKEN = -1      # as a token id (with ``from_last``): the token sampled last for the sequence
 
 
-class _DecodeGraph:
-    """Static buffers and the captured graph of one batch-size bucket."""
+class _StepGraph:
+    """Static buffers and the captured graph of one padded shape of step.
+
+    The first use runs the shape once with NO live sequence (every row a padding row: lazy builds,
+    kernel attributes and workspaces happen outside the capture, and nothing that belongs to a
+    sequence is touched), then captures, then replays: the step itself runs exactly once, so a part
+    with state of its own is advanced once.  All graphs of an engine share one memory pool; they
+    never run at the same time and keep nothing between replays but their logits."""
+
+    batch: StepBatch
+    upd_off: List[int]
+    upd_rows: int
+
+    def _buffers(self, engine: "Engine", words: int) -> None:
+        self.host = torch.zeros(words, dtype=torch.int32).pin_memory()
+        self.dev = torch.zeros(words, dtype=torch.int32, device=engine.rt.device)
+        self.event = torch.cuda.Event()
+        self.busy = False
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+        self.traced: List[Tuple[object, list]] = []
+        self.launches = 0
+
+    def _wait_host(self) -> None:
+        if self.busy:
+            self.event.synchronize()
+            self.busy = False
+
+    def _send(self) -> None:
+        self.dev.copy_(self.host, non_blocking=True)
+        self.event.record()
+        self.busy = True
+
+    def _pack(self, engine: "Engine", *step) -> None:
+        raise NotImplementedError
+
+    def fill(self, engine: "Engine", *step) -> None:
+        """Pack the step into the pinned buffer (host runtime) and start its copy; capture first if new."""
+        if self.graph is None:
+            self._capture(engine)
+        self._wait_host()
+        self._pack(engine, *step)
+        self._send()
+
+    def _body(self, engine: "Engine"):
+        for gi, o in enumerate(self.upd_off):
+            core.table_update(engine.cache.groups[gi].table, self.dev[o:o + 3 * self.upd_rows], self.upd_rows)
+        return engine.model.forward(self.batch, engine.cache)
+
+    def _capture(self, engine: "Engine") -> None:
+        tracing = [p for p in engine._tracers if getattr(p, "trace", None) is not None]
+        kept = [p.trace for p in tracing]
+        for p in tracing:
+            p.trace = None                      # the run below is nobody's step: it leaves no record
+        self._wait_host()
+        self._pack_empty(engine)
+        self._send()
+        try:
+            self._body(engine)                  # every row belongs to no sequence
+            torch.cuda.synchronize()
+        except BaseException:
+            for p, t in zip(tracing, kept):
+                p.trace = t
+            raise
+        for p in tracing:
+            p.trace = []
+        g = torch.cuda.CUDAGraph()
+        l0 = core.launches
+        try:
+            with torch.cuda.graph(g, pool=engine._graph_pool):
+                self.logits = self._body(engine)
+        finally:
+            # what the parts recorded during the capture are buffers that every replay fills again
+            self.traced = [(p, p.trace) for p in tracing]
+            for p, t in zip(tracing, kept):
+                p.trace = t
+        self.launches = core.launches - l0
+        self.graph = g
+
+    def run(self, engine: "Engine") -> torch.Tensor:
+        core.launches += self.launches
+        self.graph.replay()
+        for p, items in self.traced:
+            if p.trace is not None:
+                p.trace.extend(item.clone() if isinstance(item, torch.Tensor) else tuple(t.clone() for t in item)
+                               for item in items)
+        return self.logits
+
+
+class _DecodeGraph(_StepGraph):
+    """One token per sequence, padded to ``size`` sequences."""
 
     def __init__(self, engine: "Engine", size: int, max_end: int = 0):
         self.size = size
@@ -48,28 +139,18 @@ class _DecodeGraph:
             offs[name] = (o, n)
             o += n
         self.upd_off = []
+        self.upd_rows = size
         for _ in range(ngroups):
             self.upd_off.append(o)
             o += 3 * size
-        self.used = o
-        self.offsets = offs
         self._upd_off_c, _ = ints(self.upd_off)
-        self.host = torch.zeros(o, dtype=torch.int32).pin_memory()
-        self.dev = torch.zeros(o, dtype=torch.int32, device=engine.rt.device)
+        self._buffers(engine, o)
         views = {k: self.dev[a:a + n] for k, (a, n) in offs.items()}
         # max_end: the longest sequence this graph will see (kernels size their grids by it)
         self.batch = StepBatch(**views, num_tokens=size, num_seqs=size, num_want=size, max_new=1, max_end=max_end,
                                all_decode=True, all_fresh=False, last_token=engine.cache.last_token)
-        self.event = torch.cuda.Event()
-        self.busy = False
-        self.graph: Optional[torch.cuda.CUDAGraph] = None
-        self.logits: Optional[torch.Tensor] = None
 
-    def fill(self, engine: "Engine", slots, starts, tokens, updates: np.ndarray) -> None:
-        """Pack the step into the pinned buffer (``moe_pack_decode`` of the host runtime) and start its copy."""
-        if self.busy:
-            self.event.synchronize()
-            self.busy = False
+    def _pack(self, engine: "Engine", slots, starts, tokens, updates: np.ndarray) -> None:
         sl, B = ints(slots)
         st, _ = ints(starts)
         tk, _ = ints(tokens)
@@ -77,38 +158,14 @@ class _DecodeGraph:
         _ok(host_lib().moe_pack_decode(ctypes.cast(self.host.data_ptr(), _IP), self.size, B, sl, st, tk,
                                        engine.cache.padding_slot, len(self.upd_off), self._upd_off_c,
                                        upd.ctypes.data_as(_IP), int(upd.shape[0])))
-        self.dev.copy_(self.host, non_blocking=True)
-        self.event.record()
-        self.busy = True
 
-    def run(self, engine: "Engine") -> torch.Tensor:
-        S = self.size
-
-        def body():
-            for gi, o in enumerate(self.upd_off):
-                core.table_update(engine.cache.groups[gi].table, self.dev[o:o + 3 * S], S)
-            return engine.model.forward(self.batch, engine.cache)
-
-        if self.graph is None:
-            # one eager run first: lazy builds, kernel attributes and workspaces happen outside the
-            # capture (running the step twice is harmless: it writes the same keys to the same places)
-            body()
-            torch.cuda.synchronize()
-            g = torch.cuda.CUDAGraph()
-            l0 = core.launches
-            with torch.cuda.graph(g):
-                self.logits = body()
-            self.launches = core.launches - l0
-            self.graph = g
-        else:
-            core.launches += self.launches
-        self.graph.replay()
-        return self.logits
+    def _pack_empty(self, engine: "Engine") -> None:
+        self._pack(engine, [], [], [], np.zeros((0, 4), dtype=np.int32))
 
 
-class _PromptGraph:
-    """Static buffers and the captured graph of a step of whole prompts (every sequence from
-    position 0, the logits of each last token), padded to ``tokens`` rows and ``seqs`` sequences."""
+class _PromptGraph(_StepGraph):
+    """A step of whole prompts (every sequence from position 0, the logits of each last token),
+    padded to ``tokens`` rows and ``seqs`` sequences."""
 
     def __init__(self, engine: "Engine", tokens: int, seqs: int):
         self.tokens, self.seqs = tokens, seqs
@@ -117,57 +174,28 @@ class _PromptGraph:
         for name, n in layout(tokens, seqs, seqs):
             offs[name] = (o, n)
             o += n
-        self.upd_cap = -(-tokens // 64) + seqs          # most pages a group can hand out in such a step
+        self.upd_rows = -(-tokens // PAGE_TOKENS) + seqs          # most pages a group can hand out in such a step
         self.upd_off = []
         for _ in range(ngroups):
             self.upd_off.append(o)
-            o += 3 * self.upd_cap
+            o += 3 * self.upd_rows
         self._upd_off_c, _ = ints(self.upd_off)
-        self.host = torch.zeros(o, dtype=torch.int32).pin_memory()
-        self.dev = torch.zeros(o, dtype=torch.int32, device=engine.rt.device)
+        self._buffers(engine, o)
         views = {k: self.dev[a:a + n] for k, (a, n) in offs.items()}
         self.batch = StepBatch(**views, num_tokens=tokens, num_seqs=seqs, num_want=seqs, max_new=tokens,
                                max_end=tokens, all_decode=False, all_fresh=True, has_padding=True)
-        self.event = torch.cuda.Event()
-        self.busy = False
-        self.graph: Optional[torch.cuda.CUDAGraph] = None
-        self.logits: Optional[torch.Tensor] = None
 
-    def fill(self, engine: "Engine", slots, counts, tokens, updates: np.ndarray) -> None:
-        """Pack the step (``moe_pack_prompt`` of the host runtime) and start its copy."""
-        if self.busy:
-            self.event.synchronize()
-            self.busy = False
+    def _pack(self, engine: "Engine", slots, counts, tokens, updates: np.ndarray) -> None:
         sl, B = ints(slots)
         ct, _ = ints(counts)
         flat = np.fromiter((x for t in tokens for x in t), dtype=np.int32, count=sum(counts))
         upd = np.ascontiguousarray(updates, dtype=np.int32)
         _ok(host_lib().moe_pack_prompt(ctypes.cast(self.host.data_ptr(), _IP), self.tokens, self.seqs, B, sl, ct,
                                        flat.ctypes.data_as(_IP), engine.cache.padding_slot, len(self.upd_off),
-                                       self._upd_off_c, self.upd_cap, upd.ctypes.data_as(_IP), int(upd.shape[0])))
-        self.dev.copy_(self.host, non_blocking=True)
-        self.event.record()
-        self.busy = True
+                                       self._upd_off_c, self.upd_rows, upd.ctypes.data_as(_IP), int(upd.shape[0])))
 
-    def run(self, engine: "Engine") -> torch.Tensor:
-        def body():
-            for gi, o in enumerate(self.upd_off):
-                core.table_update(engine.cache.groups[gi].table, self.dev[o:o + 3 * self.upd_cap], self.upd_cap)
-            return engine.model.forward(self.batch, engine.cache)
-
-        if self.graph is None:
-            body()      # lazy builds and workspaces outside the capture; the step may run twice (same keys, same places)
-            torch.cuda.synchronize()
-            g = torch.cuda.CUDAGraph()
-            l0 = core.launches
-            with torch.cuda.graph(g):
-                self.logits = body()
-            self.launches = core.launches - l0
-            self.graph = g
-        else:
-            core.launches += self.launches
-        self.graph.replay()
-        return self.logits
+    def _pack_empty(self, engine: "Engine") -> None:
+        self._pack(engine, [], [], [], np.zeros((0, 4), dtype=np.int32))
 
 
 class Engine:
@@ -191,10 +219,12 @@ class Engine:
         parts = [p for b in model.blocks for p in b.parts()] + [model.embedding, model.final_norm, model.head]
         graph_safe = all(getattr(p, "graph_safe", False) for p in parts)
         self.use_graphs = graph_safe if use_graphs is None else (use_graphs and graph_safe)
-        self._routed = [p for p in parts if hasattr(p, "trace")]
+        # any part may record what it decided, per call, as tuples of tensors appended to its
+        # ``trace`` list (``Part.trace``, None when off)
+        self._tracers = list({id(p): p for p in parts}.values())
         self.prompt_graphs = os.environ.get("MOE_B200_PROMPT_GRAPHS", "1") != "0"
-        self._graphs: Dict[Tuple[int, int], _DecodeGraph] = {}
-        self._prompt_graphs: Dict[Tuple[int, int], _PromptGraph] = {}
+        self._graphs: "OrderedDict[tuple, _StepGraph]" = OrderedDict()
+        self._graph_pool = torch.cuda.graph_pool_handle() if self.use_graphs else None
         self._table_caps = [0 if g.ring_pages else g.max_pages_per_seq for g in self.cache.groups]
         self._results: List[Tuple[torch.Tensor, torch.cuda.Event]] = []     # pinned buffers for sampled tokens
 
@@ -225,6 +255,28 @@ class Engine:
         sequence's length before the step and the page-table entries that changed, [n, 4] of
         (group, slot, index, page).  (``moe_ledger_reserve`` of the host runtime.)"""
         return self.cache.ledger.reserve(slots, counts, self._table_caps, self.cache.max_tokens)
+
+    def _graph(self, key: tuple, make) -> _StepGraph:
+        """The captured step of this shape; the least recently used one is dropped beyond MAX_GRAPHS."""
+        g = self._graphs.get(key)
+        if g is None:
+            while len(self._graphs) >= MAX_GRAPHS:
+                self._graphs.popitem(last=False)
+            g = self._graphs[key] = make()
+        else:
+            self._graphs.move_to_end(key)
+        return g
+
+    def graphs_of(self, kind: str) -> List[tuple]:
+        """Keys of the captured steps of one kind ("decode" or "prompt")."""
+        return [k for k in self._graphs if k[0] == kind]
+
+    def truncate(self, slot: int, new_length: int) -> None:
+        """Forget the sequence's tokens from ``new_length`` on (src/model.rs:176-189): the next step
+        continues at that position.  Refused, changing nothing, where what was forgotten cannot be
+        brought back: a windowed layer whose ring no longer holds the keys the next token needs, or a
+        layer with state of fixed size."""
+        self.cache.truncate(slot, new_length)
 
     def _bucket(self, B: int) -> Optional[int]:
         for b in GRAPH_BUCKETS:
@@ -263,16 +315,14 @@ class Engine:
         self.steps_run += 1
 
         # ---- one token each: replay the bucket's graph -----------------------------------
+        tracing = any(getattr(p, "trace", None) is not None for p in self._tracers)
         if (self.use_graphs and all(n == 1 for n in counts) and all(len(w) == 1 for w in want)
-                and not any(p.trace is not None for p in self._routed)
                 and (from_last or min(t[0] for t in tokens) >= 0)):
             size = self._bucket(B)
             if size is not None:
                 # one graph per (batch bucket, bucket of the longest sequence: powers of two from 256)
                 reach = max(256, 1 << max(starts).bit_length())
-                g = self._graphs.get((size, reach))
-                if g is None:
-                    g = self._graphs[(size, reach)] = _DecodeGraph(self, size, reach)
+                g = self._graph(("decode", size, reach, tracing), lambda: _DecodeGraph(self, size, reach))
                 g.fill(self, slots, starts, [t[0] for t in tokens], updates)
                 logits = g.run(self)
                 self.last_batch = g.batch
@@ -285,13 +335,10 @@ class Engine:
         T = sum(counts)
         if (self.use_graphs and self.prompt_graphs and T <= PROMPT_TOKEN_BUCKETS[-1] and B <= PROMPT_SEQ_BUCKETS[-1]
                 and not any(starts) and all(len(w) == 1 and w[0] == n - 1 for w, n in zip(want, counts))
-                and not from_last
-                and not any(p.trace is not None for p in self._routed)):
+                and not from_last):
             tb = next(b for b in PROMPT_TOKEN_BUCKETS if b >= T)
             sb = next(b for b in PROMPT_SEQ_BUCKETS if b >= B)
-            g = self._prompt_graphs.get((tb, sb))
-            if g is None:
-                g = self._prompt_graphs[(tb, sb)] = _PromptGraph(self, tb, sb)
+            g = self._graph(("prompt", tb, sb, tracing), lambda: _PromptGraph(self, tb, sb))
             g.fill(self, slots, counts, tokens, updates)
             logits = g.run(self)
             self.last_batch = g.batch

@@ -5,6 +5,7 @@ Nothing here names an architecture; the spec says which parts each layer has.
 """
 from __future__ import annotations
 
+from collections.abc import Mapping
 from typing import Dict, List, Optional
 
 import torch
@@ -25,15 +26,48 @@ def _named_parts(spec: ModelSpec):
     return emb, blocks, final_norm, head
 
 
-def expected_tensors(spec: ModelSpec) -> Dict[str, TensorSpec]:
-    """Checkpoint name -> shape of every tensor the model needs."""
+class PartTensors(Mapping):
+    """The tensors of one part, by local name, fetched from the store when they are asked for and
+    not kept: a part that re-lays its weights out (one slab for all experts, say) holds a tensor of
+    the store only while it copies it.  ``pop`` is a fetch too."""
+
+    def __init__(self, store: WeightStore, prefix: str, names, dtype, device):
+        self._store, self._prefix, self._names = store, prefix, list(names)
+        self._dtype, self._device = dtype, device
+
+    def __getitem__(self, local):
+        if local not in self._names:
+            raise KeyError(local)
+        return self._store.get(self._prefix + local, self._dtype, self._device)
+
+    def pop(self, local, *default):
+        if local not in self._names and default:
+            return default[0]
+        return self[local]
+
+    def __iter__(self):
+        return iter(self._names)
+
+    def __len__(self):
+        return len(self._names)
+
+
+def _tensors_of(part: Part, store: Optional[WeightStore]) -> Dict[str, TensorSpec]:
+    if store is None:
+        return part.tensors()
+    return part.tensors_in(lambda local: store.has(part.spec.prefix + local))
+
+
+def expected_tensors(spec: ModelSpec, store: Optional[WeightStore] = None) -> Dict[str, TensorSpec]:
+    """Checkpoint name -> shape of every tensor the model needs; with a ``store``, in the layout
+    that each part finds there (a part may take several, ``Part.tensors_in``)."""
     emb, blocks, final_norm, head = _named_parts(spec)
     out: Dict[str, TensorSpec] = {}
     parts: List[Part] = [emb, final_norm, head]
     for b in blocks:
         parts.extend(b.parts())
     for p in parts:
-        for local, ts in p.tensors().items():
+        for local, ts in _tensors_of(p, store).items():
             out[p.spec.prefix + local] = ts
     return out
 
@@ -44,15 +78,12 @@ class DecoderModel:
         self.rt = rt
         self.embedding, self.blocks, self.final_norm, self.head = _named_parts(spec)
         if check:
-            store.check({n: ts.shape for n, ts in expected_tensors(spec).items()}, spec.ignorable)
+            store.check({n: ts.shape for n, ts in expected_tensors(spec, store).items()}, spec.ignorable)
         self._validate_schedule()
 
         def bind(part: Part, **kw):
-            tensors = {
-                local: store.get(part.spec.prefix + local, rt.compute_dtype, rt.device)
-                for local in part.tensors()
-            }
-            part.bind(tensors, rt, **kw)
+            part.bind(PartTensors(store, part.spec.prefix, _tensors_of(part, store), rt.compute_dtype, rt.device),
+                      rt, **kw)
 
         bind(self.embedding)
         for b in self.blocks:

@@ -64,6 +64,15 @@ class GQAttention(Part):
     def kv_request(self):
         return KVRequest(self.nkv, self.hd, self.window)
 
+    def describe(self):
+        d = f"GQA({self.nh} q / {self.nkv} kv heads, head_dim={self.hd}{', bias' if self.bias else ''})"
+        d += f", {self.position.describe()}"
+        if self.window:
+            d += f", window {self.window}"
+        if not self.own_kv:
+            d += ", reads another layer's cache"
+        return d
+
     def state_request(self):
         return None
 

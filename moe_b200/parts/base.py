@@ -51,6 +51,7 @@ class TensorSpec:
     shape: Tuple[int, ...]
     init: str = "normal"        # "normal" | "ones" | "zeros" for the random-weights mode
     vector: bool = False        # small vectors are widened to float32 when bound (exact)
+    sparse: bool = False        # read only for the tokens that are routed to it (an expert's weights)
 
 
 class Runtime:
@@ -106,6 +107,13 @@ class Part:
     # True if forward() only launches kernels on the current stream (no host synchronisation, no
     # data-dependent host control flow), so that a decode step may be captured in a CUDA graph.
     graph_safe = False
+    # A part may record what it decided in a call (a router's picks, say): when ``trace`` is a list,
+    # forward() appends one tuple of tensors per call; None switches it off.  A graph-safe part makes
+    # those tensors with device copies only (``clone``), so that a captured step fills them again.
+    # A graph-safe part must also leave rows of no sequence (``batch.seq_of_token < 0``) without
+    # effect on any sequence's cache or state: captured steps are padded with such rows, and a new
+    # shape of step is first run with nothing but such rows.
+    trace = None
 
     def __init__(self, spec: PartSpec):
         self.spec = spec
@@ -114,6 +122,27 @@ class Part:
     def tensors(self) -> Dict[str, TensorSpec]:
         """Local tensor name -> shape; the checkpoint name is spec.prefix + local name."""
         return {}
+
+    def tensors_in(self, has: Callable[[str], bool]) -> Dict[str, TensorSpec]:
+        """The tensors to read from a checkpoint in which ``has(local name)`` says what exists.  By
+        default ``tensors()``; a part that takes several checkpoint layouts picks one here, and
+        ``bind`` is then given those names."""
+        return self.tensors()
+
+    def describe(self) -> str:
+        """One line for a summary of the model: the part's kind and the constants a reader wants."""
+        return self.kind
+
+    def step_elements(self, num_tokens: int) -> float:
+        """Weight elements that a step of ``num_tokens`` tokens has to read from this part: by
+        default every tensor once.  A part that reads only what its tokens pick says so here."""
+        n = 0
+        for ts in self.tensors().values():
+            k = 1
+            for d in ts.shape:
+                k *= d
+            n += k
+        return float(n)
 
     def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         """Take ownership of the loaded tensors (re-laying them out is allowed)."""

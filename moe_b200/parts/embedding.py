@@ -25,6 +25,9 @@ class TokenEmbedding(Part):
     def tensors(self):
         return {"weight": TensorSpec((self.vocab, self.hidden))}
 
+    def step_elements(self, num_tokens):
+        return float(num_tokens * self.hidden)            # one row a token
+
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
         self.weight = tensors["weight"].contiguous()
@@ -53,6 +56,12 @@ class LMHead(Part):
 
     def tensors(self):
         return {} if self.tied else {"weight": TensorSpec((self.vocab, self.hidden))}
+
+    def describe(self):
+        return "output projection" + (" (the embedding)" if self.tied else "")
+
+    def step_elements(self, num_tokens):
+        return float(self.vocab * self.hidden)            # the whole matrix, tied or not
 
     def bind(self, tensors, rt, embedding: TokenEmbedding = None):
         super().bind(tensors, rt)

@@ -40,6 +40,9 @@ class DenseSwiGLU(Part):
             "down_proj.weight": TensorSpec((self.hidden, self.size)),
         }
 
+    def describe(self):
+        return f"dense SwiGLU {self.size}"
+
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
         self.w_gu = _fuse_rows([tensors["gate_proj.weight"], tensors["up_proj.weight"]])
@@ -99,9 +102,12 @@ class RoutedExperts(Part):
     def tensors(self):
         t = {"gate.weight": TensorSpec((self.E, self.hidden))}
         for e in range(self.E):
-            t[f"experts.{e}.gate_proj.weight"] = TensorSpec((self.size, self.hidden))
-            t[f"experts.{e}.up_proj.weight"] = TensorSpec((self.size, self.hidden))
-            t[f"experts.{e}.down_proj.weight"] = TensorSpec((self.hidden, self.size))
+            t[f"experts.{e}.gate_proj.weight"] = TensorSpec((self.size, self.hidden), sparse=True)
+            t[f"experts.{e}.up_proj.weight"] = TensorSpec((self.size, self.hidden), sparse=True)
+            t[f"experts.{e}.down_proj.weight"] = TensorSpec((self.hidden, self.size), sparse=True)
+        return self._common(t)
+
+    def _common(self, t):
         if self.shared_size:
             t["shared_expert.gate_proj.weight"] = TensorSpec((self.shared_size, self.hidden))
             t["shared_expert.up_proj.weight"] = TensorSpec((self.shared_size, self.hidden))
@@ -110,21 +116,76 @@ class RoutedExperts(Part):
             t["shared_expert_gate.weight"] = TensorSpec((1, self.hidden))
         return t
 
+    def tensors_in(self, has):
+        """Three checkpoint layouts of the experts, as the reference reads them (src/model.rs:396-420):
+        fused ``experts.gate_up_proj`` [E, 2 size, hidden] (rows [0, size) gate, then up) with
+        ``experts.down_proj`` [E, hidden, size]; stacked ``experts.{gate,up,down}_proj`` of three
+        dimensions; else one tensor per expert and projection."""
+        E, n, H = self.E, self.size, self.hidden
+        if has("experts.gate_up_proj"):
+            t = {"gate.weight": TensorSpec((E, H)), "experts.gate_up_proj": TensorSpec((E, 2 * n, H), sparse=True),
+                 "experts.down_proj": TensorSpec((E, H, n), sparse=True)}
+            return self._common(t)
+        if has("experts.gate_proj") and has("experts.up_proj"):
+            t = {"gate.weight": TensorSpec((E, H)), "experts.gate_proj": TensorSpec((E, n, H), sparse=True),
+                 "experts.up_proj": TensorSpec((E, n, H), sparse=True),
+                 "experts.down_proj": TensorSpec((E, H, n), sparse=True)}
+            return self._common(t)
+        return self.tensors()
+
+    def describe(self):
+        return (f"{self.E} experts of {self.size}, top-{self.k}, softmax gate"
+                + (", renormalised" if self.norm_topk else "")
+                + (f", scaled by {self.scale:g}" if self.scale != 1.0 else "")
+                + (f", shared expert {self.shared_size}" + (" (gated)" if self.shared_gate else "")
+                   if self.shared_size else ""))
+
+    def step_elements(self, num_tokens):
+        """The router, the shared expert, and the experts that ``num_tokens`` tokens are expected to
+        touch if each picks ``top_k`` of them evenly: E (1 - (1 - k/E)^tokens)."""
+        dense = sparse = 0
+        for ts in self.tensors().values():
+            n = 1
+            for d in ts.shape:
+                n *= d
+            if ts.sparse:
+                sparse += n
+            else:
+                dense += n
+        touched = 1.0 - (1.0 - self.k / self.E) ** max(num_tokens, 0)
+        return dense + sparse * touched
+
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
         self.w_router = tensors["gate.weight"].contiguous()
-        names = [f"experts.{e}.{n}_proj.weight" for e in range(self.E) for n in ("gate", "up", "down")]
-        dts = {tensors[n].dtype for n in names}
-        dt = dts.pop() if len(dts) == 1 else torch.float32
         dev = self.w_router.device
-        # [E, 2 * size, hidden]: rows [0, size) gate, [size, 2 size) up, as in the fused
-        # checkpoint layout the reference also reads (src/model.rs:401-411)
-        self.w_gu = torch.empty((self.E, 2 * self.size, self.hidden), dtype=dt, device=dev)
-        self.w_down = torch.empty((self.E, self.hidden, self.size), dtype=dt, device=dev)
-        for e in range(self.E):
-            self.w_gu[e, : self.size] = tensors.pop(f"experts.{e}.gate_proj.weight")
-            self.w_gu[e, self.size:] = tensors.pop(f"experts.{e}.up_proj.weight")
-            self.w_down[e] = tensors.pop(f"experts.{e}.down_proj.weight")
+        # The device layout is [E, 2 * size, hidden] (rows [0, size) gate, [size, 2 size) up) and
+        # [E, hidden, size], whatever the checkpoint's; tensors are fetched one at a time.
+        if "experts.gate_up_proj" in tensors:
+            self.w_gu = tensors["experts.gate_up_proj"].contiguous()
+            self.w_down = tensors["experts.down_proj"].contiguous()
+            if self.w_gu.dtype != self.w_down.dtype:
+                self.w_gu, self.w_down = self.w_gu.float(), self.w_down.float()
+        elif "experts.gate_proj" in tensors:
+            g, u, self.w_down = tensors["experts.gate_proj"], tensors["experts.up_proj"], tensors["experts.down_proj"]
+            dt = g.dtype if g.dtype == u.dtype == self.w_down.dtype else torch.float32
+            self.w_gu = torch.cat([g.to(dt), u.to(dt)], dim=1).contiguous()
+            self.w_down = self.w_down.to(dt).contiguous()
+        else:
+            first = tensors["experts.0.gate_proj.weight"]
+            dt = first.dtype
+            self.w_gu = torch.empty((self.E, 2 * self.size, self.hidden), dtype=dt, device=dev)
+            self.w_down = torch.empty((self.E, self.hidden, self.size), dtype=dt, device=dev)
+            for e in range(self.E):
+                for name, dst in ((f"experts.{e}.gate_proj.weight", self.w_gu[e, : self.size]),
+                                  (f"experts.{e}.up_proj.weight", self.w_gu[e, self.size:]),
+                                  (f"experts.{e}.down_proj.weight", self.w_down[e])):
+                    t = tensors[name]
+                    if t.dtype != dt:                  # a checkpoint of mixed dtypes: everything in 32-bit
+                        self.w_gu, self.w_down, dt = self.w_gu.float(), self.w_down.float(), torch.float32
+                        dst = {"gate": self.w_gu[e, : self.size], "up": self.w_gu[e, self.size:],
+                               "down": self.w_down[e]}[name.split(".")[2].split("_")[0]]
+                    dst.copy_(t)
         self.ws_gu = self.ws_down = self.w_sgate = None
         if self.shared_size:
             self.ws_gu = _fuse_rows([tensors["shared_expert.gate_proj.weight"], tensors["shared_expert.up_proj.weight"]])

@@ -20,6 +20,9 @@ class RMSNorm(Part):
     def tensors(self):
         return {"weight": TensorSpec((self.size,), init="ones", vector=True)}
 
+    def describe(self):
+        return f"RMSNorm eps {self.eps:g}"
+
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
         self.weight = tensors["weight"].to(torch.float32).contiguous()

@@ -33,6 +33,9 @@ class RotaryEncoding(Part):
         super().bind(tensors, rt)
         self.inv_freq = rotary_inv_freq(self.theta, self.rotary_dim).to(rt.device)
 
+    def describe(self):
+        return f"rope theta {self.theta:.0f}" + (f" on {self.rotary_dim} dims" if self.params.get("partial") else "")
+
     def rotary_table(self):
         """(inv_freq, rotary_dim): lets the mixer rotate inside its own kernel."""
         return self.inv_freq, self.rotary_dim
@@ -44,6 +47,9 @@ class RotaryEncoding(Part):
 
 class NoPositionEncoding(Part):
     category, kind = "position", "none"
+
+    def describe(self):
+        return "no position encoding"
 
     def rotary_table(self):
         return None, 0

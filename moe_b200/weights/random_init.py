@@ -18,6 +18,7 @@ import torch
 from ..config import registry
 from ..config.spec import ModelSpec
 from .safetensors_io import write_safetensors
+from .store import WeightStore, convert_for_compute
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32, "bf16": torch.bfloat16, "fp32": torch.float32,
            torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
@@ -27,25 +28,60 @@ def _tensor_seed(seed: int, name: str) -> int:
     return int.from_bytes(hashlib.sha256(f"{seed}:{name}".encode()).digest()[:7], "little")
 
 
+def _draw(name: str, ts, seed: int, std: float, dtype, device, norm_jitter: float, gen) -> torch.Tensor:
+    gen.manual_seed(_tensor_seed(seed, name))
+    if ts.init == "ones":
+        t = torch.ones(ts.shape, dtype=torch.float32, device=device)
+        if norm_jitter:
+            t += norm_jitter * torch.randn(ts.shape, generator=gen, dtype=torch.float32, device=device)
+    elif ts.init == "zeros":
+        t = torch.zeros(ts.shape, dtype=torch.float32, device=device)
+    else:
+        t = torch.randn(ts.shape, generator=gen, dtype=torch.float32, device=device) * std
+    return t.to(dtype)
+
+
 def random_tensors(spec: ModelSpec, seed: int, std: float = 0.02, dtype=torch.bfloat16, device="cpu",
                    norm_jitter: float = 0.0) -> Dict[str, torch.Tensor]:
     from ..models.decoder import expected_tensors
 
     dtype = _DTYPES[dtype]
-    out: Dict[str, torch.Tensor] = {}
     gen = torch.Generator(device=device)
-    for name, ts in expected_tensors(spec).items():
-        gen.manual_seed(_tensor_seed(seed, name))
-        if ts.init == "ones":
-            t = torch.ones(ts.shape, dtype=torch.float32, device=device)
-            if norm_jitter:
-                t += norm_jitter * torch.randn(ts.shape, generator=gen, dtype=torch.float32, device=device)
-        elif ts.init == "zeros":
-            t = torch.zeros(ts.shape, dtype=torch.float32, device=device)
-        else:
-            t = torch.randn(ts.shape, generator=gen, dtype=torch.float32, device=device) * std
-        out[name] = t.to(dtype)
-    return out
+    return {name: _draw(name, ts, seed, std, dtype, device, norm_jitter, gen)
+            for name, ts in expected_tensors(spec).items()}
+
+
+class RandomStore(WeightStore):
+    """The same random weights, each tensor drawn when it is asked for and kept nowhere: a model
+    built from it never holds more than itself and the tensors of the part being bound, which is
+    what lets the largest shapes be made on one device.  A tensor's values depend on (seed, name)
+    alone, so they equal ``random_tensors``'s drawn on the same kind of device."""
+
+    def __init__(self, spec: ModelSpec, seed: int, std: float = 0.02, dtype=torch.bfloat16, device="cpu",
+                 norm_jitter: float = 0.0):
+        from ..models.decoder import expected_tensors
+
+        self.expected = expected_tensors(spec)
+        self.seed, self.std, self.dtype, self.device, self.norm_jitter = seed, std, _DTYPES[dtype], device, norm_jitter
+        self._gen = torch.Generator(device=device)
+
+    def names(self):
+        return self.expected.keys()
+
+    def has(self, name):
+        return name in self.expected
+
+    def shape(self, name):
+        return tuple(self.expected[name].shape)
+
+    def stored_dtype(self, name):
+        return self.dtype
+
+    def raw(self, name):
+        return _draw(name, self.expected[name], self.seed, self.std, self.dtype, self.device, self.norm_jitter, self._gen)
+
+    def get(self, name, compute_dtype, device="cpu"):
+        return convert_for_compute(self.raw(name), compute_dtype).to(device=device).contiguous()
 
 
 def write_random_model(model_dir: str, config: Union[Dict[str, Any], Any], seed: int, std: float = 0.02,

@@ -22,10 +22,14 @@ STD = {"float32": (0.02, 0.2), "bfloat16": (0.02, 0.08)}
 # The same tokens cut differently (whole / one by one / batched), same dtype.
 TOL_CUT_F32 = 1e-5
 TOL_CUT_BF16 = 1e-2
-# A routing pick may differ from the plain implementation's only where the two experts'
-# probabilities are this close (relative).
+# A routing pick may differ from the plain implementation's only where the two experts' router
+# logits are this close, as a fraction of the root mean square of the layer's router logits
+# (``helpers.pick_margins``).  An error of relative size eps in the normed state moves a logit by
+# about eps of that scale, and the difference of two by sqrt(2) eps; with eps = 1e-2 for bfloat16
+# (half of TOL_BF16, the bound on what the same error leaves in the output logits) a three-sigma
+# event among the thousands of picks a test makes is 3 sqrt(2) eps = 4.2e-2.  In float32, eps = 2.5e-5.
 FLIP_F32 = 1e-4
-FLIP_BF16 = 3e-2
+FLIP_BF16 = 4.5e-2
 
 _engines: Dict[tuple, object] = {}
 

@@ -37,7 +37,18 @@ CONFIG_C = dict(
     vocab_size=300, rope_theta=5e4, rms_norm_eps=1e-6, use_sliding_window=True, sliding_window=70,
     max_window_layers=1, tie_word_embeddings=False, max_position_embeddings=4096, eos_token_id=299,
 )
-CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C}
+# heads of 128 (the size the benchmark's shape has), 2 query heads on 1 kv head, a width that is not
+# heads x head size, a window of 80 that crosses a page on the second layer, no q/k/v bias
+CONFIG_D = dict(
+    architectures=["Qwen2MoeForCausalLM"], model_type="qwen2_moe",
+    num_hidden_layers=2, hidden_size=264, num_attention_heads=2, num_key_value_heads=1, head_dim=128,
+    num_experts=6, num_experts_per_tok=2, moe_intermediate_size=56, shared_expert_intermediate_size=88,
+    norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[], intermediate_size=120,
+    vocab_size=331, rope_theta=1e5, rms_norm_eps=1e-6, use_sliding_window=True, sliding_window=80,
+    max_window_layers=1, tie_word_embeddings=False, max_position_embeddings=4096, eos_token_id=330,
+    qkv_bias=False,
+)
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "D": CONFIG_D}
 
 
 class ModelFolders:
@@ -214,27 +225,141 @@ def compare_with_plain(model_dir: str, engine, tokens: Sequence[int], flip_margi
 
 
 def flip_margins(cfg, w, tokens, picks) -> List[float]:
-    """For every (layer, token) whose forced pick differs from the free one: the relative gap
-    between the probabilities of the experts that were swapped."""
+    """For every (layer, token) whose forced pick differs from the free one: its margin (``pick_margins``)."""
+    return plain_with_picks(cfg, w, tokens, picks)[1]
+
+
+# ----------------------------------------------------------------------------- any schedule, against plain
+def run_schedule(engine, steps):
+    """Run ``steps`` -- each {"entries": [(request, tokens, wanted places)], "end": [requests]} --
+    through ``engine.step`` with the routed parts recording their picks.
+
+    Returns (logits, picks): logits[(request, position)] is a CPU row of logits for every wanted
+    place; picks[i][(request, position)] the experts that the i-th routed layer of the schedule
+    took for that token.  Positions count from the request's first token."""
+    parts = routed_parts(engine.model)
+    slots, done = {}, {}
+    logits, picks = {}, [dict() for _ in parts]
+    try:
+        for st in steps:
+            for p in parts:
+                p.trace = []
+            entries = st["entries"]
+            for rid, _, _ in entries:
+                if rid not in slots:
+                    slots[rid], done[rid] = engine.new_sequence(), 0
+            if entries:
+                lg = engine.step([slots[r] for r, _, _ in entries], [t for _, t, _ in entries],
+                                 [w for _, _, w in entries])
+                lg = lg.float().cpu() if lg is not None else None
+                taken, row, tok_row = {}, 0, 0
+                recorded = []
+                for p in parts:
+                    i = taken.get(id(p), 0)
+                    recorded.append(p.trace[i][0].cpu().tolist())
+                    taken[id(p)] = i + 1
+                for rid, toks, want in entries:
+                    for w in want:
+                        logits[(rid, done[rid] + w)] = lg[row]
+                        row += 1
+                    for j in range(len(toks)):
+                        for li in range(len(parts)):
+                            picks[li][(rid, done[rid] + j)] = recorded[li][tok_row + j]
+                    tok_row += len(toks)
+                    done[rid] += len(toks)
+            for rid in st.get("end", []):
+                engine.release(slots.pop(rid))
+    finally:
+        for p in parts:
+            p.trace = None
+        for s_ in slots.values():
+            engine.release(s_)
+    return logits, picks
+
+
+def pick_margins(cfg, logits: torch.Tensor, forced) -> List[float]:
+    """For every token whose forced pick differs from the free one (top k of ``logits`` [T, E], ties
+    to the lower index): the gap between the router logits of the experts that were swapped, as a
+    fraction of the root mean square of the layer's router logits.
+
+    Why that measure: a router logit is a sum over the hidden state, so an error of relative size
+    eps in the state moves each logit by about eps times the logits' own scale, whatever the width
+    and the weights' scale are; which of two experts wins is decided by the difference of two
+    logits.  (The gap between two logits is also the relative gap between their probabilities.)"""
     out = []
-    state = {"li": 0}
+    if forced is None:
+        return out
+    k = cfg["num_experts_per_tok"]
+    rms = float(logits.pow(2).mean().sqrt().clamp(min=1e-30))
+    for i in range(logits.shape[0]):
+        free = sorted(range(logits.shape[1]), key=lambda e: (-float(logits[i, e]), e))[:k]
+        mine = [int(e) for e in forced[i]]
+        if sorted(free) != sorted(mine):
+            lost = [e for e in free if e not in mine]
+            gained = [e for e in mine if e not in free]
+            hi, lo = max(float(logits[i, e]) for e in lost), min(float(logits[i, e]) for e in gained)
+            out.append((hi - lo) / rms)
+    return out
+
+
+def plain_with_picks(cfg, w, tokens, forced):
+    """The plain implementation with the given picks -> (logits [T, V], the margins of the picks
+    that differ from its own free choice, see ``pick_margins``)."""
+    margins = []
     orig = plain.route
 
-    def spy(cfg_, w_, p, n, forced=None):
-        sc = torch.softmax(n @ w_[p + "mlp.gate.weight"].T, dim=-1)
-        k = cfg_["num_experts_per_tok"]
-        for i in range(n.shape[0]):
-            free = sorted(range(sc.shape[1]), key=lambda e: (-float(sc[i, e]), e))[:k]
-            if forced is not None and sorted(free) != sorted(int(e) for e in forced[i]):
-                lost = [e for e in free if e not in forced[i]]
-                gained = [int(e) for e in forced[i] if e not in free]
-                hi, lo = max(float(sc[i, e]) for e in lost), min(float(sc[i, e]) for e in gained)
-                out.append((hi - lo) / hi)
-        return orig(cfg_, w_, p, n, forced)
+    def spy(cfg_, w_, p, n, forced_=None):
+        margins.extend(pick_margins(cfg_, n @ w_[p + "mlp.gate.weight"].T, forced_))
+        return orig(cfg_, w_, p, n, forced_)
 
     plain.route = spy
     try:
-        plain.forward(cfg, w, list(tokens), forced=picks)
+        ref = plain.forward(cfg, w, list(tokens), forced=forced)
     finally:
         plain.route = orig
-    return out
+    return ref, margins
+
+
+def check_schedule_against_plain(model_dir, requests, logits, picks, tol, flip_margin, max_flips=0.05):
+    """Every wanted place of every request against the plain implementation run with the engine's
+    picks.  A pick may differ from the plain implementation's own only at a margin below
+    ``flip_margin``; the logits may differ by ``tol`` of the request's largest logit."""
+    cfg, w = plain.read_model(model_dir)
+    flips = total = 0
+    checked = 0
+    for rid, toks in requests.items():
+        forced = [[layer[(rid, i)] for i in range(len(toks))] for layer in picks]
+        ref, margins = plain_with_picks(cfg, w, toks, forced)
+        assert not margins or max(margins) < flip_margin, f"{rid}: a routing pick differs at margin {max(margins):.3g}"
+        flips += len(margins)
+        total += len(toks) * max(len(picks), 1)
+        scale = float(ref.abs().max())
+        for (r, pos), row in logits.items():
+            if r != rid:
+                continue
+            err = float((row.double() - ref[pos]).abs().max()) / scale
+            assert err < tol, f"{rid} at position {pos} of {len(toks)}: relative error {err:.3g}"
+            checked += 1
+    assert checked == len(logits) and checked > 0
+    assert flips <= max_flips * total, f"routing differs too often: {flips} of {total}"
+
+
+def batches_schedule(requests: Dict[str, List[int]], batch_size: int, prompt_len, want_all: bool = True):
+    """Batches of ``batch_size`` requests one after another: the first ``prompt_len(request)`` tokens
+    of each in one step, then one token each; a request that has run out of tokens ends."""
+    ids = list(requests)
+    steps = []
+    for b0 in range(0, len(ids), batch_size):
+        live = ids[b0:b0 + batch_size]
+        done = {r: max(1, min(len(requests[r]), prompt_len(r))) for r in live}
+        entries = [(r, requests[r][:done[r]], list(range(done[r])) if want_all else [done[r] - 1]) for r in live]
+        while True:
+            ends = [r for r in live if done[r] >= len(requests[r])]
+            steps.append({"entries": entries, "end": ends})
+            live = [r for r in live if r not in ends]
+            if not live:
+                break
+            entries = [(r, [requests[r][done[r]]], [0]) for r in live]
+            for r in live:
+                done[r] += 1
+    return steps

@@ -69,9 +69,17 @@ def test_truncate_rules():
     assert led.length[s] == 40
     with pytest.raises(CacheError):
         led.truncate(s, 50)
-    led.extend(s, 300)                           # ring of 128 tokens has wrapped
+    led.extend(s, 300)                           # ring of 128 tokens has wrapped: it holds positions 172..299
     with pytest.raises(CacheError):
-        led.truncate(s, 250)
+        led.truncate(s, 250)                     # the window is not told: refused
+    with pytest.raises(CacheError):
+        led.truncate(s, 250, [0, 100])           # position 250 looks back to 151, which is gone
+    assert led.length[s] == 300
+    led.truncate(s, 271, [0, 100])               # position 271 looks back to 172: just still there
+    assert led.length[s] == 271
+    led.truncate(s, 271, [0, 100])               # to the same length: nothing to do, always allowed
+    led.extend(s, 280)
+    assert led.length[s] == 280
 
 
 def test_random_walk_keeps_every_invariant():

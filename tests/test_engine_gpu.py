@@ -112,7 +112,7 @@ def test_short_prompts_replayed_from_padded_graphs_equal_the_step_launched_kerne
             for s in slots:
                 e.release(s)
             out.append((first, second))
-        assert eng._prompt_graphs, "the prompt step did not take a graph"
+        assert eng.graphs_of("prompt"), "the prompt step did not take a graph"
         for a, b in zip(out[0], out[1]):
             assert torch.isfinite(a).all()
             assert helpers.max_rel_err(a, b) < G.tol_cut(dtype), lens

@@ -24,6 +24,7 @@ def register_toy():
         """s_t = decay * s_{t-1} + W_in n_t;  out_t = W_out s_t.  The carry s lives in the cache's
         per-sequence state of fixed size; tokens of a sequence are scanned in order."""
         category, kind = "mixer", "toy_decay"
+        graph_safe = True
 
         def __init__(self, spec):
             super().__init__(spec)
@@ -44,16 +45,32 @@ def register_toy():
             self.w_in, self.w_out = tensors["in_proj.weight"].float(), tensors["out_proj.weight"].float()
 
         def forward(self, rt, h, batch, cache_view, state):
+            """The scan as device operations only (no value comes back to the host), so that a step
+            may be captured: out_t = decay^(j+1) carry + sum_{i <= t, same sequence} decay^(t-i) u_i,
+            j being the token's place among its sequence's tokens of this step."""
             assert cache_view is None and state is not None
             u = h.act.float() @ self.w_in.T
-            out = torch.empty_like(u)
-            cu, slots = batch.cu_seqlens.tolist(), batch.slots.tolist()
-            for s in range(batch.num_seqs):
-                carry = state[slots[s]]
-                for t in range(cu[s], cu[s + 1]):
-                    carry = self.decay * carry + u[t]
-                    out[t] = carry
-                state[slots[s]] = carry
+            T = u.shape[0]
+            seq = batch.seq_of_token.long()                          # -1: a row of no sequence
+            live = (seq >= 0).unsqueeze(1)
+            sq = seq.clamp(min=0)
+            rows = torch.arange(T, device=u.device)
+            gap = rows.unsqueeze(1) - rows.unsqueeze(0)              # t - i
+            same = (seq.unsqueeze(1) == seq.unsqueeze(0)) & (gap >= 0) & live
+            weights = torch.where(same, torch.pow(torch.full_like(gap, self.decay, dtype=torch.float32),
+                                                  gap.clamp(min=0).float()), torch.zeros((), device=u.device))
+            place = rows - batch.cu_seqlens.long()[sq]               # j
+            carry = state[batch.slots.long()[sq]]
+            out = weights @ u + torch.pow(torch.full_like(place, self.decay, dtype=torch.float32),
+                                          (place + 1).float()).unsqueeze(1) * carry
+            out = torch.where(live, out, torch.zeros((), device=u.device))
+            # the carry after the step is the output at each sequence's last token; a sequence without
+            # tokens (padding of a captured step) sits in the padding slot, whose state nobody reads
+            cu = batch.cu_seqlens.long()
+            last = (cu[1:] - 1).clamp(min=0)
+            has = (cu[1:] > cu[:-1]).unsqueeze(1)
+            slot = batch.slots.long()
+            state.index_copy_(0, slot, torch.where(has, out[last], state[slot]))
             return (out @ self.w_out.T).contiguous()
 
     moe_b200.register_part("mixer", "toy_decay", DecayMixer)
@@ -166,8 +183,20 @@ def test_toy_architecture_with_a_stateful_mixer(tmp_path, dtype):
         assert helpers.max_rel_err(tail[rid], whole[rid]) < G.tol_cut(dtype)
         assert helpers.max_rel_err(batched[rid], whole[rid]) < G.tol_cut(dtype)
     assert eng.cache.ledger.slots.num_held == 0
+    # the mixer is graph-safe, so single-token steps were replayed from captured graphs; the first use
+    # of a graph ran the step once, not twice, or the carry would have decayed twice
+    assert eng.use_graphs and eng.graphs_of("decode")
     out = moe_b200.generate(eng, [reqs["r0"], reqs["r3"]], max_tokens=4)
     assert [len(o.tokens) for o in out] == [4, 4]
+    # state of fixed size cannot be rewound
+    from moe_b200.cache import CacheError
+
+    s = eng.new_sequence()
+    eng.step([s], [reqs["r0"]])
+    with pytest.raises(CacheError):
+        eng.truncate(s, 3)
+    eng.truncate(s, len(reqs["r0"]))               # to its own length: nothing to take back
+    eng.release(s)
 
 
 def register_toy_switch():

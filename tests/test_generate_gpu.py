@@ -161,8 +161,17 @@ def test_command_line_run_info_bench(model_dirs, tmp_path):
     lines = [json.loads(l) for l in r.stdout.strip().splitlines()]
     assert [l["index"] for l in lines] == [0, 1, 2] and all(l["generated"] == len(l["tokens"]) <= 3 for l in lines)
     r = run("info", d)
-    assert r.returncode == 0 and "Qwen2MoeForCausalLM" in r.stdout and "4 experts, top-2" in r.stdout
+    assert r.returncode == 0 and "Qwen2MoeForCausalLM" in r.stdout and "4 experts of 32, top-2" in r.stdout
     r = run("bench", d, "--prompt-len", "16", "--tokens", "4", "--batch", "2")
     assert r.returncode == 0 and "decode" in r.stdout and "tok/s" in r.stdout, r.stderr
+    assert "roofline" in r.stdout and "% of 7700 GB/s" in r.stdout
+    # random weights instead of a folder: the same verbs, nothing written
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(helpers.CONFIG_A))
+    r = run("bench", "--random", str(cfg), "--seed", "4", "--prompt-len", "8", "--tokens", "3", "--peak-gbs", "6500")
+    assert r.returncode == 0 and "% of 6500 GB/s" in r.stdout, r.stderr
+    a = run("run", "--random", str(cfg), "--seed", "4", "--ids", "1,2,3", "-n", "5", "--no-stream")
+    b = run("run", "--random", str(cfg), "--seed", "4", "--ids", "1,2,3", "-n", "5", "--no-stream")
+    assert a.returncode == 0 and a.stdout == b.stdout and len(json.loads(a.stdout.strip().splitlines()[-1])) == 5
     r = run("run", str(tmp_path / "nothing"), "--ids", "1")
     assert r.returncode == 1 and r.stderr.startswith("moe:")

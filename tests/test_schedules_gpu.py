@@ -1,0 +1,154 @@
+"""Schedules of steps beyond "one request alone": many sequences decoded together, steps that mix
+fresh prompts with continued ones and with single tokens, prompts fed in chunks.  Every wanted
+place is compared with the plain implementation directly, run with the engine's own routing picks
+(the reference compares whole, one by one and split with its oracle: tests/oracle.rs:46-75,
+100-118; it tiles prompts at 64 tokens, src/main.rs:499-505)."""
+import numpy as np
+import pytest
+import torch
+
+import gpu_util as G
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+
+def engine(model_dirs, name, dtype, max_tokens, max_slots, use_graphs=True):
+    """An engine of its own (its pool is smaller than the number of requests) on the session's model."""
+    import moe_b200
+
+    d, shared = G.engine_for(model_dirs, name, dtype)
+    return d, moe_b200.Engine(shared.model, max_tokens=max_tokens, max_slots=max_slots, use_graphs=use_graphs)
+
+
+MANY = [("A", 12, True), ("A", 70, True), ("B", 24, True), ("B", 40, False), ("D", 40, True), ("D", 12, False),
+        ("C", 33, True)]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,n,graphs", MANY)
+def test_many_sequences_decoded_together_match_plain(model_dirs, name, n, graphs, dtype):
+    """``n`` requests of unequal lengths start together and are decoded for 40 to 60 steps, the
+    shorter ones ending earlier, so that the batch shrinks through the padded sizes of the captured
+    steps; then a second batch of half as many on the same slots.  From 9 sequences on the routed
+    experts pick, invert and gather in separate launches and the products take wider token tiles."""
+    V = helpers.CONFIGS[name]["vocab_size"]
+    rng = np.random.default_rng(n)
+    total = n + n // 2
+    prompt = {f"r{i}": int(rng.integers(1, 24)) for i in range(total)}
+    reqs = {r: helpers.random_tokens(V, p + int(rng.integers(40, 61)), 1000 + i) for i, (r, p) in enumerate(prompt.items())}
+    d, eng = engine(model_dirs, name, dtype, max_tokens=128 * n, max_slots=n, use_graphs=graphs)
+    steps = helpers.batches_schedule(reqs, n, lambda r: prompt[r], want_all=(n % 2 == 0))
+    logits, picks = helpers.run_schedule(eng, steps)
+    if graphs:
+        sizes = {k[1] for k in eng.graphs_of("decode")}
+        assert max(sizes) >= min(n, 64) and len(sizes) >= 3, sizes      # the padded sizes the batch went through
+    helpers.check_schedule_against_plain(d, reqs, logits, picks, G.tol(dtype), G.flip(dtype))
+    led = eng.cache.ledger
+    assert led.slots.num_held == 0 and all(g.pool.num_free == g.pool.num_pages - 1 for g in led.groups)
+
+
+@pytest.mark.parametrize("name,dtype", [(n, dt) for n in ("A", "C") for dt in ("float32", "bfloat16")])
+def test_a_sequence_decodes_the_same_alone_and_among_63_others(model_dirs, name, dtype):
+    V = helpers.CONFIGS[name]["vocab_size"]
+    reqs = {f"r{i}": helpers.random_tokens(V, 30 + (i * 7) % 23, 300 + i) for i in range(64)}
+    d, eng = engine(model_dirs, name, dtype, max_tokens=64 * 64, max_slots=64)
+    alone, _ = helpers.run_schedule(eng, helpers.batches_schedule({"r5": reqs["r5"]}, 1, lambda r: 4))
+    among, _ = helpers.run_schedule(eng, helpers.batches_schedule(reqs, 64, lambda r: 4))
+    a = torch.stack([alone[("r5", i)] for i in range(len(reqs["r5"]))])
+    b = torch.stack([among[("r5", i)] for i in range(len(reqs["r5"]))])
+    assert helpers.max_rel_err(b, a) < G.tol_cut(dtype)
+
+
+@pytest.mark.parametrize("name,dtype", [(n, dt) for n in ("A", "B", "C", "D") for dt in ("float32", "bfloat16")])
+def test_steps_that_mix_fresh_prompts_continued_ones_and_single_tokens(model_dirs, name, dtype):
+    """One step may hold a sequence that brings one token, one that goes on by several from a
+    position beyond 0, and one that starts with a whole prompt; keys of earlier steps then come from
+    the cache and those of the step from its own buffers."""
+    V = helpers.CONFIGS[name]["vocab_size"]
+    reqs = {"a": helpers.random_tokens(V, 110, 1), "b": helpers.random_tokens(V, 160, 2),
+            "c": helpers.random_tokens(V, 150, 3), "d": helpers.random_tokens(V, 9, 4)}
+    cuts = [                      # tokens each request brings, step by step (0: it is not in the step)
+        dict(a=20, b=70),
+        dict(a=1, b=5, c=70),
+        dict(a=5, b=1, c=1, d=3),
+        dict(a=1, b=1, c=64, d=1),          # c goes on across a page's edge
+        dict(a=63, b=1, c=1, d=5),          # a ends exactly on position 89, d ends
+        dict(a=1, b=82, c=14),              # b goes on from 78 to 159: past the windows of C and D
+        dict(a=19),
+    ]
+    at = {r: 0 for r in reqs}
+    steps = []
+    for cut in cuts:
+        entries, ends = [], []
+        for r, n in cut.items():
+            toks = reqs[r][at[r]:at[r] + n]
+            assert len(toks) == n
+            entries.append((r, toks, list(range(n))))
+            at[r] += n
+            if at[r] == len(reqs[r]):
+                ends.append(r)
+        steps.append({"entries": entries, "end": ends})
+    assert at == {r: len(t) for r, t in reqs.items()}
+    d, eng = engine(model_dirs, name, dtype, max_tokens=64 * 10, max_slots=4)
+    logits, picks = helpers.run_schedule(eng, steps)
+    helpers.check_schedule_against_plain(d, reqs, logits, picks, G.tol(dtype), G.flip(dtype))
+
+
+@pytest.mark.parametrize("name,dtype", [(n, dt) for n in ("A", "B", "C", "D") for dt in ("float32", "bfloat16")])
+@pytest.mark.parametrize("chunk", [64, 50])
+def test_a_prompt_fed_in_chunks_matches_plain(model_dirs, name, dtype, chunk):
+    V = helpers.CONFIGS[name]["vocab_size"]
+    reqs = {"x": helpers.random_tokens(V, 230, 12), "y": helpers.random_tokens(V, 131, 13)}
+    steps = []
+    longest = max(len(t) for t in reqs.values())
+    for o in range(0, longest, chunk):
+        entries = [(r, t[o:o + chunk], list(range(len(t[o:o + chunk])))) for r, t in reqs.items() if o < len(t)]
+        steps.append({"entries": entries, "end": [r for r, t in reqs.items() if o < len(t) <= o + chunk]})
+    d, eng = engine(model_dirs, name, dtype, max_tokens=64 * 8, max_slots=2)
+    logits, picks = helpers.run_schedule(eng, steps)
+    helpers.check_schedule_against_plain(d, reqs, logits, picks, G.tol(dtype), G.flip(dtype))
+
+
+@pytest.mark.parametrize("name,dtype", [(n, dt) for n in ("A", "B", "D") for dt in ("float32", "bfloat16")])
+def test_rewinding_then_continuing_equals_a_fresh_sequence(model_dirs, name, dtype):
+    """Truncating the cache matches a fresh state (tests/oracle.rs:678-701): after a rewind to
+    position n the sequence goes on as if it had never held more."""
+    from moe_b200.cache import CacheError
+
+    V = helpers.CONFIGS[name]["vocab_size"]
+    d, eng = engine(model_dirs, name, dtype, max_tokens=64 * 8, max_slots=2)
+    toks = helpers.random_tokens(V, 60, 21)
+    other = helpers.random_tokens(V, 25, 22)
+    s = eng.new_sequence()
+    eng.step([s], [toks[:40]])
+    for t in other:                                  # a continuation that is then taken back
+        eng.step([s], [[t]])
+    eng.truncate(s, 40)
+    assert eng.length(s) == 40
+    got = [eng.step([s], [toks[40:50]], [list(range(10))]).float().cpu()]
+    got += [eng.step([s], [[t]], [[0]]).float().cpu() for t in toks[50:]]
+    got = torch.cat(got)
+    f = eng.new_sequence()
+    fresh = [eng.step([f], [toks[:40]], [[]])]
+    fresh = [eng.step([f], [toks[40:50]], [list(range(10))]).float().cpu()]
+    fresh += [eng.step([f], [[t]], [[0]]).float().cpu() for t in toks[50:]]
+    fresh = torch.cat(fresh)
+    assert helpers.max_rel_err(got, fresh) < 1e-5
+    ref = helpers.plain_logits(d, toks)[40:]
+    if dtype == "float32":
+        assert helpers.max_rel_err(got, ref) < G.TOL_F32
+    with pytest.raises(CacheError):
+        eng.truncate(s, 61)                          # a rewind cannot lengthen
+    # a windowed layer: once its ring has wrapped, a rewind beyond what it still holds is refused
+    win = helpers.CONFIGS[name].get("sliding_window") if helpers.CONFIGS[name].get("use_sliding_window") else None
+    if win:
+        ring = -(-win // 64) * 64
+        long = helpers.random_tokens(V, ring + 70, 23)
+        eng.step([f], [long[:ring + 70 - 60]])
+        n = eng.length(f)
+        with pytest.raises(CacheError):
+            eng.truncate(f, n - ring)                # the keys before that position are written over
+        assert eng.length(f) == n
+        eng.truncate(f, n - 1)                       # one step back is always inside the ring's slack or window
+    eng.release(s), eng.release(f)

@@ -132,3 +132,68 @@ def test_writer_and_plain_reader_agree(tmp_path):
         assert torch.equal(got[n], t[n].double())
     s = SafetensorsStore(str(tmp_path))
     assert torch.equal(s.raw("a"), t["a"]) and s.shape("z.w") == (2, 2, 2)
+
+
+def _restacked(src: SafetensorsStore, cfg, form: str):
+    """The same weights with every routed layer's experts in another checkpoint layout
+    (src/model.rs:396-420): "fused" gate_up_proj [E, 2 size, hidden] + down_proj [E, hidden, size];
+    "stacked" three tensors of three dimensions."""
+    out = {}
+    E = cfg["num_experts"]
+    per_expert = {}
+    for n in src.names():
+        parts = n.split(".")
+        if ".mlp.experts." in n:
+            layer = ".".join(parts[:3])
+            per_expert.setdefault(layer, {})[(int(parts[5]), parts[6])] = src.raw(n)
+        else:
+            out[n] = src.raw(n).clone()
+    for layer, t in per_expert.items():
+        g = torch.stack([t[(e, "gate_proj")] for e in range(E)])
+        u = torch.stack([t[(e, "up_proj")] for e in range(E)])
+        dn = torch.stack([t[(e, "down_proj")] for e in range(E)])
+        if form == "fused":
+            out[f"{layer}.mlp.experts.gate_up_proj"] = torch.cat([g, u], dim=1)
+        else:
+            out[f"{layer}.mlp.experts.gate_proj"], out[f"{layer}.mlp.experts.up_proj"] = g, u
+        out[f"{layer}.mlp.experts.down_proj"] = dn
+    return out
+
+
+@pytest.mark.parametrize("form", ["fused", "stacked"])
+def test_fused_and_stacked_expert_layouts_load_to_the_same_model(tmp_path, model_dirs, form):
+    import moe_b200
+
+    base = model_dirs.get("B", "float32", seed=2)
+    d = tmp_path / form
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(helpers.CONFIG_B))
+    write_safetensors(str(d / "model.safetensors"), _restacked(SafetensorsStore(base), helpers.CONFIG_B, form))
+    a = moe_b200.load_model(base, dtype="float32", device="cpu")
+    b = moe_b200.load_model(str(d), dtype="float32", device="cpu")
+    fa, fb = a.blocks[1].ffn, b.blocks[1].ffn
+    assert fa.w_gu.shape == (8, 96, 96) and torch.equal(fa.w_gu, fb.w_gu) and torch.equal(fa.w_down, fb.w_down)
+    assert torch.equal(fa.ws_gu, fb.ws_gu) and torch.equal(fa.w_router, fb.w_router)
+    # a wrong shape in that layout is reported by its own name
+    broken = _restacked(SafetensorsStore(base), helpers.CONFIG_B, form)
+    broken["model.layers.1.mlp.experts.down_proj"] = torch.zeros(8, 96, 47)
+    write_safetensors(str(d / "model.safetensors"), broken)
+    with pytest.raises(WeightError) as e:
+        moe_b200.load_model(str(d), dtype="float32", device="cpu")
+    assert "model.layers.1.mlp.experts.down_proj is [8, 96, 47], expected [8, 96, 48]" in str(e.value)
+
+
+def test_weights_drawn_when_asked_for_equal_those_drawn_at_once():
+    import moe_b200
+    from moe_b200.weights import RandomStore, random_tensors
+
+    arch, typed = parse_config(helpers.CONFIG_B)
+    spec = arch.model_spec(typed)
+    at_once = random_tensors(spec, 5, 0.05, "bfloat16", "cpu")
+    store = RandomStore(spec, 5, 0.05, "bfloat16", "cpu")
+    assert set(store.names()) == set(at_once)
+    for n in list(at_once)[::7] + list(at_once)[:3]:          # in another order than they were drawn at once
+        assert torch.equal(store.raw(n), at_once[n]) and store.shape(n) == tuple(at_once[n].shape)
+    m = moe_b200.random_model(helpers.CONFIG_B, seed=5, dtype="bfloat16", device="cpu", std=0.05)
+    assert torch.equal(m.blocks[1].ffn.w_gu[3, 48:], at_once["model.layers.1.mlp.experts.3.up_proj.weight"])
+    assert torch.equal(m.blocks[0].mixer.wqkv[96:128], at_once["model.layers.0.self_attn.k_proj.weight"])
