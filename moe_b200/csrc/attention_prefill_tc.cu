@@ -29,7 +29,6 @@
 namespace {
 
 constexpr int QT = 128, KT = 128;
-constexpr uint32_t WAIT_LIMIT = 1u << 24;
 // tensor-memory columns: two score buffers, the output rows, P's two terms
 constexpr uint32_t COL_S = 0, COL_O = 256, COL_PHI = 384, COL_PLO = 448, TMEM_COLS = 512;
 
@@ -54,12 +53,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: false if the barrier did not complete in time or another role gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+// Bounded wait: false if the barrier did not complete within WAIT_LIMIT_US (the site is then
+// recorded in the status word) or another role of the CTA gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int site) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (uint32_t i = 1;; i++) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 1023u) == 1023u && *abort_flag) return false;
+        if ((i & 31u) == 0) {
+            if (abort_flag && *abort_flag) return false;
+            if (global_ns() - t0 > (unsigned long long)WAIT_LIMIT_US * 1000ull) break;
+        }
     }
+    wait_ran_out(status, site);
     return false;
 }
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
@@ -251,7 +257,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             int nk = 0, nv = 0;                         // tiles whose keys / values have been requested
             auto load_k = [&](int it) {
                 const int st = it & 1;
-                if (!mbar_wait(k_empty(st), ((it >> 1) & 1) ^ 1, &s_abort)) return false;
+                if (!mbar_wait(k_empty(st), ((it >> 1) & 1) ^ 1, &s_abort, status, 0x41)) return false;
                 mbar_expect_tx(k_full(st), TILE_BYTES);
                 for (int c = 0; c < CH; c++)
                     tma_load_3d(sK(st) + c * 16384, &tmK, c * 64, kvh, tok0 + (kv_lo + it) * KT, k_full(st));
@@ -260,7 +266,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             };
             auto load_v = [&](int it) {
                 const int st = it & 1;
-                if (!mbar_wait(v_empty(st), ((it >> 1) & 1) ^ 1, &s_abort)) return false;
+                if (!mbar_wait(v_empty(st), ((it >> 1) & 1) ^ 1, &s_abort, status, 0x42)) return false;
                 mbar_expect_tx(v_full(st), TILE_BYTES);
                 for (int c = 0; c < CH; c++)
                     tma_load_3d(sV(st) + c * 16384, &tmV, c * 64, kvh, tok0 + (kv_lo + it) * KT, v_full(st));
@@ -276,19 +282,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 atomicOr(status, ST_WAIT_TIMEOUT);
                 s_abort = 1;
                 for (int i = max(0, nk - 2); i < nk; i++)       // copies in flight must land
-                    mbar_wait(k_full(i & 1), (i >> 1) & 1, &s_abort);
-                for (int i = max(0, nv - 2); i < nv; i++) mbar_wait(v_full(i & 1), (i >> 1) & 1, &s_abort);
+                    mbar_wait(k_full(i & 1), (i >> 1) & 1, nullptr, status, 0x43);
+                for (int i = max(0, nv - 2); i < nv; i++) mbar_wait(v_full(i & 1), (i >> 1) & 1, nullptr, status, 0x43);
             }
         }
     } else if (warp == 1) {
         // ---- MMA issuer ----------------------------------------------------------------------------
         if (lane == 0) {
             constexpr uint32_t idesc_s = instr_desc(KT, 0), idesc_pv = instr_desc(HD, 1);
-            bool ok = mbar_wait(q_full, 0, &s_abort);
+            bool ok = mbar_wait(q_full, 0, &s_abort, status, 0x44);
             auto issue_s = [&](int it) {           // scores of tile `it` into buffer it & 1
                 const int b = it & 1;
-                if (!mbar_wait(k_full(b), (it >> 1) & 1, &s_abort)) return false;
-                if (!mbar_wait(s_empty(b), ((it >> 1) & 1) ^ 1, &s_abort)) return false;
+                if (!mbar_wait(k_full(b), (it >> 1) & 1, &s_abort, status, 0x45)) return false;
+                if (!mbar_wait(s_empty(b), ((it >> 1) & 1) ^ 1, &s_abort, status, 0x46)) return false;
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ks++) {
@@ -304,7 +310,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 if (it + 1 < n_tiles) ok = issue_s(it + 1);
                 if (!ok) break;
                 const int st = it & 1;
-                ok = mbar_wait(v_full(st), (it >> 1) & 1, &s_abort) && mbar_wait(p_full, it & 1, &s_abort);
+                ok = mbar_wait(v_full(st), (it >> 1) & 1, &s_abort, status, 0x47) && mbar_wait(p_full, it & 1, &s_abort, status, 0x48);
                 if (!ok) break;
                 tc_fence_after();
 #pragma unroll
@@ -340,7 +346,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         bool ok = true;
         for (int it = 0; it < n_tiles; it++) {
             const int b = it & 1;
-            ok = mbar_wait(s_full(b), (it >> 1) & 1, &s_abort);
+            ok = mbar_wait(s_full(b), (it >> 1) & 1, &s_abort, status, 0x49);
             if (!ok) break;
             tc_fence_after();
             const uint32_t ts = tmem + COL_S + b * KT + lane_base + half * (KT / 2);
@@ -368,7 +374,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 x_max[b][half][r] = fmaxf(mx0, mx1);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(x_bar(qd));
-                if (!mbar_wait(x_bar(qd), it & 1, &s_abort)) return false;
+                if (!mbar_wait(x_bar(qd), it & 1, &s_abort, status, 0x4a)) return false;
                 const float mx = fmaxf(x_max[b][0][r], x_max[b][1][r]) * scale_log2;
                 // The running maximum only has to keep the exponentials in range: it moves when the
                 // tile's maximum exceeds it by more than 8 (a factor 256), which spares most rescalings.
@@ -378,8 +384,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                     alpha = (m == -INFINITY) ? 1.f : ex2_approx(m - m_new);     // nothing accumulated yet: nothing to rescale
                 }
                 // the products so far belong to the old maximum: wait for the last one, rescale the row
-                if (it > 0 && !mbar_wait(pv_done, (it - 1) & 1, &s_abort)) return false;
-                if (alpha != 1.f) {
+                if (it > 0 && !mbar_wait(pv_done, (it - 1) & 1, &s_abort, status, 0x4b)) return false;
+                // (tcgen05.ld / st are warp-wide instructions: if ANY row of the warp has to be rescaled,
+                // every lane takes part, the others with a factor of one)
+                if (__any_sync(0xffffffffu, alpha != 1.f)) {
                     tc_fence_after();
 #pragma unroll
                     for (int c = 0; c < HD / 64; c++) {
@@ -432,9 +440,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             x_sum[half][r] = l;
             __syncwarp();
             if (lane == 0) mbar_arrive(x_bar(qd));
-            ok = mbar_wait(x_bar(qd), n_tiles & 1, &s_abort);
+            ok = mbar_wait(x_bar(qd), n_tiles & 1, &s_abort, status, 0x4c);
         }
-        if (ok) ok = mbar_wait(pv_done, (n_tiles - 1) & 1, &s_abort);
+        if (ok) ok = mbar_wait(pv_done, (n_tiles - 1) & 1, &s_abort, status, 0x4d);
         if (!ok) {
             if (lane == 0) {
                 atomicOr(status, ST_WAIT_TIMEOUT);

@@ -20,6 +20,24 @@ enum : int {
     ST_BAD_ROW = 16,      // gather index outside its tensor
 };
 
+// status[1]: where the FIRST bounded wait ran out (a site number, see WAIT_SITES in ops/core.py); 0 if none.
+__device__ __forceinline__ void wait_ran_out(int* status, int site) {
+    if (status) {
+        atomicOr(status, ST_WAIT_TIMEOUT);
+        atomicCAS(status + 1, 0, site);
+    }
+}
+// Nanoseconds of the device's global timer: bounds a wait by time, not by a number of tries (one
+// try of an mbarrier wait may itself suspend the thread for a while).
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// A wait on a barrier inside a kernel may take this long (microseconds) before it gives up.  No
+// wait of a healthy kernel comes near it; it only turns a hang into an error.
+constexpr uint32_t WAIT_LIMIT_US = 2000000u;
+
 __device__ __forceinline__ float ld_f(const float* p) { return *p; }
 __device__ __forceinline__ float ld_f(const __nv_bfloat16* p) { return __bfloat162float(*p); }
 __device__ __forceinline__ void st_f(float* p, float v) { *p = v; }

@@ -40,7 +40,6 @@ namespace {
 constexpr int TILE_W = 128;   // output features per CTA (UMMA M)
 constexpr int BK = 64;        // K elements per stage = one 128-byte swizzle row of bf16
 constexpr int UMMA_K = 16;
-constexpr uint32_t WAIT_LIMIT = 1u << 24;
 constexpr int MAX_SMEM_GROUPS = 256;
 constexpr int MAX_SPLITS = 16;
 
@@ -66,6 +65,8 @@ struct Params {
     float* partials;            // [splits][M][cols] float32, cols = N or 2 N (not with cluster)
     int* tickets;               // one per (grid.y, grid.x), zero before and after the launch
     int* status;
+    uint32_t wait_limit;        // microseconds a wait on a barrier may take (WAIT_LIMIT_US, less in the wait test)
+    int test_fault;             // 0; the wait test: 1 = the producer loads nothing, 2 = no MMA is issued
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------
@@ -88,12 +89,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: false if the barrier did not complete in time or another role gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+// Bounded wait: false if the barrier did not complete within limit_us microseconds (the site is then
+// recorded in the status word) or another role of the CTA gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t limit_us,
+                                          int* status, int site) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (uint32_t i = 1;; i++) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (abort_flag && (i & 1023u) == 1023u && *abort_flag) return false;
+        if ((i & 31u) == 0) {
+            if (abort_flag && *abort_flag) return false;
+            if (global_ns() - t0 > (unsigned long long)limit_us * 1000ull) break;
+        }
     }
+    wait_ran_out(status, site);
     return false;
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
@@ -351,7 +360,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             int issued = 0;
             bool ok = true;
             int kb_next = kb0;
-            if (!wait_first) {
+            if (p.test_fault == 1) {
+                if (!wait_first) pdl_sync();
+                kb_next = kb1;                   // the wait test: nothing is loaded, the MMA issuer's wait runs out
+            } else if (!wait_first) {
                 // weight tiles of the first stages, then wait for the predecessor, then their activations
                 const int pre = min(C::STAGES, kb1 - kb0);
                 for (int i = 0; i < pre; i++) {
@@ -368,7 +380,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             for (int kb = kb_next; kb < kb1 && ok; kb++, issued++) {
                 const int s = issued % C::STAGES;
                 const uint32_t ph = (issued / C::STAGES) & 1;
-                ok = mbar_wait(empty_bar(s), ph ^ 1, &s_abort);
+                ok = mbar_wait(empty_bar(s), ph ^ 1, &s_abort, p.wait_limit, p.status, 0x11);
                 if (!ok) break;
                 const uint32_t st = base + s * C::STAGE_BYTES;
                 mbar_expect_tx(full_bar(s), stage_tx);
@@ -381,18 +393,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 s_abort = 1;
                 // copies already issued must land before the CTA may leave
                 for (int i = max(0, issued - C::STAGES); i < issued; i++)
-                    mbar_wait(full_bar(i % C::STAGES), (i / C::STAGES) & 1, nullptr);
+                    mbar_wait(full_bar(i % C::STAGES), (i / C::STAGES) & 1, nullptr, p.wait_limit, p.status, 0x12);
             }
         }
     } else if (warp == 1) {
         // ---- MMA issuer -------------------------------------------------------------------
         if (lane == 0) {
             const uint32_t idesc = instr_desc(n_eff);
+            const bool issue = p.test_fault != 2;   // the wait test: nothing is issued, producer and epilogue run out
             bool ok = true;
             int it = 0;
-            for (int kb = kb0; kb < kb1; kb++, it++) {
+            for (int kb = kb0; kb < kb1 && issue; kb++, it++) {
                 const int s = it % C::STAGES;
-                ok = mbar_wait(full_bar(s), (it / C::STAGES) & 1, &s_abort);
+                ok = mbar_wait(full_bar(s), (it / C::STAGES) & 1, &s_abort, p.wait_limit, p.status, 0x14);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t st = base + s * C::STAGE_BYTES;
@@ -406,7 +419,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 }
                 umma_commit(empty_bar(s));      // frees the stage when these MMAs have read it
             }
-            if (ok) {
+            if (!issue) {
+                // (the others find out by themselves)
+            } else if (ok) {
                 umma_commit(acc_bar);           // accumulator complete
             } else {
                 atomicOr(p.status, ST_WAIT_TIMEOUT);
@@ -418,7 +433,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         const int q = warp & 3;                        // tensor-memory lane group of this warp
         const int n = n0 + q * 32 + lane;              // output feature of this thread
         const bool n_ok = n < p.N;
-        const bool ok = mbar_wait(acc_bar, 0, &s_abort);
+        const bool ok = mbar_wait(acc_bar, 0, &s_abort, p.wait_limit, p.status, 0x15);
         if (!ok) {
             if (lane == 0) {
                 atomicOr(p.status, ST_WAIT_TIMEOUT);
@@ -764,7 +779,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
         if (lane == 0) {
             int issued = 0;
             bool ok = true;
-            for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+            for (int item = blockIdx.x; item < items && ok && p.test_fault != 1; item += gridDim.x) {
                 const Tile t = tile_of<BN, TW>(item, m_tiles, p, s_prefix, s_offs);
                 const int n_eff = min(BN, (min(BN, t.row_end - t.row0) + 15) & ~15);
                 const int xchunks = (n_eff + C::XBOX - 1) / C::XBOX;
@@ -772,7 +787,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
                 const int w_row = t.g * p.w_rows_per_group + t.n0;
                 for (int kb = 0; kb < kbs; kb++, issued++) {
                     const int s = issued % C::STAGES;
-                    ok = mbar_wait(empty_bar(s), ((issued / C::STAGES) & 1) ^ 1, &s_abort);
+                    ok = mbar_wait(empty_bar(s), ((issued / C::STAGES) & 1) ^ 1, &s_abort, p.wait_limit, p.status, 0x21);
                     if (!ok) break;
                     const uint32_t st = base + s * C::STAGE_BYTES;
                     mbar_expect_tx(full_bar(s), stage_tx);
@@ -793,7 +808,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
                 atomicOr(p.status, ST_WAIT_TIMEOUT);
                 s_abort = 1;
                 for (int i = max(0, issued - C::STAGES); i < issued; i++)     // copies in flight must land
-                    mbar_wait(full_bar(i % C::STAGES), (i / C::STAGES) & 1, nullptr);
+                    mbar_wait(full_bar(i % C::STAGES), (i / C::STAGES) & 1, nullptr, p.wait_limit, p.status, 0x22);
             }
         }
     } else if (warp == 1) {
@@ -801,18 +816,18 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
         if (lane == 0) {
             int consumed = 0, local = 0;
             bool ok = true;
-            for (int item = blockIdx.x; item < items && ok; item += gridDim.x, local++) {
+            for (int item = blockIdx.x; item < items && ok && p.test_fault != 2; item += gridDim.x, local++) {
                 const Tile t = tile_of<BN, TW>(item, m_tiles, p, s_prefix, s_offs);
                 const int n_eff = min(BN, (min(BN, t.row_end - t.row0) + 15) & ~15);
                 const uint32_t idesc = instr_desc(n_eff);
                 const int b = local % C::NBUF;
-                ok = mbar_wait(acc_empty(b), ((local / C::NBUF) & 1) ^ 1, &s_abort);   // the epilogue has drained it
+                ok = mbar_wait(acc_empty(b), ((local / C::NBUF) & 1) ^ 1, &s_abort, p.wait_limit, p.status, 0x23);   // the epilogue has drained it
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t acc_addr = tmem + b * C::ACC_COLS;
                 for (int kb = 0; kb < kbs; kb++, consumed++) {
                     const int s = consumed % C::STAGES;
-                    ok = mbar_wait(full_bar(s), (consumed / C::STAGES) & 1, &s_abort);
+                    ok = mbar_wait(full_bar(s), (consumed / C::STAGES) & 1, &s_abort, p.wait_limit, p.status, 0x24);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t st = base + s * C::STAGE_BYTES;
@@ -842,7 +857,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
         for (int item = blockIdx.x; item < items && ok; item += gridDim.x, local++) {
             const Tile t = tile_of<BN, TW>(item, m_tiles, p, s_prefix, s_offs);
             const int b = local % C::NBUF;
-            ok = mbar_wait(acc_full(b), (local / C::NBUF) & 1, &s_abort);
+            ok = mbar_wait(acc_full(b), (local / C::NBUF) & 1, &s_abort, p.wait_limit, p.status, 0x25);
             if (!ok) break;
             tc_fence_after();
             const uint32_t taddr = tmem + b * C::ACC_COLS + ((uint32_t)(q * 32) << 16);
@@ -970,7 +985,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                 const int x_row = t.row0 + (int)rank * half;
                 for (int kb = 0; kb < kbs; kb++, issued++) {
                     const int s = issued % C::STAGES;
-                    ok = mbar_wait(empty_bar(s), ((issued / C::STAGES) & 1) ^ 1, &s_abort);
+                    ok = mbar_wait(empty_bar(s), ((issued / C::STAGES) & 1) ^ 1, &s_abort, p.wait_limit, p.status, 0x31);
                     if (!ok) break;
                     const uint32_t st = base + s * C::STAGE_BYTES;
                     const uint32_t bar = mapa_cluster(full_bar(s), 0);
@@ -987,7 +1002,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                 s_abort = 1;
                 if (rank == 0)
                     for (int i = max(0, issued - C::STAGES); i < issued; i++)     // copies in flight must land
-                        mbar_wait(full_bar(i % C::STAGES), (i / C::STAGES) & 1, nullptr);
+                        mbar_wait(full_bar(i % C::STAGES), (i / C::STAGES) & 1, nullptr, p.wait_limit, p.status, 0x32);
             }
         }
     } else if (warp == 1) {
@@ -1000,13 +1015,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                 const int n_eff = min(BN, (min(BN, t.row_end - t.row0) + 15) & ~15);
                 const uint32_t idesc = instr_desc(n_eff, PAIR_W);
                 const int b = local & 1;
-                ok = mbar_wait(acc_empty(b), ((local >> 1) & 1) ^ 1, &s_abort);   // both epilogues have drained it
+                ok = mbar_wait(acc_empty(b), ((local >> 1) & 1) ^ 1, &s_abort, p.wait_limit, p.status, 0x33);   // both epilogues have drained it
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t acc_addr = tmem + b * C::ACC_COLS;
                 for (int kb = 0; kb < kbs; kb++, consumed++) {
                     const int s = consumed % C::STAGES;
-                    ok = mbar_wait(full_bar(s), (consumed / C::STAGES) & 1, &s_abort);
+                    ok = mbar_wait(full_bar(s), (consumed / C::STAGES) & 1, &s_abort, p.wait_limit, p.status, 0x34);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t st = base + s * C::STAGE_BYTES;
@@ -1036,7 +1051,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         for (int item = pair; item < items && ok; item += pairs, local++) {
             const Tile t = tile_of<BN, PAIR_W>(item, m_tiles, p, s_prefix, s_offs);
             const int b = local & 1;
-            ok = mbar_wait(acc_full(b), (local >> 1) & 1, &s_abort);
+            ok = mbar_wait(acc_full(b), (local >> 1) & 1, &s_abort, p.wait_limit, p.status, 0x35);
             if (!ok) break;
             tc_fence_after();
             const uint32_t taddr = tmem + b * C::ACC_COLS + ((uint32_t)(q * 32) << 16);
@@ -1128,6 +1143,8 @@ int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, Params p, dim3 grid, 
 }
 
 int g_persistent = 1;
+uint32_t g_wait_limit = WAIT_LIMIT_US;
+int g_test_fault = 0;
 
 int sm_count() {
     static int n = 0;
@@ -1208,6 +1225,7 @@ MOE_API int moe_gemm_tc(const void* X, int ldx, const void* W, int num_groups, i
     p.out = out, p.out_bf16 = out_bf16, p.ldo = ldo, p.bias = bias, p.group_offsets = group_offsets;
     p.num_groups = num_groups, p.M = M, p.N = N, p.K = K, p.w_rows_per_group = w_rows, p.splits = splits;
     p.kb_per_split = per, p.partials = partials, p.tickets = tickets, p.status = status;
+    p.wait_limit = g_wait_limit, p.test_fault = g_test_fault;
     // token tiles: sum over groups of ceil(rows / bn) <= (non-empty groups) + floor(M / bn); CTAs past
     // the real count leave at once, but each still reserves its shared memory, so the bound is kept tight
     if (splits == 1 && bn >= 128 && g_persistent && (!group_offsets || num_groups <= MAX_SMEM_GROUPS)) {
@@ -1264,6 +1282,16 @@ MOE_API void moe_tc_set_persistent(int enabled) { g_persistent = enabled ? 1 : 0
 
 // The one-accumulator SwiGLU form of the persistent kernel on or off (on by default).
 MOE_API void moe_tc_set_swiglu_interleaved(int enabled) { g_swiglu_il = enabled ? 1 : 0; }
+
+// For the test of the bounded waits only: ``fault`` 1 makes the producer of the single-CTA kernels
+// load nothing, 2 makes their MMA issuer issue nothing, so that the other roles' waits run out after
+// ``wait_limit`` microseconds (0: the normal limit); the CTAs then set ST_WAIT_TIMEOUT in the status word,
+// wait for their own copies in flight, free their tensor memory and return.  (0, 0) restores the
+// normal behaviour.  Nothing faults and nothing waits without a limit.
+MOE_API void moe_tc_set_wait_test(int fault, unsigned wait_limit) {
+    g_test_fault = (fault == 1 || fault == 2) ? fault : 0;
+    g_wait_limit = wait_limit ? wait_limit : WAIT_LIMIT_US;
+}
 
 // Pairs of CTAs (cta_group::2) for the persistent form on or off (off by default: measured equal or
 // slower than single CTAs at the sizes tried, so what bounds those is not the activation traffic).

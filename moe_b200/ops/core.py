@@ -131,16 +131,42 @@ STATUS_BITS = {
 }
 
 
+# Where a bounded wait ran out (status[1]; the first one of a step): kernel and role, barrier.
+WAIT_SITES = {
+    0x10: "tensor-core product, one CTA a tile", 0x20: "tensor-core product, persistent",
+    0x30: "tensor-core product, pairs of CTAs", 0x40: "tensor-core prompt attention",
+}
+WAIT_ROLES = {
+    0x1: "producer: a free stage", 0x2: "producer: its own copies in flight", 0x3: "MMA issuer: a free accumulator",
+    0x4: "MMA issuer: a loaded stage", 0x5: "epilogue: a finished accumulator",
+}
+WAIT_ROLES_ATTENTION = {
+    0x1: "producer: a free key stage", 0x2: "producer: a free value stage", 0x3: "producer: its own copies in flight",
+    0x4: "MMA issuer: the queries", 0x5: "MMA issuer: a key tile", 0x6: "MMA issuer: a free score buffer",
+    0x7: "MMA issuer: a value tile", 0x8: "MMA issuer: P", 0x9: "softmax: the scores", 0xa: "softmax: its partner's maximum",
+    0xb: "softmax: the last P V product", 0xc: "softmax: its partner's sum", 0xd: "softmax: the final P V product",
+}
+
+
+def wait_site(code: int) -> str:
+    kernel, role = code & 0xf0, code & 0xf
+    roles = WAIT_ROLES_ATTENTION if kernel == 0x40 else WAIT_ROLES
+    return f"{WAIT_SITES.get(kernel, 'kernel ?')}, {roles.get(role, 'wait ?')} (site 0x{code:02x})"
+
+
 def new_status(device) -> torch.Tensor:
     return torch.zeros(4, dtype=torch.int32, device=device)
 
 
 def check_status(status: torch.Tensor):
     """Read the status word (synchronises) and raise if a kernel flagged a fault."""
-    v = int(status[0].item())
+    v, site = (int(x) for x in status[:2].tolist())
     if v:
         status.zero_()
-        raise KernelError("; ".join(m for b, m in STATUS_BITS.items() if v & b) or f"status {v}")
+        msg = "; ".join(m for b, m in STATUS_BITS.items() if v & b) or f"status {v}"
+        if v & 8 and site:
+            msg += f" [{wait_site(site)}]"
+        raise KernelError(msg)
 
 
 # --------------------------------------------------------------------------- kernels

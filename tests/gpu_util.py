@@ -19,6 +19,9 @@ import helpers
 TOL_F32 = 5e-5
 TOL_BF16 = 2e-2
 STD = {"float32": (0.02, 0.2), "bfloat16": (0.02, 0.08)}
+# for the configuration that is 264 wide (and whose heads are 128 long, so its sums are longer too): the
+# same gain per matrix, std * sqrt(width), as 0.2 / 0.08 give at a width of 96
+STD_WIDE = {"float32": 0.12, "bfloat16": 0.048}
 # The same tokens cut differently (whole / one by one / batched), same dtype.
 TOL_CUT_F32 = 1e-5
 TOL_CUT_BF16 = 1e-2
@@ -41,7 +44,8 @@ def engine_for(model_dirs, name: str, dtype: str, std: Optional[float] = None, s
     import moe_b200
     from moe_b200.engine import Engine
 
-    std = STD[dtype][1] if std is None else std
+    if std is None:
+        std = STD_WIDE[dtype] if helpers.CONFIGS[name]["hidden_size"] > 200 else STD[dtype][1]
 
     d = model_dirs.get(name, dtype, seed=seed, std=std, overrides=overrides)
     key = (d, dtype, max_tokens, max_slots)

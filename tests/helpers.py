@@ -363,3 +363,23 @@ def batches_schedule(requests: Dict[str, List[int]], batch_size: int, prompt_len
             for r in live:
                 done[r] += 1
     return steps
+
+
+def whole_schedule(requests):
+    """Each request alone and whole, logits at every place."""
+    return [{"entries": [(r, list(t), list(range(len(t))))], "end": [r]} for r, t in requests.items()]
+
+
+def tail_schedule(requests, tail: int = 32):
+    """Each request alone: all but the last ``tail`` tokens in one step, then one by one."""
+    steps = []
+    for r, t in requests.items():
+        head = max(1, len(t) - tail)
+        steps.append({"entries": [(r, list(t[:head]), list(range(head)))], "end": [r] if head == len(t) else []})
+        for i in range(head, len(t)):
+            steps.append({"entries": [(r, [t[i]], [0])], "end": [r] if i == len(t) - 1 else []})
+    return steps
+
+
+def stacked(logits, rid, n):
+    return torch.stack([logits[(rid, i)] for i in range(n)])

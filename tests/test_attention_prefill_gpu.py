@@ -79,3 +79,50 @@ def test_a_far_key_among_hundreds_and_the_windows_edge(tc, kernel):
     assert not torch.allclose(win[far + 100], vd[far, 0].float().cpu(), atol=0.2)
     ref = plain.attention(qd.double().cpu(), kd.double().cpu(), vd.double().cpu(), 100)
     assert float((win.double() - ref).abs().max()) < 2e-2 * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("kernel", ["tcgen05", "mma"])
+@pytest.mark.parametrize("window", [None, 80])
+@pytest.mark.parametrize("lens", [[5], [77], [150], [260], [150, 260, 9]])
+def test_two_heads_on_one_kv_head_of_128(tc, kernel, window, lens):
+    """The sizes of one of the engine tests' configurations: 2 query heads on 1 kv head of 128, a
+    window of 80, single sequences shorter and longer than a tile (the tensors end inside a tile)."""
+    nh, nkv, hd = 2, 1, 128
+    torch.manual_seed(sum(lens))
+    T = sum(lens)
+    q = torch.randn(T, nh, hd, device=DEV).to(torch.bfloat16)
+    k = torch.randn(T, nkv, hd, device=DEV).to(torch.bfloat16)
+    v = torch.randn(T, nkv, hd, device=DEV).to(torch.bfloat16)
+    out = run(tc, q, k, v, lens, nh, nkv, hd, window, kernel).double().cpu()
+    o = 0
+    for n in lens:
+        ref = plain.attention(q[o:o + n].double().cpu(), k[o:o + n].double().cpu(), v[o:o + n].double().cpu(), window)
+        assert float((out[o:o + n] - ref).abs().max()) < 2e-2 * float(ref.abs().max()), n
+        o += n
+
+
+@pytest.mark.parametrize("kernel,hd", [("tcgen05", 64), ("tcgen05", 128), ("mma", 64)])
+@pytest.mark.parametrize("window", [None, 150])
+def test_the_running_maximum_jumps_in_a_later_tile_for_some_rows_only(tc, kernel, hd, window):
+    """A key in the SECOND key tile scores far above everything before it, but only for a few
+    queries scattered over the rows of a warp: those rows' accumulated output has to be rescaled
+    (the maximum moves by much more than the slack the kernel allows itself), their neighbours' not.
+    Random inputs never do this: their scores stay within the slack after the first tile."""
+    nh = nkv = 1
+    n, far = 400, 200
+    torch.manual_seed(3)
+    q, k, v = torch.randn(n, 1, hd) * 0.1, torch.randn(n, 1, hd) * 0.1, torch.randn(n, 1, hd)
+    u = torch.zeros(hd)
+    u[5] = 1.0
+    k[far, 0] = 30.0 * u
+    hot = [far, far + 3, far + 17, far + 40, far + 41, far + 100, far + 149, far + 150, n - 1]
+    for r in hot:
+        q[r, 0] = 30.0 * u                       # score 900 / sqrt(hd) against key `far`, about 0 against the others
+    qd, kd, vd = (t.to(DEV).to(torch.bfloat16) for t in (q, k, v))
+    out = run(tc, qd, kd, vd, [n], nh, nkv, hd, window, kernel).double().cpu()
+    ref = plain.attention(qd.double().cpu(), kd.double().cpu(), vd.double().cpu(), window)
+    assert torch.isfinite(out).all()
+    assert float((out - ref).abs().max()) < 2e-2 * float(ref.abs().max())
+    for r in hot:
+        inside = window is None or far >= r + 1 - window
+        assert torch.allclose(out[r].float(), vd[far, 0].float().cpu(), atol=2e-2) == inside, r

@@ -31,58 +31,64 @@ def run_trace(model_dir, dtype, out_dir, steps, max_tokens):
     return done
 
 
-@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("A", "bfloat16"), ("B", "bfloat16")])
-def test_replay_in_unequal_batches_with_slots_reused(model_dirs, tmp_path, name, dtype):
-    d = model_dirs.get(name, dtype, seed=1, std=G.STD[dtype][1])
-    V = helpers.CONFIGS[name]["vocab_size"]
-    reqs = {f"q{i}": helpers.random_tokens(V, n, 200 + i) for i, n in enumerate([40, 9, 70, 3, 21])}
-    steps, where = [], {}                         # where[(request, position)] = (step, row)
-    step = 0
-    for batch in (["q0", "q1", "q2"], ["q3", "q4"]):     # 64 + 64 + 128 tokens held, then 64 + 64: max-tokens 256
-        live = list(batch)
-        done = {r: max(1, len(reqs[r]) // 2) for r in live}
-        entries, row = [], 0
-        for r in live:
-            want = list(range(0, done[r], 2)) + ([done[r] - 1] if (done[r] - 1) % 2 else [])
-            entries.append({"id": r, "tokens": reqs[r][:done[r]], "want": want})
+def as_trace(steps):
+    """The steps of ``helpers.run_schedule`` in the program's own format, and where each wanted
+    place lands: (request, position) -> (step, row)."""
+    out, where, at = [], {}, {}
+    for i, st in enumerate(steps):
+        row = 0
+        entries = []
+        for rid, toks, want in st["entries"]:
+            entries.append({"id": rid, "tokens": list(toks), "want": list(want)})
             for w in want:
-                where[(r, w)] = (step, row)
+                where[(rid, at.get(rid, 0) + w)] = (i, row)
                 row += 1
-        ends = [r for r in live if done[r] >= len(reqs[r])]
-        steps.append({"step": step, "entries": entries, "end": ends})
-        live = [r for r in live if r not in ends]
-        step += 1
-        while live:
-            entries = [{"id": r, "tokens": [reqs[r][done[r]]], "want": [0]} for r in live]
-            for i, r in enumerate(live):
-                where[(r, done[r])] = (step, i)
-                done[r] += 1
-            ends = [r for r in live if done[r] >= len(reqs[r])]
-            steps.append({"step": step, "entries": entries, "end": ends})
-            live = [r for r in live if r not in ends]
-            step += 1
+            at[rid] = at.get(rid, 0) + len(toks)
+        out.append({"step": i, "entries": entries, "end": list(st.get("end", []))})
+    return out, where
+
+
+def cut_steps(cut, reqs):
+    if cut == "whole":
+        return helpers.whole_schedule(reqs), 320
+    if cut == "tail":
+        return helpers.tail_schedule(reqs, 32), 320
+    # batches of unequal lengths on room for 256 tokens: (64 + 64 + 128), then (64 + 64 + 128)
+    ids = list(reqs)
+    return (helpers.batches_schedule({r: reqs[r] for r in ids}, 3, lambda r: len(reqs[r]) // 2, want_all=True), 256)
+
+
+@pytest.mark.parametrize("cut", ["whole", "tail", "batches"])
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "bfloat16"), ("D", "float32"), ("D", "bfloat16")])
+def test_the_program_replays_every_cut_and_matches_plain(model_dirs, tmp_path, name, dtype, cut):
+    """The program is driven as a user drives it (steps on standard input, files out) in the three
+    cuts: each request alone and whole; all but the last 32 tokens, then one by one; batches of
+    unequal lengths whose shorter requests end earlier, one batch after another on room for fewer
+    requests than there are, so that slots are used again.  Its files equal, to rounding of the last
+    bit, what the same schedule gives inside this process on an engine of the same size; and that
+    result is compared with the plain implementation directly, run with the engine's picks."""
+    import moe_b200
+
+    d, shared = G.engine_for(model_dirs, name, dtype)
+    V = helpers.CONFIGS[name]["vocab_size"]
+    lengths = [40, 9, 70, 3, 21, 100] if cut == "batches" else [40, 9, 70, 3, 150]
+    reqs = {f"q{i}": helpers.random_tokens(V, n, 200 + i) for i, n in enumerate(lengths)}
+    steps, max_tokens = cut_steps(cut, reqs)
+    trace, where = as_trace(steps)
     out = str(tmp_path / "out")
-    run_trace(d, dtype, out, steps, max_tokens=256)
+    run_trace(d, dtype, out, trace, max_tokens=max_tokens)
+    eng = moe_b200.Engine(shared.model, max_tokens=max_tokens)
+    logits, picks = helpers.run_schedule(eng, steps)
+    helpers.check_schedule_against_plain(d, reqs, logits, picks, G.tol(dtype), G.flip(dtype))
+    assert set(where) == set(logits)
     files = {}
-    scale, worst = 0.0, 0.0
-    _, eng = G.engine_for(model_dirs, name, dtype)
-    for rid, toks in reqs.items():
-        if dtype == "float32":
-            ref = helpers.plain_logits(d, toks)
-            limit = G.TOL_F32
-        else:
-            ref = helpers.replay_whole(eng, {rid: toks})[rid].double()      # in-process engine, whole request
-            limit = G.TOL_CUT_BF16
-        for (r, pos), (st, row) in where.items():
-            if r != rid:
-                continue
-            if st not in files:
-                files[st] = np.fromfile(os.path.join(out, f"{st}.f32"), dtype="<f4").reshape(-1, V)
-            got = torch.from_numpy(files[st][row].astype(np.float64))
-            worst = max(worst, float((got - ref[pos]).abs().max() / ref.abs().max()))
-        assert worst < limit, f"{rid}: {worst:.3g}"
-    # a step with nothing wanted writes no file
-    assert not os.path.exists(os.path.join(out, f"{step}.f32"))
+    for (rid, pos), (st, row) in where.items():
+        if st not in files:
+            files[st] = torch.from_numpy(np.fromfile(os.path.join(out, f"{st}.f32"), dtype="<f4").reshape(-1, V))
+        got, mine = files[st][row], logits[(rid, pos)]
+        assert float((got - mine).abs().max()) <= 1e-6 * float(mine.abs().max()), (rid, pos, st, row)
+    wanted_steps = {st for st, _ in where.values()}
+    assert sorted(os.listdir(out)) == sorted(f"{st}.f32" for st in wanted_steps)
 
 
 def test_steps_without_wanted_logits_write_nothing(model_dirs, tmp_path):
