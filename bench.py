@@ -68,6 +68,7 @@ class ClockSampler:
         self.rows, self.proc = [], None
 
     def start(self):
+        self.rows = []
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
                                           "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
@@ -126,14 +127,30 @@ def run_ours(args):
     clocks = ClockSampler()
 
     def decode_run(B, steps, warmup, sample_clocks=False, prompt_len=PROMPT_LEN):
-        """-> (ms per step, launches per step, h2d bytes per step, mean cache tokens, unique experts per layer)"""
-        eng = moe_b200.Engine(model, max_tokens=B * (-(-(prompt_len + steps + warmup + 8) // 64) * 64), max_slots=B)
+        """``prompt_len``: one length for all sequences, or (lo, hi) for unequal lengths drawn from a
+        seeded generator.  -> (ms per step, launches per step, h2d bytes per step, mean cache tokens a
+        sequence, unique experts per layer, clocks)"""
+        if isinstance(prompt_len, tuple):
+            import random
+
+            rng = random.Random(B)
+            lens = [rng.randint(*prompt_len) for _ in range(B)]
+        else:
+            lens = [prompt_len] * B
+        room = sum(-(-(n + steps + warmup + 8) // 64) * 64 for n in lens)
+        eng = moe_b200.Engine(model, max_tokens=room, max_slots=B)
         sampler = DeviceSampler(eng.cache.rng_states, eng.rt.device)
         greedy = SamplingParams()
         slots = [eng.new_sequence() for _ in range(B)]
-        prompts = [[(i * 7 + 13 + 31 * b) % V for i in range(prompt_len)] for b in range(B)]
-        for b0 in range(0, B, 8):                       # prompts in groups, to bound the workspace
-            eng.step(slots[b0:b0 + 8], prompts[b0:b0 + 8], [[] for _ in slots[b0:b0 + 8]])
+        prompts = [[(i * 7 + 13 + 31 * b) % V for i in range(lens[b])] for b in range(B)]
+        b0 = 0
+        while b0 < B:                                   # prompts in groups of at most 4,096 tokens, to bound the workspace
+            b1, held = b0, 0
+            while b1 < B and (b1 == b0 or held + lens[b1] <= 4096) and b1 - b0 < 8:
+                held += lens[b1]
+                b1 += 1
+            eng.step(slots[b0:b1], prompts[b0:b1], [[] for _ in slots[b0:b1]])
+            b0 = b1
 
         def one(i):
             logits = eng.step(slots, [[(i * 13 + 7 * b) % V] for b in range(B)], check=False)
@@ -146,7 +163,7 @@ def run_ours(args):
         for r in routed:
             r.trace = []
         one(warmup)
-        uniq = sum(len(torch.unique(r.trace[0][0])) for r in routed) / max(len(routed), 1)
+        uniq = sum(len(torch.unique(r.trace[0][0][:B])) for r in routed) / max(len(routed), 1)   # (rows past B: padding)
         for r in routed:
             r.trace = None
         torch.cuda.synchronize()
@@ -164,7 +181,7 @@ def run_ours(args):
         clk = clocks.stop() if sample_clocks else None
         eng.rt.check()
         launches = (core.launches - l0) / steps
-        mean_len = prompt_len + warmup + 1 + steps / 2
+        mean_len = sum(lens) / B + warmup + 1 + steps / 2
         h2d = (3 * B + 4 * B + 2 + B) * 4
         for s in slots:
             eng.release(s)
@@ -181,11 +198,14 @@ def run_ours(args):
     if args.sweep:
         # decode only, one line per batch size (not the benchmark record)
         for b in [int(v) for v in args.sweep.split(",")]:
-            m, _, _, mean_len, uniq, _ = decode_run(b, max(8, args.steps // 2), args.warmup,
-                                                    prompt_len=args.prompt_len or PROMPT_LEN)
-            gbs = decode_bytes(b, mean_len, uniq) / (m / 1e3) / 1e9
-            print(json.dumps({"batch": b, "cache_tokens": int(mean_len), "ms_per_step": round(m, 4), "tokens_per_s": round(b / (m / 1e3), 1),
-                              "hbm_frac": round(gbs / pk["hbm_gbs"], 4)}))
+            plen = (256, 2048) if args.unequal else (args.prompt_len or PROMPT_LEN)
+            m, _, _, mean_len, uniq, _ = decode_run(b, max(8, args.steps // 2), args.warmup, prompt_len=plen)
+            nb = decode_bytes(b, mean_len, uniq)
+            gbs = nb / (m / 1e3) / 1e9
+            print(json.dumps({"shape": args.shape, "layers": layers, "batch": b, "cache_tokens": int(mean_len),
+                              "experts_per_layer": round(uniq, 1), "bytes_per_step": int(nb), "ms_per_step": round(m, 4),
+                              "tokens_per_s": round(b / (m / 1e3), 1), "hbm_gbs": round(gbs, 1),
+                              "hbm_frac": round(gbs / pk["hbm_gbs"], 4)}), flush=True)
         return 0
 
     # ---- headline: batch 8 ---------------------------------------------------------------
@@ -195,11 +215,16 @@ def run_ours(args):
     nbytes = decode_bytes(B, mean_len, uniq)
     achieved = nbytes / (ms / 1e3) / 1e9
 
-    # ---- other batch sizes ----------------------------------------------------------------
-    points = {}
+    # ---- other batch sizes: at least 64 steps each, with clocks and roofline of their own --------
+    points, points_detail = {}, {}
     for b in (1, 64):
-        m, *_ = decode_run(b, max(8, args.steps // 4), args.warmup)
+        n_steps = max(64, args.steps)
+        m, _, _, ml, uq, ck = decode_run(b, n_steps, args.warmup, sample_clocks=True)
         points[f"decode_b{b}"] = round(b / (m / 1e3), 1)
+        gbs = decode_bytes(b, ml, uq) / (m / 1e3) / 1e9
+        points_detail[f"decode_b{b}"] = {"ms_per_step": round(m, 4), "steps": n_steps, "hbm_gbs": round(gbs, 1),
+                                         "hbm_frac": round(gbs / pk["hbm_gbs"], 4), "experts_per_layer": round(uq, 1),
+                                         "sm_mhz": ck["sm_mhz"], "reasons": ck["reasons"]}
 
     # ---- prefill of 2,048 tokens ------------------------------------------------------------
     eng = moe_b200.Engine(model, max_tokens=PREFILL_TOKENS + 64, max_slots=1)
@@ -256,6 +281,7 @@ def run_ours(args):
                      "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(nbytes),
                      "experts_per_layer": round(uniq, 1), "of": pk["source"]},
         "points": points,
+        "points_detail": points_detail,
     }
     print(json.dumps(out))
     return 0
@@ -331,6 +357,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8, help="with --profile-step decode: sequences in the batch")
     ap.add_argument("--shape", choices=["a2.7b", "57b"], default="a2.7b", help="with --sweep: the layer sizes")
     ap.add_argument("--prompt-len", type=int, default=0, help="with --sweep: tokens in each prompt (default 512)")
+    ap.add_argument("--unequal", action="store_true", help="with --sweep: prompts of unequal lengths, 256 to 2,048 tokens")
     ap.add_argument("--sweep", default=None, help="comma-separated batch sizes: print decode throughput for each "
                                                   "and no benchmark line")
     args = ap.parse_args()

@@ -19,6 +19,8 @@
 // transpose-reduction across the lanes that share a key row: no shared memory, no
 // per-lane strided walk.  Head sizes whose rows are not 64, 128, 256 or 512 bytes
 // take the slower row-per-lane kernel.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace {
@@ -113,7 +115,7 @@ attn_decode_fast_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
                         float* __restrict__ partial, const int* __restrict__ seq_of_token,
                         const int* __restrict__ pos, const int* __restrict__ slots, const int* __restrict__ tables,
                         int table_stride, int ring, int page_size, int num_pages, int nh, int nkv, int window,
-                        float scale, int* status, const FusedArgs fa) {
+                        float scale, int* status, const FusedArgs fa, int l2_prefetch_budget) {
     constexpr int EPC = Chunk<T>::N;       // elements per 16-byte chunk
     constexpr int HD = LPR * EPC;
     constexpr int RPI = 32 / LPR;          // rows per load instruction
@@ -127,10 +129,16 @@ attn_decode_fast_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
     // (positions, slots and page tables were written at the start of the step, more than one
     // kernel ago) and on the cache of earlier steps.  The CTA asks for its keys and values in L2
     // and forms the rotation angles, so that their latency passes while the predecessor ends.
-    const int split = blockIdx.x, nsplit = gridDim.x, kvh = blockIdx.y, t = blockIdx.z;
+    // grid.y: the kv heads, each `npass` times: block (kvh, pass) takes the query heads
+    // [pass * GH, pass * GH + GH) of the group.  (A group of more than GH heads used to be walked by
+    // one block, pass after pass; as blocks of their own the passes run side by side, and a group of
+    // seven heads, with many sequences, no longer takes four times the time of its keys.)
+    const int group = nh / nkv;
+    const int npass = (group + GH - 1) / GH;
+    const int split = blockIdx.x, nsplit = gridDim.x, kvh = blockIdx.y / npass, t = blockIdx.z;
+    const int h0 = (blockIdx.y % npass) * GH;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane % LPR, rgrp = lane / LPR;
-    const int group = nh / nkv;
     const int s = seq_of_token[t];
     const int p = s < 0 ? 0 : pos[t];
     const int lo = window > 0 ? max(0, p + 1 - window) : 0;
@@ -138,34 +146,41 @@ attn_decode_fast_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
     const int hi = FUSED ? p - 1 : p;
     const int half = FUSED ? fa.rot / 2 : 0;
     const int width = (nh + 2 * nkv) * HD;
-    const bool owner = FUSED && split == nsplit - 1 && warp == 0;   // takes the new key and appends it
+    const bool owner = FUSED && split == nsplit - 1 && warp == 0;   // takes the new key (and, for h0 == 0, appends it)
     // tiles of 32 positions, aligned to 32: the keys of a tile are contiguous in one page
     const int tile_lo = lo / 32, tile_hi = p / 32 + 1;
     const int tps = (tile_hi - tile_lo + nsplit - 1) / nsplit;
     const int tb = tile_lo + split * tps, te = min(tile_hi, tb + tps);
     const int* table = tables + (size_t)(s < 0 ? 0 : slots[s]) * table_stride;
-    if (s >= 0) {
+    if (s >= 0 && h0 == 0) {
         constexpr int LINES = 32 * HD * (int)sizeof(T) / 128;     // 128-byte lines of a tile of keys
-        for (int i = threadIdx.x; i < (te - tb) * 2 * LINES; i += blockDim.x) {
+        // Only as much as L2 can hold for ALL blocks of the launch (a quarter of it is left to them):
+        // with many sequences the blocks' keys and values together are larger than L2, and lines
+        // asked for too early would be gone again before they are used, to be read twice.
+        constexpr long long TILE_BYTES = 2ll * 32 * HD * (long long)sizeof(T);
+        const long long blocks = (long long)gridDim.x * gridDim.y * gridDim.z;
+        const long long share = (long long)l2_prefetch_budget / (blocks * TILE_BYTES);
+        const int ahead = (int)max(1ll, min((long long)(te - tb), share));
+        for (int i = threadIdx.x; i < ahead * 2 * LINES; i += blockDim.x) {
             const int tile = tb + i / (2 * LINES), r = i % (2 * LINES);
             const CachePos cp = cache_pos(tile * 32, ring, table, page_size, num_pages, nullptr);
             const size_t at = cache_index(cp, kvh, nkv, page_size, HD) + (size_t)(r % LINES) * (128 / sizeof(T));
             prefetch_l2((r < LINES ? k_cache : v_cache) + at);
         }
-        if (FUSED)
-            for (int i = threadIdx.x; i < half; i += blockDim.x)
-                sincosf((float)p * fa.inv_freq[i], &ang[half + i], &ang[i]);
     }
+    if (s >= 0 && FUSED)
+        for (int i = threadIdx.x; i < half; i += blockDim.x)
+            sincosf((float)p * fa.inv_freq[i], &ang[half + i], &ang[i]);
     pdl_sync();
     if (s < 0) {                                         // padding row: zeros (unfused: by the merge kernel)
-        if (FUSED && split == 0)
+        if (FUSED && split == 0 && h0 == 0)
             for (int i = threadIdx.x; i < group * HD; i += blockDim.x)
                 st_f((T*)fa.out + ((size_t)t * nh + (size_t)kvh * group) * HD + i, 0.f);
         return;
     }
     if (FUSED) __syncthreads();
 
-    for (int h0 = 0; h0 < group; h0 += GH) {
+    {
         const int gh = min(GH, group - h0);
         float qc[GH][EPC];
 #pragma unroll
@@ -337,7 +352,7 @@ attn_decode_fast_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
     __syncthreads();
     if (threadIdx.x == 0) {
         int* ticket = fa.tickets + (size_t)t * nkv + kvh;
-        const int last = atomicAdd(ticket, 1) == nsplit - 1;
+        const int last = atomicAdd(ticket, 1) == nsplit * npass - 1;
         if (last) *ticket = 0;                 // ready for the next launch
         s_last = last;
     }
@@ -528,13 +543,27 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ partial, T* _
     }
 }
 
+// Bytes of keys and values that the blocks of one launch may ask for in L2 ahead of their wait:
+// a quarter of the device's L2.
+int l2_prefetch_bytes() {
+    static int bytes = 0;
+    if (!bytes) {
+        int dev = 0, l2 = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, dev) != cudaSuccess)
+            l2 = 0;
+        bytes = l2 > 0 ? l2 / 4 : (8 << 20);
+        if (const char* e = getenv("MOE_B200_ATTN_L2_MB")) bytes = atoi(e) > 0 ? atoi(e) << 20 : 1;      // for measurements
+    }
+    return bytes;
+}
+
 template <typename T>
 int launch(const void* q, const void* k_cache, const void* v_cache, void* out, float* partial,
            const int* seq_of_token, const int* pos, const int* slots, const int* tables, int table_stride, int ring,
            int page_size, int num_pages, int num_tokens, int nh, int nkv, int hd, int window, float scale, int nsplit,
            int* status, cudaStream_t stream, const FusedArgs* fused = nullptr) {
-    dim3 grid(nsplit, nkv, num_tokens);
     const int group = nh / nkv;
+    dim3 grid(nsplit, nkv, num_tokens);
     const int row_bytes = hd * (int)sizeof(T);
     // the fast kernel reads q 16 bytes at a time: a q that is not 16-byte aligned (a view into the
     // middle of a buffer) takes the row-per-lane kernel, which reads it element by element.  Both
@@ -544,16 +573,19 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, f
                       (row_bytes == 64 || row_bytes == 128 || row_bytes == 256 || row_bytes == 512);
     if (fused && !fast) return -1;
     const FusedArgs fa = fused ? *fused : FusedArgs{};
+    const int budget = l2_prefetch_bytes();
 #define FAST(LPR, GH)                                                                                             \
     do {                                                                                                          \
+        grid.y = (unsigned)(nkv * ((group + GH - 1) / GH));                                                       \
+        if (grid.y > 65535) return (int)cudaErrorInvalidValue;                                                    \
         if (fused)                                                                                                \
             rc = launch_pdl(attn_decode_fast_kernel<T, LPR, GH, true>, grid, WARPS * 32, 0, stream, (const T*)q,  \
                             (const T*)k_cache, (const T*)v_cache, partial, seq_of_token, pos, slots, tables,      \
-                            table_stride, ring, page_size, num_pages, nh, nkv, window, scale, status, fa);        \
+                            table_stride, ring, page_size, num_pages, nh, nkv, window, scale, status, fa, budget); \
         else                                                                                                      \
             rc = launch_pdl(attn_decode_fast_kernel<T, LPR, GH, false>, grid, WARPS * 32, 0, stream, (const T*)q, \
                             (const T*)k_cache, (const T*)v_cache, partial, seq_of_token, pos, slots, tables,      \
-                            table_stride, ring, page_size, num_pages, nh, nkv, window, scale, status, fa);        \
+                            table_stride, ring, page_size, num_pages, nh, nkv, window, scale, status, fa, budget); \
     } while (0)
 #define FAST_G(LPR)                  \
     do {                             \

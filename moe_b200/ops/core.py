@@ -379,6 +379,12 @@ def decode_splits(device, num_tokens: int, nkv: int, max_end: int = 0) -> int:
     return n
 
 
+def _head_blocks(nh: int, nkv: int) -> int:
+    """Blocks along the heads of the decode attention's grid: a kv head's query heads two at a time."""
+    group = max(1, nh // max(nkv, 1))
+    return nkv * (1 if group == 1 else -(-group // 2))
+
+
 def attention_decode(q, view, batch, out, *, nh, window, scale, status):
     """Attention of one new token per sequence over the cache alone (its own key already
     appended); split along the keys and merged."""
@@ -386,7 +392,7 @@ def attention_decode(q, view, batch, out, *, nh, window, scale, status):
     T = batch.num_tokens
     if q.dtype != g.dtype or out.dtype != q.dtype:
         raise KernelError("attention: dtypes of queries, cache and output must agree")
-    nsplit = decode_splits(q.device, T, g.num_kv_heads, getattr(batch, "max_end", 0))
+    nsplit = decode_splits(q.device, T, _head_blocks(nh, g.num_kv_heads), getattr(batch, "max_end", 0))
     partial = torch.empty(T * nh * nsplit * (g.head_dim + 2), dtype=torch.float32, device=q.device)
     _ok(lib().moe_attention_decode(_p(q), _p(view.k), _p(view.v), _p(out), _p(partial), _dt(q),
                                    _p(batch.seq_of_token), _p(batch.pos), _p(batch.slots), _p(g.table),
@@ -420,7 +426,7 @@ def attention_decode_fused(qkv, inv_freq, rot, view, batch, out, *, nh, window, 
         raise KernelError("attention_decode_fused: shapes or dtypes do not fit the cache")
     if rot:
         _chk(inv_freq, "inv_freq", torch.float32, 1)
-    nsplit = decode_splits(qkv.device, T, g.num_kv_heads, getattr(batch, "max_end", 0))
+    nsplit = decode_splits(qkv.device, T, _head_blocks(nh, g.num_kv_heads), getattr(batch, "max_end", 0))
     partial = torch.empty(T * nh * nsplit * (g.head_dim + 2), dtype=torch.float32, device=qkv.device)
     tickets = _tickets(qkv.device, T * g.num_kv_heads)
     code = lib().moe_attention_decode_fused(_p(qkv), _p(inv_freq) if rot else None, rot, _p(view.k), _p(view.v),

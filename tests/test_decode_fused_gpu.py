@@ -92,7 +92,8 @@ def test_route_dispatch_equals_router_align_gather(core, E, k, H, norm, T, wdt):
 
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh,nkv,hd,rot,window", [(4, 2, 32, 32, None), (3, 1, 64, 32, 72), (2, 2, 128, 128, None),
-                                                  (5, 1, 128, 64, 100), (6, 2, 16, 16, None), (2, 1, 48, 48, None)])
+                                                  (5, 1, 128, 64, 100), (6, 2, 16, 16, None), (2, 1, 48, 48, None),
+                                                  (28, 4, 128, 128, None), (7, 1, 64, 64, 150)])
 def test_attention_decode_fused_equals_rope_commit_then_attention(core, dt, nh, nkv, hd, rot, window):
     """Rotation + append + attention + merge in one launch against the three launches it replaces:
     the same cache afterwards and the same output.  Sequences at a page's first and last place, in

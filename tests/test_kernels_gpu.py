@@ -227,7 +227,7 @@ def _attention_case(core, dt, nh, nkv, hd, window, lens_before, lens_new, seed=0
 
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 16, None), (3, 1, 32, 8), (6, 3, 48, 100), (2, 2, 128, None),
-                                               (5, 1, 80, 70), (1, 1, 256, 64)])
+                                               (5, 1, 80, 70), (1, 1, 256, 64), (28, 4, 128, None), (7, 1, 64, 150)])
 def test_attention_over_cache_and_new_keys(core, dt, nh, nkv, hd, window):
     tol = 2e-5 if dt == torch.float32 else 2e-2
     # prompts from an empty cache, unequal lengths
