@@ -50,6 +50,7 @@ def host_lib():
             "moe_ledger_extend": ([P, I, I, _IP, I], I), "moe_ledger_truncate": ([P, I, I, _IP], I),
             "moe_ledger_tokens_held": ([P], LL),
             "moe_ledger_reserve": ([P, I, _IP, _IP, _IP, _IP, _IP, I, LL], I),
+            "moe_ledger_check": ([P, I, _IP, _IP, _IP, LL], I),
             "moe_pack_step": ([_IP, LL, I, _IP, _IP, _IP, _IP, _IP, _IP, _IP, _IP], LL),
             "moe_pack_decode": ([_IP, I, I, _IP, _IP, _IP, I, I, _IP, _IP, I], I),
             "moe_pack_prompt": ([_IP, I, I, I, _IP, _IP, _IP, I, I, _IP, I, _IP, I], I),
@@ -262,6 +263,13 @@ class CacheLedger:
         if n > cap:
             raise CacheError("internal: more page-table updates than a step can make")
         return list(starts[:B]), upd[:n]
+
+    def check(self, slots: Sequence[int], counts: Sequence[int], table_caps: Sequence[int], max_tokens: int = 0) -> None:
+        """Raise what ``reserve`` would raise for this step; change nothing."""
+        sl, B = ints(slots)
+        ct, _ = ints(counts)
+        caps, _ = ints(table_caps)
+        _ok(_lib.moe_ledger_check(self._h, B, sl, ct, caps, max_tokens))
 
     def truncate(self, slot: int, new_length: int, windows: Sequence[int] = ()) -> None:
         """Forget everything at or after ``new_length`` (src/model.rs:176-189).  Pages are

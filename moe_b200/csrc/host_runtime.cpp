@@ -291,13 +291,14 @@ MOE_API long long moe_ledger_tokens_held(void* p) {
 // sequence may hold in group g (its page table's width; 0: no limit).  Writes each sequence's
 // length before the step to starts[] and the changed page-table entries to updates[] as
 // (group, slot, index, page); returns their number (which may exceed cap: call again with more).
-MOE_API int moe_ledger_reserve(void* p, int B, const int* slots, const int* counts, const int* table_cap, int* starts,
-                               int* updates, int cap, long long max_tokens) {
-    Ledger& L = *static_cast<Ledger*>(p);
+// What a step needs, without changing anything: 0 if every sequence finds its room in every group
+// (total_updates: the page-table entries that would change), else the error of moe_ledger_reserve.
+static int check_step(Ledger& L, int B, const int* slots, const int* counts, const int* table_cap, long long max_tokens,
+                      long long* total_updates) {
     const int G = (int)L.groups.size();
     std::vector<char> seen(L.slots.num_slots, 0);
     std::vector<long long> need(G, 0);
-    long long total_updates = 0;
+    *total_updates = 0;
     for (int i = 0; i < B; i++) {
         const int s = slots[i];
         if (!L.slots.is_held(s)) return fail(ERR_CACHE, "slot " + std::to_string(s) + " is not held");
@@ -317,8 +318,17 @@ MOE_API int moe_ledger_reserve(void* p, int B, const int* slots, const int* coun
             return fail(ERR_CACHE, "the cache is full: this step needs " + std::to_string(need[g]) + " more pages of " +
                                        std::to_string(PAGE_TOKENS) + " tokens, " + std::to_string(L.groups[g].pool.num_free()) +
                                        " are free (max_tokens = " + std::to_string(max_tokens) + ")");
-        total_updates += need[g];
+        *total_updates += need[g];
     }
+    return 0;
+}
+
+MOE_API int moe_ledger_reserve(void* p, int B, const int* slots, const int* counts, const int* table_cap, int* starts,
+                               int* updates, int cap, long long max_tokens) {
+    Ledger& L = *static_cast<Ledger*>(p);
+    long long total_updates = 0;
+    const int rc = check_step(L, B, slots, counts, table_cap, max_tokens, &total_updates);
+    if (rc) return rc;
     if (total_updates > cap) return (int)std::min<long long>(total_updates, INT32_MAX);   // nothing changed yet
     int at = 0;
     for (int i = 0; i < B; i++) {
@@ -326,6 +336,14 @@ MOE_API int moe_ledger_reserve(void* p, int B, const int* slots, const int* coun
         at = L.grow(slots[i], L.length[slots[i]] + counts[i], updates, cap, at);
     }
     return at;
+}
+
+// Would moe_ledger_reserve succeed?  0, or its error; nothing changes either way.  (A step that the
+// engine runs in several pieces asks this first, so that it fails before its first piece or not at all.)
+MOE_API int moe_ledger_check(void* p, int B, const int* slots, const int* counts, const int* table_cap,
+                             long long max_tokens) {
+    long long total_updates = 0;
+    return check_step(*static_cast<Ledger*>(p), B, slots, counts, table_cap, max_tokens, &total_updates);
 }
 
 // ---- packing a step ------------------------------------------------------------------------------

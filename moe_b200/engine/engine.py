@@ -35,6 +35,9 @@ GRAPH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 # from graphs, padded to these numbers of token rows and of sequences.
 PROMPT_TOKEN_BUCKETS = (64, 128, 256, 512)
 PROMPT_SEQ_BUCKETS = (1, 2, 4, 8)
+# A step of more tokens than this is run in pieces of at most this many (the reference tiles a prompt
+# at 64 tokens, src/main.rs:499-505): what a step needs beside the cache grows with its tokens.
+MAX_STEP_TOKENS = int(os.environ.get("MOE_B200_MAX_STEP_TOKENS", "8192"))
 MAX_GRAPHS = 48      # captured steps an engine keeps; the one used longest ago goes first
 LAST_TOKEN = -1      # as a token id (with ``from_last``): the token sampled last for the sequence
 
@@ -216,6 +219,7 @@ class Engine:
         self._stage_event = torch.cuda.Event()
         self._stage_busy = False
         self.steps_run = 0
+        self.max_step_tokens = MAX_STEP_TOKENS
         parts = [p for b in model.blocks for p in b.parts()] + [model.embedding, model.final_norm, model.head]
         graph_safe = all(getattr(p, "graph_safe", False) for p in parts)
         self.use_graphs = graph_safe if use_graphs is None else (use_graphs and graph_safe)
@@ -311,6 +315,8 @@ class Engine:
             for i in w:
                 if not 0 <= i < n:
                     raise ValueError(f"wanted place {i} is not among the {n} tokens of this step")
+        if sum(counts) > self.max_step_tokens and not from_last:
+            return self._step_in_pieces(slots, tokens, want, counts, check)
         starts, updates = self._reserve(slots, counts)
         self.steps_run += 1
 
@@ -376,6 +382,39 @@ class Engine:
         if check:
             self.rt.check()
         return logits
+
+    def _step_in_pieces(self, slots, tokens, want, counts, check) -> Optional[torch.Tensor]:
+        """A step too large for one go: the sequences' tokens are fed in pieces of at most
+        ``max_step_tokens`` together, sequence after sequence, each piece a step of its own that goes
+        on from the cache.  The logits come back in the order asked for.  The cache is asked first
+        whether the WHOLE step fits, so that it fails before the first piece or not at all."""
+        self.cache.ledger.check(slots, counts, self._table_caps, self.cache.max_tokens)
+        B = len(slots)
+        done = [0] * B
+        rows: Dict[Tuple[int, int], torch.Tensor] = {}
+        while any(d < n for d, n in zip(done, counts)):
+            room = self.max_step_tokens
+            sl, tk, wn, who = [], [], [], []
+            for i in range(B):
+                n = min(counts[i] - done[i], room)
+                if n <= 0:
+                    continue
+                lo, hi = done[i], done[i] + n
+                sl.append(slots[i]), tk.append(tokens[i][lo:hi]), who.append(i)
+                wn.append([w - lo for w in want[i] if lo <= w < hi])
+                room -= n
+            lg = self.step(sl, tk, wn, check=False)
+            at = 0
+            for i, w in zip(who, wn):
+                for x in w:
+                    rows[(i, x + done[i])] = lg[at].clone()
+                    at += 1
+            for i, t in zip(who, tk):
+                done[i] += len(t)
+        if check:
+            self.rt.check()
+        order = [(i, w) for i in range(B) for w in want[i]]
+        return torch.stack([rows[k] for k in order]) if order else None
 
     def begin_step_and_sample(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], sampler, params,
                               histories=None, from_last: bool = False):

@@ -31,8 +31,8 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompil
 
 # library name -> sources; what a model needs is decided by the caller
 LIBRARIES: Dict[str, List[str]] = {
-    "core": ["embed_norm.cu", "gemm_generic.cu", "rope_cache.cu", "attention_generic.cu", "attention_decode.cu",
-             "moe.cu", "sampling.cu"],
+    "core": ["embed_norm.cu", "gemm_generic.cu", "rope_cache.cu", "attention_generic.cu", "attention_tiled.cu",
+             "attention_decode.cu", "moe.cu", "sampling.cu"],
     # tcgen05 / TMA kernels of the bfloat16 path; a float32 model never builds or loads them
     "tc": ["gemm_tc.cu", "attention_prefill.cu", "attention_prefill_tc.cu"],
     # host side of a step (cache ledger, step packing): plain C++, no CUDA

@@ -44,6 +44,7 @@ def lib():
             "moe_route_dispatch": [P, P, I, I, I, I, I, F, P, P, P, P, P, P, P, P, I, P, P],
             "moe_rope_commit": [P, P, P, I, I, I, I, I, P, P, P, I, P, P, P, I, I, I, I, P, P],
             "moe_attention_decode": [P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],
+            "moe_attention_tiled": [P, P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P],
             "moe_attention_decode_fused": [P, P, I, P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],
             "moe_norm_route": [P, P, P, F, I, I, P, P, P, P, I, I, I, I, F, P, P, P, P, P, P, P, P, P, P, P],
             "moe_align": [P, I, I, I, P, P, P, P, P],
@@ -330,6 +331,24 @@ def attention_generic(q, k_new, v_new, view, batch, out, *, nh, window, scale, u
                                     _p(batch.slots), _p(g.table), g.table.stride(0), g.ring, g.page_size,
                                     g.num_pages, T, nh, g.num_kv_heads, g.head_dim, int(window or 0), float(scale),
                                     1 if use_local else 0, _p(status), _stream()), "attention_generic")
+
+
+def attention_tiled(q, k_new, v_new, view, batch, out, *, nh, window, scale, use_local, status) -> bool:
+    """The same as ``attention_generic`` with 64 queries of a (sequence, head) to a block and the
+    keys staged through shared memory (32-bit arithmetic on the CUDA cores).  False, with nothing
+    launched, for a layout it does not take (a page size other than 64, unaligned rows)."""
+    g = view.group
+    if q.dtype != g.dtype or out.dtype != q.dtype:
+        raise KernelError("attention: dtypes of queries, cache and output must agree")
+    code = lib().moe_attention_tiled(_p(q), _p(k_new), _p(v_new), _p(view.k), _p(view.v), _p(out), _dt(q),
+                                     _p(batch.cu_seqlens), _p(batch.seq_start), _p(batch.slots), _p(g.table),
+                                     g.table.stride(0), g.ring, g.page_size, g.num_pages, batch.num_seqs,
+                                     batch.num_tokens, nh, g.num_kv_heads, g.head_dim, int(window or 0), float(scale),
+                                     1 if use_local else 0, _p(status), _stream())
+    if code == -1:
+        return False
+    _ok(code, "attention_tiled")
+    return True
 
 
 def router(h32, w_router, top_k, norm_topk, scale, topk_idx, topk_w, *, shared_gate_w=None, shared_gate=None,

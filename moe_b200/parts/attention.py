@@ -133,9 +133,11 @@ class GQAttention(Part):
                 done = tc.attention_prefill(q, k_new, v_new, batch, ctx, nh=self.nh, nkv=self.nkv, hd=self.hd,
                                             window=self.window, scale=self.scale, status=rt.status)
             if not done:
-                # keys of earlier steps from the cache, keys of this step from its own buffers
-                core.attention_generic(q, k_new, v_new, cache_view, batch, ctx, nh=self.nh, window=self.window,
-                                       scale=self.scale, use_local=self.own_kv, status=rt.status)
+                # keys of earlier steps from the cache, keys of this step from its own buffers: 64
+                # queries to a block, 32-bit arithmetic (the plain kernel where that one declines)
+                kw = dict(nh=self.nh, window=self.window, scale=self.scale, use_local=self.own_kv, status=rt.status)
+                if not core.attention_tiled(q, k_new, v_new, cache_view, batch, ctx, **kw):
+                    core.attention_generic(q, k_new, v_new, cache_view, batch, ctx, **kw)
             if self.own_kv and not committed:
                 core.kv_commit(k_new, v_new, cache_view, batch, rt.status)
         return linear(rt, ctx, self.wo)

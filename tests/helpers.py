@@ -254,9 +254,13 @@ def run_schedule(engine, steps):
                 lg = lg.float().cpu() if lg is not None else None
                 taken, row, tok_row = {}, 0, 0
                 recorded = []
+                times = {id(p): sum(1 for x in parts if x is p) for p in parts}     # runs of a part in one pass
                 for p in parts:
                     i = taken.get(id(p), 0)
-                    recorded.append(p.trace[i][0].cpu().tolist())
+                    # (a step that the engine runs in pieces leaves one record per piece and run: the
+                    # pieces' tokens, one after another, are the step's tokens in their order)
+                    mine = p.trace[i::times[id(p)]]
+                    recorded.append([pick for rec in mine for pick in rec[0].cpu().tolist()])
                     taken[id(p)] = i + 1
                 for rid, toks, want in entries:
                     for w in want:

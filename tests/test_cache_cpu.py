@@ -115,3 +115,18 @@ def test_random_walk_keeps_every_invariant():
     for s in list(live):
         led.release(s)
     assert all(g.pool.num_free == g.pool.num_pages - 1 for g in led.groups) and led.slots.num_free == 8
+
+
+def test_check_says_what_reserve_would_and_changes_nothing():
+    led = CacheLedger(2, [5, 5], [0, 2])
+    a, b = led.acquire(), led.acquire()
+    led.check([a, b], [100, 100], [4, 0])                    # 2 + 2 pages of the 4 free in either group
+    with pytest.raises(CacheError):
+        led.check([a, b], [100, 200], [4, 0])                # 2 + 4 pages: more than the 4 free
+    with pytest.raises(CacheError):
+        led.check([a], [300], [4, 0])                        # 5 pages: more than the page table holds
+    with pytest.raises(ValueError):
+        led.check([a, a], [1, 1], [4, 0])
+    assert led.length[a] == 0 and led.length[b] == 0 and led.groups[0].pool.num_free == 4
+    starts, upd = led.reserve([a, b], [100, 100], [4, 0])
+    assert starts == [0, 0] and led.groups[0].pool.num_free == 0

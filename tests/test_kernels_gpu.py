@@ -202,6 +202,11 @@ def _attention_case(core, dt, nh, nkv, hd, window, lens_before, lens_new, seed=0
     out = torch.empty(q.shape[0], nh * hd, device=DEV, dtype=dt)
     scale = 1.0 / math.sqrt(hd)
     core.attention_generic(q, kn, vn, view, b1, out, nh=nh, window=window, scale=scale, use_local=True, status=st)
+    # the tiled kernel (64 queries to a block) gives the same as the plain one
+    tiled = torch.full_like(out, float("nan"))
+    assert core.attention_tiled(q, kn, vn, view, b1, tiled, nh=nh, window=window, scale=scale, use_local=True, status=st)
+    cut = 2e-6 if dt == torch.float32 else 1e-2
+    assert float((tiled.double() - out.double()).abs().max()) <= cut * float(out.double().abs().max())
     # after the commit, the same queries must see the same thing from the cache alone
     core.kv_commit(kn, vn, view, b1, st)
     out2 = torch.empty_like(out)
@@ -213,6 +218,9 @@ def _attention_case(core, dt, nh, nkv, hd, window, lens_before, lens_new, seed=0
         assert float((out3.double() - out2.double()).abs().max()) < 2e-2 * float(out3.double().abs().max())
     elif window is None:
         core.attention_generic(q, kn, vn, view, b1, out2, nh=nh, window=window, scale=scale, use_local=False, status=st)
+        t2 = torch.full_like(out, float("nan"))
+        assert core.attention_tiled(q, kn, vn, view, b1, t2, nh=nh, window=window, scale=scale, use_local=False, status=st)
+        assert float((t2.double() - out2.double()).abs().max()) <= cut * float(out2.double().abs().max())
     else:
         out2 = None
     assert int(st[0]) == 0
@@ -239,6 +247,9 @@ def test_attention_over_cache_and_new_keys(core, dt, nh, nkv, hd, window):
     assert out2 is not None and float((out2 - ref).abs().max()) < tol * float(ref.abs().max())
     # a continuation by several tokens
     out, out2, ref = _attention_case(core, dt, nh, nkv, hd, window, [10, 100], [7, 30], seed=2)
+    assert float((out - ref).abs().max()) < tol * float(ref.abs().max())
+    # chunks of a long prompt: more than one tile of queries, past a page's and a tile's edge
+    out, out2, ref = _attention_case(core, dt, nh, nkv, hd, window, [130, 64, 0], [70, 129, 200], seed=3)
     assert float((out - ref).abs().max()) < tol * float(ref.abs().max())
 
 

@@ -152,3 +152,28 @@ def test_rewinding_then_continuing_equals_a_fresh_sequence(model_dirs, name, dty
         assert eng.length(f) == n
         eng.truncate(f, n - 1)                       # one step back is always inside the ring's slack or window
     eng.release(s), eng.release(f)
+
+
+@pytest.mark.parametrize("name,dtype", [(n, dt) for n in ("A", "B", "D") for dt in ("float32", "bfloat16")])
+@pytest.mark.parametrize("piece", [64, 100])
+def test_a_step_too_large_for_one_go_is_run_in_pieces_with_the_same_result(model_dirs, name, dtype, piece):
+    """The engine runs a step of more than ``max_step_tokens`` tokens in pieces (the reference tiles
+    its prompts at 64 tokens and tests that the result does not depend on it: src/main.rs:499-505,
+    tests/oracle.rs:71-75): two prompts in ONE step, every place wanted, against the plain
+    implementation; and a step that does not fit the cache fails before its first piece."""
+    from moe_b200.cache import CacheError
+
+    V = helpers.CONFIGS[name]["vocab_size"]
+    reqs = {"x": helpers.random_tokens(V, 230, 31), "y": helpers.random_tokens(V, 131, 32)}
+    d, eng = engine(model_dirs, name, dtype, max_tokens=64 * 7, max_slots=2)
+    eng.max_step_tokens = piece
+    steps = [{"entries": [(r, t, list(range(len(t)))) for r, t in reqs.items()], "end": list(reqs)}]
+    before = eng.steps_run
+    logits, picks = helpers.run_schedule(eng, steps)
+    assert eng.steps_run - before == -(-361 // piece)
+    helpers.check_schedule_against_plain(d, reqs, logits, picks, G.tol(dtype), G.flip(dtype))
+    a, b = eng.new_sequence(), eng.new_sequence()
+    with pytest.raises(CacheError):
+        eng.step([a, b], [reqs["x"], reqs["x"]])         # 4 + 4 pages of the 7 there are
+    assert eng.length(a) == 0 and eng.length(b) == 0
+    eng.release(a), eng.release(b)
