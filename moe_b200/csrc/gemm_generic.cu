@@ -149,6 +149,116 @@ gemm_generic_kernel(const AT* __restrict__ A, int lda, const int* __restrict__ a
     }
 }
 
+// The same product for FEW rows (a step of one token per sequence): the time is the weight stream.
+// A block takes 64 output features and up to RT rows of A; chunk by chunk of KC k it brings the
+// weights [64][KC] (coalesced, 16 bytes a thread) and the rows [RT][KC] into shared memory, and
+// thread (feature f, row pair) walks the chunk with ONE accumulator per output, k ascending: the very
+// order of the tile kernel above, so that a token's product is the same to the bit whether it comes
+// alone (a decode step) or among thousands (a prompt).  Groups and gathered rows as above, in tiles
+// of RT rows.
+constexpr int RT = 8, RF = 64, KC = 128, WS = KC + 4, RTHREADS = 256;
+
+template <typename AT, typename WT, typename OT>
+__global__ void __launch_bounds__(RTHREADS)
+gemm_rows_kernel(const AT* __restrict__ A, int lda, const int* __restrict__ a_rows, int a_src_rows,
+                 const WT* __restrict__ W, long long w_group_stride, OT* __restrict__ C, int ldc,
+                 const float* __restrict__ bias, const int* __restrict__ group_offsets, int num_groups, int M, int N,
+                 int K, int a_vec_ok, int w_vec_ok, int* status) {
+    __shared__ __align__(16) float Ws[RF][WS];
+    __shared__ __align__(16) float As[RT][KC];
+    __shared__ int s_group, s_row0, s_row1;
+    __shared__ long long s_src[RT];
+    if (threadIdx.x == 0) {
+        int g = 0, r0 = 0, r1 = M;
+        int tile = blockIdx.y;
+        if (group_offsets) {
+            g = -1;
+            for (int i = 0; i < num_groups; i++) {
+                const int b = group_offsets[i], e = group_offsets[i + 1];
+                const int tiles = (e - b + RT - 1) / RT;
+                if (tile < tiles) {
+                    g = i, r0 = b + tile * RT, r1 = e;
+                    break;
+                }
+                tile -= tiles;
+            }
+        } else {
+            r0 = tile * RT;
+            if (r0 >= M) g = -1;
+        }
+        s_group = g, s_row0 = r0, s_row1 = r1;
+    }
+    __syncthreads();
+    const int g = s_group;
+    if (g < 0) return;
+    const int row0 = s_row0, rows = min(RT, s_row1 - row0);
+    if (threadIdx.x < RT) {
+        long long src = -1;
+        if ((int)threadIdx.x < rows) {
+            src = a_rows ? a_rows[row0 + threadIdx.x] : row0 + threadIdx.x;
+            if (src < 0 || src >= a_src_rows) {
+                atomicOr(status, ST_BAD_ROW);
+                src = -1;
+            }
+        }
+        s_src[threadIdx.x] = src;
+    }
+    const int tid = threadIdx.x, f = tid % RF, rg = tid / RF;      // this thread's feature and pair of rows
+    const int n0 = blockIdx.x * RF;
+    const WT* Wg = W + (size_t)g * (size_t)w_group_stride;
+    float acc0 = 0.f, acc1 = 0.f;
+
+    // A chunk's loads are issued one chunk ahead, into registers, and so are in flight while the
+    // chunk before it is multiplied.
+    constexpr int WPT = RF * (KC / 4) / RTHREADS;      // 16-byte pieces of the weight chunk per thread
+    float wr[WPT][4], ar[4];
+    __syncthreads();                                   // s_src is written
+    auto fetch = [&](int c0) {
+        const int kc = min(KC, K - c0);
+#pragma unroll
+        for (int i = 0; i < WPT; i++) {
+            const int idx = tid + i * RTHREADS, fl = idx / (KC / 4), k = (idx % (KC / 4)) * 4;
+            const int valid = min(4, kc - k);
+            wr[i][0] = wr[i][1] = wr[i][2] = wr[i][3] = 0.f;
+            if (n0 + fl < N && valid > 0) load4<WT>(Wg + (size_t)(n0 + fl) * K + c0 + k, w_vec_ok, valid, wr[i]);
+        }
+        const int r = tid / (KC / 4), k = (tid % (KC / 4)) * 4;           // RT * KC / 4 == RTHREADS
+        const long long src = s_src[r];
+        const int valid = min(4, kc - k);
+        ar[0] = ar[1] = ar[2] = ar[3] = 0.f;
+        if (src >= 0 && valid > 0) load4<AT>(A + (size_t)src * lda + c0 + k, a_vec_ok, valid, ar);
+    };
+    if (K > 0) fetch(0);
+    for (int c0 = 0; c0 < K; c0 += KC) {
+        const int kc = min(KC, K - c0);
+        __syncthreads();              // the previous chunk is no longer read
+#pragma unroll
+        for (int i = 0; i < WPT; i++) {
+            const int idx = tid + i * RTHREADS, fl = idx / (KC / 4), k = (idx % (KC / 4)) * 4;
+            *reinterpret_cast<float4*>(&Ws[fl][k]) = make_float4(wr[i][0], wr[i][1], wr[i][2], wr[i][3]);
+        }
+        *reinterpret_cast<float4*>(&As[tid / (KC / 4)][(tid % (KC / 4)) * 4]) = make_float4(ar[0], ar[1], ar[2], ar[3]);
+        __syncthreads();
+        if (c0 + KC < K) fetch(c0 + KC);
+#pragma unroll 8
+        for (int k = 0; k < KC; k += 4) {
+            if (k >= kc) break;       // (a chunk's tail is zero anyway; this only saves the work)
+            const float4 w = *reinterpret_cast<const float4*>(&Ws[f][k]);
+            const float4 a = *reinterpret_cast<const float4*>(&As[2 * rg][k]);
+            const float4 b = *reinterpret_cast<const float4*>(&As[2 * rg + 1][k]);
+            acc0 = fmaf(a.x, w.x, acc0), acc0 = fmaf(a.y, w.y, acc0), acc0 = fmaf(a.z, w.z, acc0), acc0 = fmaf(a.w, w.w, acc0);
+            acc1 = fmaf(b.x, w.x, acc1), acc1 = fmaf(b.y, w.y, acc1), acc1 = fmaf(b.z, w.z, acc1), acc1 = fmaf(b.w, w.w, acc1);
+        }
+    }
+    const int n = n0 + f;
+    if (n < N) {
+        const float bv = bias ? bias[n] : 0.f;
+        if (2 * rg < rows) st_f(C + (size_t)(row0 + 2 * rg) * ldc + n, bias ? acc0 + bv : acc0);
+        if (2 * rg + 1 < rows) st_f(C + (size_t)(row0 + 2 * rg + 1) * ldc + n, bias ? acc1 + bv : acc1);
+    }
+}
+static_assert(RT * (KC / 4) == RTHREADS && RT == 2 * (RTHREADS / RF), "the thread layout of gemm_rows_kernel");
+
 template <typename AT, typename WT, typename OT>
 int launch(const void* A, int lda, const int* a_rows, int a_src_rows, const void* W, long long w_group_stride, void* C,
            int ldc, const float* bias, const int* group_offsets, int num_groups, int M, int N, int K, int* status,
@@ -156,6 +266,15 @@ int launch(const void* A, int lda, const int* a_rows, int a_src_rows, const void
     if (M <= 0 || N <= 0) return 0;
     const int a_vec = (K % 4 == 0) && (lda % 4 == 0) && ((uintptr_t)A % 16 == 0);
     const int w_vec = (K % 4 == 0) && ((uintptr_t)W % 16 == 0) && ((w_group_stride * (long long)sizeof(WT)) % 16 == 0);
+    if (M <= (group_offsets ? 8 * RT : 2 * RT)) {
+        // few rows: the weight stream is what takes the time
+        const int r_tiles = group_offsets ? (M < num_groups ? M : num_groups) + M / RT : (M + RT - 1) / RT;
+        dim3 rgrid((N + RF - 1) / RF, r_tiles);
+        gemm_rows_kernel<AT, WT, OT><<<rgrid, RTHREADS, 0, stream>>>(
+            (const AT*)A, lda, a_rows, a_src_rows, (const WT*)W, w_group_stride, (OT*)C, ldc, bias, group_offsets,
+            num_groups, M, N, K, a_vec, w_vec, status);
+        return launch_status();
+    }
     const int m_tiles = (M + BM - 1) / BM + (group_offsets ? num_groups : 0);
     dim3 grid((N + BN - 1) / BN, m_tiles);
     if (grid.y > 65535) return (int)cudaErrorInvalidValue;

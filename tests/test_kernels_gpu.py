@@ -66,7 +66,8 @@ def test_rmsnorm_with_residual_rows_and_bf16_copy(core, H):
                                          (torch.bfloat16, torch.bfloat16, torch.float32),
                                          (torch.bfloat16, torch.float32, torch.bfloat16),
                                          (torch.float32, torch.bfloat16, torch.float32)])
-@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (37, 53, 19), (130, 200, 96), (64, 64, 16), (3, 1000, 333)])
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (37, 53, 19), (130, 200, 96), (64, 64, 16), (3, 1000, 333), (8, 2048, 1408),
+                                    (16, 61, 2048), (13, 331, 1100), (17, 40, 2052)])
 def test_gemm_generic_any_size_and_dtype(core, adt, wdt, odt, M, N, K):
     a = torch.randn(M, K, device=DEV).to(adt)
     w = torch.randn(N, K, device=DEV).to(wdt)
@@ -76,6 +77,21 @@ def test_gemm_generic_any_size_and_dtype(core, adt, wdt, odt, M, N, K):
     ref = a.double() @ w.double().T + b.double()
     tol = 1e-5 if odt == torch.float32 else 1e-2
     assert float((out.double() - ref).abs().max() / ref.abs().max()) < tol
+
+
+def test_gemm_generic_gives_a_row_the_same_to_the_bit_alone_and_among_many(core):
+    """Few rows and many rows take different kernels; both add the products of one output in the
+    order of k with one accumulator, so a token's projection does not depend on its company."""
+    torch.manual_seed(4)
+    for K, N in ((2048, 300), (1100, 64), (72, 1000)):
+        a = torch.randn(200, K, device=DEV)
+        w = torch.randn(N, K, device=DEV)
+        many = torch.empty(200, N, device=DEV)
+        core.gemm_generic(a, w, many, status=status())
+        for rows in ([5], [0, 17, 199], list(range(40, 48))):
+            few = torch.empty(len(rows), N, device=DEV)
+            core.gemm_generic(a[rows].contiguous(), w, few, status=status())
+            assert torch.equal(few, many[rows]), (K, N, rows)
 
 
 def test_gemm_generic_is_true_32_bit(core):
@@ -91,11 +107,11 @@ def test_gemm_generic_is_true_32_bit(core):
 
 
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
-def test_gemm_generic_grouped_with_gather(core, dt):
-    G_, N, K, S = 5, 45, 70, 23
+@pytest.mark.parametrize("counts", [[0, 70, 3, 0, 9], [2, 0, 11, 1, 8], [0, 0, 1, 0, 0]])     # many rows; few rows: another kernel
+def test_gemm_generic_grouped_with_gather(core, dt, counts):
+    G_, N, K, S = 5, 45, 1070, 23
     a = torch.randn(S, K, device=DEV).to(dt)
     w = torch.randn(G_, N, K, device=DEV).to(dt)
-    counts = [0, 70, 3, 0, 9]                              # empty groups, one longer than a tile
     offs = torch.tensor(np.concatenate([[0], np.cumsum(counts)]), dtype=torch.int32, device=DEV)
     M = sum(counts)
     rows = torch.randint(0, S, (M,), device=DEV, dtype=torch.int32)
@@ -108,7 +124,7 @@ def test_gemm_generic_grouped_with_gather(core, dt):
         o += c
     assert float((out.double() - ref).abs().max() / ref.abs().max()) < 1e-5
     st = status()
-    rows[2] = S + 4
+    rows[M // 2] = S + 4
     core.gemm_generic(a, w, out, a_rows=rows, group_offsets=offs, status=st)
     assert int(st[0]) & 16
 
