@@ -287,6 +287,81 @@ def run_ours(args):
     return 0
 
 
+def run_fp32_long(args):
+    """The true 32-bit path at the model's layer sizes and a long context: 8 sequences of unequal
+    prompts (4,096 to 24,576 tokens, seeded) inside 32,768 positions, a window of 4,096 on the last
+    three layers, then 64 decode steps; and the logits of two of the prompts against the bfloat16
+    path on the same (bfloat16-representable) weights.  Prints one JSON line; not the benchmark record."""
+    import random
+
+    import torch
+
+    import moe_b200
+
+    pk = peaks()
+    cfg = dict(A27B, use_sliding_window=True, sliding_window=4096, max_window_layers=21, max_position_embeddings=32768)
+    layers = args.layers or cfg["num_hidden_layers"]
+    cfg["num_hidden_layers"] = layers
+    cfg["max_window_layers"] = max(0, layers - 3)
+    V = cfg["vocab_size"]
+    rng = random.Random(5)
+    lens = [rng.randint(4096, 24576) for _ in range(8)] if not args.prompt_len else [args.prompt_len] * 8
+    steps = 64
+    model = moe_b200.random_model(cfg, seed=0, dtype="float32", device="cuda:0", stored_dtype="bfloat16")
+    room = sum(-(-(n + steps + 8) // 64) * 64 for n in lens)
+    eng = moe_b200.Engine(model, max_tokens=room, max_slots=8)
+    prompts = [[(i * 7 + 13 + 31 * b) % V for i in range(n)] for b, n in enumerate(lens)]
+    slots = [eng.new_sequence() for _ in lens]
+    last = {}
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for b in range(8):
+        last[b] = eng.step([slots[b]], [prompts[b]]).float().clone()     # (the engine runs it in pieces)
+    torch.cuda.synchronize()
+    prefill_s = time.perf_counter() - t0
+    nums = model_numbers(cfg, layers)
+    a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for i in range(3):
+        eng.step(slots, [[(i * 13 + 7 * b) % V] for b in range(8)], check=False)
+    a.record()
+    for i in range(steps):
+        eng.step(slots, [[(i * 13 + 7 * b + 3) % V] for b in range(8)], check=False)
+    z.record()
+    torch.cuda.synchronize()
+    eng.rt.check()
+    ms = a.elapsed_time(z) / steps
+    full, win = cfg["max_window_layers"], layers - cfg["max_window_layers"]
+    kv_tok = 2 * cfg["num_key_value_heads"] * cfg["head_dim"] * 4
+    mean = [n + 3 + steps / 2 for n in lens]
+    kv = kv_tok * (full * sum(mean) + win * sum(min(m, 4096) for m in mean))
+    uniq = cfg["num_experts"] * (1 - (1 - cfg["num_experts_per_tok"] / cfg["num_experts"]) ** 8)
+    weights = 4 * (layers * (nums["attn"] + nums["shared"] + nums["router"] + uniq * nums["expert"]) + nums["head"])
+    gbs = (weights + kv) / (ms / 1e3) / 1e9
+    out = {"workload": "float32, context 32768, 8 unequal prompts, 64 decode steps", "layers": layers, "prompt_tokens": lens,
+           "prefill_tokens_per_s": round(sum(lens) / prefill_s, 1), "prefill_s": round(prefill_s, 2),
+           "decode_ms_per_step": round(ms, 3), "decode_tokens_per_s": round(8 / (ms / 1e3), 1),
+           "decode_bytes_per_step": int(weights + kv), "decode_hbm_gbs": round(gbs, 1),
+           "decode_hbm_frac": round(gbs / pk["hbm_gbs"], 4)}
+    # ---- the bfloat16 path on the same weights: the two shortest prompts' last logits --------------
+    for s_ in slots:
+        eng.release(s_)
+    short = sorted(range(8), key=lambda b: lens[b])[:2]
+    del eng
+    torch.cuda.empty_cache()
+    m16 = moe_b200.random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+    e16 = moe_b200.Engine(m16, max_tokens=sum(-(-(lens[b] + 8) // 64) * 64 for b in short), max_slots=2)
+    worst = 0.0
+    for b in short:
+        s_ = e16.new_sequence()
+        lg = e16.step([s_], [prompts[b]]).float()
+        e16.release(s_)
+        worst = max(worst, float((lg - last[b]).abs().max() / last[b].abs().max()))
+    out["bf16_vs_fp32_last_logits_rel"] = round(worst, 5)
+    out["bf16_vs_fp32_prompts"] = [lens[b] for b in short]
+    print(json.dumps(out))
+    return 0
+
+
 def profile_step(args):
     """A small case for a profiler: the model's layer sizes, few layers, graphs off (every kernel is
     a launch of its own); only the steps between cudaProfilerStart and cudaProfilerStop matter."""
@@ -357,6 +432,8 @@ def main():
     ap.add_argument("--batch", type=int, default=8, help="with --profile-step decode: sequences in the batch")
     ap.add_argument("--shape", choices=["a2.7b", "57b"], default="a2.7b", help="with --sweep: the layer sizes")
     ap.add_argument("--prompt-len", type=int, default=0, help="with --sweep: tokens in each prompt (default 512)")
+    ap.add_argument("--workload", choices=["fp32-32k"], default=None,
+                    help="fp32-32k: the true 32-bit path at a context of 32,768 (prints its own line, no benchmark record)")
     ap.add_argument("--unequal", action="store_true", help="with --sweep: prompts of unequal lengths, 256 to 2,048 tokens")
     ap.add_argument("--sweep", default=None, help="comma-separated batch sizes: print decode throughput for each "
                                                   "and no benchmark line")
@@ -371,6 +448,8 @@ def main():
     args.warmup = max(args.warmup, 3)
     if args.profile_step:
         return profile_step(args)
+    if args.workload == "fp32-32k":
+        return run_fp32_long(args)
     return run_ours(args)
 
 

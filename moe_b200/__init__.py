@@ -43,9 +43,12 @@ def load_model(model_dir: str, dtype="bfloat16", device="cuda"):
 
 
 def random_model(config: Union[Dict[str, Any], Any], seed: int = 0, dtype="bfloat16", device="cuda",
-                 std: float = 0.02):
+                 std: float = 0.02, stored_dtype=None):
     """A model with random weights drawn on ``device`` (no files written), part by part: at no
-    time is more held than the model itself and the tensors of the part being bound."""
+    time is more held than the model itself and the tensors of the part being bound.
+    ``stored_dtype``: the dtype the weights are drawn in, as if a checkpoint of that dtype were read
+    (default: ``dtype``); a float32 model of bfloat16 weights has exactly the weights of the
+    bfloat16 model of the same seed."""
     from .models import DecoderModel
 
     if isinstance(config, dict):
@@ -56,7 +59,8 @@ def random_model(config: Union[Dict[str, Any], Any], seed: int = 0, dtype="bfloa
         arch, typed = _config.lookup(_arch_of(config)), config
     spec = arch.model_spec(typed)
     dt = _dtype(dtype)
-    model = DecoderModel(spec, RandomStore(spec, seed, std, dt, device), Runtime(device, dt), check=False)
+    model = DecoderModel(spec, RandomStore(spec, seed, std, _dtype(stored_dtype) if stored_dtype else dt, device),
+                         Runtime(device, dt), check=False)
     model.config = typed
     return model
 
