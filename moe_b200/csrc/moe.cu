@@ -894,6 +894,58 @@ MOE_API int moe_router(const float* h, const void* wr, const void* wsg, int w_dt
                       top_k, norm_topk, scale, topk_idx, topk_w, shared_gate);
 }
 
+// Picks, weights and shared gate from logits that are already there ([T, rows] float32).
+MOE_API int moe_router_topk(float* logits, const int* seq_of_token, int num_tokens, int num_experts, int has_gate_row,
+                            int top_k, int norm_topk, float scale, int* topk_idx, float* topk_w, float* shared_gate,
+                            cudaStream_t stream) {
+    if (num_tokens <= 0) return 0;
+    if (top_k <= 0 || top_k > num_experts || num_experts > 2048 || !logits || (has_gate_row && !shared_gate))
+        return (int)cudaErrorInvalidValue;
+    const int rows = num_experts + (has_gate_row ? 1 : 0);
+    const size_t smem = (size_t)4 * (rows + num_experts + top_k) * sizeof(float);
+    if (smem > 48 * 1024) {
+        const cudaError_t e = cudaFuncSetAttribute(router_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return launch_pdl(router_topk_kernel, (num_tokens + 3) / 4, 128, smem, stream, logits, (const float*)nullptr, 0,
+                      seq_of_token, num_tokens, num_experts, rows, top_k, norm_topk, scale, topk_idx, topk_w, shared_gate);
+}
+
+// A float32 row as three bfloat16 terms, x = p0 + p1 + p2 exactly (8 + 8 + 8 bits of mantissa):
+// out[t] = [p0 (hidden) | p1 (hidden) | p2 (hidden)].  A product of these with bfloat16 weights on
+// the tensor cores, accumulated in float32, is a float32-accurate product of x: every partial
+// product is exact.  (The router's logits for a prompt.)  hidden a multiple of 4.
+__global__ void split3_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ out, long long n4, int hidden) {
+    pdl_sync();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n4) return;
+    const long long t = (i * 4) / hidden;
+    const int c = (int)((i * 4) % hidden);
+    const float4 v = reinterpret_cast<const float4*>(x)[i];
+    const float in[4] = {v.x, v.y, v.z, v.w};
+    __nv_bfloat16 p[3][4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        float r = in[e];
+#pragma unroll
+        for (int k = 0; k < 3; k++) {
+            p[k][e] = __float2bfloat16_rn(r);
+            r -= __bfloat162float(p[k][e]);          // exact: the difference fits in float32
+        }
+    }
+    __nv_bfloat16* o = out + t * 3 * hidden + c;
+#pragma unroll
+    for (int k = 0; k < 3; k++) *reinterpret_cast<uint2*>(o + (size_t)k * hidden) = *reinterpret_cast<const uint2*>(p[k]);
+}
+MOE_API int moe_split3(const float* x, void* out, long long num_tokens, int hidden, cudaStream_t stream) {
+    if (num_tokens <= 0) return 0;
+    if (hidden <= 0 || hidden % 4 || ((uintptr_t)x & 15) || ((uintptr_t)out & 7)) return (int)cudaErrorInvalidValue;
+    const long long n4 = num_tokens * hidden / 4;
+    if ((n4 + 255) / 256 > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
+    return launch_pdl(split3_kernel, (unsigned)((n4 + 255) / 256), 256, 0, stream, x, (__nv_bfloat16*)out, n4, hidden);
+}
+
 MOE_API int moe_align(const int* topk_idx, int num_tokens, int top_k, int num_experts, int* offsets,
                       int* sorted_token, int* pos_of_pair, int* status, cudaStream_t stream) {
     if (num_experts > 4096) return (int)cudaErrorInvalidValue;

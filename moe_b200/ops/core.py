@@ -41,6 +41,8 @@ def lib():
             "moe_attention_generic": [P, P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],
             "moe_router": [P, P, P, I, P, I, I, I, I, I, F, P, P, P, P, P, LL, P],
             "moe_router_logits": [P, P, P, I, I, I, I, P, P, LL, P],
+            "moe_router_topk": [P, P, I, I, I, I, I, F, P, P, P, P],
+            "moe_split3": [P, P, LL, I, P],
             "moe_route_dispatch": [P, P, I, I, I, I, I, F, P, P, P, P, P, P, P, P, I, P, P],
             "moe_rope_commit": [P, P, P, I, I, I, I, I, P, P, P, I, P, P, P, I, I, I, I, P, P],
             "moe_attention_decode": [P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],
@@ -372,6 +374,27 @@ def router(h32, w_router, top_k, norm_topk, scale, topk_idx, topk_w, *, shared_g
     _ok(lib().moe_router(_p(h32), _p(w_router), _p(shared_gate_w), _dt(w_router), _p(seq_of_token), T, H, E, top_k,
                          1 if norm_topk else 0, float(scale), _p(logits), _p(topk_idx), _p(topk_w), _p(shared_gate),
                          _p(scratch), need, _stream()), "router")
+
+
+def split3(x32: torch.Tensor) -> torch.Tensor:
+    """[T, H] float32 -> [T, 3 H] bfloat16 with x = p0 + p1 + p2 exactly (three terms of 8 bits)."""
+    _chk(x32, "x", torch.float32, 2)
+    T, H = x32.shape
+    out = torch.empty((T, 3 * H), dtype=torch.bfloat16, device=x32.device)
+    _ok(lib().moe_split3(_p(x32), _p(out), T, H, _stream()), "split3")
+    return out
+
+
+def router_topk(logits, top_k, norm_topk, scale, topk_idx, topk_w, *, num_experts, shared_gate=None, seq_of_token=None):
+    """Picks and weights from logits [T, E (+ 1 row for the shared gate)] that are already there."""
+    _chk(logits, "logits", torch.float32, 2)
+    T = logits.shape[0]
+    gate_row = logits.shape[1] == num_experts + 1
+    if logits.shape[1] not in (num_experts, num_experts + 1) or (gate_row and shared_gate is None):
+        raise KernelError("router_topk: logits must have one column per expert (and one for the shared gate)")
+    _ok(lib().moe_router_topk(_p(logits), _p(seq_of_token), T, num_experts, 1 if gate_row else 0, top_k,
+                              1 if norm_topk else 0, float(scale), _p(topk_idx), _p(topk_w), _p(shared_gate), _stream()),
+        "router_topk")
 
 
 _SMS = {}

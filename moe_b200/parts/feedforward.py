@@ -98,6 +98,9 @@ class RoutedExperts(Part):
         # (measured on a B200, ms a decode step at 16 / 32 / 64 tokens: 4.65 / 5.89 / 7.38 with one
         # block up to 64 tokens, 4.48 / 5.75 / 7.07 with one block up to 8)
         self.route_dispatch_tokens = int(os.environ.get("MOE_B200_ROUTE_DISPATCH_MAX", "8"))
+        # from this many tokens on (a prompt) the router's logits are a tensor-core product of the
+        # 32-bit activations split into three bfloat16 terms (35 -> about 15 us at 2,048 tokens)
+        self.tc_router_tokens = int(os.environ.get("MOE_B200_TC_ROUTER_MIN", "257"))
 
     def tensors(self):
         t = {"gate.weight": TensorSpec((self.E, self.hidden))}
@@ -192,6 +195,13 @@ class RoutedExperts(Part):
             self.ws_down = tensors["shared_expert.down_proj.weight"].contiguous()
         if self.shared_gate:
             self.w_sgate = tensors["shared_expert_gate.weight"].reshape(-1).to(self.w_router.dtype).contiguous()
+        # For prompts the router's logits come from the tensor cores: the 32-bit activations as three
+        # bfloat16 terms against the (bfloat16, hence exact) router rows, three times side by side.
+        self.w_router3 = None
+        if rt.is_bf16 and self.w_router.dtype == torch.bfloat16 and self.hidden % 8 == 0:
+            rows = [self.w_router] + ([self.w_sgate.reshape(1, -1)] if self.w_sgate is not None else [])
+            one = torch.cat(rows, dim=0)
+            self.w_router3 = torch.cat([one, one, one], dim=1).contiguous()
 
     def route(self, rt, h, batch):
         """-> (topk_idx [T, k] int32, topk_w [T, k] float32, shared_gate [T] float32 or None)"""
@@ -199,6 +209,14 @@ class RoutedExperts(Part):
         topk_idx = rt.empty((T, self.k), torch.int32)
         topk_w = rt.empty((T, self.k), torch.float32)
         sg = rt.empty((T,), torch.float32) if self.w_sgate is not None else None
+        if self.w_router3 is not None and T >= self.tc_router_tokens:
+            from ..ops import tc
+
+            logits = rt.empty((T, self.w_router3.shape[0]), torch.float32)
+            if tc.gemm_tc(core.split3(h.f32), self.w_router3, logits, bn=64, splits=8, status=rt.status):
+                core.router_topk(logits, self.k, self.norm_topk, self.scale, topk_idx, topk_w, num_experts=self.E,
+                                 shared_gate=sg, seq_of_token=getattr(batch, "seq_of_token", None))
+                return topk_idx, topk_w, sg
         core.router(h.f32, self.w_router, self.k, self.norm_topk, self.scale, topk_idx, topk_w,
                     shared_gate_w=self.w_sgate, shared_gate=sg, seq_of_token=getattr(batch, "seq_of_token", None))
         return topk_idx, topk_w, sg

@@ -368,3 +368,46 @@ def test_table_update_and_seed_rng(core):
     core.seed_rng(states, slots, seeds)
     got = states.cpu().numpy().view(np.uint64)
     assert int(got[4]) == plain.Rng(7).s and int(got[1]) == plain.Rng(0).s and int(got[0]) == 0
+
+
+def test_three_bfloat16_terms_hold_a_float32_exactly(core):
+    torch.manual_seed(0)
+    x = torch.randn(37, 264, device=DEV) * torch.logspace(-6, 6, 264, device=DEV)
+    x[0, :4] = torch.tensor([0.0, -0.0, 1.0, 3.0e38], device=DEV)
+    p = core.split3(x).float().reshape(37, 3, 264)
+    assert torch.equal(p[:, 0] + p[:, 1] + p[:, 2], x)                  # added in this order, nothing is lost
+    assert torch.equal(p[:, 0], x.to(torch.bfloat16).float())            # the first term is the rounded value
+
+
+@pytest.mark.parametrize("T,E,k,H,gate", [(300, 60, 4, 2048, True), (1000, 7, 2, 264, False), (2048, 64, 8, 3584, True)])
+def test_router_logits_on_the_tensor_cores_equal_the_32_bit_ones(core, T, E, k, H, gate):
+    """A prompt's router logits as a tensor-core product of the activations' three bfloat16 terms
+    against the bfloat16 router rows: the same logits as the 32-bit kernel to a few units of the
+    last place of a sum of H terms, and the same picks wherever two experts are not closer than that."""
+    from moe_b200.ops import tc
+
+    torch.manual_seed(T + E)
+    h = torch.randn(T, H, device=DEV)
+    wr = (torch.randn(E, H, device=DEV) * 0.05).to(torch.bfloat16)
+    wg = (torch.randn(H, device=DEV) * 0.05).to(torch.bfloat16) if gate else None
+    rows = torch.cat([wr] + ([wg.reshape(1, -1)] if gate else []), dim=0)
+    w3 = torch.cat([rows, rows, rows], dim=1).contiguous()
+    logits = torch.empty(T, rows.shape[0], device=DEV)
+    assert tc.gemm_tc(core.split3(h), w3, logits, bn=64, splits=8, status=status())
+    ref = h.double() @ rows.double().T
+    scale = float(ref.abs().max())
+    assert float((logits.double() - ref).abs().max()) < 3e-6 * scale
+    idx, w = torch.empty(T, k, dtype=torch.int32, device=DEV), torch.empty(T, k, device=DEV)
+    sg = torch.empty(T, device=DEV) if gate else None
+    core.router_topk(logits, k, True, 1.0, idx, w, num_experts=E, shared_gate=sg)
+    idx2, w2 = torch.empty_like(idx), torch.empty_like(w)
+    sg2 = torch.empty(T, device=DEV) if gate else None
+    core.router(h, wr, k, True, 1.0, idx2, w2, shared_gate_w=wg, shared_gate=sg2)
+    same = (idx.sort(dim=1).values == idx2.sort(dim=1).values).all(dim=1)
+    top = torch.sort(ref[:, :E], dim=1, descending=True).values
+    margin = (top[:, k - 1] - top[:, k]) / scale if E > k else torch.ones(T, device=DEV, dtype=torch.float64)
+    assert bool((same | (margin < 1e-5)).all())
+    assert float(same.float().mean()) > 0.99
+    assert torch.allclose(w[same], w2[same], atol=1e-5)
+    if gate:
+        assert torch.allclose(sg, sg2, atol=1e-5)
