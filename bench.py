@@ -390,7 +390,7 @@ def profile_step(args):
         model = None
     else:
         cfg["num_hidden_layers"] = args.layers or 2
-        model = moe_b200.random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+        model = moe_b200.random_model(cfg, seed=0, dtype=args.dtype, device="cuda:0")
     if args.profile_step == "sample":
         pass
     elif args.profile_step == "decode":
@@ -430,6 +430,8 @@ def main():
                     help="run a few steps of one kind between cudaProfilerStart/Stop (for ncu "
                          "--profile-from-start off) and print no benchmark line")
     ap.add_argument("--batch", type=int, default=8, help="with --profile-step decode: sequences in the batch")
+    ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
+                    help="with --profile-step: the path whose kernels are wanted")
     ap.add_argument("--shape", choices=["a2.7b", "57b"], default="a2.7b", help="with --sweep: the layer sizes")
     ap.add_argument("--prompt-len", type=int, default=0, help="with --sweep: tokens in each prompt (default 512)")
     ap.add_argument("--workload", choices=["fp32-32k"], default=None,

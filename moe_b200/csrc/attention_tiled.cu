@@ -16,7 +16,8 @@
 // rows 4 ty .. 4 ty + 3 against key columns 4 tx .. 4 tx + 3, and of the output the same rows and
 // the head-dimension columns 4 tx + 64 i.  Q and K sit in shared memory transposed ([d][row]), so
 // that both operands of the score product are read as float4; P goes through shared memory to
-// every thread of its rows.  Key tiles start at multiples of 64 = the page size, so a tile of
+// every thread of its rows (in the keys' place, which keeps a block of heads of 128 at 103 KB: two
+// to an SM).  Key tiles start at multiples of 64 = the page size, so a tile of
 // cached keys is one contiguous [64][head_dim] block of one page.
 #include "common.cuh"
 
@@ -50,7 +51,9 @@ attn_tiled_kernel(const T* __restrict__ q, const T* __restrict__ k_new, const T*
     float* Qt = sm;                               // [hd][BQ + PAD]
     float* Kt = Qt + (size_t)hd * (BQ + PAD);     // [hd][BK + PAD]
     float* V = Kt + (size_t)hd * (BK + PAD);      // [BK][hd + PAD]
-    float* P = V + (size_t)BK * (hd + PAD);       // [BQ][BK + PAD]
+    float* P = Kt;                                // [BQ][BK + PAD]: in the keys' place, once the scores are formed
+                                                  // (hd >= 64; smaller heads get room of their own behind V)
+    if (hd < BQ) P = V + (size_t)BK * (hd + PAD);
     const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
     const int h = blockIdx.y, kvh = h / (nh / nkv);
 
@@ -138,6 +141,7 @@ attn_tiled_kernel(const T* __restrict__ q, const T* __restrict__ k_new, const T*
                 for (int c = 0; c < 4; c++) s[r][c] = fmaf(av[r], bv[c], s[r][c]);
         }
         // ---- mask, running maximum and sum, P --------------------------------------------------
+        __syncthreads();                 // every thread has read the keys: P may take their place
 #pragma unroll
         for (int r = 0; r < 4; r++) {
             const int row = ty * 4 + r, p = p_first + row;
@@ -216,8 +220,9 @@ attn_tiled_kernel(const T* __restrict__ q, const T* __restrict__ k_new, const T*
 }
 
 size_t tiled_smem(int hd) {
-    return ((size_t)hd * (BQ + PAD) + (size_t)hd * (BK + PAD) + (size_t)BK * (hd + PAD) + (size_t)BQ * (BK + PAD)) *
-           sizeof(float);
+    // Q, K (P takes K's place when the head is at least as long as a tile is wide), V
+    return ((size_t)hd * (BQ + PAD) + (size_t)hd * (BK + PAD) + (size_t)BK * (hd + PAD) +
+            (hd < BQ ? (size_t)BQ * (BK + PAD) : 0)) * sizeof(float);
 }
 
 }  // namespace
