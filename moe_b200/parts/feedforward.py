@@ -235,9 +235,11 @@ class RoutedExperts(Part):
         """The block's offer to take the norm before this feed-forward along: for a step of few
         tokens, norm, router and dispatch are one launch.  None if the sizes or the kind of norm do
         not allow it (the block then runs the norm itself and calls ``forward``)."""
-        if getattr(norm, "kind", None) != "rmsnorm" or x.shape[0] > self.fused_norm_tokens or self.E > 256:
+        rms = getattr(norm, "rms_params", None)          # the norm says whether it can be run by a neighbour
+        if rms is None or x.shape[0] > self.fused_norm_tokens or self.E > 256:
             return None
-        routed = core.norm_route(x, delta, norm.weight, norm.eps, self.w_router, self.k, self.norm_topk, self.scale,
+        norm_w, norm_eps = rms()
+        routed = core.norm_route(x, delta, norm_w, norm_eps, self.w_router, self.k, self.norm_topk, self.scale,
                                  bf16=rt.is_bf16, shared_gate_w=self.w_sgate,
                                  seq_of_token=getattr(batch, "seq_of_token", None), status=rt.status)
         if routed is None:

@@ -23,6 +23,12 @@ class RMSNorm(Part):
     def describe(self):
         return f"RMSNorm eps {self.eps:g}"
 
+    def rms_params(self):
+        """(weight, eps): what a neighbour needs to run this norm inside a kernel of its own (a
+        feed-forward that fuses the norm before it with its first step asks for this; a norm
+        that is no plain RMS norm simply has no such method)."""
+        return self.weight, self.eps
+
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
         self.weight = tensors["weight"].to(torch.float32).contiguous()

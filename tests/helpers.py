@@ -48,7 +48,18 @@ CONFIG_D = dict(
     max_window_layers=1, tie_word_embeddings=False, max_position_embeddings=4096, eos_token_id=330,
     qkv_bias=False,
 )
-CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "D": CONFIG_D}
+# sizes that the fast kernels refuse, so that the bfloat16 path takes its other kernels: a width that is
+# no multiple of 8 (no TMA row), heads of 48 (no tensor-core attention, rows of 96 bytes in the cache),
+# one expert a token, no shared expert, one layer, expert and dense sizes that are odd multiples of 4
+CONFIG_E = dict(
+    architectures=["Qwen2MoeForCausalLM"], model_type="qwen2_moe",
+    num_hidden_layers=2, hidden_size=100, num_attention_heads=3, num_key_value_heads=3, head_dim=48,
+    num_experts=3, num_experts_per_tok=1, moe_intermediate_size=20, shared_expert_intermediate_size=0,
+    norm_topk_prob=False, decoder_sparse_step=2, mlp_only_layers=[], intermediate_size=44,
+    vocab_size=97, rope_theta=3e4, rms_norm_eps=1e-5, use_sliding_window=True, sliding_window=33,
+    max_window_layers=0, tie_word_embeddings=True, max_position_embeddings=4096, eos_token_id=96,
+)
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "D": CONFIG_D, "E": CONFIG_E}
 
 
 class ModelFolders:

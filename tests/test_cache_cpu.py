@@ -3,7 +3,8 @@ import random
 
 import pytest
 
-from moe_b200.cache import PAGE_TOKENS, CacheError, CacheLedger, PagePool, SlotPool, pages_for
+from moe_b200.cache import PAGE_TOKENS, CacheError, CacheLedger, pages_for
+from pools import PagePool, SlotPool
 
 
 def test_slots_are_unique_and_reused():

@@ -11,7 +11,7 @@ import helpers
 pytestmark = pytest.mark.gpu
 
 CASES = [(n, dt, std) for n in ("A", "B") for dt in ("float32", "bfloat16") for std in G.STD[dt]]
-CASES += [("C", dt, G.STD[dt][-1]) for dt in ("float32", "bfloat16")]
+CASES += [(n, dt, G.STD[dt][-1]) for n in ("C", "E") for dt in ("float32", "bfloat16")]
 # D is 264 wide: weights of the same scale would have a gain of 0.2 sqrt(264) = 3.2 a matrix (1.6 to 2.5
 # for the others) and amplify every rounding far more; its scales keep the gain that B has
 CASES += [("D", dt, G.STD_WIDE[dt]) for dt in ("float32", "bfloat16")]

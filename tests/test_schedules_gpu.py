@@ -22,7 +22,7 @@ def engine(model_dirs, name, dtype, max_tokens, max_slots, use_graphs=True):
 
 
 MANY = [("A", 12, True), ("A", 70, True), ("B", 24, True), ("B", 40, False), ("D", 40, True), ("D", 12, False),
-        ("C", 33, True)]
+        ("C", 33, True), ("E", 20, True), ("E", 9, False)]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -60,7 +60,7 @@ def test_a_sequence_decodes_the_same_alone_and_among_63_others(model_dirs, name,
     assert helpers.max_rel_err(b, a) < G.tol_cut(dtype)
 
 
-@pytest.mark.parametrize("name,dtype", [(n, dt) for n in ("A", "B", "C", "D") for dt in ("float32", "bfloat16")])
+@pytest.mark.parametrize("name,dtype", [(n, dt) for n in ("A", "B", "C", "D", "E") for dt in ("float32", "bfloat16")])
 def test_steps_that_mix_fresh_prompts_continued_ones_and_single_tokens(model_dirs, name, dtype):
     """One step may hold a sequence that brings one token, one that goes on by several from a
     position beyond 0, and one that starts with a whole prompt; keys of earlier steps then come from
@@ -95,7 +95,7 @@ def test_steps_that_mix_fresh_prompts_continued_ones_and_single_tokens(model_dir
     helpers.check_schedule_against_plain(d, reqs, logits, picks, G.tol(dtype), G.flip(dtype))
 
 
-@pytest.mark.parametrize("name,dtype", [(n, dt) for n in ("A", "B", "C", "D") for dt in ("float32", "bfloat16")])
+@pytest.mark.parametrize("name,dtype", [(n, dt) for n in ("A", "B", "C", "D", "E") for dt in ("float32", "bfloat16")])
 @pytest.mark.parametrize("chunk", [64, 50])
 def test_a_prompt_fed_in_chunks_matches_plain(model_dirs, name, dtype, chunk):
     V = helpers.CONFIGS[name]["vocab_size"]
