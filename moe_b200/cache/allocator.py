@@ -53,7 +53,7 @@ def host_lib():
             "moe_ledger_check": ([P, I, _IP, _IP, _IP, LL], I),
             "moe_pack_step": ([_IP, LL, I, _IP, _IP, _IP, _IP, _IP, _IP, _IP, _IP], LL),
             "moe_pack_decode": ([_IP, I, I, _IP, _IP, _IP, I, I, _IP, _IP, I], I),
-            "moe_pack_prompt": ([_IP, I, I, I, _IP, _IP, _IP, I, I, _IP, I, _IP, I], I),
+            "moe_pack_padded": ([_IP, I, I, I, I, _IP, _IP, _IP, _IP, _IP, _IP, I, I, _IP, I, _IP, I], I),
         }
         for name, (args, res) in sig.items():
             fn = getattr(L, name)

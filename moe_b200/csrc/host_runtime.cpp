@@ -397,34 +397,43 @@ MOE_API long long moe_pack_step(int* buf, long long cap, int B, const int* slots
     return o;
 }
 
-// A step of whole prompts (every sequence starts at position 0, the logits of each last token are
-// wanted), padded for a captured graph to `tp` token rows and `bb` sequences: rows past the tokens
-// belong to no sequence (seq_of_token -1, position 0, token 0), sequences past B are empty and sit in
-// the padding slot.  Layout: token_ids[tp] seq_of_token[tp] pos[tp] cu_seqlens[bb + 1] slots[bb]
-// seq_start[bb] seq_end[bb] want_rows[bb], then per cache group `upd_cap` page-table updates at
-// upd_off[g], padded as in moe_pack_decode.
-MOE_API int moe_pack_prompt(int* buf, int tp, int bb, int B, const int* slots, const int* counts, const int* tokens,
+// Any step, padded for a captured graph to `tp` token rows, `bb` sequences and `wb` wanted places:
+// rows past the tokens belong to no sequence (seq_of_token -1, position 0, token 0), sequences past B
+// are empty and sit in the padding slot, wanted places past the real ones repeat row 0 (the caller
+// drops them).  Layout: token_ids[tp] seq_of_token[tp] pos[tp] cu_seqlens[bb + 1] slots[bb]
+// seq_start[bb] seq_end[bb] want_rows[wb], then per cache group `upd_cap` page-table updates at
+// upd_off[g], padded as in moe_pack_decode.  starts, want_counts, want: as in moe_pack_step.
+MOE_API int moe_pack_padded(int* buf, int tp, int bb, int wb, int B, const int* slots, const int* starts,
+                            const int* counts, const int* tokens, const int* want_counts, const int* want,
                             int pad_slot, int num_groups, const int* upd_off, int upd_cap, const int* updates,
                             int num_updates) {
     if (B > bb || B < 0) return fail(ERR_VALUE, "more sequences than the bucket holds");
-    long long T = 0;
+    long long T = 0, W = 0;
     for (int i = 0; i < B; i++) {
         if (counts[i] <= 0) return fail(ERR_VALUE, "every sequence of a step brings at least one token");
-        T += counts[i];
+        T += counts[i], W += want_counts[i];
     }
     if (T > tp) return fail(ERR_VALUE, "more tokens than the bucket holds");
+    if (W > wb) return fail(ERR_VALUE, "more wanted places than the bucket holds");
     int* tok = buf;
     int *sot = tok + tp, *pos = sot + tp, *cu = pos + tp, *sl = cu + bb + 1, *st = sl + bb, *en = st + bb;
     int* wr = en + bb;
-    int at = 0;
+    int at = 0, wi = 0;
+    const int* w = want;
     for (int i = 0; i < bb; i++) {
-        const int n = i < B ? counts[i] : 0;
-        for (int j = 0; j < n; j++) tok[at + j] = tokens[at + j], sot[at + j] = i, pos[at + j] = j;
-        cu[i] = at, sl[i] = i < B ? slots[i] : pad_slot, st[i] = 0, en[i] = n;
-        wr[i] = n > 0 ? at + n - 1 : 0;
+        const int n = i < B ? counts[i] : 0, s0 = i < B ? starts[i] : 0;
+        for (int j = 0; j < n; j++) tok[at + j] = tokens[at + j], sot[at + j] = i, pos[at + j] = s0 + j;
+        cu[i] = at, sl[i] = i < B ? slots[i] : pad_slot, st[i] = s0, en[i] = s0 + n;
+        for (int j = 0; i < B && j < want_counts[i]; j++, w++) {
+            if (*w < 0 || *w >= n)
+                return fail(ERR_VALUE, "wanted place " + std::to_string(*w) + " is not among the " + std::to_string(n) +
+                                           " tokens of this step");
+            wr[wi++] = at + *w;
+        }
         at += n;
     }
     cu[bb] = at;
+    for (; wi < wb; wi++) wr[wi] = 0;
     for (int t = at; t < tp; t++) tok[t] = 0, sot[t] = -1, pos[t] = 0;
     for (int g = 0; g < num_groups; g++) {
         int* u = buf + upd_off[g];

@@ -11,7 +11,9 @@ A step in which every sequence brings one token is launch-bound, so it is
 replayed from a CUDA graph: one graph per batch-size bucket, captured the first
 time the bucket is met.  The batch is padded to the bucket with rows that belong
 to no sequence (``seq_of_token = -1``): they read and write only the scratch page,
-get no expert and change no result.
+get no expert and change no result.  Every other step of up to 512 tokens and 64
+sequences (prompts, chunks, continued and fresh sequences mixed, any wanted
+places) is replayed the same way from a graph of its padded shape.
 """
 from __future__ import annotations
 
@@ -31,10 +33,11 @@ from ..ops import core
 from .batch import StepBatch, fill_host, layout
 
 GRAPH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
-# Short prompts are bound by the host's launches (hundreds of kernels a step), so they too are replayed
-# from graphs, padded to these numbers of token rows and of sequences.
-PROMPT_TOKEN_BUCKETS = (64, 128, 256, 512)
-PROMPT_SEQ_BUCKETS = (1, 2, 4, 8)
+# Short steps of any other kind (prompts, chunks of prompts, continued sequences, any wanted places)
+# are bound by the host's launches (hundreds of kernels a step), so they too are replayed from
+# graphs, padded to these numbers of token rows and of sequences.
+STEP_TOKEN_BUCKETS = (64, 128, 256, 512)
+STEP_SEQ_BUCKETS = (1, 2, 4, 8, 16, 32, 64)
 # A step of more tokens than this is run in pieces of at most this many (the reference tiles a prompt
 # at 64 tokens, src/main.rs:499-505): what a step needs beside the cache grows with its tokens.
 MAX_STEP_TOKENS = int(os.environ.get("MOE_B200_MAX_STEP_TOKENS", "8192"))
@@ -166,18 +169,22 @@ class _DecodeGraph(_StepGraph):
         self._pack(engine, [], [], [], np.zeros((0, 4), dtype=np.int32))
 
 
-class _PromptGraph(_StepGraph):
-    """A step of whole prompts (every sequence from position 0, the logits of each last token),
-    padded to ``tokens`` rows and ``seqs`` sequences."""
+class _PaddedGraph(_StepGraph):
+    """Any step of several tokens a sequence, padded to ``tokens`` rows, ``seqs`` sequences and
+    ``wants`` wanted places.  ``fresh``: every sequence starts at position 0 (whole prompts, which
+    read nothing from the cache and take the kernels for that); else sequences go on from any
+    position and may be mixed with fresh ones."""
 
-    def __init__(self, engine: "Engine", tokens: int, seqs: int):
-        self.tokens, self.seqs = tokens, seqs
+    def __init__(self, engine: "Engine", tokens: int, seqs: int, wants: int, fresh: bool):
+        self.tokens, self.seqs, self.wants = tokens, seqs, wants
         ngroups = len(engine.cache.groups)
         offs, o = {}, 0
-        for name, n in layout(tokens, seqs, seqs):
+        for name, n in layout(tokens, seqs, wants):
             offs[name] = (o, n)
             o += n
-        self.upd_rows = -(-tokens // PAGE_TOKENS) + seqs          # most pages a group can hand out in such a step
+        # most pages a group can hand out in such a step: a sequence that goes on from the middle of
+        # a page may touch one page more than its tokens fill
+        self.upd_rows = -(-tokens // PAGE_TOKENS) + (1 if fresh else 2) * seqs
         self.upd_off = []
         for _ in range(ngroups):
             self.upd_off.append(o)
@@ -185,20 +192,24 @@ class _PromptGraph(_StepGraph):
         self._upd_off_c, _ = ints(self.upd_off)
         self._buffers(engine, o)
         views = {k: self.dev[a:a + n] for k, (a, n) in offs.items()}
-        self.batch = StepBatch(**views, num_tokens=tokens, num_seqs=seqs, num_want=seqs, max_new=tokens,
-                               max_end=tokens, all_decode=False, all_fresh=True, has_padding=True)
+        self.batch = StepBatch(**views, num_tokens=tokens, num_seqs=seqs, num_want=wants, max_new=tokens,
+                               max_end=tokens if fresh else 0, all_decode=False, all_fresh=fresh, has_padding=True)
 
-    def _pack(self, engine: "Engine", slots, counts, tokens, updates: np.ndarray) -> None:
+    def _pack(self, engine: "Engine", slots, starts, counts, tokens, want, updates: np.ndarray) -> None:
         sl, B = ints(slots)
+        st, _ = ints(starts)
         ct, _ = ints(counts)
+        wc, _ = ints([len(w) for w in want])
         flat = np.fromiter((x for t in tokens for x in t), dtype=np.int32, count=sum(counts))
+        wflat = np.fromiter((x for w in want for x in w), dtype=np.int32)
         upd = np.ascontiguousarray(updates, dtype=np.int32)
-        _ok(host_lib().moe_pack_prompt(ctypes.cast(self.host.data_ptr(), _IP), self.tokens, self.seqs, B, sl, ct,
-                                       flat.ctypes.data_as(_IP), engine.cache.padding_slot, len(self.upd_off),
-                                       self._upd_off_c, self.upd_rows, upd.ctypes.data_as(_IP), int(upd.shape[0])))
+        _ok(host_lib().moe_pack_padded(ctypes.cast(self.host.data_ptr(), _IP), self.tokens, self.seqs, self.wants, B,
+                                       sl, st, ct, flat.ctypes.data_as(_IP), wc, wflat.ctypes.data_as(_IP),
+                                       engine.cache.padding_slot, len(self.upd_off), self._upd_off_c, self.upd_rows,
+                                       upd.ctypes.data_as(_IP), int(upd.shape[0])))
 
     def _pack_empty(self, engine: "Engine") -> None:
-        self._pack(engine, [], [], [], np.zeros((0, 4), dtype=np.int32))
+        self._pack(engine, [], [], [], [], [], np.zeros((0, 4), dtype=np.int32))
 
 
 class Engine:
@@ -226,7 +237,7 @@ class Engine:
         # any part may record what it decided, per call, as tuples of tensors appended to its
         # ``trace`` list (``Part.trace``, None when off)
         self._tracers = list({id(p): p for p in parts}.values())
-        self.prompt_graphs = os.environ.get("MOE_B200_PROMPT_GRAPHS", "1") != "0"
+        self.padded_graphs = os.environ.get("MOE_B200_PADDED_GRAPHS", "1") != "0"
         self._graphs: "OrderedDict[tuple, _StepGraph]" = OrderedDict()
         self._graph_pool = torch.cuda.graph_pool_handle() if self.use_graphs else None
         self._table_caps = [0 if g.ring_pages else g.max_pages_per_seq for g in self.cache.groups]
@@ -272,7 +283,8 @@ class Engine:
         return g
 
     def graphs_of(self, kind: str) -> List[tuple]:
-        """Keys of the captured steps of one kind ("decode" or "prompt")."""
+        """Keys of the captured steps of one kind: "decode" (one token each), "prompt" (every
+        sequence from position 0) or "continued" (any other step)."""
         return [k for k in self._graphs if k[0] == kind]
 
     def truncate(self, slot: int, new_length: int) -> None:
@@ -337,24 +349,25 @@ class Engine:
                     self.rt.check()
                 return logits[:B]
 
-        # ---- short whole prompts, last logits wanted: replay the bucket's graph ------------------
-        T = sum(counts)
-        if (self.use_graphs and self.prompt_graphs and T <= PROMPT_TOKEN_BUCKETS[-1] and B <= PROMPT_SEQ_BUCKETS[-1]
-                and not any(starts) and all(len(w) == 1 and w[0] == n - 1 for w, n in zip(want, counts))
-                and not from_last):
-            tb = next(b for b in PROMPT_TOKEN_BUCKETS if b >= T)
-            sb = next(b for b in PROMPT_SEQ_BUCKETS if b >= B)
-            g = self._graph(("prompt", tb, sb, tracing), lambda: _PromptGraph(self, tb, sb))
-            g.fill(self, slots, counts, tokens, updates)
+        # ---- any other short step: replay the graph of its padded shape ------------------------
+        T, W = sum(counts), sum(len(w) for w in want)
+        if (self.use_graphs and self.padded_graphs and T <= STEP_TOKEN_BUCKETS[-1] and B <= STEP_SEQ_BUCKETS[-1]
+                and W <= T and not from_last):
+            tb = next(b for b in STEP_TOKEN_BUCKETS if b >= T)
+            sb = next(b for b in STEP_SEQ_BUCKETS if b >= B)
+            wb = sb if W <= sb else tb          # the last place of each sequence, or up to every place
+            fresh = not any(starts)
+            g = self._graph(("prompt" if fresh else "continued", tb, sb, wb, tracing),
+                            lambda: _PaddedGraph(self, tb, sb, wb, fresh))
+            g.fill(self, slots, starts, counts, tokens, want, updates)
             logits = g.run(self)
             self.last_batch = g.batch
             self.last_rows = B
             if check:
                 self.rt.check()
-            return logits[:B]
+            return logits[:W] if W else None
 
         # ---- the general step -----------------------------------------------------------------
-        T, W = sum(counts), sum(len(w) for w in want)
         n_upd = int(updates.shape[0])
         host, dev = self._staging(3 * T + 4 * B + 2 + max(W, 1) + 3 * n_upd)
         info = fill_host(host, slots, starts, tokens, want)

@@ -269,9 +269,10 @@ def run_schedule(engine, steps):
                 for p in parts:
                     i = taken.get(id(p), 0)
                     # (a step that the engine runs in pieces leaves one record per piece and run: the
-                    # pieces' tokens, one after another, are the step's tokens in their order)
+                    # pieces' tokens, one after another, are the step's tokens in their order; a step
+                    # replayed from a padded graph also records its rows of no sequence, with picks of -1)
                     mine = p.trace[i::times[id(p)]]
-                    recorded.append([pick for rec in mine for pick in rec[0].cpu().tolist()])
+                    recorded.append([pick for rec in mine for pick in rec[0].cpu().tolist() if pick[0] >= 0])
                     taken[id(p)] = i + 1
                 for rid, toks, want in entries:
                     for w in want:

@@ -113,3 +113,48 @@ def test_pack_decode_pads_with_rows_of_no_sequence():
     with pytest.raises(ValueError):
         _ok(host_lib().moe_pack_decode(buf.ctypes.data_as(_IP), 2, 3, sl, st, tk, pad, groups, uo,
                                        updates.ctypes.data_as(_IP), 3))
+
+
+def test_pack_padded_pads_tokens_sequences_and_wanted_places():
+    tp, bb, wb, pad, groups, cap = 16, 4, 4, 99, 2, 3
+    n_arrays = sum(n for _, n in layout(tp, bb, wb))
+    upd_off = [n_arrays, n_arrays + 3 * cap]
+    buf = np.full(n_arrays + 2 * 3 * cap + 4, -7, dtype=np.int32)
+    sl, _ = ints([4, 6])
+    st, _ = ints([62, 0])
+    ct, _ = ints([3, 5])
+    tk, _ = ints([7, 8, 9, 1, 2, 3, 4, 5])
+    wc, _ = ints([1, 2])
+    wn, _ = ints([2, 0, 4])
+    uo, _ = ints(upd_off)
+    updates = np.array([[0, 4, 1, 5], [0, 6, 0, 3], [1, 6, 0, 2]], dtype=np.int32)
+
+    def pack(tp=tp, bb=bb, wb=wb, cap=cap, wn=wn):
+        _ok(host_lib().moe_pack_padded(buf.ctypes.data_as(_IP), tp, bb, wb, 2, sl, st, ct, tk, wc, wn, pad, groups, uo,
+                                       cap, updates.ctypes.data_as(_IP), 3))
+
+    pack()
+    o, v = 0, {}
+    for name, n in layout(tp, bb, wb):
+        v[name] = buf[o:o + n].tolist()
+        o += n
+    assert v["token_ids"] == [7, 8, 9, 1, 2, 3, 4, 5] + [0] * 8
+    assert v["seq_of_token"] == [0] * 3 + [1] * 5 + [-1] * 8
+    assert v["pos"] == [62, 63, 64, 0, 1, 2, 3, 4] + [0] * 8
+    assert v["cu_seqlens"] == [0, 3, 8, 8, 8]
+    assert v["slots"] == [4, 6, pad, pad]
+    assert v["seq_start"] == [62, 0, 0, 0] and v["seq_end"] == [65, 5, 0, 0]
+    assert v["want_rows"] == [2, 3, 7, 0]
+    g0 = buf[upd_off[0]:upd_off[0] + 3 * cap].reshape(cap, 3).tolist()
+    g1 = buf[upd_off[1]:upd_off[1] + 3 * cap].reshape(cap, 3).tolist()
+    assert g0 == [[4, 1, 5], [6, 0, 3], [pad, 0, 0]]
+    assert g1 == [[6, 0, 2]] + [[pad, 0, 0]] * 2
+    assert buf[-4:].tolist() == [-7] * 4
+    # the same arrays as the unpadded packer writes, where both have something
+    plain = np.zeros(64, dtype=np.int32)
+    info = fill_host(plain, [4, 6], [62, 0], [[7, 8, 9], [1, 2, 3, 4, 5]], [[2], [0, 4]])
+    for name, (a, n) in info["offsets"].items():
+        assert v[name][:n] == plain[a:a + n].tolist(), name
+    for bad in (dict(tp=7), dict(bb=1), dict(wb=2), dict(cap=1), dict(wn=ints([3, 0, 4])[0])):
+        with pytest.raises(ValueError):
+            pack(**bad)

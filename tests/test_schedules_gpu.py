@@ -92,7 +92,14 @@ def test_steps_that_mix_fresh_prompts_continued_ones_and_single_tokens(model_dir
     assert at == {r: len(t) for r, t in reqs.items()}
     d, eng = engine(model_dirs, name, dtype, max_tokens=64 * 10, max_slots=4)
     logits, picks = helpers.run_schedule(eng, steps)
+    # every such step is replayed from the captured graph of its padded shape
+    assert eng.graphs_of("prompt") and len(eng.graphs_of("continued")) >= 2 and not eng.graphs_of("decode")
     helpers.check_schedule_against_plain(d, reqs, logits, picks, G.tol(dtype), G.flip(dtype))
+    if dtype == "float32":        # the same steps launched kernel by kernel, unpadded
+        d, eng = engine(model_dirs, name, dtype, max_tokens=64 * 10, max_slots=4, use_graphs=False)
+        again, _ = helpers.run_schedule(eng, steps)
+        worst = max(helpers.max_rel_err(logits[k], again[k]) for k in logits)
+        assert worst < G.tol_cut(dtype), worst
 
 
 @pytest.mark.parametrize("name,dtype", [(n, dt) for n in ("A", "B", "C", "D", "E") for dt in ("float32", "bfloat16")])
@@ -107,6 +114,7 @@ def test_a_prompt_fed_in_chunks_matches_plain(model_dirs, name, dtype, chunk):
         steps.append({"entries": entries, "end": [r for r, t in reqs.items() if o < len(t) <= o + chunk]})
     d, eng = engine(model_dirs, name, dtype, max_tokens=64 * 8, max_slots=2)
     logits, picks = helpers.run_schedule(eng, steps)
+    assert eng.graphs_of("prompt") and eng.graphs_of("continued")
     helpers.check_schedule_against_plain(d, reqs, logits, picks, G.tol(dtype), G.flip(dtype))
 
 
