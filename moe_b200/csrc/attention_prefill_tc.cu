@@ -1,4 +1,5 @@
-// Attention of whole prompts on the 5th-generation tensor cores (tcgen05), head sizes 64 and 128.
+// Attention of a step of several tokens a sequence on the 5th-generation tensor cores (tcgen05),
+// head sizes 64 and 128: whole prompts, and sequences that go on from the cache.
 //
 // Same formulas as attention_prefill.cu (reference: src/model.rs:794-827): causal, optional window
 // [p + 1 - w, p], scale 1/sqrt(d), kv head = head / (heads / kv_heads); scores, running maximum
@@ -7,6 +8,12 @@
 //
 // One CTA takes 128 query rows of one (sequence, head) and walks the key tiles of 128 that the
 // causal window allows:
+//
+// The keys of a query tile come in two runs of tiles: first the positions before the step, from the
+// pages of the cache (tiles of 128 absolute positions, each two pages of 64 fetched by a copy of
+// its own; none for a sequence that starts at 0), then the step's own keys from its buffers (tiles
+// of 128 of its new tokens).  The step's keys are never read from the cache, so they may be put
+// there before or after, and a ring of a window's size is enough.
 //
 //   warp 0      TMA producer: Q once, then K and V tiles through a ring of two stages
 //   warp 1      MMA issuer: S = Q K^T (operands in shared memory, S in tensor memory, two
@@ -72,6 +79,12 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
         ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
         : "memory");
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
@@ -167,9 +180,11 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 template <int HD>
 __global__ void __launch_bounds__(320)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                       const __grid_constant__ CUtensorMap tmV, __nv_bfloat16* __restrict__ out,
-                       const int* __restrict__ cu_seqlens, int num_seqs, int nh, int nkv, int window, float scale_log2,
-                       int* status) {
+                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmKc,
+                       const __grid_constant__ CUtensorMap tmVc, __nv_bfloat16* __restrict__ out,
+                       const int* __restrict__ cu_seqlens, const int* __restrict__ seq_start,
+                       const int* __restrict__ slots, const int* __restrict__ tables, int table_stride, int ring,
+                       int num_pages, int num_seqs, int nh, int nkv, int window, float scale_log2, int* status) {
     constexpr int CH = HD / 64;                      // 128-byte chunks of a row
     constexpr int TILE_BYTES = CH * 128 * 128;       // a 128-row operand tile
     constexpr int STAGE_BYTES = 2 * TILE_BYTES;      // K, then V
@@ -203,8 +218,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     const int q0 = q_tile * QT;
     const int head = blockIdx.x % nh, kvh = head / (nh / nkv);
     const int q_last = min(q0 + QT, len) - 1;
-    const int kv_lo = window > 0 ? max(0, q0 + 1 - window) / KT : 0;
-    const int n_tiles = q_last / KT - kv_lo + 1;
+    // positions: the sequence held `start` tokens before the step; the query of row r stands at
+    // start + q0 + r.  Key tiles: `nc` tiles of absolute positions [kt_lo * KT, ...) below `start`
+    // from the cache, then tiles t_lo ... of the step's own tokens.
+    const int start = seq_start ? seq_start[seq] : 0;
+    const int lo_pos = window > 0 ? max(0, start + q0 + 1 - window) : 0;      // oldest key any row of the tile sees
+    const int kt_lo = lo_pos / KT;
+    const int nc = lo_pos < start ? (start - 1) / KT - kt_lo + 1 : 0;
+    const int t_lo = window > 0 ? max(0, q0 + 1 - window) / KT : 0;
+    const int n_tiles = nc + q_last / KT - t_lo + 1;
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t sQ = base;
@@ -255,21 +277,50 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             // the values, as the MMA issuer asks for them (scores of tile j + 1 before P V of tile j).
             bool ok = true;
             int nk = 0, nv = 0;                         // tiles whose keys / values have been requested
+            const int* table = nc > 0 ? tables + (size_t)slots[seq] * table_stride : nullptr;
+            int page_row[2][2];                         // of a cache tile's two pages: first row in the cache seen
+                                                        // as rows of one head's keys, [page][kv head][64] of them
+            auto find_pages = [&](int it) {
+                for (int h = 0; h < 2; h++) {
+                    const int a = (kt_lo + it) * KT + h * 64;         // first position of the page
+                    int page = table[(ring > 0 ? a % ring : a) >> 6];
+                    if (page < 0 || page >= num_pages) {
+                        // only a page that holds a key some row needs is an error; the half of a tile
+                        // beyond the sequence's cached tokens just has to be finite, and every page is
+                        if (a < start && a + 63 >= lo_pos) atomicOr(status, ST_BAD_PAGE);
+                        page = 0;
+                    }
+                    page_row[it & 1][h] = (page * nkv + kvh) * 64;
+                }
+            };
             auto load_k = [&](int it) {
                 const int st = it & 1;
                 if (!mbar_wait(k_empty(st), ((it >> 1) & 1) ^ 1, &s_abort, status, 0x41)) return false;
+                if (it < nc) find_pages(it);
                 mbar_expect_tx(k_full(st), TILE_BYTES);
-                for (int c = 0; c < CH; c++)
-                    tma_load_3d(sK(st) + c * 16384, &tmK, c * 64, kvh, tok0 + (kv_lo + it) * KT, k_full(st));
+                for (int c = 0; c < CH; c++) {
+                    if (it < nc) {
+                        tma_load_2d(sK(st) + c * 16384, &tmKc, c * 64, page_row[st][0], k_full(st));
+                        tma_load_2d(sK(st) + c * 16384 + 8192, &tmKc, c * 64, page_row[st][1], k_full(st));
+                    } else {
+                        tma_load_3d(sK(st) + c * 16384, &tmK, c * 64, kvh, tok0 + (t_lo + it - nc) * KT, k_full(st));
+                    }
+                }
                 nk = it + 1;
                 return true;
             };
-            auto load_v = [&](int it) {
+            auto load_v = [&](int it) {             // (after load_k of the same tile, which found its pages)
                 const int st = it & 1;
                 if (!mbar_wait(v_empty(st), ((it >> 1) & 1) ^ 1, &s_abort, status, 0x42)) return false;
                 mbar_expect_tx(v_full(st), TILE_BYTES);
-                for (int c = 0; c < CH; c++)
-                    tma_load_3d(sV(st) + c * 16384, &tmV, c * 64, kvh, tok0 + (kv_lo + it) * KT, v_full(st));
+                for (int c = 0; c < CH; c++) {
+                    if (it < nc) {
+                        tma_load_2d(sV(st) + c * 16384, &tmVc, c * 64, page_row[st][0], v_full(st));
+                        tma_load_2d(sV(st) + c * 16384 + 8192, &tmVc, c * 64, page_row[st][1], v_full(st));
+                    } else {
+                        tma_load_3d(sV(st) + c * 16384, &tmV, c * 64, kvh, tok0 + (t_lo + it - nc) * KT, v_full(st));
+                    }
+                }
                 nv = it + 1;
                 return true;
             };
@@ -340,7 +391,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         const int half = (warp - 2) >> 2;                      // which half of the columns
         const int r = qd * 32 + lane;                          // row of the tile
         const uint32_t lane_base = (uint32_t)(qd * 32) << 16;
-        const int row = q0 + r;                                // position of this thread's query
+        const int row = q0 + r;                                // this thread's query among the step's tokens
+        const int prow = start + row;                          // and its position
         const uint32_t to = tmem + COL_O + lane_base + half * (HD / 2);
         float m = -INFINITY, l = 0.f;
         bool ok = true;
@@ -350,12 +402,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             if (!ok) break;
             tc_fence_after();
             const uint32_t ts = tmem + COL_S + b * KT + lane_base + half * (KT / 2);
-            const int j0 = (kv_lo + it) * KT, jh = j0 + half * (KT / 2);
+            // the tile's first position, and the end of what its source holds of the sequence
+            const int j0 = it < nc ? (kt_lo + it) * KT : start + (t_lo + it - nc) * KT;
+            const int jmax = it < nc ? start : start + len;
+            const int jh = j0 + half * (KT / 2);
             // a tile strictly below the diagonal, inside the window and inside the sequence needs no mask
-            const bool full = j0 + KT - 1 <= q0 && j0 + KT <= len && (window <= 0 || j0 >= q0 + QT - window);
+            const bool full = j0 + KT - 1 <= start + q0 && j0 + KT <= jmax &&
+                              (window <= 0 || j0 >= start + q0 + QT - window);
             auto tile_softmax = [&](auto masked_tag) -> bool {
                 constexpr bool MASKED = decltype(masked_tag)::value;
-                auto visible = [&](int j) { return j <= row && j < len && (window <= 0 || j >= row + 1 - window); };
+                auto visible = [&](int j) { return j <= prow && j < jmax && (window <= 0 || j >= prow + 1 - window); };
                 float s[2][32];                                  // this thread's 64 scores
                 // pass 1: the maximum of the half row (of the raw scores: the scale is positive)
                 float mx0 = -INFINITY, mx1 = -INFINITY;
@@ -510,9 +566,30 @@ bool make_map(CUtensorMap* map, const void* ptr, int tokens, int heads, int hd) 
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// one layer's keys (or values) in the cache, bf16 [pages][kv heads][64][hd], as rows of hd elements;
+// box = 64 elements of the 64 rows of one (page, head), 128-byte swizzle
+bool make_cache_map(CUtensorMap* map, const void* ptr, long long rows, int hd) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+    cuuint32_t box[2] = {64, 64};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct CacheArgs {
+    CUtensorMap tmK, tmV;
+    const int *seq_start, *slots, *tables;
+    int table_stride, ring, num_pages;
+};
+
 template <int HD>
-int launch(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, void* out, const int* cu_seqlens,
-           int num_seqs, int num_tokens, int nh, int nkv, int window, float scale, int* status, cudaStream_t stream) {
+int launch(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const CacheArgs& c, void* out,
+           const int* cu_seqlens, int num_seqs, int num_tokens, int nh, int nkv, int window, float scale, int* status,
+           cudaStream_t stream) {
     constexpr int TILE_BYTES = (HD / 64) * 128 * 128;
     const int smem = 5 * TILE_BYTES + 1024 + 192;
     static bool configured = false;
@@ -522,8 +599,21 @@ int launch(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tm
         configured = true;
     }
     dim3 grid(((num_tokens + QT - 1) / QT + num_seqs) * nh);
-    return launch_pdl(attn_prefill_tc_kernel<HD>, grid, 320, (size_t)smem, stream, tmQ, tmK, tmV, (__nv_bfloat16*)out,
-                      cu_seqlens, num_seqs, nh, nkv, window, scale * 1.4426950408889634f, status);
+    return launch_pdl(attn_prefill_tc_kernel<HD>, grid, 320, (size_t)smem, stream, tmQ, tmK, tmV, c.tmK, c.tmV,
+                      (__nv_bfloat16*)out, cu_seqlens, c.seq_start, c.slots, c.tables, c.table_stride, c.ring,
+                      c.num_pages, num_seqs, nh, nkv, window, scale * 1.4426950408889634f, status);
+}
+
+int run(const void* q, const void* k, const void* v, CacheArgs& c, void* out, const int* cu_seqlens, int num_seqs,
+        int num_tokens, int nh, int nkv, int hd, int window, float scale, int* status, cudaStream_t stream) {
+    CUtensorMap tmQ, tmK, tmV;
+    if (!make_map(&tmQ, q, num_tokens, nh, hd) || !make_map(&tmK, k, num_tokens, nkv, hd) ||
+        !make_map(&tmV, v, num_tokens, nkv, hd))
+        return -1;
+    if (!c.seq_start) c.tmK = tmK, c.tmV = tmV;         // never used: no tile comes from the cache
+    if (hd == 64)
+        return launch<64>(tmQ, tmK, tmV, c, out, cu_seqlens, num_seqs, num_tokens, nh, nkv, window, scale, status, stream);
+    return launch<128>(tmQ, tmK, tmV, c, out, cu_seqlens, num_seqs, num_tokens, nh, nkv, window, scale, status, stream);
 }
 
 }  // namespace
@@ -538,11 +628,33 @@ MOE_API int moe_attention_prefill_tc(const void* q, const void* k, const void* v
     if (nkv <= 0 || nh % nkv != 0 || nh > 65535) return (int)cudaErrorInvalidValue;
     if (hd != 64 && hd != 128) return -1;
     if ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15) != 0) return -1;
-    CUtensorMap tmQ, tmK, tmV;
-    if (!make_map(&tmQ, q, num_tokens, nh, hd) || !make_map(&tmK, k, num_tokens, nkv, hd) ||
-        !make_map(&tmV, v, num_tokens, nkv, hd))
+    CacheArgs c{};
+    return run(q, k, v, c, out, cu_seqlens, num_seqs, num_tokens, nh, nkv, hd, window, scale, status, stream);
+}
+
+// The same for sequences that go on from the cache: sequence i held seq_start[i] tokens before the
+// step (0: a fresh one), whose keys and values lie in the pages of one layer's cache, k_cache and
+// v_cache [num_pages][nkv][64][hd] bfloat16, listed in row slots[i] of `tables` (table_stride ints a
+// row; position p in page table[(ring ? p % ring : p) / 64]).  The step's own keys and values are
+// read from k and v, never from the cache.  Returns -1 for what this kernel does not take (then with
+// nothing launched): the caller uses the kernel on the CUDA cores.
+MOE_API int moe_attention_cached_tc(const void* q, const void* k, const void* v, const void* k_cache,
+                                    const void* v_cache, void* out, const int* cu_seqlens, const int* seq_start,
+                                    const int* slots, const int* tables, int table_stride, int ring, int page_size,
+                                    int num_pages, int num_seqs, int num_tokens, int nh, int nkv, int hd, int window,
+                                    float scale, int* status, cudaStream_t stream) {
+    if (num_tokens <= 0) return 0;
+    if (nkv <= 0 || nh % nkv != 0 || nh > 65535 || num_pages <= 0) return (int)cudaErrorInvalidValue;
+    if (!seq_start || !slots || !tables || !k_cache || !v_cache) return (int)cudaErrorInvalidValue;
+    if (hd != 64 && hd != 128) return -1;
+    if (page_size != 64 || ring % 64 != 0 || (long long)num_pages * nkv * 64 > 0x7fffffffLL) return -1;
+    if ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) != 0)
         return -1;
-    if (hd == 64)
-        return launch<64>(tmQ, tmK, tmV, out, cu_seqlens, num_seqs, num_tokens, nh, nkv, window, scale, status, stream);
-    return launch<128>(tmQ, tmK, tmV, out, cu_seqlens, num_seqs, num_tokens, nh, nkv, window, scale, status, stream);
+    CacheArgs c{};
+    c.seq_start = seq_start, c.slots = slots, c.tables = tables;
+    c.table_stride = table_stride, c.ring = ring, c.num_pages = num_pages;
+    if (!make_cache_map(&c.tmK, k_cache, (long long)num_pages * nkv * 64, hd) ||
+        !make_cache_map(&c.tmV, v_cache, (long long)num_pages * nkv * 64, hd))
+        return -1;
+    return run(q, k, v, c, out, cu_seqlens, num_seqs, num_tokens, nh, nkv, hd, window, scale, status, stream);
 }

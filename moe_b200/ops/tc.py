@@ -35,6 +35,8 @@ def lib():
         L.moe_attention_prefill_bf16.restype = c_int
         L.moe_attention_prefill_tc.argtypes = [P, P, P, P, P, I, I, I, I, I, I, c_float, P, P]
         L.moe_attention_prefill_tc.restype = c_int
+        L.moe_attention_cached_tc.argtypes = [P] * 10 + [I] * 10 + [c_float, P, P]
+        L.moe_attention_cached_tc.restype = c_int
         L.moe_tc_set_pdl.argtypes = [c_int]
         L.moe_tc_set_pdl.restype = None
         import os
@@ -204,6 +206,28 @@ def attention_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, batch, 
     if code == -1:
         return False
     core._ok(code, "attention_prefill")
+    return True
+
+
+def attention_cached(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, view, batch, out: torch.Tensor, *,
+                     nh: int, window, scale: float, status) -> bool:
+    """Causal (optionally windowed) attention of a step whose sequences go on from the cache, on
+    tcgen05: the keys before the step from the pages of ``view`` (one layer's cache), the step's own
+    from ``k_new`` / ``v_new``.  False, with nothing launched, for what the kernel does not take
+    (head sizes other than 64 and 128, another dtype or page size)."""
+    g = view.group
+    hd = g.head_dim
+    if q.dtype != torch.bfloat16 or g.dtype != torch.bfloat16 or hd not in (64, 128) or not _ATTN_TC:
+        return False
+    code = lib().moe_attention_cached_tc(q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(), view.k.data_ptr(),
+                                         view.v.data_ptr(), out.data_ptr(), batch.cu_seqlens.data_ptr(),
+                                         batch.seq_start.data_ptr(), batch.slots.data_ptr(), g.table.data_ptr(),
+                                         g.table.stride(0), g.ring, g.page_size, g.num_pages, batch.num_seqs,
+                                         batch.num_tokens, nh, g.num_kv_heads, hd, int(window or 0), float(scale),
+                                         status.data_ptr(), core._stream())
+    if code == -1:
+        return False
+    core._ok(code, "attention_cached_tc")
     return True
 
 

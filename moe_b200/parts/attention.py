@@ -132,9 +132,16 @@ class GQAttention(Part):
 
                 done = tc.attention_prefill(q, k_new, v_new, batch, ctx, nh=self.nh, nkv=self.nkv, hd=self.hd,
                                             window=self.window, scale=self.scale, status=rt.status)
+            elif self.own_kv and rt.is_bf16:
+                # keys of earlier steps from the pages of the cache, keys of this step from its own
+                # buffers; the same tensor-core kernel
+                from ..ops import tc
+
+                done = tc.attention_cached(q, k_new, v_new, cache_view, batch, ctx, nh=self.nh, window=self.window,
+                                           scale=self.scale, status=rt.status)
             if not done:
-                # keys of earlier steps from the cache, keys of this step from its own buffers: 64
-                # queries to a block, 32-bit arithmetic (the plain kernel where that one declines)
+                # the same on the CUDA cores in 32-bit arithmetic, 64 queries to a block (the plain
+                # kernel where that one declines)
                 kw = dict(nh=self.nh, window=self.window, scale=self.scale, use_local=self.own_kv, status=rt.status)
                 if not core.attention_tiled(q, k_new, v_new, cache_view, batch, ctx, **kw):
                     core.attention_generic(q, k_new, v_new, cache_view, batch, ctx, **kw)
