@@ -362,6 +362,46 @@ def run_fp32_long(args):
     return 0
 
 
+def run_long_prompt(args):
+    """One prompt of ``--prompt-len`` tokens (32,768 unless given) in bfloat16 through the engine's
+    step, which runs it in pieces of at most 8,192 tokens that go on from the cache.  Prints one JSON
+    line; not the benchmark record."""
+    import torch
+
+    import moe_b200
+
+    pk = peaks()
+    cfg = dict(A27B, max_position_embeddings=131072)
+    layers = args.layers or cfg["num_hidden_layers"]
+    cfg["num_hidden_layers"] = layers
+    V = cfg["vocab_size"]
+    T = args.prompt_len or 32768
+    model = moe_b200.random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+    eng = moe_b200.Engine(model, max_tokens=-(-T // 64) * 64 + 64, max_slots=1)
+    ids = [(i * 7 + 13) % V for i in range(T)]
+    times = []
+    for it in range(3):
+        s = eng.new_sequence()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        eng.step([s], [ids], check=False)
+        b.record()
+        torch.cuda.synchronize()
+        eng.rt.check()
+        eng.release(s)
+        times.append(a.elapsed_time(b))
+    ms = sorted(times)[1]
+    nums = model_numbers(cfg, layers)
+    flops = 2 * T * nums["active_per_token"] + 2 * nums["head"] \
+        + layers * 4 * cfg["num_attention_heads"] * cfg["head_dim"] * T * (T + 1) // 2
+    print(json.dumps({"workload": "bfloat16, one prompt, pieces of %d tokens" % eng.max_step_tokens, "layers": layers,
+                      "prompt_tokens": T, "ms": round(ms, 2), "tokens_per_s": round(T / (ms / 1e3), 1),
+                      "tflops": round(flops / (ms / 1e3) / 1e12, 1),
+                      "frac": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}))
+    return 0
+
+
 def profile_step(args):
     """A small case for a profiler: the model's layer sizes, few layers, graphs off (every kernel is
     a launch of its own); only the steps between cudaProfilerStart and cudaProfilerStop matter."""
@@ -434,8 +474,9 @@ def main():
                     help="with --profile-step: the path whose kernels are wanted")
     ap.add_argument("--shape", choices=["a2.7b", "57b"], default="a2.7b", help="with --sweep: the layer sizes")
     ap.add_argument("--prompt-len", type=int, default=0, help="with --sweep: tokens in each prompt (default 512)")
-    ap.add_argument("--workload", choices=["fp32-32k"], default=None,
-                    help="fp32-32k: the true 32-bit path at a context of 32,768 (prints its own line, no benchmark record)")
+    ap.add_argument("--workload", choices=["fp32-32k", "long-prompt"], default=None,
+                    help="fp32-32k: the true 32-bit path at a context of 32,768; long-prompt: one bfloat16 prompt of "
+                         "--prompt-len tokens [32768] run in pieces (each prints its own line, no benchmark record)")
     ap.add_argument("--unequal", action="store_true", help="with --sweep: prompts of unequal lengths, 256 to 2,048 tokens")
     ap.add_argument("--sweep", default=None, help="comma-separated batch sizes: print decode throughput for each "
                                                   "and no benchmark line")
@@ -450,6 +491,8 @@ def main():
     args.warmup = max(args.warmup, 3)
     if args.profile_step:
         return profile_step(args)
+    if args.workload == "long-prompt":
+        return run_long_prompt(args)
     if args.workload == "fp32-32k":
         return run_fp32_long(args)
     return run_ours(args)
