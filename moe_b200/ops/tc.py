@@ -111,8 +111,12 @@ def register_side_stream(stream) -> None:
     _side_handles.add(stream.cuda_stream)
 
 
-def token_tile(rows_per_group: float) -> int:
-    """Smallest token tile (the MMA's N) that holds the expected rows of a group."""
+def token_tile(rows_per_group: float, grouped: bool = False) -> int:
+    """Smallest token tile (the MMA's N) that holds the expected rows of a group.  Grouped products
+    of more than 16 rows a group take a tile of at least 128, i.e. the persistent form (measured at
+    60 groups of 2048 x 1408: equal at 17 rows a group, 12 % faster at 34)."""
+    if grouped and rows_per_group > 16:
+        return 128 if rows_per_group <= 128 else 256
     for bn in (16, 32, 64, 128, 256):
         if rows_per_group <= bn:
             return bn
@@ -141,7 +145,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swiglu: bool
         raise core.KernelError("gemm_tc: group_offsets must have G + 1 entries")
     grouped = group_offsets is not None
     if bn is None:
-        bn = token_tile(M / max(G, 1) if grouped else min(M, 256))
+        bn = token_tile(M / max(G, 1), True) if grouped else token_tile(min(M, 256))
     L = lib()
     n_tiles = -(-N // 128)
     gy = c_int(0)
