@@ -439,6 +439,17 @@ def profile_step(args):
         slots = [eng.new_sequence() for _ in range(B)]
         eng.step(slots, [[(i * 7 + 31 * b) % V for i in range(PROMPT_LEN)] for b in range(B)], [[] for _ in slots])
         run = lambda i: eng.step(slots, [[(i * 13 + 7 * b) % V] for b in range(B)])
+    elif args.profile_step == "chunk":
+        # a piece of a long prompt: --prompt-len tokens [2048] that go on from 6,144 tokens in the cache
+        n, past = args.prompt_len or PREFILL_TOKENS, 6144
+        eng = moe_b200.Engine(model, max_tokens=past + n + 64, max_slots=1, use_graphs=False)
+        s = eng.new_sequence()
+        eng.step([s], [[(i * 7 + 13) % V for i in range(past)]], [[]])
+        ids = [(i * 11 + 5) % V for i in range(n)]
+
+        def run(i):
+            eng.step([s], [ids])
+            eng.truncate(s, past)
     else:
         eng = moe_b200.Engine(model, max_tokens=PREFILL_TOKENS + 64, max_slots=1, use_graphs=False)
         ids = [(i * 7 + 13) % V for i in range(PREFILL_TOKENS)]
@@ -466,7 +477,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (reported in config)")
-    ap.add_argument("--profile-step", choices=["decode", "prefill", "sample"], default=None,
+    ap.add_argument("--profile-step", choices=["decode", "prefill", "chunk", "sample"], default=None,
                     help="run a few steps of one kind between cudaProfilerStart/Stop (for ncu "
                          "--profile-from-start off) and print no benchmark line")
     ap.add_argument("--batch", type=int, default=8, help="with --profile-step decode: sequences in the batch")
