@@ -21,11 +21,16 @@
 //               MN-major operand
 //   warps 2-9   two threads per query row (half of the columns each): read the scores from tensor
 //               memory, mask, keep the running maximum and sum, and write P (two bfloat16 terms)
-//               back to tensor memory.  The output row accumulates in tensor memory over all
-//               tiles; its threads rescale it there when the running maximum moves
+//               back to tensor memory IN THE PLACE OF THE SCORES they were made from (a thread's
+//               64 scores of 32 bits are the room of its 64 + 64 values of 16 bits).  The output
+//               row accumulates in tensor memory over all tiles; its threads rescale it there
+//               when the running maximum moves
 //
-// S of tile j + 1 is issued before the softmax of tile j has finished, so the tensor cores work
-// on the next scores meanwhile.  Every barrier wait is bounded (ST_WAIT_TIMEOUT).
+// S of tile j + 1 is issued before the softmax of tile j has finished, and since P of tile j + 1
+// lies in the other score buffer, its softmax runs while the tensor cores still work on P V of
+// tile j.  The MMAs of one thread run in the order they were issued: S of tile j + 2, which
+// overwrites P of tile j, is issued after P V of tile j and needs no barrier of its own.
+// Every barrier wait is bounded (ST_WAIT_TIMEOUT).
 #include <cuda.h>
 
 #include <mutex>
@@ -36,8 +41,9 @@
 namespace {
 
 constexpr int QT = 128, KT = 128;
-// tensor-memory columns: two score buffers, the output rows, P's two terms
-constexpr uint32_t COL_S = 0, COL_O = 256, COL_PHI = 384, COL_PLO = 448, TMEM_COLS = 512;
+// tensor-memory columns: two score buffers (each later holds P: for every 32 keys 16 columns of the
+// first term, then 16 of the second, in the place of their scores), the output rows
+constexpr uint32_t COL_S = 0, COL_O = 256, TMEM_COLS = 512;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -178,7 +184,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 template <int HD>
-__global__ void __launch_bounds__(320)
+__global__ void __launch_bounds__(320, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                        const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmKc,
                        const __grid_constant__ CUtensorMap tmVc, __nv_bfloat16* __restrict__ out,
@@ -239,7 +245,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     auto v_full = [&](int st) { return bars + 8u * (15 + st); };
     auto v_empty = [&](int st) { return bars + 8u * (17 + st); };
     auto s_full = [&](int b) { return bars + 8u * (5 + b); };
-    auto s_empty = [&](int b) { return bars + 8u * (7 + b); };
     const uint32_t p_full = bars + 8u * 9, pv_done = bars + 8u * 10;
     auto x_bar = [&](int q) { return bars + 8u * (11 + q); };
 
@@ -251,7 +256,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             mbar_init(v_full(i), 1);
             mbar_init(v_empty(i), 1);
             mbar_init(s_full(i), 1);
-            mbar_init(s_empty(i), 8);        // one arrival per softmax warp
         }
         mbar_init(p_full, 8);
         for (int i = 0; i < 4; i++) mbar_init(x_bar(i), 2);      // the two warps that share 32 rows
@@ -345,7 +349,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             auto issue_s = [&](int it) {           // scores of tile `it` into buffer it & 1
                 const int b = it & 1;
                 if (!mbar_wait(k_full(b), (it >> 1) & 1, &s_abort, status, 0x45)) return false;
-                if (!mbar_wait(s_empty(b), ((it >> 1) & 1) ^ 1, &s_abort, status, 0x46)) return false;
+                // (buffer b held P of tile it - 2: its P V product was issued before this, and the
+                // MMAs run in order)
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ks++) {
@@ -364,12 +369,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 ok = mbar_wait(v_full(st), (it >> 1) & 1, &s_abort, status, 0x47) && mbar_wait(p_full, it & 1, &s_abort, status, 0x48);
                 if (!ok) break;
                 tc_fence_after();
+                const uint32_t tp = tmem + COL_S + st * KT;      // P lies where the tile's scores were
 #pragma unroll
-                for (int half = 0; half < 2; half++) {
+                for (int term = 0; term < 2; term++) {
 #pragma unroll
                     for (int ks = 0; ks < KT / 16; ks++)         // 16 keys per step: 8 columns of packed P
-                        umma_ts(tmem + COL_O, tmem + (half ? COL_PLO : COL_PHI) + ks * 8, desc_mn_major(sV(st) + ks * 2048),
-                                idesc_pv, (it | half | ks) != 0);       // the output row accumulates over all tiles
+                        umma_ts(tmem + COL_O, tp + (ks / 2) * 32 + term * 16 + (ks % 2) * 8,
+                                desc_mn_major(sV(st) + ks * 2048), idesc_pv,
+                                (it | term | ks) != 0);          // the output row accumulates over all tiles
                 }
                 umma_commit(pv_done);
                 umma_commit(v_empty(st));
@@ -412,18 +419,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             auto tile_softmax = [&](auto masked_tag) -> bool {
                 constexpr bool MASKED = decltype(masked_tag)::value;
                 auto visible = [&](int j) { return j <= prow && j < jmax && (window <= 0 || j >= prow + 1 - window); };
-                float s[2][32];                                  // this thread's 64 scores
                 // pass 1: the maximum of the half row (of the raw scores: the scale is positive)
                 float mx0 = -INFINITY, mx1 = -INFINITY;
-                tmem_ld32_issue(ts, s[0]);
-                tmem_ld32_issue(ts + 32, s[1]);
-                tmem_ld_wait();
+                {
+                    float s[2][32];                              // this thread's 64 scores
+                    tmem_ld32_issue(ts, s[0]);
+                    tmem_ld32_issue(ts + 32, s[1]);
+                    tmem_ld_wait();
 #pragma unroll
-                for (int c = 0; c < 2; c++) {
+                    for (int c = 0; c < 2; c++) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        if (!MASKED || visible(jh + c * 32 + i)) mx0 = fmaxf(mx0, s[c][i]);
-                        if (!MASKED || visible(jh + c * 32 + i + 1)) mx1 = fmaxf(mx1, s[c][i + 1]);
+                        for (int i = 0; i < 32; i += 2) {
+                            if (!MASKED || visible(jh + c * 32 + i)) mx0 = fmaxf(mx0, s[c][i]);
+                            if (!MASKED || visible(jh + c * 32 + i + 1)) mx1 = fmaxf(mx1, s[c][i + 1]);
+                        }
                     }
                 }
                 // ... and of the whole row
@@ -440,10 +449,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                     alpha = (m == -INFINITY) ? 1.f : ex2_approx(m - m_new);     // nothing accumulated yet: nothing to rescale
                 }
                 // the products so far belong to the old maximum: wait for the last one, rescale the row
-                if (it > 0 && !mbar_wait(pv_done, (it - 1) & 1, &s_abort, status, 0x4b)) return false;
                 // (tcgen05.ld / st are warp-wide instructions: if ANY row of the warp has to be rescaled,
-                // every lane takes part, the others with a factor of one)
+                // every lane takes part, the others with a factor of one).  The last product is P V
+                // of tile it - 1; none later can have been issued, since that needs this warp's P.
                 if (__any_sync(0xffffffffu, alpha != 1.f)) {
+                    if (it > 0 && !mbar_wait(pv_done, (it - 1) & 1, &s_abort, status, 0x4b)) return false;
                     tc_fence_after();
 #pragma unroll
                     for (int c = 0; c < HD / 64; c++) {
@@ -455,15 +465,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                         tmem_st32(to + c * 32, t);
                     }
                 }
-                // pass 2: P in two bfloat16 terms, into tensor memory (two keys per 32-bit column)
+                // pass 2: P in two bfloat16 terms, into tensor memory (two keys per 32-bit column), 32
+                // scores at a time, read again (they are not kept over the exchange above: registers)
+                // and overwritten by their own P: 16 columns of the first term, 16 of the second
                 const float neg_m = m_new == -INFINITY ? 0.f : -m_new;     // no key seen yet: every p is 0 anyway
                 float rs = 0.f, rs1 = 0.f;
 #pragma unroll
                 for (int c = 0; c < 2; c++) {
+                    float sc[32];
                     uint32_t hi[16], lo[16];
+                    tmem_ld32_issue(ts + c * 32, sc);
+                    tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-                        float x0 = fmaf(s[c][i], scale_log2, neg_m), x1 = fmaf(s[c][i + 1], scale_log2, neg_m);
+                        float x0 = fmaf(sc[i], scale_log2, neg_m), x1 = fmaf(sc[i + 1], scale_log2, neg_m);
                         if (MASKED) {
                             if (!visible(jh + c * 32 + i)) x0 = -INFINITY;
                             if (!visible(jh + c * 32 + i + 1)) x1 = -INFINITY;
@@ -474,8 +489,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                         hi[i / 2] = h;
                         lo[i / 2] = pack_bf16(p0 - __uint_as_float(h << 16), p1 - __uint_as_float(h & 0xffff0000u));
                     }
-                    tmem_st16(tmem + COL_PHI + lane_base + half * (KT / 4) + c * 16, hi);
-                    tmem_st16(tmem + COL_PLO + lane_base + half * (KT / 4) + c * 16, lo);
+                    tmem_st16(ts + c * 32, hi);
+                    tmem_st16(ts + c * 32 + 16, lo);
                 }
                 l = l * alpha + (rs + rs1);
                 m = m_new;
@@ -486,10 +501,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(s_empty(b));       // the scores have been read
-                mbar_arrive(p_full);           // P is in place, and the output row is rescaled
-            }
+            if (lane == 0) mbar_arrive(p_full);       // P is in place, and the output row is rescaled
         }
         // the row's sum: the two halves, in a fixed order
         if (ok) {

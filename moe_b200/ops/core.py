@@ -145,7 +145,7 @@ WAIT_ROLES = {
 }
 WAIT_ROLES_ATTENTION = {
     0x1: "producer: a free key stage", 0x2: "producer: a free value stage", 0x3: "producer: its own copies in flight",
-    0x4: "MMA issuer: the queries", 0x5: "MMA issuer: a key tile", 0x6: "MMA issuer: a free score buffer",
+    0x4: "MMA issuer: the queries", 0x5: "MMA issuer: a key tile",
     0x7: "MMA issuer: a value tile", 0x8: "MMA issuer: P", 0x9: "softmax: the scores", 0xa: "softmax: its partner's maximum",
     0xb: "softmax: the last P V product", 0xc: "softmax: its partner's sum", 0xd: "softmax: the final P V product",
 }
