@@ -93,6 +93,7 @@ class RoutedExperts(Part):
         # measured on a B200: the fused norm + router + dispatch launch wins up to 8 tokens and loses
         # from 16 on, where its single gathering block is the bottleneck
         self.fused_norm_tokens = int(os.environ.get("MOE_B200_NORM_ROUTE_MAX", "8"))
+        self.shared_beside = os.environ.get("MOE_B200_SHARED_BESIDE", "1") != "0"
         # up to this many tokens one block picks, inverts and gathers (one launch after the logits);
         # beyond, a warp per token picks and the inversion and the gather are launches of their own
         # (measured on a B200, ms a decode step at 16 / 32 / 64 tokens: 4.65 / 5.89 / 7.38 with one
@@ -203,8 +204,10 @@ class RoutedExperts(Part):
             one = torch.cat(rows, dim=0)
             self.w_router3 = torch.cat([one, one, one], dim=1).contiguous()
 
-    def route(self, rt, h, batch):
-        """-> (topk_idx [T, k] int32, topk_w [T, k] float32, shared_gate [T] float32 or None)"""
+    def route(self, rt, h, batch, after_logits=None):
+        """-> (topk_idx [T, k] int32, topk_w [T, k] float32, shared_gate [T] float32 or None)
+        ``after_logits``: called once the logits' product is launched (or, where logits and picks are one
+        launch, after that)."""
         T = h.f32.shape[0]
         topk_idx = rt.empty((T, self.k), torch.int32)
         topk_w = rt.empty((T, self.k), torch.float32)
@@ -214,11 +217,15 @@ class RoutedExperts(Part):
 
             logits = rt.empty((T, self.w_router3.shape[0]), torch.float32)
             if tc.gemm_tc(core.split3(h.f32), self.w_router3, logits, bn=64, splits=8, status=rt.status):
+                if after_logits is not None:
+                    after_logits()
                 core.router_topk(logits, self.k, self.norm_topk, self.scale, topk_idx, topk_w, num_experts=self.E,
                                  shared_gate=sg, seq_of_token=getattr(batch, "seq_of_token", None))
                 return topk_idx, topk_w, sg
         core.router(h.f32, self.w_router, self.k, self.norm_topk, self.scale, topk_idx, topk_w,
                     shared_gate_w=self.w_sgate, shared_gate=sg, seq_of_token=getattr(batch, "seq_of_token", None))
+        if after_logits is not None:
+            after_logits()
         return topk_idx, topk_w, sg
 
     def _shared(self, rt, h):
@@ -271,7 +278,20 @@ class RoutedExperts(Part):
                 gather=h.act if h.act.dtype == torch.bfloat16 and T <= 16 else None, status=rt.status)
             # (more tokens: the gather by that one block would take longer than a launch of its own)
         else:
-            topk_idx, topk_w, sg = self.route(rt, h, batch)
+            def shared_beside():
+                # Many tokens: pick, table inversion and gather are small launches that leave the GPU
+                # idle (37 us of a layer at 2,048 tokens), so the shared expert starts beside them on
+                # a second stream.  (Not before the logits' product: the shared expert's CTAs fill every
+                # SM's shared memory, and that product would wait for them to end.)
+                nonlocal ys, side
+                main = torch.cuda.current_stream()
+                side = rt.side_stream()
+                side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    ys = self._shared(rt, h)
+
+            topk_idx, topk_w, sg = self.route(rt, h, batch,
+                                              after_logits=shared_beside if self.ws_gu is not None and self.shared_beside else None)
             offsets = rt.empty((self.E + 1,), torch.int32)
             sorted_token = rt.empty((P,), torch.int32)
             pos_of_pair = rt.empty((P,), torch.int32)
