@@ -291,7 +291,7 @@ class RoutedExperts(Part):
                     ys = self._shared(rt, h)
 
             topk_idx, topk_w, sg = self.route(rt, h, batch,
-                                              after_logits=shared_beside if self.ws_gu is not None and self.shared_beside else None)
+                                              after_logits=shared_beside if self.ws_gu is not None and side is None and self.shared_beside else None)
             offsets = rt.empty((self.E + 1,), torch.int32)
             sorted_token = rt.empty((P,), torch.int32)
             pos_of_pair = rt.empty((P,), torch.int32)
