@@ -24,10 +24,13 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_tokens: int = 128, te
              top_p: float = 0.95, top_k: int = 0, repeat_penalty: float = 1.0, seed: int = 0,
              eos: Optional[Sequence[int]] = None, batch_size: Optional[int] = None, ctx: Optional[int] = None,
              on_token: Optional[Callable[[int, int], bool]] = None,
-             stats: Optional[GenerationStats] = None, lookahead: Optional[bool] = None) -> List[GenerationResult]:
+             stats: Optional[GenerationStats] = None, lookahead: Optional[bool] = None,
+             logprobs: int = 0) -> List[GenerationResult]:
     """Generate after each prompt (lists of token ids); see ``engine.generate.generate``.
 
-    ``eos`` defaults to the model's ``eos_token_id``; pass ``()`` to ignore it."""
+    ``eos`` defaults to the model's ``eos_token_id``; pass ``()`` to ignore it.  ``logprobs`` N > 0
+    (the reference's ``Plan::logprobs``, src/generate.rs:31): each result also lists, per emitted
+    token, its logprob and the N most likely tokens at its place, from the raw logits."""
     if eos is None:
         eos = engine.model.spec.eos_token_ids
     params = SamplingParams(temp=temp, top_p=top_p, top_k=top_k, repeat_penalty=repeat_penalty, seed=seed)
@@ -35,4 +38,4 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_tokens: int = 128, te
     if stepper is None:
         stepper = engine._stepper = EngineStepper(engine)
     return _loop(stepper, prompts, max_tokens=max_tokens, sampling=params, eos=eos, batch_size=batch_size, ctx=ctx,
-                 on_token=on_token, stats=stats, lookahead=lookahead)
+                 on_token=on_token, stats=stats, lookahead=lookahead, logprobs=logprobs if logprobs > 0 else None)

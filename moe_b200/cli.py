@@ -44,6 +44,7 @@ RUN OPTIONS
       --top-k N             candidate cutoff, 0 = off     [0]
       --repeat-penalty F    penalty on recent tokens      [1.0]
       --seed N              sampler seed                  [0]
+      --logprobs N          report each token's logprob and N alternatives, from the raw logits   [0]
       --batch N             requests per batch            [all]
       --no-stream           print only the finished list
       --stats               throughput detail
@@ -254,10 +255,17 @@ def cmd_run(path: str, opt) -> None:
     outs = moe_b200.generate(
         engine, prompts, max_tokens=n_gen, temp=_num(opt, "temp", 0.0, float), top_p=_num(opt, "top-p", 0.95, float),
         top_k=_num(opt, "top-k", 0, int), repeat_penalty=_num(opt, "repeat-penalty", 1.0, float),
-        seed=_num(opt, "seed", 0, int), batch_size=batch, ctx=ctx, on_token=on_token, stats=stats)
+        seed=_num(opt, "seed", 0, int), batch_size=batch, ctx=ctx, on_token=on_token, stats=stats,
+        logprobs=_num(opt, "logprobs", 0, int))
+
+    def probes(o):
+        return [{"token": t, "logprob": round(lp, 6), "top": [[i, round(l, 6)] for i, l in top]}
+                for t, (lp, top) in zip(o.tokens, o.logprobs)]
+
     if "prompts" in opt:
         lines = [json.dumps({"index": i, "prompt": prompts[i], "tokens": o.tokens, "generated": len(o.tokens),
-                             "prompt_tokens": o.prompt_tokens, "finish": o.finish_reason})
+                             "prompt_tokens": o.prompt_tokens, "finish": o.finish_reason,
+                             **({"logprobs": probes(o)} if o.logprobs is not None else {})})
                  for i, o in enumerate(outs)]
         if "out" in opt:
             with open(opt["out"], "w") as f:
@@ -269,6 +277,8 @@ def cmd_run(path: str, opt) -> None:
         print()
     else:
         print(outs[0].tokens)
+    if "prompts" not in opt and outs[0].logprobs is not None:
+        print(json.dumps(probes(outs[0])))
     gen = sum(len(o.tokens) for o in outs)
     print(f"\nload {load_s:.2f}s | prefill {stats.prefill_tokens} tok in {stats.prefill_seconds:.2f}s "
           f"({stats.prefill_tokens / max(stats.prefill_seconds, 1e-6):.1f} tok/s) | decode {gen} tok in "

@@ -504,7 +504,85 @@ __global__ void seed_rng_kernel(unsigned long long* states, const int* slots, co
     if (i < n) states[slots[i]] = (seeds[i] * 0x9e3779b97f4a7c15ull) | 1ull;
 }
 
+// What the model thought of a token it committed (reference: src/generate.rs:78-105, `probe`):
+// from the RAW logits of a row, logprob = logit[token] - logsumexp(row), and the `top` most likely
+// tokens with their logprobs, strongest first (of equal logits the lower id first).  One block a row.
+__global__ void __launch_bounds__(1024)
+logprob_kernel(const float* __restrict__ logits_all, int vocab, const int* __restrict__ tokens, int top,
+               float* __restrict__ out_lp, int* __restrict__ top_ids, float* __restrict__ top_lps) {
+    __shared__ float red[32];
+    __shared__ unsigned long long best[32];
+    __shared__ unsigned long long s_prev;
+    const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float* logits = logits_all + (size_t)row * vocab;
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) mx = fmaxf(mx, logits[i]);
+    mx = block_max(mx, red);
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = logits[i];
+        if (v == v) sum += expf(v - mx);             // (a NaN counts for nothing, as in the samplers)
+    }
+    sum = block_sum(sum, red);
+    const float lse = mx + logf(sum);
+    if (threadIdx.x == 0) {
+        const int t = tokens[row];
+        out_lp[row] = (t >= 0 && t < vocab) ? logits[t] - lse : -INFINITY;
+    }
+    // A key that orders (logit descending, id ascending) as one unsigned number, larger = better:
+    // the float's bits made monotone in the high word, the complement of the id in the low word.
+    auto key_of = [](float v, int i) {
+        unsigned u = __float_as_uint(v);
+        u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+        return ((unsigned long long)u << 32) | (unsigned)(0x7fffffff - i);
+    };
+    unsigned long long prev = ~0ull;                 // the key picked last: the next pick lies below it
+    for (int k = 0; k < top; k++) {
+        unsigned long long b = 0;
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+            const float v = logits[i];
+            if (v != v) continue;                    // (a NaN is no candidate)
+            const unsigned long long key = key_of(v, i);
+            if (key < prev && key > b) b = key;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(0xffffffffu, b, o);
+            b = other > b ? other : b;
+        }
+        if (lane == 0) best[warp] = b;
+        __syncthreads();
+        if (warp == 0) {
+            b = lane < (int)(blockDim.x >> 5) ? best[lane] : 0;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const unsigned long long other = __shfl_xor_sync(0xffffffffu, b, o);
+                b = other > b ? other : b;
+            }
+            if (lane == 0) {
+                s_prev = b;
+                const int id = b ? 0x7fffffff - (int)(unsigned)(b & 0xffffffffu) : -1;
+                top_ids[(size_t)row * top + k] = id;
+                top_lps[(size_t)row * top + k] = id >= 0 ? logits[id] - lse : -INFINITY;
+            }
+        }
+        __syncthreads();
+        prev = s_prev;                               // (0: fewer candidates than asked for, the rest stay -1)
+    }
+}
+
 }  // namespace
+
+// logits: [rows, vocab] float32, raw (before any penalty or temperature); tokens: [rows] the
+// committed tokens.  out_lp [rows]; top_ids, top_lps [rows, top] (top may be 0, at most 64).
+MOE_API int moe_logprobs(const float* logits, int rows, int vocab, const int* tokens, int top, float* out_lp,
+                         int* top_ids, float* top_lps, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (vocab <= 0 || top < 0 || top > 64 || !tokens || !out_lp || (top && (!top_ids || !top_lps)))
+        return (int)cudaErrorInvalidValue;
+    logprob_kernel<<<rows, 1024, 0, stream>>>(logits, vocab, tokens, top, out_lp, top_ids, top_lps);
+    return launch_status();
+}
 
 static size_t cluster_smem(int per_cta) {
     return (size_t)per_cta * 8 + (size_t)NBIN * ST * 4 + (size_t)(3 * MAILS + 32) * 4;

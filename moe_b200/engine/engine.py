@@ -212,6 +212,18 @@ class _PaddedGraph(_StepGraph):
         self._pack(engine, [], [], [], [], [], np.zeros((0, 4), dtype=np.int32))
 
 
+class StepHandle:
+    """A step that was begun: where its sampled tokens (and, if asked for, what the model thought of
+    them) arrive on the host."""
+
+    def __init__(self, host: torch.Tensor, event: torch.cuda.Event, rows: int):
+        self.host, self.event, self.rows = host, event, rows
+        self.probe_host: Optional[torch.Tensor] = None
+        self.top = 0
+        # after the step is finished, per row: (logprob of its token, [(token, logprob)] strongest first)
+        self.probes: Optional[List[Tuple[float, List[Tuple[int, float]]]]] = None
+
+
 class Engine:
     def __init__(self, model: DecoderModel, max_tokens: int, max_slots: Optional[int] = None,
                  use_graphs: Optional[bool] = None):
@@ -430,28 +442,44 @@ class Engine:
         return torch.stack([rows[k] for k in order]) if order else None
 
     def begin_step_and_sample(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], sampler, params,
-                              histories=None, from_last: bool = False):
+                              histories=None, from_last: bool = False, logprobs: Optional[int] = None):
         """Launch one step and the sampling of one token per sequence from the logits at its last
         place, and start the copy of those tokens (and of the device status word) to pinned host
         memory.  Nothing waits for the device; ``finish_step_and_sample`` does.  A token id of
         ``LAST_TOKEN`` (with ``from_last``) is the token sampled last for that sequence, so the next
-        step can be begun before this one is finished."""
+        step can be begun before this one is finished.  With ``logprobs`` (a number of alternatives,
+        0 for none) the handle also brings what the model thought of each token, from the raw logits
+        (``StepHandle.probes`` after the step is finished)."""
         logits = self.step(slots, tokens, None, check=False, from_last=from_last)
         B = len(slots)
+        raw = logits
+        if logprobs is not None and params.repeat_penalty != 1.0:
+            raw = logits.clone()             # the penalty is applied to the logits in place
         picked = sampler.sample(logits, self.last_batch.slots[:B], params, histories)
         host, event = self._results.pop() if self._results else (
             torch.empty(self.cache.max_slots + 2, dtype=torch.int32).pin_memory(), torch.cuda.Event())
         host[:B + 1].copy_(torch.cat([picked, self.rt.status[:1]]), non_blocking=True)
+        handle = StepHandle(host, event, B)
+        if logprobs is not None:
+            lp, ids, lps = core.logprobs(raw[:B], picked, int(logprobs))
+            n = int(logprobs)
+            handle.probe_host = torch.empty((B, 1 + 2 * n), dtype=torch.float32).pin_memory()
+            handle.probe_host.copy_(torch.cat([lp[:, None], ids.to(torch.float32), lps], dim=1), non_blocking=True)
+            handle.top = n
         event.record()
-        return host, event, B
+        return handle
 
     def finish_step_and_sample(self, handle) -> List[int]:
-        host, event, B = handle
-        event.synchronize()
-        out = host[:B + 1].tolist()
-        self._results.append((host, event))
+        handle.event.synchronize()
+        B = handle.rows
+        out = handle.host[:B + 1].tolist()
+        self._results.append((handle.host, handle.event))
         if out[-1]:
             self.rt.check()
+        if handle.probe_host is not None:
+            n = handle.top
+            rows = handle.probe_host.tolist()
+            handle.probes = [(r[0], [(int(i), l) for i, l in zip(r[1:1 + n], r[1 + n:]) if i >= 0]) for r in rows]
         return out[:-1]
 
     def step_and_sample(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], sampler, params,

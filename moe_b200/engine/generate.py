@@ -44,6 +44,9 @@ class GenerationResult:
     stop: str = LENGTH
     prompt_tokens: int = 0
     steps: int = 0            # decode steps this sequence took part in
+    # with ``logprobs``: one entry per emitted token, (logprob of the token, [(token, logprob)] of the
+    # most likely tokens at its place, strongest first), from the raw logits (src/generate.rs:78-105)
+    logprobs: Optional[List[tuple]] = None
 
     @property
     def finish_reason(self) -> str:
@@ -78,8 +81,9 @@ class EngineStepper:
     def seed(self, slots, seeds) -> None:
         self.sampler.seed(slots, seeds)
 
-    def begin(self, slots, tokens, histories, params: SamplingParams, from_last: bool = False):
-        return self.engine.begin_step_and_sample(slots, tokens, self.sampler, params, histories, from_last)
+    def begin(self, slots, tokens, histories, params: SamplingParams, from_last: bool = False,
+              logprobs: Optional[int] = None):
+        return self.engine.begin_step_and_sample(slots, tokens, self.sampler, params, histories, from_last, logprobs)
 
     def finish(self, handle) -> List[int]:
         return self.engine.finish_step_and_sample(handle)
@@ -91,7 +95,8 @@ class EngineStepper:
 def generate(stepper, prompts: Sequence[Sequence[int]], max_tokens: int = 128,
              sampling: Optional[SamplingParams] = None, eos: Sequence[int] = (), batch_size: Optional[int] = None,
              ctx: Optional[int] = None, on_token: Optional[Callable[[int, int], bool]] = None,
-             stats: Optional[GenerationStats] = None, lookahead: Optional[bool] = None) -> List[GenerationResult]:
+             stats: Optional[GenerationStats] = None, lookahead: Optional[bool] = None,
+             logprobs: Optional[int] = None) -> List[GenerationResult]:
     """Generate up to ``max_tokens`` tokens after each prompt.
 
     ``on_token(request_index, token)`` sees every emitted token and returns False to
@@ -99,7 +104,9 @@ def generate(stepper, prompts: Sequence[Sequence[int]], max_tokens: int = 128,
     cache (stop reason Context).  Request i samples with seed ``sampling.seed + i``.
     ``lookahead`` (default: on if the stepper has ``begin``/``finish``) begins each step
     before the one before it is finished; it is off with a repeat penalty, whose history
-    the host must know."""
+    the host must know.  ``logprobs`` (None: off; else the number of alternatives, 0 for none)
+    reports for every emitted token what the model thought of it (``GenerationResult.logprobs``);
+    it needs a stepper with ``begin``/``finish`` that brings them."""
     from ..cache.allocator import CacheError
 
     sampling = (sampling or SamplingParams()).validate()
@@ -118,6 +125,13 @@ def generate(stepper, prompts: Sequence[Sequence[int]], max_tokens: int = 128,
     look = split and (lookahead is None or lookahead) and sampling.repeat_penalty == 1.0
     if lookahead and not look:
         raise ValueError("lookahead needs a stepper with begin/finish and no repeat penalty")
+    if logprobs is not None:
+        if not split:
+            raise ValueError("logprobs need a stepper with begin/finish")
+        if not 0 <= int(logprobs) <= 64:
+            raise ValueError("logprobs: between 0 and 64 alternatives")
+        for r in results:
+            r.logprobs = []
 
     for b0 in range(0, n, batch_size):
         ids = list(range(b0, min(n, b0 + batch_size)))
@@ -127,7 +141,7 @@ def generate(stepper, prompts: Sequence[Sequence[int]], max_tokens: int = 128,
             history = {i: list(prompts[i]) for i in ids}
             alive = set(ids)
 
-            def commit(i: int, tok: int, cached: int) -> bool:
+            def commit(i: int, tok: int, cached: int, probe=None) -> bool:
                 """Judge the token sampled for request i, whose sequence then holds ``cached`` tokens
                 in the cache; True if the request goes on."""
                 r = results[i]
@@ -139,6 +153,8 @@ def generate(stepper, prompts: Sequence[Sequence[int]], max_tokens: int = 128,
                     return False
                 history[i].append(tok)
                 r.tokens.append(tok)
+                if r.logprobs is not None:
+                    r.logprobs.append(probe)
                 if on_token is not None and not on_token(i, tok):
                     r.stop = CALLER
                     return False
@@ -150,6 +166,8 @@ def generate(stepper, prompts: Sequence[Sequence[int]], max_tokens: int = 128,
             def launch(who, toks, cached, from_last):
                 """Begin a step; ``cached[i]`` is the length of i's sequence in the cache after it."""
                 sl, hs = [slot[i] for i in who], [history[i] for i in who]
+                if split and logprobs is not None:
+                    return who, stepper.begin(sl, toks, hs, sampling, from_last, logprobs=int(logprobs)), cached
                 if split:
                     return who, stepper.begin(sl, toks, hs, sampling, from_last), cached
                 return who, stepper.step_and_sample(sl, toks, hs, sampling), cached
@@ -172,19 +190,20 @@ def generate(stepper, prompts: Sequence[Sequence[int]], max_tokens: int = 128,
                             pass        # no room for all of them: wait for the tokens, some may stop
                 who, handle, cached = flights.pop(0)
                 picked = stepper.finish(handle) if split else handle
+                probes = getattr(handle, "probes", None) if logprobs is not None else None
                 if prefill:
                     stats.prefill_seconds += clock() - t0
                     stats.prefill_tokens += sum(len(prompts[i]) for i in ids)
                     t0 = clock()
                 elif any(i in alive for i in who):
                     stats.decode_steps += 1
-                for i, tok in zip(who, picked):
+                for row, (i, tok) in enumerate(zip(who, picked)):
                     if i not in alive:
                         continue            # stopped while this step was already in flight
                     if not prefill:
                         results[i].steps += 1
                         stats.decode_tokens += 1
-                    if not commit(i, int(tok), cached[i]):
+                    if not commit(i, int(tok), cached[i], probes[row] if probes is not None else None):
                         alive.discard(i)
                         stepper.release(slot.pop(i))
                 prefill = False

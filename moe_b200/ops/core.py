@@ -53,6 +53,7 @@ def lib():
             "moe_swiglu": [P, P, I, LL, I, P],
             "moe_combine": [P, P, P, I, P, P, P, I, I, P],
             "moe_sample": [P, I, I, P, P, P, I, F, I, F, F, P, P, P, LL, I, P],
+            "moe_logprobs": [P, I, I, P, I, P, P, P, P],
             "moe_seed_rng": [P, P, P, I, P],
             "moe_table_update": [P, I, P, I, P],
         }
@@ -534,6 +535,22 @@ def sample(logits, slots, rng_states, out_tokens, *, temp=0.0, top_k=0, top_p=1.
     _ok(lib().moe_sample(_p(logits), R, V, _p(slots), _p(rng_states), _p(history), hl, float(temp), int(top_k),
                          float(top_p), float(repeat_penalty), _p(out_tokens), _p(last_token), _p(ws), ws.numel() * 8,
                          1 if kernel == "global" else 0, _stream()), "sample")
+
+
+def logprobs(logits, tokens, top: int):
+    """What the model thought of the committed ``tokens`` [rows], from the raw ``logits`` [rows, vocab]:
+    (logprob [rows] float32, ids [rows, top] int32, logprobs [rows, top] float32), the ``top`` most
+    likely tokens strongest first (reference: src/generate.rs:91-105)."""
+    _chk(logits, "logits", torch.float32, 2), _chk(tokens, "tokens", torch.int32, 1)
+    R, V = logits.shape
+    if tokens.numel() < R or not 0 <= top <= 64:
+        raise KernelError("logprobs: fewer tokens than rows, or more than 64 alternatives")
+    lp = torch.empty(R, dtype=torch.float32, device=logits.device)
+    ids = torch.empty((R, top), dtype=torch.int32, device=logits.device)
+    lps = torch.empty((R, top), dtype=torch.float32, device=logits.device)
+    _ok(lib().moe_logprobs(_p(logits), R, V, _p(tokens), top, _p(lp), _p(ids) if top else None,
+                           _p(lps) if top else None, _stream()), "logprobs")
+    return lp, ids, lps
 
 
 def seed_rng(rng_states, slots, seeds):

@@ -264,3 +264,38 @@ def test_repeat_penalty_turns_looking_ahead_off():
     assert st.most_open == 1
     with pytest.raises(ValueError):
         generate(AheadStepper(), PROMPTS[:2], max_tokens=4, sampling=SamplingParams(repeat_penalty=1.3), lookahead=True)
+
+
+# ---- what the model thought of each token ---------------------------------------------------------
+class ProbingStepper(AheadStepper):
+    """Brings, like the engine's handle, a probe per row: here (minus the token, [(token, -1.0)])."""
+
+    class Handle(list):
+        probes = None
+
+    def begin(self, slots, tokens, histories, params, from_last=False, logprobs=None):
+        out = self.Handle(AheadStepper.begin(self, slots, tokens, histories, params, from_last))
+        self.asked = logprobs
+        if logprobs is not None:
+            out.probes = [(-float(t), [(t, -1.0)] * logprobs) for t in out]
+        return out
+
+
+@pytest.mark.parametrize("lookahead", [False, True])
+def test_logprobs_follow_the_emitted_tokens(lookahead):
+    full, _ = expected(PROMPTS[0], 8)
+    st = ProbingStepper()
+    outs = generate(st, PROMPTS[:3], max_tokens=6, eos={full[3]}, logprobs=2, lookahead=lookahead)
+    assert st.asked == 2
+    for o in outs:
+        # one entry per EMITTED token (the end-of-sequence token is not one), in order
+        assert [lp for lp, _ in o.logprobs] == [-float(t) for t in o.tokens]
+        assert all(top == [(t, -1.0)] * 2 for t, (_, top) in zip(o.tokens, o.logprobs))
+    assert outs[0].stop == "eos" and len(outs[0].tokens) == 3
+    plain_outs = generate(AheadStepper(), PROMPTS[:3], max_tokens=6, eos={full[3]})
+    same(outs, plain_outs)
+    assert all(o.logprobs is None for o in plain_outs)
+    with pytest.raises(ValueError):
+        generate(FakeStepper(), PROMPTS[:1], max_tokens=2, logprobs=1)       # no begin / finish
+    with pytest.raises(ValueError):
+        generate(ProbingStepper(), PROMPTS[:1], max_tokens=2, logprobs=65)

@@ -160,6 +160,13 @@ def test_command_line_run_info_bench(model_dirs, tmp_path):
     assert r.returncode == 0, r.stderr
     lines = [json.loads(l) for l in r.stdout.strip().splitlines()]
     assert [l["index"] for l in lines] == [0, 1, 2] and all(l["generated"] == len(l["tokens"]) <= 3 for l in lines)
+    assert all("logprobs" not in l for l in lines)
+    r = run("run", d, "--prompts", str(pf), "--tokens=3", "--logprobs", "2")
+    assert r.returncode == 0, r.stderr
+    for l in (json.loads(x) for x in r.stdout.strip().splitlines()):
+        assert [e["token"] for e in l["logprobs"]] == l["tokens"]
+        assert all(len(e["top"]) == 2 and e["logprob"] <= 0 and e["top"][0][1] >= e["top"][1][1] for e in l["logprobs"])
+        assert all(e["top"][0][0] == e["token"] for e in l["logprobs"])           # greedy: the strongest was taken
     r = run("info", d)
     assert r.returncode == 0 and "Qwen2MoeForCausalLM" in r.stdout and "4 experts of 32, top-2" in r.stdout
     r = run("bench", d, "--prompt-len", "16", "--tokens", "4", "--batch", "2")
@@ -175,3 +182,30 @@ def test_command_line_run_info_bench(model_dirs, tmp_path):
     assert a.returncode == 0 and a.stdout == b.stdout and len(json.loads(a.stdout.strip().splitlines()[-1])) == 5
     r = run("run", str(tmp_path / "nothing"), "--ids", "1")
     assert r.returncode == 1 and r.stderr.startswith("moe:")
+
+
+@pytest.mark.parametrize("dtype,kw", [("float32", dict(temp=0.0)), ("float32", dict(temp=0.9, seed=5, repeat_penalty=1.3)),
+                                      ("bfloat16", dict(temp=0.0))])
+def test_logprobs_of_generated_tokens_match_plain(model_dirs, dtype, kw):
+    """What the model thought of each emitted token comes from the RAW logits (before the penalty and
+    the temperature, src/generate.rs:78-82), the plain implementation's for the same history."""
+    import moe_b200
+
+    d, eng = G.engine_for(model_dirs, "B", dtype)
+    prompts = [helpers.random_tokens(384, n, 60 + n) for n in (4, 11)]
+    outs = moe_b200.generate(eng, prompts, max_tokens=7, eos=(), logprobs=3, **kw)
+    cfg, w = plain.read_model(d)
+    tol = 2e-4 if dtype == "float32" else 5e-2
+    for p, o in zip(prompts, outs):
+        assert len(o.logprobs) == len(o.tokens) == 7
+        ref = torch.log_softmax(plain.forward(cfg, w, p + o.tokens)[len(p) - 1:-1].double(), -1)
+        for j, (tok, (lp, top)) in enumerate(zip(o.tokens, o.logprobs)):
+            assert abs(lp - float(ref[j, tok])) < tol, (j, lp, float(ref[j, tok]))
+            assert len(top) == 3 and all(abs(l - float(ref[j, i])) < tol for i, l in top)
+            assert [l for _, l in top] == sorted((l for _, l in top), reverse=True)
+            if dtype == "float32":
+                best = torch.topk(ref[j], 4).values
+                if float(best[2] - best[3]) > 1e-3:
+                    assert sorted(i for i, _ in top) == sorted(torch.topk(ref[j], 3).indices.tolist())
+    plain_outs = moe_b200.generate(eng, prompts, max_tokens=7, eos=(), **kw)
+    assert [o.tokens for o in plain_outs] == [o.tokens for o in outs] and plain_outs[0].logprobs is None

@@ -161,3 +161,36 @@ def test_temperature_sampling_follows_the_distribution(sampler):
     got = s.sample(logits, slots, P(temp=1.0, top_p=1.0)).cpu().numpy()
     p = np.exp([1.0, 2.0, 0.5, -0.5])
     assert np.abs(np.bincount(got, minlength=4) / 2000 - p / p.sum()).max() < 0.04
+
+
+@pytest.mark.parametrize("vocab,top", [(97, 0), (97, 5), (300, 64), (151936, 20), (5, 8)])
+def test_logprobs_and_alternatives_from_raw_logits(vocab, top):
+    """src/generate.rs:91-105: logprob = logit - logsumexp; the strongest alternatives first, of equal
+    logits the lower id first; fewer candidates than asked for leave -1."""
+    from moe_b200.ops import core
+
+    torch.manual_seed(vocab + top)
+    rows = 3
+    logits = (torch.randn(rows, vocab, device=DEV) * 3).contiguous()
+    logits[0, 1] = logits[0, 3] = logits[0].max() + 1.0          # a tie at the top: the lower id first
+    if vocab > 50:
+        logits[1, 7] = float("nan")                              # no candidate
+        logits[2, 11] = float("-inf")
+    toks = torch.tensor([3, 0, vocab - 1], dtype=torch.int32, device=DEV)
+    lp, ids, lps = core.logprobs(logits, toks, top)
+    torch.cuda.synchronize()
+    clean = torch.nan_to_num(logits.double().cpu(), nan=-1e300)
+    ref = torch.log_softmax(clean, -1)
+    for r in range(rows):
+        assert abs(float(lp[r]) - float(ref[r, int(toks[r])])) < 1e-4
+        n = min(top, vocab - (1 if r == 1 and vocab > 50 else 0))
+        order = sorted(range(vocab), key=lambda i: (-float(clean[r, i]), i))
+        order = [i for i in order if not (r == 1 and vocab > 50 and i == 7)][:n]
+        assert ids[r, :n].tolist() == order, (r, ids[r].tolist()[:8], order[:8])
+        assert ids[r, n:].tolist() == [-1] * (top - n)
+        got = lps[r, :n].double().cpu()
+        want = ref[r, order]
+        fin = torch.isfinite(want)
+        assert torch.equal(torch.isfinite(got), fin) and float((got[fin] - want[fin]).abs().max() if fin.any() else 0) < 1e-4
+    if top >= 2:
+        assert ids[0, :2].tolist() == [1, 3]
