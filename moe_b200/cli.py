@@ -45,6 +45,7 @@ RUN OPTIONS
       --repeat-penalty F    penalty on recent tokens      [1.0]
       --seed N              sampler seed                  [0]
       --logprobs N          report each token's logprob and N alternatives, from the raw logits   [0]
+      --trace PATH          with --ids: write every token's routing decisions (experts, weights) as JSON lines
       --batch N             requests per batch            [all]
       --no-stream           print only the finished list
       --stats               throughput detail
@@ -219,6 +220,46 @@ def _numel(shape) -> int:
     return n
 
 
+def tracing_parts(model):
+    """(layer index, feed-forward part) for every run of a layer, in the order of the schedule.  A part
+    that routes records its decisions in its ``trace`` list when that is set (``Part.trace``); one that
+    does not leaves the list empty."""
+    return [(e.layer, model.blocks[e.layer].ffn) for e in model.spec.schedule]
+
+
+def write_trace(path: str, model, runs, tokens) -> int:
+    """One JSON object per (token, routed layer): which experts it chose and with what weight, after a
+    header line that explains the file (src/main.rs:771-799).  ``runs``: what ``tracing_parts`` gave,
+    their ``trace`` lists filled by a run of ONE request fed in order (prompt, then token by token)."""
+    runs = [(layer, p) for layer, p in runs if p.trace]
+    times = {id(p): sum(1 for _, q in runs if q is p) for _, p in runs}
+    taken = {}
+    per_run = []                    # per run of a layer: [(experts, weights)] by position
+    for layer, part in runs:
+        i = taken.get(id(part), 0)
+        taken[id(part)] = i + 1
+        rows = []
+        for idx, w in part.trace[i::times[id(part)]]:
+            for e_row, w_row in zip(idx.tolist(), w.tolist()):
+                if e_row and e_row[0] >= 0:             # (rows of no sequence, from a padded step, carry -1)
+                    rows.append((e_row, w_row))
+        per_run.append((layer, rows))
+    spec = model.spec
+    first = runs[0][1] if runs else None
+    n = 0
+    with open(path, "w") as f:
+        f.write(json.dumps({"model": spec.architecture, "layers": len(spec.layers),
+                            "experts": getattr(first, "E", 0), "top_k": getattr(first, "k", 0)}) + "\n")
+        positions = min((len(r) for _, r in per_run), default=0)
+        for pos in range(positions):
+            for layer, rows in per_run:
+                e_row, w_row = rows[pos]
+                f.write(json.dumps({"pos": pos, "layer": layer, "token": tokens[pos] if pos < len(tokens) else None,
+                                    "experts": [[e, round(w, 6)] for e, w in zip(e_row, w_row)]}) + "\n")
+                n += 1
+    return n
+
+
 def cmd_run(path: str, opt) -> None:
     import moe_b200
     from moe_b200.engine.generate import GenerationStats
@@ -251,12 +292,24 @@ def cmd_run(path: str, opt) -> None:
             print(tok, end=" ", flush=True)
         return True
 
+    runs = []
+    if "trace" in opt:
+        if len(prompts) != 1:
+            fail("--trace records one request: give --ids")
+        runs = tracing_parts(model)
+        for _, part in runs:
+            part.trace = []
     stats = GenerationStats()
     outs = moe_b200.generate(
         engine, prompts, max_tokens=n_gen, temp=_num(opt, "temp", 0.0, float), top_p=_num(opt, "top-p", 0.95, float),
         top_k=_num(opt, "top-k", 0, int), repeat_penalty=_num(opt, "repeat-penalty", 1.0, float),
         seed=_num(opt, "seed", 0, int), batch_size=batch, ctx=ctx, on_token=on_token, stats=stats,
-        logprobs=_num(opt, "logprobs", 0, int))
+        logprobs=_num(opt, "logprobs", 0, int), lookahead=False if runs else None)
+    if runs:
+        n = write_trace(opt["trace"], model, runs, prompts[0] + outs[0].tokens)
+        for _, part in runs:
+            part.trace = None
+        print(f"wrote {n} routing records to {opt['trace']}", file=sys.stderr)
 
     def probes(o):
         return [{"token": t, "logprob": round(lp, 6), "top": [[i, round(l, 6)] for i, l in top]}

@@ -167,6 +167,24 @@ def test_command_line_run_info_bench(model_dirs, tmp_path):
         assert [e["token"] for e in l["logprobs"]] == l["tokens"]
         assert all(len(e["top"]) == 2 and e["logprob"] <= 0 and e["top"][0][1] >= e["top"][1][1] for e in l["logprobs"])
         assert all(e["top"][0][0] == e["token"] for e in l["logprobs"])           # greedy: the strongest was taken
+    # the routing trace of one request: a header, then one record per (position, routed layer)
+    tr = tmp_path / "routes.jsonl"
+    r = run("run", d, "--ids", "5,17,3,9", "-n", "6", "--no-stream", "--trace", str(tr))
+    assert r.returncode == 0 and json.loads(r.stdout.strip().splitlines()[-1]) == toks, r.stderr
+    recs = [json.loads(x) for x in tr.read_text().splitlines()]
+    assert recs[0] == {"model": "Qwen2MoeForCausalLM", "layers": 2, "experts": 4, "top_k": 2}
+    fed = [5, 17, 3, 9] + toks[:-1]                       # the last token is sampled, never fed
+    assert [(x["pos"], x["layer"]) for x in recs[1:]] == [(p_, l) for p_ in range(len(fed)) for l in (0, 1)]
+    assert [x["token"] for x in recs[1::2]] == fed
+    cfg_a, w_a = plain.read_model(d)
+    picks = []
+    plain.forward(cfg_a, w_a, fed, trace=picks)
+    agree = 0
+    for x in recs[1:]:
+        assert len(x["experts"]) == 2 and 0 < sum(w for _, w in x["experts"]) <= 1.0 + 1e-3
+        ref = sorted(int(v) for v in picks[x["layer"]][0][x["pos"]])
+        agree += sorted(e for e, _ in x["experts"]) == ref
+    assert agree >= 0.8 * (len(recs) - 1), agree          # (bfloat16: a close call may fall the other way)
     r = run("info", d)
     assert r.returncode == 0 and "Qwen2MoeForCausalLM" in r.stdout and "4 experts of 32, top-2" in r.stdout
     r = run("bench", d, "--prompt-len", "16", "--tokens", "4", "--batch", "2")
