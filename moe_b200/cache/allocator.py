@@ -13,7 +13,6 @@ the split into slots and pages is this library's own.
 """
 from __future__ import annotations
 
-import ctypes
 from ctypes import POINTER, c_char_p, c_int, c_longlong, c_void_p
 from typing import List, Sequence, Tuple
 

@@ -8,7 +8,7 @@ the reference engine applies when a key is absent (src/spec.rs:255-337), except
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Dict, List, Optional, Tuple
 
 from .registry import Architecture, ConfigError, register_architecture

@@ -26,7 +26,7 @@ import torch
 import ctypes
 import os
 
-from ..cache.allocator import _IP, PAGE_TOKENS, CacheError, _ok, host_lib, ints
+from ..cache.allocator import _IP, PAGE_TOKENS, _ok, host_lib, ints
 from ..cache.kv import KVCache
 from ..models.decoder import DecoderModel
 from ..ops import core

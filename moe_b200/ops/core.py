@@ -6,7 +6,6 @@ library that cannot be built raises.
 """
 from __future__ import annotations
 
-import ctypes
 import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional

@@ -7,7 +7,7 @@ no multiple of 8 elements, an unaligned pointer); the caller then uses the plain
 from __future__ import annotations
 
 import os
-from ctypes import c_int, c_void_p
+from ctypes import byref, c_int, c_void_p
 from typing import Optional
 
 import torch
@@ -168,7 +168,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swiglu: bool
             if _SPLIT_TARGET:                              # for measurements
                 target = _SPLIT_TARGET
             splits = max(1, min(8, target // max(tiles, 1), -(-K // 64) // 4))
-    splits = L.moe_gemm_tc_plan(K, int(splits), M, bn, G, 1 if grouped else 0, core.ctypes.byref(gy))
+    splits = L.moe_gemm_tc_plan(K, int(splits), M, bn, G, 1 if grouped else 0, byref(gy))
     partials = tickets = None
     if splits > 1:
         ws = workspace(x.device)

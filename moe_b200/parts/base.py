@@ -20,7 +20,7 @@ A pending delta may be a ``LazyDelta``; ``delta_for(norm, delta, rt)`` gives wha
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, Optional, Tuple
+from typing import Callable, Dict, Optional, Tuple
 
 import torch
 

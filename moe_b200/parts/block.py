@@ -9,7 +9,7 @@ reads and writes the stream once instead of twice.
 from __future__ import annotations
 
 from ..config.spec import LayerSpec
-from .base import delta_for, make_part, register_part
+from .base import delta_for, make_part
 
 
 class PreNormBlock:

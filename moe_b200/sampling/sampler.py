@@ -6,7 +6,7 @@ follows the sequence through batches of any composition.
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
+from typing import Optional, Sequence
 
 import numpy as np
 import torch

@@ -16,7 +16,7 @@ Dtype policy when a tensor is handed to a part:
 from __future__ import annotations
 
 import fnmatch
-from typing import Dict, Iterable, List, Optional, Tuple
+from typing import Dict, Iterable, List, Tuple
 
 import torch
 

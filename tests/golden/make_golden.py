@@ -18,7 +18,6 @@ exactly), and ``lm_head`` is dropped because the embedding is tied.
 import importlib.util
 import json
 import os
-import struct
 import sys
 
 

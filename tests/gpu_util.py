@@ -1,7 +1,7 @@
 """Helpers of the GPU tests: engines per configuration, hand-made step batches."""
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, Optional, Sequence
 
 import numpy as np
 import torch

@@ -1,12 +1,11 @@
 """The host runtime (C++, csrc/host_runtime.cpp): the reservation of a whole step and the packing
 of a step's index arrays, against their definitions restated here in Python.  No GPU needed."""
-import ctypes
 import random
 
 import numpy as np
 import pytest
 
-from moe_b200.cache import PAGE_TOKENS, CacheError, CacheLedger, pages_for
+from moe_b200.cache import CacheError, CacheLedger
 from moe_b200.cache.allocator import _IP, _ok, host_lib, ints
 from moe_b200.engine.batch import fill_host, layout
 

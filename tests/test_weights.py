@@ -10,7 +10,7 @@ import helpers
 import plain_qwen2moe as plain
 from moe_b200.config import parse_config
 from moe_b200.models import expected_tensors
-from moe_b200.weights import SafetensorsError, SafetensorsStore, WeightError, write_random_model, write_safetensors
+from moe_b200.weights import SafetensorsError, SafetensorsStore, WeightError, write_safetensors
 from moe_b200.weights.store import convert_for_compute
 
 
