@@ -57,6 +57,7 @@ BENCH OPTIONS
       --batch N             sequences decoded together    [1]
 
       --peak-gbs F          memory bandwidth the roofline line is a percentage of   [7700]
+      --kernels             then a table of a decode step's device time by kind of kernel
 
 GLOBAL
       --random CONFIG.json  instead of <model>: random weights of this configuration, drawn on
@@ -67,7 +68,7 @@ GLOBAL
   -V, --version             version
 """
 
-FLAGS = {"help", "no-stream", "stats", "version"}
+FLAGS = {"help", "kernels", "no-stream", "stats", "version"}
 ALIASES = {"n": "tokens", "o": "out", "h": "help", "V": "version"}
 
 
@@ -376,6 +377,44 @@ def cmd_bench(path: str, opt) -> None:
     gbs = (wb + cb) / max(dc / max(n, 1), 1e-12) / 1e9
     print(f"roofline {human(int(wb))} weights + {human(int(cb))} cache a step   {gbs:.0f} GB/s   "
           f"{100.0 * gbs / peak:.1f}% of {peak:.0f} GB/s")
+    if "kernels" in opt:
+        print()
+        print(kernel_table(lambda i: engine.step(slots, [[i % V]] * B, check=False), steps=4))
+
+
+def kernel_table(step, steps: int = 4) -> str:
+    """Device time of a decode step by kind of kernel: ``steps`` more steps under the CUDA activity
+    tracer, each kernel's time summed by its name without template arguments.  (Kernels that overlap,
+    on two streams or through programmatic dependent launch, are each counted in full, so the sum
+    can exceed the step's time.)"""
+    import re
+
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    import warnings
+
+    torch.cuda.synchronize()
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for i in range(steps):
+                step(i)
+            torch.cuda.synchronize()
+    kinds: Dict[str, List[float]] = {}
+    for e in prof.events():
+        if e.device_type != torch.autograd.DeviceType.CUDA:
+            continue
+        name = re.sub(r"\(anonymous namespace\)::|^void ", "", e.name)
+        name = re.sub(r"<.*", "", name.split("(")[0]).strip() or e.name
+        k = kinds.setdefault(name, [0.0, 0])
+        k[0] += e.time_range.end - e.time_range.start
+        k[1] += 1
+    total = sum(v[0] for v in kinds.values()) or 1.0
+    lines = [f"{'kernel':<34}{'us/step':>10}{'share':>8}{'launches/step':>15}"]
+    for name, (us, n) in sorted(kinds.items(), key=lambda kv: -kv[1][0]):
+        lines.append(f"{name[:33]:<34}{us / steps:>10.1f}{100.0 * us / total:>7.1f}%{n / steps:>15.1f}")
+    return "\n".join(lines)
 
 
 def main(argv=None) -> int:

@@ -193,8 +193,10 @@ def test_command_line_run_info_bench(model_dirs, tmp_path):
     # random weights instead of a folder: the same verbs, nothing written
     cfg = tmp_path / "config.json"
     cfg.write_text(json.dumps(helpers.CONFIG_A))
-    r = run("bench", "--random", str(cfg), "--seed", "4", "--prompt-len", "8", "--tokens", "3", "--peak-gbs", "6500")
+    r = run("bench", "--random", str(cfg), "--seed", "4", "--prompt-len", "8", "--tokens", "3", "--peak-gbs", "6500",
+            "--kernels")
     assert r.returncode == 0 and "% of 6500 GB/s" in r.stdout, r.stderr
+    assert "us/step" in r.stdout and "attn_decode" in r.stdout and "launches/step" in r.stdout
     a = run("run", "--random", str(cfg), "--seed", "4", "--ids", "1,2,3", "-n", "5", "--no-stream")
     b = run("run", "--random", str(cfg), "--seed", "4", "--ids", "1,2,3", "-n", "5", "--no-stream")
     assert a.returncode == 0 and a.stdout == b.stdout and len(json.loads(a.stdout.strip().splitlines()[-1])) == 5
