@@ -185,3 +185,46 @@ def test_a_step_too_large_for_one_go_is_run_in_pieces_with_the_same_result(model
         eng.step([a, b], [reqs["x"], reqs["x"]])         # 4 + 4 pages of the 7 there are
     assert eng.length(a) == 0 and eng.length(b) == 0
     eng.release(a), eng.release(b)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_wanted_places_of_every_kind_through_the_padded_graphs(model_dirs, dtype):
+    """A captured step takes any wanted places: none at all, a few, every place, and (outside the
+    graphs) a place asked for twice; the rows come back in the order asked for and equal those of a
+    step that asks for every place."""
+    V = helpers.CONFIGS["C"]["vocab_size"]
+    d, eng = engine(model_dirs, "C", dtype, max_tokens=64 * 8, max_slots=3)
+    toks = [helpers.random_tokens(V, n, 70 + n) for n in (37, 5, 90)]
+    more = [helpers.random_tokens(V, n, 80 + n) for n in (3, 20, 1)]
+
+    def run(want0, want1):
+        slots = [eng.new_sequence() for _ in toks]
+        a = eng.step(slots, toks, want0)
+        b = eng.step(slots, more, want1)
+        for s in slots:
+            eng.release(s)
+        return (None if a is None else a.float().cpu().clone()), (None if b is None else b.float().cpu().clone())
+
+    full0 = [list(range(len(t))) for t in toks]
+    full1 = [list(range(len(t))) for t in more]
+    ref0, ref1 = run(full0, full1)
+    row0 = lambda i, j: ref0[sum(len(t) for t in toks[:i]) + j]
+    row1 = lambda i, j: ref1[sum(len(t) for t in more[:i]) + j]
+    before = len(eng.graphs_of("prompt")) + len(eng.graphs_of("continued"))
+    assert before >= 2
+    tol = 1e-6 if dtype == "float32" else G.tol_cut(dtype)
+    for want0, want1 in (([[], [], []], [[], [], []]),                    # nothing wanted: the step still runs
+                         ([[36], [], [0, 89]], [[2, 0], [19], []]),       # a few, not in ascending order
+                         ([[0], [4], [89]], [[2], [19], [0]]),            # one each
+                         ([[5, 5, 5] * 20, [], []], [[0, 0, 1, 1, 2, 2], [], []])):   # more places than tokens
+        a, b = run(want0, want1)
+        for got, want, row in ((a, want0, row0), (b, want1, row1)):
+            flat = [(i, j) for i, w in enumerate(want) for j in w]
+            if not flat:
+                assert got is None
+                continue
+            assert got.shape[0] == len(flat)
+            worst = max(helpers.max_rel_err(got[n], row(i, j)) for n, (i, j) in enumerate(flat))
+            assert worst < tol, (want, worst)
+    # the cache went on from where the first step left it, whatever was wanted
+    assert eng.cache.ledger.slots.num_held == 0
