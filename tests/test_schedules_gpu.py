@@ -228,3 +228,33 @@ def test_wanted_places_of_every_kind_through_the_padded_graphs(model_dirs, dtype
             assert worst < tol, (want, worst)
     # the cache went on from where the first step left it, whatever was wanted
     assert eng.cache.ledger.slots.num_held == 0
+
+
+def test_more_shapes_of_step_than_captured_graphs_are_kept(model_dirs):
+    """An engine keeps at most MAX_GRAPHS captured steps and drops the one used longest ago; a shape
+    that was dropped is captured again and gives the same logits as the first time."""
+    from moe_b200.engine import engine as E
+
+    V = helpers.CONFIGS["A"]["vocab_size"]
+    d, eng = engine(model_dirs, "A", "float32", max_tokens=64 * 80, max_slots=8)
+    first = {}
+    shapes = [(b, n, every, fresh) for fresh in (True, False) for every in (False, True)
+              for b in (1, 2, 3, 5) for n in (7, 20, 40, 70)]            # 64 padded shapes (a few share a key)
+    for rnd in range(2):
+        for b, n, every, fresh in shapes:
+            slots = [eng.new_sequence() for _ in range(b)]
+            if not fresh:
+                eng.step(slots, [helpers.random_tokens(V, 3 + i, i) for i in range(b)], [[] for _ in slots])
+            toks = [helpers.random_tokens(V, n + i, 10 * n + i) for i in range(b)]
+            want = [list(range(len(t))) if every else [len(t) - 1] for t in toks]
+            lg = eng.step(slots, toks, want).float().cpu().clone()
+            for s in slots:
+                eng.release(s)
+            key = (b, n, every, fresh)
+            if rnd == 0:
+                first[key] = lg
+            else:
+                assert torch.equal(lg, first[key]), key
+            assert len(eng._graphs) <= E.MAX_GRAPHS
+    assert len(eng._graphs) == E.MAX_GRAPHS            # more shapes were met than are kept
+    assert eng.cache.ledger.slots.num_held == 0
