@@ -197,3 +197,46 @@ def test_weights_drawn_when_asked_for_equal_those_drawn_at_once():
     m = moe_b200.random_model(helpers.CONFIG_B, seed=5, dtype="bfloat16", device="cpu", std=0.05)
     assert torch.equal(m.blocks[1].ffn.w_gu[3, 48:], at_once["model.layers.1.mlp.experts.3.up_proj.weight"])
     assert torch.equal(m.blocks[0].mixer.wqkv[96:128], at_once["model.layers.0.self_attn.k_proj.weight"])
+
+
+def test_mutated_files_load_or_are_refused_never_anything_else(tmp_path):
+    """A sweep in the manner of the reference's malformed-input tests (tests/malformed.rs, fuzz/):
+    bytes of a valid file's length word and header are flipped, cut or repeated; every result is
+    either a store whose tensors can all be read or ONE of the loader's own errors."""
+    import random
+
+    tensors = {"a.weight": torch.arange(12, dtype=torch.float32).reshape(3, 4),
+               "b.weight": torch.ones(5, dtype=torch.bfloat16), "c": torch.zeros(2, 2, dtype=torch.float16)}
+    src = tmp_path / "src"
+    src.mkdir()
+    write_safetensors(str(src / "model.safetensors"), tensors)
+    good = (src / "model.safetensors").read_bytes()
+    head_len = struct.unpack("<Q", good[:8])[0]
+    rng = random.Random(7)
+    d = tmp_path / "mut"
+    d.mkdir()
+    loaded = refused = 0
+    for trial in range(400):
+        b = bytearray(good)
+        kind = trial % 4
+        if kind == 0:                                   # flip bytes in the length word or the header
+            for _ in range(rng.randint(1, 4)):
+                i = rng.randrange(0, 8 + head_len)
+                b[i] = rng.randrange(256)
+        elif kind == 1:                                 # cut the file somewhere
+            b = b[:rng.randrange(0, len(b))]
+        elif kind == 2:                                 # a digit of the header becomes another digit
+            digits = [i for i in range(8, 8 + head_len) if chr(b[i]).isdigit()]
+            b[rng.choice(digits)] = ord(str(rng.randrange(10)))
+        else:                                           # a stretch of the header is repeated or dropped
+            i, j = sorted(rng.sample(range(8, 8 + head_len), 2))
+            b = b[:i] + (b[i:j] * 2 if trial % 8 == 3 else b"") + b[j:]
+        (d / "model.safetensors").write_bytes(bytes(b))
+        try:
+            st = SafetensorsStore(str(d))
+            for name in st.names():
+                st.get(name, torch.float32)
+            loaded += 1
+        except (SafetensorsError, WeightError):
+            refused += 1
+    assert loaded + refused == 400 and refused > 200 and loaded > 0
