@@ -103,3 +103,23 @@ def test_steps_without_wanted_logits_write_nothing(model_dirs, tmp_path):
     got = torch.from_numpy(np.fromfile(os.path.join(out, "1.f32"), dtype="<f4").astype(np.float64))
     ref = helpers.plain_logits(d, [1, 2, 3, 4])[3]
     assert float((got - ref).abs().max() / ref.abs().max()) < G.TOL_F32
+
+
+@pytest.mark.parametrize("bad,needle", [
+    ('{"step": 1, "entries": [{"id": "b", "tokens": [1] * 200, "want": []}]}'.replace("[1] * 200", str([1] * 200)), "CacheError"),
+    ('{"entries": []}', "KeyError"),
+    ('not a step', "JSONDecodeError"),
+    ('{"step": 1, "entries": [{"id": "a", "tokens": [5], "want": [3]}]}', "wanted place"),
+])
+def test_a_bad_line_ends_the_program_with_one_message(model_dirs, tmp_path, bad, needle):
+    """A line that is no step, a wanted place outside the step or a step the cache has no room for:
+    exit code 1 and one line that names the input line, after the steps before it were done."""
+    d = model_dirs.get("A", "float32", seed=1, std=0.2)
+    first = json.dumps({"step": 0, "entries": [{"id": "a", "tokens": [1, 2, 3], "want": [2]}], "end": []})
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", d, "--dtype", "float32",
+                        "--out", str(tmp_path / "o"), "--max-tokens", "128"], input=first + "\n" + bad + "\n",
+                       capture_output=True, text=True, timeout=600)
+    assert p.returncode == 1 and p.stdout.strip().splitlines() == ["done 0"]
+    last = p.stderr.strip().splitlines()[-1]
+    assert last.startswith("trace_run: input line 2:") and needle in last, p.stderr
+    assert os.path.exists(tmp_path / "o" / "0.f32")
