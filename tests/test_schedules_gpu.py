@@ -22,7 +22,7 @@ def engine(model_dirs, name, dtype, max_tokens, max_slots, use_graphs=True):
 
 
 MANY = [("A", 12, True), ("A", 70, True), ("B", 24, True), ("B", 40, False), ("D", 40, True), ("D", 12, False),
-        ("C", 33, True), ("E", 20, True), ("E", 9, False)]
+        ("C", 33, True), ("E", 20, True), ("E", 9, False), ("A", 140, True)]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
